@@ -1,0 +1,364 @@
+"""CPU oracle: weight/activation formats of the quantized-linear hot path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing the library ships imports this module; it is
+the checker for the CUDA kernels (tests, the smoke run, the CPU leg of the
+benchmark).  Every function restates, in numpy, the arithmetic of one piece of
+the reference (hanzo-quant) and cites the file:line it follows.
+
+Pinned against (see tests/test_oracle_*.py and tests/golden/):
+  * gguf-py `dequantize` for Q8_0 and Q4_K bytes (bit-exact),
+  * the reference's own Python Q4_K quantizer (scripts/convert_fp8_to_gguf.py)
+    through committed golden bytes,
+  * the reference's known-answer tests for FP8 block / vector dequant and the
+    MXFP4 value table.
+Parity unpinned (no reference vector exists, third-party crate arithmetic):
+  e4m3 rounding at exact ties (crate `float8` 0.7.0) -- round-to-nearest-even
+  is assumed, as in `ml_dtypes.float8_e4m3fn`.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+QK8_0 = 32          # elements per Q8_0 block
+Q8_0_BYTES = 34     # half d + 32 int8
+QK_K = 256          # elements per k-quant super-block
+Q4_K_BYTES = 144    # half d, half dmin, 12 scale bytes, 128 nibble bytes
+MXFP4_BLOCK = 32
+FP8_MAX = 448.0
+
+# ----------------------------------------------------------------------------
+# Q8_0  (block_q8_0 {half d; int8 qs[32]}: hanzo-quant/kernels/mmvq_gguf/mmvq_gguf.cu:134-137)
+# ----------------------------------------------------------------------------
+
+
+def q8_0_quantize(w: np.ndarray) -> np.ndarray:
+    """f32 [rows, K] -> uint8 [rows, K/32*34].  d = absmax/127 (fp16), q = round(x/d).
+
+    Any valid block bytes are acceptable test data: parity is defined against
+    the dequantization of the same bytes.  Matches gguf-py's Q8_0 quantizer.
+    """
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    rows, k = w.shape
+    assert k % QK8_0 == 0
+    blk = w.reshape(rows, k // QK8_0, QK8_0)
+    amax = np.abs(blk).max(axis=2, keepdims=True)
+    d = amax / np.float32(127.0)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        inv = np.where(d > 0, np.float32(1.0) / d, np.float32(0.0)).astype(np.float32)
+    q = np.rint(blk * inv).astype(np.int8)
+    out = np.empty((rows, k // QK8_0, Q8_0_BYTES), np.uint8)
+    out[:, :, 0:2] = d.astype(np.float16).view(np.uint8).reshape(rows, -1, 2)
+    out[:, :, 2:] = q.view(np.uint8)
+    return out.reshape(rows, -1)
+
+
+def q8_0_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/32*34] -> f32 [rows, K]; value = d * q (mmvq_gguf.cu:134-137)."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    blk = raw.reshape(rows, k // QK8_0, Q8_0_BYTES)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)          # [rows, nb, 1]
+    q = blk[:, :, 2:].copy().view(np.int8).astype(np.float32)
+    return (d * q).reshape(rows, k)
+
+
+# ----------------------------------------------------------------------------
+# Q4_K  (block_q4_K {half2 dm; uint8 scales[12]; uint8 qs[128]}: mmvq_gguf.cu:166-170;
+#        6-bit scale/min unpack :595-606; value = d*sc*q - dmin*m :385-404;
+#        element order inside a super-block: scripts/convert_fp8_to_gguf.py:191-211)
+# ----------------------------------------------------------------------------
+
+
+def q4_k_unpack_scales(sc_bytes: np.ndarray):
+    """uint8 [..., 12] -> (sc [..., 8], m [..., 8]) 6-bit integers (mmvq_gguf.cu:595-606)."""
+    b = sc_bytes.astype(np.uint8)
+    sc = np.empty(b.shape[:-1] + (8,), np.uint8)
+    mn = np.empty_like(sc)
+    for j in range(4):
+        sc[..., j] = b[..., j] & 63
+        mn[..., j] = b[..., j + 4] & 63
+    for j in range(4, 8):
+        sc[..., j] = (b[..., j + 4] & 0x0F) | ((b[..., j - 4] >> 6) << 4)
+        mn[..., j] = (b[..., j + 4] >> 4) | ((b[..., j] >> 6) << 4)
+    return sc, mn
+
+
+def q4_k_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/256*144] -> f32 [rows, K].
+
+    Sub-block j=2c takes the LOW nibbles of qs[32c..32c+31], sub-block 2c+1 the
+    HIGH nibbles of the same bytes; value = (d*sc_j)*q - (dmin*m_j).
+    """
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    nsb = k // QK_K
+    blk = raw.reshape(rows, nsb, Q4_K_BYTES)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)          # [rows, nsb, 1]
+    dmin = blk[:, :, 2:4].copy().view(np.float16).astype(np.float32)
+    sc, mn = q4_k_unpack_scales(blk[:, :, 4:16])
+    qs = blk[:, :, 16:].reshape(rows, nsb, 4, 32)
+    q = np.empty((rows, nsb, 8, 32), np.float32)
+    q[:, :, 0::2, :] = (qs & 0x0F).astype(np.float32)
+    q[:, :, 1::2, :] = (qs >> 4).astype(np.float32)
+    d1 = (d * sc.astype(np.float32))[..., None]                            # [rows, nsb, 8, 1]
+    m1 = (dmin * mn.astype(np.float32))[..., None]
+    return (d1 * q - m1).reshape(rows, k)
+
+
+def _nearest_int(f: np.ndarray) -> np.ndarray:
+    # round-half-even of a float32, as the magic-number trick in ggml does
+    return np.rint(np.asarray(f, dtype=np.float32)).astype(np.int32)
+
+
+def _fit_scale_min(x: np.ndarray, wts: np.ndarray, nmax: int, nstep: int = 20,
+                   rmin: float = -1.0, rdelta: float = 0.1):
+    """Weighted least-squares (scale, min) search over 32-vectors, the published
+    ggml `make_qkx2_quants` procedure, vectorised over the leading axis.
+    Returns (scale >= 0, minus_min >= 0)."""
+    x = x.astype(np.float32)
+    lo = np.minimum(x.min(1), 0.0).astype(np.float32)
+    hi = x.max(1).astype(np.float32)
+    span = hi - lo
+    ok = span > 0
+    sw = wts.sum(1)
+    sx = (wts * x).sum(1)
+    span_s = np.where(ok, span, 1.0)
+    inv = np.where(ok, nmax / span_s, 0.0).astype(np.float32)
+    scale = np.where(ok, span_s / nmax, 0.0).astype(np.float32)
+    lv = np.clip(_nearest_int(inv[:, None] * (x - lo[:, None])), 0, nmax)
+    err = scale[:, None] * lv + lo[:, None] - x
+    best = (wts * err * err).sum(1)
+    cur_lo = lo.copy()
+    for step in range(nstep + 1):
+        den = np.where(ok, hi - cur_lo, 1.0)
+        inv = np.where(ok, (rmin + rdelta * step + nmax) / den, 0.0).astype(np.float32)
+        la = np.clip(_nearest_int(inv[:, None] * (x - cur_lo[:, None])), 0, nmax).astype(np.float64)
+        sl = (wts * la).sum(1)
+        sl2 = (wts * la * la).sum(1)
+        sxl = (wts * la * x).sum(1)
+        det = sw * sl2 - sl * sl
+        good = ok & (det > 0)
+        det_s = np.where(good, det, 1.0)
+        s_new = (sw * sxl - sx * sl) / det_s
+        m_new = (sl2 * sx - sl * sxl) / det_s
+        clip = m_new > 0.0
+        s_new = np.where(clip, sxl / np.where(sl2 > 0, sl2, 1.0), s_new)
+        m_new = np.where(clip, 0.0, m_new)
+        e = s_new[:, None] * la + m_new[:, None] - x
+        mad = (wts * e * e).sum(1)
+        take = good & (mad < best)
+        best = np.where(take, mad, best)
+        scale = np.where(take, s_new, scale)
+        cur_lo = np.where(take, m_new, cur_lo)
+    return scale.astype(np.float32), (-cur_lo).astype(np.float32)
+
+
+def q4_k_quantize(w: np.ndarray) -> np.ndarray:
+    """f32 [rows, K] (K % 256 == 0) -> uint8 [rows, K/256*144], the published
+    ggml `quantize_row_q4_K_ref` procedure (what the reference's Python
+    converter, scripts/convert_fp8_to_gguf.py:155-216, also follows)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    rows, k = w.shape
+    assert k % QK_K == 0
+    nsb = rows * (k // QK_K)
+    sub = w.reshape(nsb * 8, 32)
+    rms = np.sqrt((sub * sub).sum(1) / 32.0)
+    sc_f, mn_f = _fit_scale_min(sub, rms[:, None] + np.abs(sub), 15)
+    sc_f = sc_f.reshape(nsb, 8)
+    mn_f = mn_f.reshape(nsb, 8)
+    top_s = sc_f.max(1)
+    top_m = mn_f.max(1)
+    inv_s = np.where(top_s > 0, 63.0 / np.where(top_s > 0, top_s, 1.0), 0.0)
+    inv_m = np.where(top_m > 0, 63.0 / np.where(top_m > 0, top_m, 1.0), 0.0)
+    ls = np.minimum(_nearest_int(inv_s[:, None] * sc_f), 63).astype(np.uint8)
+    lm = np.minimum(_nearest_int(inv_m[:, None] * mn_f), 63).astype(np.uint8)
+    packed = np.zeros((nsb, 12), np.uint8)
+    packed[:, 0:4] = ls[:, 0:4] | ((ls[:, 4:8] >> 4) << 6)
+    packed[:, 4:8] = lm[:, 0:4] | ((lm[:, 4:8] >> 4) << 6)
+    packed[:, 8:12] = (ls[:, 4:8] & 0x0F) | ((lm[:, 4:8] & 0x0F) << 4)
+    d = (top_s / 63.0).astype(np.float16)
+    dmin = (top_m / 63.0).astype(np.float16)
+    sc_i, mn_i = q4_k_unpack_scales(packed)
+    d1 = d.astype(np.float32)[:, None] * sc_i.astype(np.float32)
+    m1 = dmin.astype(np.float32)[:, None] * mn_i.astype(np.float32)
+    vals = w.reshape(nsb, 8, 32)
+    d1s = np.where(d1 != 0, d1, 1.0)[:, :, None]
+    lvl = np.where(d1[:, :, None] != 0,
+                   np.clip(_nearest_int((vals + m1[:, :, None]) / d1s), 0, 15), 0).astype(np.uint8)
+    qs = (lvl[:, 0::2, :] | (lvl[:, 1::2, :] << 4)).reshape(nsb, 128)
+    out = np.concatenate([d.view(np.uint8).reshape(nsb, 2), dmin.view(np.uint8).reshape(nsb, 2),
+                          packed, qs], axis=1)
+    return out.reshape(rows, (k // QK_K) * Q4_K_BYTES)
+
+
+# ----------------------------------------------------------------------------
+# FP8 e4m3 (weights with 128x128 f32 block scales, activations with 1x128 scales)
+# ----------------------------------------------------------------------------
+
+
+def _build_e4m3_table() -> np.ndarray:
+    """All 256 e4m3fn codes -> f32.  4 exponent bits (bias 7), 3 mantissa bits,
+    no infinities, 0x7f/0xff are NaN, largest finite 448."""
+    t = np.zeros(256, np.float32)
+    for c in range(256):
+        s = -1.0 if c & 0x80 else 1.0
+        e = (c >> 3) & 0xF
+        m = c & 7
+        if e == 0xF and m == 7:
+            v = np.nan
+        elif e == 0:
+            v = s * (m / 8.0) * 2.0 ** (-6)
+        else:
+            v = s * (1.0 + m / 8.0) * 2.0 ** (e - 7)
+        t[c] = v
+    return t
+
+
+E4M3_TABLE = _build_e4m3_table()
+
+
+def e4m3_decode(codes: np.ndarray) -> np.ndarray:
+    return E4M3_TABLE[np.asarray(codes, dtype=np.uint8)]
+
+
+def e4m3_encode(x: np.ndarray) -> np.ndarray:
+    """f32 -> e4m3fn code, round-to-nearest-even, inputs already clamped to +-448
+    (the reference clamps before converting: blockwise_fp8/ops.rs:399)."""
+    x = np.asarray(x, dtype=np.float32)
+    a = np.abs(x).astype(np.float64)
+    sign = (np.signbit(x)).astype(np.uint8) << 7
+    # quantum of the target grid at |x|: 2^-9 below 2^-6 (subnormals), else 2^(floor(log2 a) - 3)
+    with np.errstate(divide="ignore"):
+        ex = np.floor(np.log2(np.where(a > 0, a, 1.0)))
+    ex = np.clip(ex, -6, 8)
+    q = 2.0 ** (ex - 3)
+    n = np.rint(a / q)                     # numpy rint = half-to-even
+    v = np.minimum(n * q, FP8_MAX)
+    # re-derive exponent after rounding (n may have carried to the next binade)
+    with np.errstate(divide="ignore"):
+        ex2 = np.floor(np.log2(np.where(v > 0, v, 1.0)))
+    ex2 = np.clip(ex2, -6, 8)
+    sub = v < 2.0 ** (-6)
+    mant = np.where(sub, np.rint(v / 2.0 ** (-9)), np.rint((v / 2.0 ** ex2 - 1.0) * 8.0)).astype(np.int64)
+    expo = np.where(sub, 0, ex2 + 7).astype(np.int64)
+    code = (expo << 3 | mant).astype(np.uint8)
+    return (code | sign).astype(np.uint8)
+
+
+def fp8_block_dequant(codes: np.ndarray, scale: np.ndarray, by: int = 128, bx: int = 128) -> np.ndarray:
+    """e4m3 [N, K] x scale [ceil(N/by), ceil(K/bx)] -> f32 [N, K]; edge blocks are
+    clipped (hanzo-quant/src/blockwise_fp8/ops.rs:11-59)."""
+    n, k = codes.shape
+    s = np.repeat(np.repeat(scale.astype(np.float32), by, axis=0), bx, axis=1)[:n, :k]
+    return e4m3_decode(codes) * s
+
+
+def fp8_block_quant(w: np.ndarray, by: int = 128, bx: int = 128):
+    """f32 [N, K] -> (codes uint8 [N, K], scale f32 [ceil(N/by), ceil(K/bx)]).
+    scale = absmax/448 (1e-12 for an all-zero block), q = e4m3(clamp(v/scale, +-448))
+    (blockwise_fp8/ops.rs:329-411)."""
+    w = np.asarray(w, dtype=np.float32)
+    n, k = w.shape
+    gy, gx = -(-n // by), -(-k // bx)
+    pad = np.zeros((gy * by, gx * bx), np.float32)
+    pad[:n, :k] = w
+    blk = pad.reshape(gy, by, gx, bx)
+    amax = np.abs(blk).max(axis=(1, 3))
+    scale = np.where(amax > 0, amax / np.float32(FP8_MAX), np.float32(1e-12)).astype(np.float32)
+    scaled = np.clip(blk / scale[:, None, :, None], -FP8_MAX, FP8_MAX).astype(np.float32)
+    codes = e4m3_encode(scaled).reshape(gy * by, gx * bx)[:n, :k]
+    return np.ascontiguousarray(codes), scale
+
+
+def fp8_vector_quant(x: np.ndarray, group: int = 128):
+    """flat groups of `group` elements: scale = absmax/448 (or 1e-12), codes as
+    above (hanzo-quant/src/vector_fp8/ops.rs:235-287).  x [..., K], K % group == 0
+    -> (codes uint8 same shape, scale f32 [..., K/group])."""
+    x = np.asarray(x, dtype=np.float32)
+    shp = x.shape
+    g = x.reshape(-1, group)
+    amax = np.abs(g).max(1)
+    scale = np.where(amax > 0, amax / np.float32(FP8_MAX), np.float32(1e-12)).astype(np.float32)
+    scaled = np.clip(g / scale[:, None], -FP8_MAX, FP8_MAX).astype(np.float32)
+    codes = e4m3_encode(scaled).reshape(shp)
+    return codes, scale.reshape(shp[:-1] + (shp[-1] // group,))
+
+
+def fp8_vector_dequant(codes: np.ndarray, scale: np.ndarray, group: int = 128) -> np.ndarray:
+    """inverse of fp8_vector_quant (vector_fp8/ops.rs, KAT :459-480)."""
+    v = e4m3_decode(codes)
+    return v * np.repeat(scale.astype(np.float32), group, axis=-1)
+
+
+# ----------------------------------------------------------------------------
+# MXFP4 (e2m1 nibbles, 32-element blocks, e8m0 shared exponent)
+# ----------------------------------------------------------------------------
+
+FP4_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0,
+                       -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], np.float32)
+
+
+def e8m0_to_f32(s: np.ndarray) -> np.ndarray:
+    """The reference builds the scale as f32::from_bits(s << 23)
+    (hanzo-quant/src/mxfp4/mod.rs:480): s = 0 decodes to 0.0, s = 255 to +inf."""
+    return (np.asarray(s, dtype=np.uint32) << np.uint32(23)).view(np.float32)
+
+
+def mxfp4_quantize(w: np.ndarray):
+    """f32 [N, K] -> (blocks uint8 [N, K/2], scales uint8 [N, K/32])
+    (mxfp4/mod.rs:216-333).  e = clamp(floor(log2(absmax/6)) + 127, 0, 254), 127
+    for an all-zero block; nibble chosen by midpoint thresholds; byte i holds
+    element 2i in its low nibble and 2i+1 in its high nibble."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n, k = w.shape
+    assert k % MXFP4_BLOCK == 0
+    blk = w.reshape(n, k // MXFP4_BLOCK, MXFP4_BLOCK)
+    amax = np.abs(blk).max(2)
+    with np.errstate(divide="ignore"):
+        raw = np.floor(np.log2((amax / np.float32(6.0)).astype(np.float32))).astype(np.float64) + 127
+    e = np.where(amax == 0, 127, np.clip(raw, 0, 254)).astype(np.uint8)
+    sf = np.exp2(e.astype(np.float32) - 127).astype(np.float32)
+    inv = np.where(sf == 0, np.float32(0), np.float32(1) / sf).astype(np.float32)
+    v = blk * inv[:, :, None]
+    a = np.abs(v)
+    nib = np.select([a < 0.25, a < 0.75, a < 1.25, a < 1.75, a < 2.5, a < 3.5, a < 5.0],
+                    [0, 1, 2, 3, 4, 5, 6], default=7).astype(np.uint8)
+    nib = nib | ((v < 0).astype(np.uint8) << 3)
+    nib = nib.reshape(n, k)
+    packed = (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)
+    return packed, e
+
+
+def mxfp4_dequant(blocks: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """(uint8 [N, K/2], uint8 [N, K/32]) -> f32 [N, K] via the reference's
+    DEQUANT_LUT[scale][nibble] = fp4[nibble] * from_bits(scale << 23)
+    (mxfp4/mod.rs:473-545)."""
+    blocks = np.asarray(blocks, dtype=np.uint8)
+    n, kh = blocks.shape
+    k = kh * 2
+    nib = np.empty((n, k), np.uint8)
+    nib[:, 0::2] = blocks & 0x0F
+    nib[:, 1::2] = blocks >> 4
+    sf = np.repeat(e8m0_to_f32(scales), MXFP4_BLOCK, axis=1)
+    with np.errstate(invalid="ignore"):
+        return FP4_VALUES[nib] * sf
+
+
+# ----------------------------------------------------------------------------
+# 16-bit rounding helpers
+# ----------------------------------------------------------------------------
+
+
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    """f32 -> nearest-even bf16, returned as f32."""
+    u = np.asarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return r.astype(np.uint32).view(np.float32)
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    return (round_bf16(x).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(b: np.ndarray) -> np.ndarray:
+    return (np.asarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
