@@ -1,0 +1,251 @@
+// C ABI entry points: argument validation on the host, then kernel launches on
+// the caller's stream.  Nothing here allocates or synchronises.
+#include "hq_common.cuh"
+#include "hq_kernels.h"
+
+using namespace hq;
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool valid_dtype(int d) { return d == HQ_DT_F32 || d == HQ_DT_F16 || d == HQ_DT_BF16; }
+
+int64_t weight_row_bytes(int format, int64_t k) {
+  switch (format) {
+    case HQ_FMT_Q8_0: return k / 32 * 34;
+    case HQ_FMT_Q4_K: return k / 256 * 144;
+    case HQ_FMT_FP8_BLOCK: return k;
+    case HQ_FMT_MXFP4: return k / 2;
+    default: return -1;
+  }
+}
+
+int32_t check_weight(const hq_weight* w) {
+  if (w == nullptr || w->data == nullptr) return HQ_ERR_NULL;
+  if (w->n <= 0 || w->k <= 0 || w->n_experts <= 0) return HQ_ERR_SHAPE;
+  if (w->n > (1ll << 30) || w->k > (1ll << 30)) return HQ_ERR_SHAPE;
+  switch (w->format) {
+    case HQ_FMT_Q8_0:
+    case HQ_FMT_Q4_K:
+      if (w->k % 256 != 0) return HQ_ERR_SHAPE;
+      break;
+    case HQ_FMT_FP8_BLOCK:
+      if (w->k % 128 != 0 || w->k > 256 * 128) return HQ_ERR_SHAPE;
+      if (w->scales == nullptr) return HQ_ERR_NULL;
+      break;
+    case HQ_FMT_MXFP4:
+      if (w->k % 32 != 0) return HQ_ERR_SHAPE;
+      if (w->scales == nullptr) return HQ_ERR_NULL;
+      break;
+    default:
+      return HQ_ERR_FORMAT;
+  }
+  if (!aligned16(w->data)) return HQ_ERR_ALIGN;
+  if (weight_row_bytes(w->format, w->k) % 16 != 0) return HQ_ERR_ALIGN;
+  if (w->bias != nullptr && !valid_dtype(w->bias_dtype)) return HQ_ERR_FORMAT;
+  return HQ_OK;
+}
+
+void fill_weight(GemvParams& p, const hq_weight* w, const hq_weight* w_up) {
+  p.format = w->format;
+  p.n = (int)w->n;
+  p.k = (int)w->k;
+  p.w = w->data;
+  p.scales = w->scales;
+  p.bias = w->bias;
+  p.bias_dtype = w->bias_dtype;
+  p.w_up = w_up ? w_up->data : nullptr;
+  p.scales_up = w_up ? w_up->scales : nullptr;
+  p.bias_up = w_up ? w_up->bias : nullptr;
+  p.n_banks = w_up ? 2 : 1;
+  p.w_expert_stride = w->n * weight_row_bytes(w->format, w->k);
+  if (w->format == HQ_FMT_FP8_BLOCK) p.scale_expert_stride = ((w->n + 127) / 128) * ((w->k + 127) / 128);
+  else if (w->format == HQ_FMT_MXFP4) p.scale_expert_stride = w->n * (w->k / 32);
+  else p.scale_expert_stride = 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t hq_abi_version(void) { return HQ_ABI_VERSION; }
+
+const char* hq_error_string(int32_t code) {
+  switch (code) {
+    case HQ_OK: return "ok";
+    case HQ_ERR_NULL: return "required pointer is NULL";
+    case HQ_ERR_SHAPE: return "unsupported size";
+    case HQ_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
+    case HQ_ERR_FORMAT: return "unknown format, dtype or mode";
+    case HQ_ERR_CUDA: return "CUDA launch failed";
+    case HQ_ERR_WORKSPACE: return "workspace missing or too small";
+    case HQ_ERR_TOO_LARGE: return "size beyond the fixed maximum of this entry point";
+    default: return "unknown status";
+  }
+}
+
+int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* stream) {
+  if (status_dev == nullptr || out_host == nullptr) return HQ_ERR_NULL;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(out_host, status_dev, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return HQ_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return HQ_ERR_CUDA;
+  return HQ_OK;
+}
+
+int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, int64_t x_stride, void* y,
+                          int32_t y_dtype, int64_t y_stride, int64_t m, int32_t* status_dev, void* stream) {
+  int32_t rc = check_weight(w);
+  if (rc != HQ_OK) return rc;
+  if (m < 0 || m > (1 << 24)) return HQ_ERR_SHAPE;
+  if (m == 0) return HQ_OK;
+  if (x == nullptr || y == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return HQ_ERR_FORMAT;
+  if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
+  if (x_stride < w->k || y_stride < w->n) return HQ_ERR_SHAPE;
+  GemvParams p{};
+  fill_weight(p, w, nullptr);
+  p.m = (int)m;
+  p.x = x; p.x_dtype = x_dtype; p.x_stride = x_stride;
+  p.y = y; p.y_dtype = y_dtype; p.y_stride = y_stride;
+  p.act.act = HQ_ACT_NONE;
+  p.status = status_dev;
+  return launch_gemv(p, (int)((m + 7) / 8), (cudaStream_t)stream);
+}
+
+int32_t hq_router_topk(const void* logits, int32_t logits_dtype, int64_t n_rows, const hq_router_args* args,
+                       uint32_t* ids_out, float* weights_out, void* stream) {
+  if (args == nullptr) return HQ_ERR_NULL;
+  if (n_rows < 0) return HQ_ERR_SHAPE;
+  if (n_rows == 0) return HQ_OK;
+  if (logits == nullptr || ids_out == nullptr || weights_out == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(logits_dtype)) return HQ_ERR_FORMAT;
+  if (args->n_experts < 1 || args->n_experts > 1024) return HQ_ERR_SHAPE;
+  if (args->top_k < 1 || args->top_k > 32 || args->top_k > args->n_experts) return HQ_ERR_SHAPE;
+  if (args->score_mode < 0 || args->score_mode > 2 || args->weight_mode < 0 || args->weight_mode > 2)
+    return HQ_ERR_FORMAT;
+  return launch_router(logits, logits_dtype, n_rows, *args, ids_out, weights_out, (cudaStream_t)stream);
+}
+
+int64_t hq_moe_dispatch_workspace_bytes(int64_t n_tokens, int32_t top_k, int32_t n_experts) {
+  if (n_tokens < 0 || top_k < 1 || n_experts < 1) return -1;
+  return dispatch_layout(n_tokens, top_k, n_experts).total_words * 4;
+}
+
+int32_t hq_moe_dispatch_build(const uint32_t* ids, int64_t n_tokens, int32_t top_k, int32_t n_experts,
+                              int32_t* expert_bounds, int32_t* sorted_assign, int32_t* sorted_token,
+                              int32_t* inv_perm, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (n_tokens < 0 || top_k < 1 || top_k > 64 || n_experts < 1 || n_experts > 4096) return HQ_ERR_SHAPE;
+  if (n_tokens * top_k > (1ll << 30)) return HQ_ERR_SHAPE;
+  if (expert_bounds == nullptr || workspace == nullptr) return HQ_ERR_NULL;
+  if (n_tokens > 0 && (ids == nullptr || sorted_assign == nullptr || sorted_token == nullptr || inv_perm == nullptr))
+    return HQ_ERR_NULL;
+  if (workspace_bytes < hq_moe_dispatch_workspace_bytes(n_tokens, top_k, n_experts)) return HQ_ERR_WORKSPACE;
+  return launch_dispatch(ids, n_tokens, top_k, n_experts, expert_bounds, sorted_assign, sorted_token, inv_perm,
+                         (int32_t*)workspace, (cudaStream_t)stream);
+}
+
+int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const hq_act_args* act, const void* x,
+                              int32_t x_dtype, int32_t x_layout, int64_t n_tokens, int32_t top_k,
+                              const int32_t* expert_bounds, const int32_t* sorted_assign,
+                              const int32_t* sorted_token, const void* workspace, void* out, int32_t out_dtype,
+                              int32_t out_layout, int32_t* status_dev, void* stream) {
+  int32_t rc = check_weight(w);
+  if (rc != HQ_OK) return rc;
+  if (w_up != nullptr) {
+    rc = check_weight(w_up);
+    if (rc != HQ_OK) return rc;
+    if (w_up->format != w->format || w_up->n != w->n || w_up->k != w->k || w_up->n_experts != w->n_experts)
+      return HQ_ERR_SHAPE;
+    if (act == nullptr || act->act == HQ_ACT_NONE) return HQ_ERR_FORMAT;
+  }
+  if (n_tokens < 0 || top_k < 1) return HQ_ERR_SHAPE;
+  if (n_tokens == 0) return HQ_OK;
+  if (x == nullptr || out == nullptr || expert_bounds == nullptr || sorted_assign == nullptr ||
+      sorted_token == nullptr || workspace == nullptr)
+    return HQ_ERR_NULL;
+  if (!valid_dtype(x_dtype) || !valid_dtype(out_dtype)) return HQ_ERR_FORMAT;
+  if (x_layout < 0 || x_layout > 2 || (out_layout != HQ_ROWS_PER_SLOT && out_layout != HQ_ROWS_SORTED))
+    return HQ_ERR_FORMAT;
+  if (!aligned16(x) || (w->k * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
+  const bool has_act = act != nullptr && act->act != HQ_ACT_NONE;
+  if (has_act && w_up == nullptr && (w->n % 2) != 0) return HQ_ERR_SHAPE;
+  const DispatchLayout l = dispatch_layout(n_tokens, top_k, w->n_experts);
+  const int32_t* ws = (const int32_t*)workspace;
+  GemvParams p{};
+  fill_weight(p, w, w_up);
+  p.m = 0;
+  p.x = x; p.x_dtype = x_dtype; p.x_stride = w->k;
+  p.y = out; p.y_dtype = out_dtype;
+  p.y_stride = (has_act && w_up == nullptr) ? w->n / 2 : w->n;
+  p.tiles = ws + l.off_tiles8;
+  p.tile_count = ws;
+  p.expert_bounds = expert_bounds;
+  p.x_rows = x_layout == HQ_ROWS_PER_TOKEN ? sorted_token : (x_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr);
+  p.y_rows = out_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr;
+  if (has_act) p.act = *act; else p.act.act = HQ_ACT_NONE;
+  p.status = status_dev;
+  if (l.max_tiles8 > 65535) return HQ_ERR_TOO_LARGE;
+  return launch_gemv(p, (int)l.max_tiles8, (cudaStream_t)stream);
+}
+
+int32_t hq_moe_weighted_reduce(const void* y, int32_t y_dtype, const float* w, const int32_t* row_map,
+                               const void* addend, void* out, int32_t out_dtype, int64_t n_tokens, int32_t top_k,
+                               int64_t hidden, void* stream) {
+  if (n_tokens < 0 || top_k < 1 || top_k > 64 || hidden < 1) return HQ_ERR_SHAPE;
+  if (n_tokens == 0) return HQ_OK;
+  if (y == nullptr || w == nullptr || out == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(y_dtype) || !valid_dtype(out_dtype)) return HQ_ERR_FORMAT;
+  if (!aligned16(y) || (hidden * dtype_size(y_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
+  return launch_weighted_reduce(y, y_dtype, w, row_map, addend, out, out_dtype, n_tokens, top_k, hidden,
+                                (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_vector_quant(const void* x, int32_t x_dtype, int64_t n_elems, uint8_t* codes, float* scales,
+                            void* stream) {
+  if (n_elems < 0 || n_elems % 128 != 0) return HQ_ERR_SHAPE;
+  if (n_elems == 0) return HQ_OK;
+  if (x == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(x_dtype)) return HQ_ERR_FORMAT;
+  if ((reinterpret_cast<uintptr_t>(codes) & 3u) != 0) return HQ_ERR_ALIGN;
+  return launch_fp8_vector_quant(x, x_dtype, n_elems, codes, scales, (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_vector_dequant(const uint8_t* codes, const float* scales, int64_t n_elems, void* out,
+                              int32_t out_dtype, void* stream) {
+  if (n_elems < 0 || n_elems % 128 != 0) return HQ_ERR_SHAPE;
+  if (n_elems == 0) return HQ_OK;
+  if (codes == nullptr || scales == nullptr || out == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(out_dtype)) return HQ_ERR_FORMAT;
+  return launch_fp8_vector_dequant(codes, scales, n_elems, out, out_dtype, (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_block_quant(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t by, int32_t bx,
+                           uint8_t* codes, float* scales, void* stream) {
+  if (rows < 0 || cols < 0 || by < 1 || bx < 1) return HQ_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return HQ_OK;
+  if (w == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(w_dtype)) return HQ_ERR_FORMAT;
+  if ((rows + by - 1) / by > 65535) return HQ_ERR_SHAPE;
+  return launch_fp8_block_quant(w, w_dtype, rows, cols, by, bx, codes, scales, (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t rows, int64_t cols, int32_t by,
+                             int32_t bx, void* out, int32_t out_dtype, void* stream) {
+  if (rows < 0 || cols < 0 || by < 1 || bx < 1) return HQ_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return HQ_OK;
+  if (codes == nullptr || scales == nullptr || out == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(out_dtype)) return HQ_ERR_FORMAT;
+  return launch_fp8_block_dequant(codes, scales, rows, cols, by, bx, out, out_dtype, (cudaStream_t)stream);
+}
+
+int32_t hq_gated_act(const void* gate, const void* up, int32_t dtype, int64_t n_elems, int32_t interleaved,
+                     const hq_act_args* act, void* out, void* stream) {
+  if (n_elems < 0) return HQ_ERR_SHAPE;
+  if (n_elems == 0) return HQ_OK;
+  if (gate == nullptr || out == nullptr || act == nullptr || (!interleaved && up == nullptr)) return HQ_ERR_NULL;
+  if (!valid_dtype(dtype) || (act->act != HQ_ACT_SWIGLU && act->act != HQ_ACT_GPTOSS)) return HQ_ERR_FORMAT;
+  return launch_gated_act(gate, up, dtype, n_elems, interleaved, *act, out, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,165 @@
+// Token -> expert dispatch tables: a stable counting sort of the flat
+// assignment index t*top_k+s by expert id, built without output atomics so the
+// permutation is identical on every run (the reference's CUDA scatter orders
+// rows by atomic arrival; its host grouping is the stable order reproduced
+// here).
+//
+//   pass 1  per-chunk expert histograms (1024 assignments per block)
+//   pass 2  one block: per-expert exclusive prefix over chunks, expert bounds,
+//           tile lists (work items of <= 8 and <= 128 sorted rows per expert)
+//   pass 3  stable scatter: warps take their 32 assignments in turn; inside a
+//           warp the rank among equal experts comes from a match mask + popcount
+//
+// HBM bytes: T*k*4 read twice + T*k*4*3 written; negligible next to the GEMMs.
+#include "hq_common.cuh"
+#include "hq_kernels.h"
+
+namespace hq {
+
+DispatchLayout dispatch_layout(int64_t n_tokens, int top_k, int n_experts) {
+  DispatchLayout l;
+  const int64_t total = n_tokens * top_k;
+  l.n_blocks = (total + kDispatchChunk - 1) / kDispatchChunk;
+  if (l.n_blocks < 1) l.n_blocks = 1;
+  l.off_counts = 4;
+  l.max_tiles8 = (total + 7) / 8 + n_experts;
+  l.max_tiles128 = (total + 127) / 128 + n_experts;
+  l.off_tiles8 = l.off_counts + l.n_blocks * n_experts;
+  l.off_tiles128 = l.off_tiles8 + 2 * l.max_tiles8;
+  l.total_words = l.off_tiles128 + 2 * l.max_tiles128;
+  return l;
+}
+
+__global__ void __launch_bounds__(1024) dispatch_count_kernel(const uint32_t* __restrict__ ids, int total,
+                                                              int n_experts, int32_t* __restrict__ counts) {
+  extern __shared__ int32_t hist[];
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * kDispatchChunk + threadIdx.x;
+  if (i < total) {
+    const uint32_t e = ids[i];
+    if (e < (uint32_t)n_experts) atomicAdd(&hist[e], 1);  // integer counts: order does not matter
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[(int64_t)blockIdx.x * n_experts + e] = hist[e];
+}
+
+// counts[b][e] -> exclusive offset of chunk b inside expert e (in place); bounds; tile lists
+__global__ void __launch_bounds__(1024) dispatch_scan_kernel(int32_t* __restrict__ counts, int n_blocks,
+                                                             int n_experts, int32_t* __restrict__ bounds,
+                                                             int32_t* __restrict__ header,
+                                                             int32_t* __restrict__ tiles8,
+                                                             int32_t* __restrict__ tiles128) {
+  extern __shared__ int32_t sm[];
+  int32_t* tot = sm;                    // [E] expert totals, then exclusive bounds
+  int32_t* t8 = sm + n_experts;         // [E] tile8 offsets
+  int32_t* t128 = sm + 2 * n_experts;   // [E] tile128 offsets
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    int32_t run = 0;
+    for (int b = 0; b < n_blocks; ++b) {
+      const int32_t c = counts[(int64_t)b * n_experts + e];
+      counts[(int64_t)b * n_experts + e] = run;
+      run += c;
+    }
+    tot[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // warp scan over experts, 32 at a time, carrying the running totals
+    int32_t carry = 0, c8 = 0, c128 = 0;
+    for (int base = 0; base < n_experts; base += 32) {
+      const int e = base + threadIdx.x;
+      const int32_t cnt = e < n_experts ? tot[e] : 0;
+      int32_t v = cnt, v8 = (cnt + 7) / 8, v128 = (cnt + 127) / 128;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int32_t o = __shfl_up_sync(0xffffffffu, v, d);
+        const int32_t o8 = __shfl_up_sync(0xffffffffu, v8, d);
+        const int32_t o128 = __shfl_up_sync(0xffffffffu, v128, d);
+        if ((int)threadIdx.x >= d) { v += o; v8 += o8; v128 += o128; }
+      }
+      if (e < n_experts) {
+        bounds[e] = carry + v - cnt;
+        tot[e] = carry + v - cnt;
+        t8[e] = c8 + v8 - (cnt + 7) / 8;
+        t128[e] = c128 + v128 - (cnt + 127) / 128;
+      }
+      carry += __shfl_sync(0xffffffffu, v, 31);
+      c8 += __shfl_sync(0xffffffffu, v8, 31);
+      c128 += __shfl_sync(0xffffffffu, v128, 31);
+    }
+    if (threadIdx.x == 0) {
+      bounds[n_experts] = carry;
+      header[0] = c8;
+      header[1] = c128;
+      header[2] = carry;
+      header[3] = 0;
+    }
+  }
+  __syncthreads();
+  // add the expert base to every chunk offset
+  for (int64_t i = threadIdx.x; i < (int64_t)n_blocks * n_experts; i += blockDim.x) counts[i] += tot[i % n_experts];
+  // tile lists
+  for (int e = 0; e < n_experts; ++e) {
+    const int32_t start = tot[e];
+    const int32_t cnt = (e + 1 < n_experts ? tot[e + 1] : bounds[n_experts]) - start;
+    for (int i = threadIdx.x; i < (cnt + 7) / 8; i += blockDim.x) {
+      tiles8[2 * (t8[e] + i)] = e;
+      tiles8[2 * (t8[e] + i) + 1] = start + 8 * i;
+    }
+    for (int i = threadIdx.x; i < (cnt + 127) / 128; i += blockDim.x) {
+      tiles128[2 * (t128[e] + i)] = e;
+      tiles128[2 * (t128[e] + i) + 1] = start + 128 * i;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(1024) dispatch_scatter_kernel(const uint32_t* __restrict__ ids, int total,
+                                                                int top_k, int n_experts,
+                                                                const int32_t* __restrict__ offsets,
+                                                                int32_t* __restrict__ sorted_assign,
+                                                                int32_t* __restrict__ sorted_token,
+                                                                int32_t* __restrict__ inv_perm) {
+  extern __shared__ int32_t cur[];  // running position per expert for this chunk
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) cur[e] = offsets[(int64_t)blockIdx.x * n_experts + e];
+  __syncthreads();
+  const int i = blockIdx.x * kDispatchChunk + threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool ok = i < total;
+  const uint32_t e = ok ? ids[i] : 0xFFFFFFFFu;
+  const bool routed = ok && e < (uint32_t)n_experts;
+  // rank inside the warp among lanes with the same expert
+  const uint32_t peers = __match_any_sync(0xffffffffu, e);
+  const int rank = __popc(peers & ((1u << lane) - 1u));
+  const int group = __popc(peers);
+  const bool leader = rank == 0;
+  // warps commit in index order so earlier assignments get earlier positions
+  for (int w = 0; w < kDispatchChunk / 32; ++w) {
+    if (w == warp && routed) {
+      const int pos = cur[e] + rank;
+      sorted_assign[pos] = i;
+      sorted_token[pos] = i / top_k;
+      inv_perm[i] = pos;
+    }
+    __syncthreads();
+    if (w == warp && routed && leader) cur[e] += group;
+    __syncthreads();
+  }
+}
+
+int32_t launch_dispatch(const uint32_t* ids, int64_t n_tokens, int top_k, int n_experts, int32_t* bounds,
+                        int32_t* sorted_assign, int32_t* sorted_token, int32_t* inv_perm, int32_t* ws,
+                        cudaStream_t stream) {
+  const DispatchLayout l = dispatch_layout(n_tokens, top_k, n_experts);
+  const int total = (int)(n_tokens * top_k);
+  int32_t* counts = ws + l.off_counts;
+  const size_t sm1 = (size_t)n_experts * 4;
+  dispatch_count_kernel<<<(unsigned)l.n_blocks, 1024, sm1, stream>>>(ids, total, n_experts, counts);
+  dispatch_scan_kernel<<<1, 1024, 3 * sm1, stream>>>(counts, (int)l.n_blocks, n_experts, bounds, ws,
+                                                    ws + l.off_tiles8, ws + l.off_tiles128);
+  dispatch_scatter_kernel<<<(unsigned)l.n_blocks, 1024, sm1, stream>>>(ids, total, top_k, n_experts, counts,
+                                                                      sorted_assign, sorted_token, inv_perm);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+}  // namespace hq

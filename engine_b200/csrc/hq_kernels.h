@@ -1,0 +1,76 @@
+// Internal launch interfaces shared by the .cu files (not part of the C ABI).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/hanzoquant_b200.h"
+
+namespace hq {
+
+// ---- decode mat-vec (hq_gemv.cu) ----------------------------------------------
+struct GemvParams {
+  int format;
+  int n, k, m;                 // m: dense activation rows (ignored when tiles != nullptr)
+  int n_banks;                 // 1, or 2 = gate bank + up bank feeding one gated activation
+  const void* w;
+  const void* w_up;
+  const void* scales;
+  const void* scales_up;
+  const void* bias;
+  const void* bias_up;
+  int bias_dtype;
+  int64_t w_expert_stride;      // bytes between experts in w
+  int64_t scale_expert_stride;  // scale elements between experts
+  const void* x;
+  int x_dtype;
+  int64_t x_stride;             // elements
+  void* y;
+  int y_dtype;
+  int64_t y_stride;             // elements
+  // expert-indexed mode: work items of <= 8 sorted rows of one expert
+  const int32_t* tiles;         // [n_items][2] = (expert, first sorted row)
+  const int32_t* tile_count;    // device word holding n_items
+  const int32_t* expert_bounds; // [E+1]
+  const int32_t* x_rows;        // sorted row -> activation row (nullptr = identity)
+  const int32_t* y_rows;        // sorted row -> output row (nullptr = identity)
+  hq_act_args act;
+  int32_t* status;
+};
+int32_t launch_gemv(const GemvParams& p, int grid_y, cudaStream_t stream);
+
+// ---- dispatch tables (hq_dispatch.cu) -------------------------------------------
+constexpr int kDispatchChunk = 1024;  // flat assignments per block
+struct DispatchLayout {
+  int64_t n_blocks;      // ceil(T*k / kDispatchChunk)
+  int64_t off_counts;    // int32 words
+  int64_t off_tiles8;    // int32 words, [max8][2]
+  int64_t max_tiles8;
+  int64_t off_tiles128;  // int32 words, [max128][2]
+  int64_t max_tiles128;
+  int64_t total_words;
+};
+DispatchLayout dispatch_layout(int64_t n_tokens, int top_k, int n_experts);
+int32_t launch_dispatch(const uint32_t* ids, int64_t n_tokens, int top_k, int n_experts, int32_t* bounds,
+                        int32_t* sorted_assign, int32_t* sorted_token, int32_t* inv_perm, int32_t* ws,
+                        cudaStream_t stream);
+
+// ---- router (hq_router.cu) --------------------------------------------------------
+int32_t launch_router(const void* logits, int dtype, int64_t n_rows, const hq_router_args& a, uint32_t* ids,
+                      float* weights, cudaStream_t stream);
+
+// ---- elementwise / reduce (hq_elementwise.cu) --------------------------------------
+int32_t launch_weighted_reduce(const void* y, int y_dtype, const float* w, const int32_t* row_map,
+                               const void* addend, void* out, int out_dtype, int64_t n_tokens, int top_k,
+                               int64_t hidden, cudaStream_t stream);
+int32_t launch_fp8_vector_quant(const void* x, int x_dtype, int64_t n, uint8_t* codes, float* scales,
+                                cudaStream_t stream);
+int32_t launch_fp8_vector_dequant(const uint8_t* codes, const float* scales, int64_t n, void* out, int out_dtype,
+                                  cudaStream_t stream);
+int32_t launch_fp8_block_quant(const void* w, int w_dtype, int64_t rows, int64_t cols, int by, int bx,
+                               uint8_t* codes, float* scales, cudaStream_t stream);
+int32_t launch_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t rows, int64_t cols, int by,
+                                 int bx, void* out, int out_dtype, cudaStream_t stream);
+int32_t launch_gated_act(const void* gate, const void* up, int dtype, int64_t n, int interleaved,
+                         const hq_act_args& act, void* out, cudaStream_t stream);
+
+}  // namespace hq

@@ -1,0 +1,126 @@
+"""Host-side mirror of the reference's MoE glue over the C ABI: `moe_router_topk`
+(hanzo-engine/src/ops.rs:225-335), `MoEExperts.forward`
+(hanzo-engine/src/moe/experts/mod.rs:241-266, backends.rs:560-605) and the gpt-oss
+expert block (hanzo-engine/src/models/gpt_oss.rs:384-443)."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib as L
+from .quant import (DispatchTables, QuantMethod, _ptr, _require_cuda, _stream, dt_code, moe_dispatch_build)
+
+
+@dataclass
+class MoeRouterTopKConfig:
+    """Field for field the reference's config struct (hanzo-engine/src/ops.rs:225-233)."""
+    top_k: int
+    score_function: int = L.SCORE_SOFTMAX      # Raw / Softmax / Sigmoid
+    selected_weight: int = L.WEIGHT_SCORE      # Score / Softmax / Sigmoid
+    renormalize: bool = False
+    norm_min: float = 0.0
+    output_scale: float = 1.0
+    logit_clip: tuple[float, float] | None = None
+
+
+@dataclass
+class TopKOutput:
+    values: torch.Tensor    # f32 [T, k]
+    indices: torch.Tensor   # int32 [T, k] (bit pattern of the reference's u32 ids)
+
+
+def moe_router_topk(logits: torch.Tensor, config: MoeRouterTopKConfig, selection_bias: torch.Tensor | None = None,
+                    expert_scale: torch.Tensor | None = None) -> TopKOutput:
+    _require_cuda(logits, "logits")
+    t, e = logits.shape
+    logits = logits.contiguous()
+    ids = torch.empty((t, config.top_k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((t, config.top_k), dtype=torch.float32, device=logits.device)
+    bias = None if selection_bias is None else selection_bias.to(torch.float32).contiguous()
+    scale = None if expert_scale is None else expert_scale.to(torch.float32).contiguous()
+    clip = config.logit_clip
+    args = L.HqRouterArgs(e, config.top_k, config.score_function, config.selected_weight, int(config.renormalize),
+                          int(clip is not None), clip[0] if clip else 0.0, clip[1] if clip else 0.0,
+                          config.norm_min, config.output_scale, 0 if bias is None else bias.data_ptr(),
+                          0 if scale is None else scale.data_ptr())
+    L.check(L.lib().hq_router_topk(_ptr(logits), dt_code(logits.dtype), t, C.byref(args), _ptr(ids), _ptr(w),
+                                   _stream()), "hq_router_topk")
+    return TopKOutput(w, ids)
+
+
+def moe_weighted_reduce(y: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, row_map: torch.Tensor | None = None,
+                        addend: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = sum_s w[t, s] * y[row(t, s)] (+ addend[t]); y [T*k, H] or [T, k, H]."""
+    t, k = w.shape
+    h = y.shape[-1]
+    out = torch.empty((t, h), dtype=out_dtype, device=y.device)
+    if addend is not None and addend.dtype != out_dtype:
+        addend = addend.to(out_dtype)
+    L.check(L.lib().hq_moe_weighted_reduce(_ptr(y.contiguous()), dt_code(y.dtype), _ptr(w.contiguous()),
+                                           _ptr(row_map), _ptr(None if addend is None else addend.contiguous()),
+                                           _ptr(out), dt_code(out_dtype), t, k, h, _stream()),
+            "hq_moe_weighted_reduce")
+    return out
+
+
+def gated_act(gate: torch.Tensor, up: torch.Tensor | None, act: int, limit: float | None = None,
+              alpha: float = 1.702, interleaved: bool = False) -> torch.Tensor:
+    """fused_glu / gptoss_swiglu as a stand-alone op (hanzo-quant/kernels/ops/ops.cu:335-360, :845-858)."""
+    gate = gate.contiguous()
+    n = gate.numel() // 2 if interleaved else gate.numel()
+    shape = gate.shape[:-1] if interleaved else gate.shape
+    out = torch.empty(shape, dtype=gate.dtype, device=gate.device)
+    a = L.HqActArgs(act, int(limit is not None), 0.0 if limit is None else limit, alpha)
+    L.check(L.lib().hq_gated_act(_ptr(gate), _ptr(None if up is None else up.contiguous()), dt_code(gate.dtype), n,
+                                 int(interleaved), C.byref(a), _ptr(out), _stream()), "hq_gated_act")
+    return out
+
+
+class MoEExperts:
+    """Expert block: gate/up projection + gated activation + down projection + weighted sum over slots.
+
+    gate_proj/up_proj [E, I, H] and down_proj [E, H, I] as separate banks (Qwen3, DeepSeek), or a single
+    `gate_up_proj` [E, 2I, H] whose rows interleave gate/up (gpt-oss).  The intermediate stays expert-sorted
+    between the two projections; one dispatch build serves both."""
+
+    def __init__(self, down_proj: QuantMethod, gate_proj: QuantMethod | None = None, up_proj: QuantMethod | None = None,
+                 gate_up_proj: QuantMethod | None = None, act: int = L.ACT_SWIGLU, limit: float | None = None,
+                 alpha: float = 1.702, inter_dtype: torch.dtype = torch.float16):
+        if (gate_up_proj is None) == (gate_proj is None):
+            raise L.HqError("give either gate_proj+up_proj or gate_up_proj")
+        self.gate, self.up, self.gate_up, self.down = gate_proj, up_proj, gate_up_proj, down_proj
+        self.act = L.HqActArgs(act, int(limit is not None), 0.0 if limit is None else limit, alpha)
+        self.inter_dtype = inter_dtype
+        self.n_experts = down_proj.n_experts
+
+    def forward(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+                tables: DispatchTables | None = None) -> torch.Tensor:
+        _require_cuda(xs, "xs")
+        lead = xs.shape[:-1]
+        x = xs.reshape(-1, xs.shape[-1]).contiguous()
+        t, k = topk_ids.shape
+        tables = tables or moe_dispatch_build(topk_ids, self.n_experts)
+        first = self.gate_up if self.gate_up is not None else self.gate
+        inter = first.n // 2 if self.gate_up is not None else first.n
+        h = torch.empty((t * k, inter), dtype=self.inter_dtype, device=x.device)
+        w0 = first._weight_struct()
+        w1 = self.up._weight_struct() if self.up is not None else None
+        status = first._status_buf(x.device)
+        L.check(L.lib().hq_moe_gather_forward(C.byref(w0), None if w1 is None else C.byref(w1), C.byref(self.act),
+                                              _ptr(x), dt_code(x.dtype), L.ROWS_PER_TOKEN, t, k,
+                                              _ptr(tables.expert_bounds), _ptr(tables.sorted_assign),
+                                              _ptr(tables.sorted_token), _ptr(tables.workspace), _ptr(h),
+                                              dt_code(h.dtype), L.ROWS_SORTED, _ptr(status), _stream()),
+                "hq_moe_gather_forward(gate/up)")
+        y = torch.empty((t * k, self.down.n), dtype=torch.float32, device=x.device)
+        wd = self.down._weight_struct()
+        L.check(L.lib().hq_moe_gather_forward(C.byref(wd), None, None, _ptr(h), dt_code(h.dtype), L.ROWS_SORTED, t, k,
+                                              _ptr(tables.expert_bounds), _ptr(tables.sorted_assign),
+                                              _ptr(tables.sorted_token), _ptr(tables.workspace), _ptr(y),
+                                              dt_code(y.dtype), L.ROWS_SORTED, _ptr(status), _stream()),
+                "hq_moe_gather_forward(down)")
+        out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype or xs.dtype, tables.inv_perm, shared_out)
+        return out.reshape(*lead, self.down.n)

@@ -1,0 +1,331 @@
+"""Host-side mirror of hanzo-quant's `QuantMethod` API over the C ABI.
+
+Same names and argument meaning as the reference trait
+(hanzo-quant/src/lib.rs:1004-1108): `forward`, `forward_raw`, `gather_forward`,
+`gather_forward_raw`, `dequantize_w`, `quantized_act_type`, implemented by
+`GgufMatMul` (hanzo-quant/src/gguf/mod.rs:31-399), `BlockwiseFP8Linear`
+(blockwise_fp8/mod.rs:24-198) and `MXFP4Layer` (mxfp4/mod.rs:29-174).  torch is
+used only for device memory and the stream; every computation is a call into
+libhanzoquant_b200.so.  The reference is Rust; with no Rust toolchain available
+this Python layer is the tested host binding of the same C entry points.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib as L
+
+_DT = {torch.float32: L.DT_F32, torch.float16: L.DT_F16, torch.bfloat16: L.DT_BF16}
+
+
+def dt_code(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise L.HqError(f"unsupported dtype {dtype}: expected f32, f16 or bf16") from None
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise L.HqError(f"{name} must be a CUDA tensor: this library has no CPU path")
+
+
+@dataclass
+class DispatchTables:
+    """Output of `moe_dispatch_build` (hanzo-quant/src/gguf/cuda.rs:538-578): expert-sorted views of
+    the flat assignment list t*k+s."""
+    n_tokens: int
+    top_k: int
+    n_experts: int
+    expert_bounds: torch.Tensor   # int32 [E+1]
+    sorted_assign: torch.Tensor   # int32 [T*k] flat assignment index
+    sorted_token: torch.Tensor    # int32 [T*k] token index
+    inv_perm: torch.Tensor        # int32 [T*k] flat index -> sorted position
+    workspace: torch.Tensor       # int32 words (tile lists)
+
+
+def moe_dispatch_build(ids: torch.Tensor, n_experts: int) -> DispatchTables:
+    _require_cuda(ids, "ids")
+    t, k = ids.shape
+    ids = ids.contiguous()
+    if ids.dtype not in (torch.int32, torch.uint32):
+        ids = ids.to(torch.int32)
+    dev = ids.device
+    ws_bytes = L.lib().hq_moe_dispatch_workspace_bytes(t, k, n_experts)
+    bounds = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    sa = torch.empty(t * k, dtype=torch.int32, device=dev)
+    st = torch.empty(t * k, dtype=torch.int32, device=dev)
+    inv = torch.empty(t * k, dtype=torch.int32, device=dev)
+    ws = torch.empty(ws_bytes // 4, dtype=torch.int32, device=dev)
+    L.check(L.lib().hq_moe_dispatch_build(_ptr(ids), t, k, n_experts, _ptr(bounds), _ptr(sa), _ptr(st), _ptr(inv),
+                                          _ptr(ws), ws_bytes, _stream()), "hq_moe_dispatch_build")
+    return DispatchTables(t, k, n_experts, bounds, sa, st, inv, ws)
+
+
+class QuantMethod:
+    """Base of the quantized layers; weights are [N, K] (dense) or [E, N, K] (expert bank)."""
+
+    format: int
+    n_experts: int
+    n: int
+    k: int
+
+    def __init__(self):
+        self._status = None
+
+    # -- plumbing -------------------------------------------------------------------
+    def _weight_struct(self) -> L.HqWeight:
+        raise NotImplementedError
+
+    def _status_buf(self, dev) -> torch.Tensor:
+        if self._status is None or self._status.device != dev:
+            self._status = torch.zeros(4, dtype=torch.int32, device=dev)
+        return self._status
+
+    def device_status(self) -> list[int]:
+        """Reads the device status word (synchronises the current stream); [0] != 0 means a kernel gave up on
+        a bounded wait."""
+        if self._status is None:
+            return [0, 0, 0, 0]
+        out = (C.c_int32 * 4)()
+        L.check(L.lib().hq_status_read(_ptr(self._status), C.byref(out), _stream()), "hq_status_read")
+        return list(out)
+
+    # -- QuantMethod API ------------------------------------------------------------------
+    def quantized_act_type(self):
+        """Activation dtype the layer computes in; None = use the input's (lib.rs:1065)."""
+        return None
+
+    def forward(self, a: torch.Tensor) -> torch.Tensor:
+        """y = a . W^T (+ b); leading dims are flattened to rows (lib.rs:1014-1021)."""
+        return self.forward_raw(a)
+
+    def forward_raw(self, a: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        _require_cuda(a, "a")
+        if self.n_experts != 1:
+            raise L.HqError("forward on an expert bank: use gather_forward")
+        if a.shape[-1] != self.k:
+            raise L.HqError(f"shape mismatch: input has {a.shape[-1]} features, weight expects {self.k}")
+        lead = a.shape[:-1]
+        x = a.reshape(-1, self.k)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        m = x.shape[0]
+        out_dtype = out_dtype or a.dtype
+        y = torch.empty((m, self.n), dtype=out_dtype, device=a.device)
+        w = self._weight_struct()
+        L.check(L.lib().hq_linear_forward(C.byref(w), _ptr(x), dt_code(x.dtype), x.stride(0) if m > 1 else self.k,
+                                          _ptr(y), dt_code(out_dtype), self.n, m,
+                                          _ptr(self._status_buf(a.device)), _stream()), "hq_linear_forward")
+        return y.reshape(*lead, self.n)
+
+    def gather_forward(self, a: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        """Per-assignment projection out of the bank (lib.rs:1032-1040): a is [T, K], [T, 1, K] (one row per
+        token) or [T, k, K] (one row per slot); indices [T, k]; returns [T, k, N] in a's dtype."""
+        return self.gather_forward_raw(a, indices)
+
+    def gather_forward_raw(self, a: torch.Tensor, indices: torch.Tensor, out_dtype: torch.dtype | None = None,
+                           tables: DispatchTables | None = None) -> torch.Tensor:
+        _require_cuda(a, "a")
+        t, k = indices.shape
+        if a.dim() == 2:
+            layout = L.ROWS_PER_TOKEN
+        elif a.shape[1] == 1 and not self._3d_input_is_per_slot():
+            layout = L.ROWS_PER_TOKEN
+        else:
+            layout = L.ROWS_PER_SLOT
+            if a.shape[1] != k:
+                raise L.HqError(f"per-slot input has {a.shape[1]} slots, indices have {k}")
+        if a.shape[0] != t or a.shape[-1] != self.k:
+            raise L.HqError("gather_forward: input / indices / weight shapes disagree")
+        x = a.contiguous()
+        tables = tables or moe_dispatch_build(indices, self.n_experts)
+        out_dtype = out_dtype or a.dtype
+        out = torch.empty((t, k, self.n), dtype=out_dtype, device=a.device)
+        w = self._weight_struct()
+        L.check(L.lib().hq_moe_gather_forward(C.byref(w), None, None, _ptr(x), dt_code(x.dtype), layout, t, k,
+                                              _ptr(tables.expert_bounds), _ptr(tables.sorted_assign),
+                                              _ptr(tables.sorted_token), _ptr(tables.workspace), _ptr(out),
+                                              dt_code(out_dtype), L.ROWS_PER_SLOT,
+                                              _ptr(self._status_buf(a.device)), _stream()),
+                "hq_moe_gather_forward")
+        return out
+
+    def _3d_input_is_per_slot(self) -> bool:
+        return False
+
+    def dequantize_w(self) -> torch.Tensor:
+        """f32 weights [N, K] / [E, N, K], computed on the device by pushing the identity through the layer's
+        own kernels (every product is exact, each sum has one non-zero term)."""
+        dev = self._device()
+        eye = torch.eye(self.k, dtype=torch.float16, device=dev)
+        outs = []
+        for e in range(self.n_experts):
+            layer = self._expert_view(e)
+            outs.append(layer.forward_raw(eye, torch.float32).t().contiguous())
+        return outs[0] if self.n_experts == 1 else torch.stack(outs)
+
+    def _device(self):
+        raise NotImplementedError
+
+    def _expert_view(self, e: int) -> "QuantMethod":
+        raise NotImplementedError
+
+
+GGML_Q8_0, GGML_Q4_K = "Q8_0", "Q4_K"
+_GGML = {GGML_Q8_0: (L.FMT_Q8_0, 32, 34), GGML_Q4_K: (L.FMT_Q4_K, 256, 144)}
+
+
+class GgufMatMul(QuantMethod):
+    """GGUF block-quantized linear / expert bank (hanzo-quant/src/gguf/mod.rs:31-399); `data` holds the raw
+    GGUF block bytes exactly as a .gguf file stores them: uint8 [N, K/blk*bytes] or [E, N, ...]."""
+
+    def __init__(self, data: torch.Tensor, qtype: str, k: int, bias: torch.Tensor | None = None):
+        super().__init__()
+        if qtype not in _GGML:
+            raise L.HqError(f"GGML type {qtype} is not on this path (Q8_0 and Q4_K are)")
+        _require_cuda(data, "data")
+        self.format, blk, nbytes = _GGML[qtype]
+        self.qtype = qtype
+        if k % 256:
+            raise L.HqError(f"K = {k} must be a multiple of 256")
+        row_bytes = k // blk * nbytes
+        if data.dtype != torch.uint8 or data.shape[-1] != row_bytes:
+            raise L.HqError(f"expected uint8 rows of {row_bytes} bytes")
+        self.data = data.contiguous()
+        self.n_experts = data.shape[0] if data.dim() == 3 else 1
+        self.n = data.shape[-2]
+        self.k = k
+        self.bias = bias
+
+    def _weight_struct(self):
+        return L.HqWeight(self.format, self.n_experts, self.n, self.k, self.data.data_ptr(), 0,
+                          0 if self.bias is None else self.bias.data_ptr(),
+                          0 if self.bias is None else dt_code(self.bias.dtype), 0)
+
+    def _device(self):
+        return self.data.device
+
+    def _expert_view(self, e):
+        if self.n_experts == 1:
+            return self
+        return GgufMatMul(self.data[e], self.qtype, self.k)
+
+
+class BlockwiseFP8Linear(QuantMethod):
+    """e4m3 weight with a 128x128 f32 `weight_scale_inv` grid (hanzo-quant/src/blockwise_fp8/mod.rs:24-198).
+    weight uint8/float8 [N, K] or [E, N, K]; scale f32 [ceil(N/128), ceil(K/128)] (+ leading E)."""
+
+    def __init__(self, weight: torch.Tensor, weight_scale_inv: torch.Tensor, bias: torch.Tensor | None = None,
+                 weight_block_size=(128, 128)):
+        super().__init__()
+        _require_cuda(weight, "weight")
+        if tuple(weight_block_size) != (128, 128):
+            raise L.HqError("only 128x128 weight blocks are supported")
+        if weight.dtype != torch.uint8:
+            weight = weight.view(torch.uint8)
+        self.format = L.FMT_FP8_BLOCK
+        self.weight = weight.contiguous()
+        self.scale = weight_scale_inv.to(torch.float32).contiguous()
+        self.n_experts = weight.shape[0] if weight.dim() == 3 else 1
+        self.n, self.k = weight.shape[-2], weight.shape[-1]
+        want = (-(-self.n // 128), -(-self.k // 128))
+        if tuple(self.scale.shape[-2:]) != want:
+            raise L.HqError(f"scale grid {tuple(self.scale.shape)} does not match {want}")
+        self.bias = bias
+
+    def _weight_struct(self):
+        return L.HqWeight(self.format, self.n_experts, self.n, self.k, self.weight.data_ptr(), self.scale.data_ptr(),
+                          0 if self.bias is None else self.bias.data_ptr(),
+                          0 if self.bias is None else dt_code(self.bias.dtype), 0)
+
+    def _device(self):
+        return self.weight.device
+
+    def _expert_view(self, e):
+        return self if self.n_experts == 1 else BlockwiseFP8Linear(self.weight[e], self.scale[e])
+
+
+class MXFP4Layer(QuantMethod):
+    """MXFP4 expert bank / linear (hanzo-quant/src/mxfp4/mod.rs:29-174): blocks uint8 [E, N, K/2] (low nibble =
+    even element), scales uint8 [E, N, K/32] (e8m0), optional bias [E, N].  Any 3-D input to gather_forward is
+    taken as one row per slot with top_k = dim 1 (mxfp4/ops.rs:349-355)."""
+
+    def __init__(self, blocks: torch.Tensor, scales: torch.Tensor, bias: torch.Tensor | None = None):
+        super().__init__()
+        _require_cuda(blocks, "blocks")
+        self.format = L.FMT_MXFP4
+        self.blocks = blocks.contiguous()
+        self.scales = scales.contiguous()
+        self.n_experts = blocks.shape[0] if blocks.dim() == 3 else 1
+        self.n, self.k = blocks.shape[-2], blocks.shape[-1] * 2
+        if self.k % 32 or tuple(scales.shape[-2:]) != (self.n, self.k // 32):
+            raise L.HqError("MXFP4: K must be a multiple of 32 and scales [.., N, K/32]")
+        self.bias = None if bias is None else bias.contiguous()
+
+    def _weight_struct(self):
+        return L.HqWeight(self.format, self.n_experts, self.n, self.k, self.blocks.data_ptr(),
+                          self.scales.data_ptr(), 0 if self.bias is None else self.bias.data_ptr(),
+                          0 if self.bias is None else dt_code(self.bias.dtype), 0)
+
+    def _3d_input_is_per_slot(self):
+        return True
+
+    def _device(self):
+        return self.blocks.device
+
+    def _expert_view(self, e):
+        return self if self.n_experts == 1 else MXFP4Layer(self.blocks[e], self.scales[e])
+
+
+# ---- FP8 quantizers (hanzo-quant/src/vector_fp8/ops.rs, blockwise_fp8/ops.rs) --------------------
+
+def fp8_vector_quantize(x: torch.Tensor):
+    """1x128 groups along the flattened tensor -> (codes uint8 like x, scales f32 [numel/128])."""
+    _require_cuda(x, "x")
+    x = x.contiguous()
+    n = x.numel()
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(n // 128, dtype=torch.float32, device=x.device)
+    L.check(L.lib().hq_fp8_vector_quant(_ptr(x), dt_code(x.dtype), n, _ptr(codes), _ptr(scales), _stream()),
+            "hq_fp8_vector_quant")
+    return codes, scales
+
+
+def fp8_vector_dequantize(codes: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    out = torch.empty(codes.shape, dtype=out_dtype, device=codes.device)
+    L.check(L.lib().hq_fp8_vector_dequant(_ptr(codes.contiguous()), _ptr(scales), codes.numel(), _ptr(out),
+                                          dt_code(out_dtype), _stream()), "hq_fp8_vector_dequant")
+    return out
+
+
+def fp8_blockwise_quantize(w: torch.Tensor, weight_block_size=(128, 128)):
+    _require_cuda(w, "w")
+    w = w.contiguous()
+    rows, cols = w.shape
+    by, bx = weight_block_size
+    codes = torch.empty((rows, cols), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((-(-rows // by), -(-cols // bx)), dtype=torch.float32, device=w.device)
+    L.check(L.lib().hq_fp8_block_quant(_ptr(w), dt_code(w.dtype), rows, cols, by, bx, _ptr(codes), _ptr(scales),
+                                       _stream()), "hq_fp8_block_quant")
+    return codes, scales
+
+
+def fp8_blockwise_dequantize(codes: torch.Tensor, scales: torch.Tensor, weight_block_size, out_dtype):
+    rows, cols = codes.shape
+    by, bx = weight_block_size
+    out = torch.empty((rows, cols), dtype=out_dtype, device=codes.device)
+    L.check(L.lib().hq_fp8_block_dequant(_ptr(codes.contiguous()), _ptr(scales.contiguous()), rows, cols, by, bx,
+                                         _ptr(out), dt_code(out_dtype), _stream()), "hq_fp8_block_dequant")
+    return out

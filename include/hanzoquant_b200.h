@@ -1,0 +1,212 @@
+/*
+ * libhanzoquant_b200 -- C ABI of the B200 (sm_100a) quantized-linear and
+ * sparse-MoE expert path.
+ *
+ * This is the boundary a host binding (Rust FFI, ctypes, cgo ...) links
+ * against.  It replaces the `extern "C" launch_*` families that hanzo-quant
+ * declares in hanzo-quant/src/gguf/ffi.rs, blockwise_fp8/ffi.rs,
+ * vector_fp8/ffi.rs, mxfp4/ffi.rs, utils/ffi.rs and
+ * hanzo-engine/src/cuda/ffi.rs:466-520; each entry point below names the
+ * reference interface it stands in for.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless
+ *     the parameter name ends in `_host`;
+ *   - the caller owns every buffer, including scratch (`*_workspace_bytes`
+ *     tells how much); nothing here allocates unless stated otherwise;
+ *   - all work is enqueued on the `stream` argument (a cudaStream_t passed as
+ *     void*), nothing synchronises the host;
+ *   - every call returns an int32 status: 0 = enqueued, < 0 = argument error
+ *     found on the host before any launch (see HQ_ERR_*).  A kernel that gave
+ *     up on a bounded wait writes a code into the optional device status word
+ *     (int32[4], see hq_status_*), it never spins forever.
+ *   - there is no CPU fallback: without a CUDA device the calls fail with
+ *     HQ_ERR_CUDA.
+ */
+#ifndef HANZOQUANT_B200_H
+#define HANZOQUANT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HQ_ABI_VERSION 1
+
+/* status codes */
+#define HQ_OK 0
+#define HQ_ERR_NULL (-1)        /* required pointer is NULL */
+#define HQ_ERR_SHAPE (-2)       /* size not supported (divisibility, range) */
+#define HQ_ERR_ALIGN (-3)       /* pointer or stride not 16-byte aligned */
+#define HQ_ERR_FORMAT (-4)      /* unknown format / dtype / mode code */
+#define HQ_ERR_CUDA (-5)        /* CUDA runtime error at launch (no device, bad config) */
+#define HQ_ERR_WORKSPACE (-6)   /* workspace missing or too small */
+#define HQ_ERR_TOO_LARGE (-7)   /* size beyond a stated fixed maximum */
+
+/* weight formats (hanzo-quant: GgufMatMul Q8_0 / Q4_K, BlockwiseFP8Linear, MXFP4Layer) */
+#define HQ_FMT_Q8_0 0       /* GGUF block_q8_0 {half d; int8 qs[32]}, 34 B / 32 weights   */
+#define HQ_FMT_Q4_K 1       /* GGUF block_q4_K, 144 B / 256 weights                        */
+#define HQ_FMT_FP8_BLOCK 2  /* e4m3 codes [N,K] + f32 scale[ceil(N/128), ceil(K/128)]      */
+#define HQ_FMT_MXFP4 3      /* e2m1 nibbles [N,K/2] (low nibble = even k) + e8m0 [N,K/32]  */
+
+/* element types of activations, outputs, biases */
+#define HQ_DT_F32 0
+#define HQ_DT_F16 1
+#define HQ_DT_BF16 2
+
+/* router codes: hanzo-engine/src/ops.rs:194-222 */
+#define HQ_SCORE_RAW 0
+#define HQ_SCORE_SOFTMAX 1
+#define HQ_SCORE_SIGMOID 2
+#define HQ_WEIGHT_SCORE 0
+#define HQ_WEIGHT_SOFTMAX 1
+#define HQ_WEIGHT_SIGMOID 2
+
+/* gated activation fused behind a gate/up projection */
+#define HQ_ACT_NONE 0
+#define HQ_ACT_SWIGLU 1        /* silu(gate) * up, optional clamp (hanzo-engine/src/ops.rs:3545-3556) */
+#define HQ_ACT_GPTOSS 2        /* (clamp(up,+-L)+1) * g*sigmoid(alpha*g), g=min(gate,L) (models/gpt_oss.rs:116-135) */
+
+/* A quantized weight matrix [N, K] or expert bank [E, N, K], row-major, in the
+ * exact byte layout the reference keeps on the device (hanzo-quant
+ * kernels/mmvq_gguf/mmvq_gguf.cu:134-170, src/blockwise_fp8/mod.rs:24-30,
+ * src/mxfp4/mod.rs:29-41).  Expert e starts at data + e*N*row_bytes. */
+typedef struct hq_weight {
+  int32_t format;      /* HQ_FMT_* */
+  int32_t n_experts;   /* 1 for a dense layer */
+  int64_t n;           /* output features */
+  int64_t k;           /* input features */
+  const void* data;    /* block bytes / e4m3 codes / packed nibbles */
+  const void* scales;  /* FP8: f32 [E, ceil(N/128), ceil(K/128)]; MXFP4: u8 [E, N, K/32]; else NULL */
+  const void* bias;    /* optional [E, N] in bias_dtype, or NULL */
+  int32_t bias_dtype;  /* HQ_DT_* */
+  int32_t reserved;
+} hq_weight;
+
+/* ---- library ------------------------------------------------------------ */
+int32_t hq_abi_version(void);
+const char* hq_error_string(int32_t code);
+/* Reads the 4-word device status buffer after synchronising `stream`
+ * (test / debug helper; the hot path never calls it). */
+int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* stream);
+
+/* ---- dense quantized linear: QuantMethod::forward ------------------------
+ * y[m, n] = sum_k x[m, k] * dequant(W)[n, k] (+ bias[n]).
+ * Replaces launch_mmvq_gguf_quantize_q8_1_* + launch_mmvq_gguf_{q4_k,q8_0}_*_plain
+ * (hanzo-quant/src/gguf/fast_mmvq.rs:107-148, :343-368), launch_fp8_matmul_*
+ * (blockwise_fp8/ffi.rs) and launch_mxfp4_matmul_* (mxfp4/ffi.rs).  Activations
+ * are NOT quantized to int8 (the reference's Q8_1 step): x is used at 16-bit
+ * precision, products accumulate in f32.
+ * x: [m, k] with row stride x_stride elements; y: [m, n] with row stride y_stride.
+ * Requires K % 256 == 0 for Q8_0/Q4_K, K % 128 == 0 for FP8, K % 32 == 0 for
+ * MXFP4; x rows 16-byte aligned.  Any m >= 0 (rows are processed 8 at a time
+ * on the decode path). */
+int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, int64_t x_stride, void* y,
+                          int32_t y_dtype, int64_t y_stride, int64_t m, int32_t* status_dev, void* stream);
+
+/* ---- router: moe_router_topk ---------------------------------------------
+ * Replaces moe_router_topk_{f32,bf16,f16} (hanzo-engine/src/cuda/ffi.rs:466-520,
+ * kernel hanzo-engine/src/cuda/sort.cu:1048-1201) with the canonical tie-break
+ * (score DESC, expert id ASC; hanzo-engine/src/ops.rs:241-251) always on.
+ * logits [n_rows, n_experts]; ids_out uint32 [n_rows, top_k] in descending
+ * selection order; weights_out f32 [n_rows, top_k].  selection_bias /
+ * expert_scale: f32 [n_experts] or NULL.  n_experts <= 1024, top_k <= 32. */
+typedef struct hq_router_args {
+  int32_t n_experts, top_k;
+  int32_t score_mode, weight_mode;   /* HQ_SCORE_*, HQ_WEIGHT_* */
+  int32_t renormalize, clamp_logits;
+  float clamp_min, clamp_max;
+  float norm_min, output_scale;
+  const float* selection_bias;
+  const float* expert_scale;
+} hq_router_args;
+int32_t hq_router_topk(const void* logits, int32_t logits_dtype, int64_t n_rows, const hq_router_args* args,
+                       uint32_t* ids_out, float* weights_out, void* stream);
+
+/* ---- dispatch tables: moe_dispatch_build ----------------------------------
+ * Replaces launch_moe_dispatch (hanzo-quant/src/gguf/ffi.rs:251-262; kernels
+ * moe_grouped.cu:632-676) with a deterministic, stable permutation: flat
+ * assignment indices t*top_k+s sorted by expert id, ties in (t, s) order -- the
+ * order of the reference's host grouping (hanzo-quant/src/mxfp4/ops.rs:237-271).
+ * Outputs: expert_bounds int32 [E+1]; sorted_assign int32 [T*k] (flat index);
+ * sorted_token int32 [T*k] (token index); inv_perm int32 [T*k] (flat index ->
+ * sorted position).  Also fills two tile lists for the expert GEMMs in the
+ * workspace (see hq_moe_dispatch_workspace_bytes). */
+int64_t hq_moe_dispatch_workspace_bytes(int64_t n_tokens, int32_t top_k, int32_t n_experts);
+int32_t hq_moe_dispatch_build(const uint32_t* ids, int64_t n_tokens, int32_t top_k, int32_t n_experts,
+                              int32_t* expert_bounds, int32_t* sorted_assign, int32_t* sorted_token,
+                              int32_t* inv_perm, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ---- expert projection: QuantMethod::gather_forward ------------------------
+ * out[t, s, :] = dequant(W[ids[t,s]]) . x_row (+ bias[ids[t,s]]), out [T, k, N].
+ * x_layout: HQ_ROWS_PER_TOKEN = [T, K], one row per token shared by its k slots;
+ * HQ_ROWS_PER_SLOT = [T, k, K] in (token, slot) order; HQ_ROWS_SORTED = [T*k, K]
+ * in expert-sorted order (the order of sorted_assign).  out_layout:
+ * HQ_ROWS_PER_SLOT = [T, k, N] (what gather_forward returns) or HQ_ROWS_SORTED
+ * (kept expert-sorted for a following down projection).  Replaces launch_indexed_moe_forward_{q4k,q8_0}_q8_1,
+ * launch_moe_grouped_gemm_*, launch_mmq_gguf_*_moe (hanzo-quant/src/gguf/ffi.rs),
+ * launch_fp8_indexed_moe_gemm_* (blockwise_fp8/ffi.rs) and
+ * launch_mxfp4_indexed_moe_gemm_* / launch_mxfp4_moe_grouped_gemm_* (mxfp4/ffi.rs).
+ * Needs the dispatch tables built by hq_moe_dispatch_build for the same ids
+ * (`workspace` is that call's workspace).
+ * act != HQ_ACT_NONE fuses the gated activation: with `w_up` given, W is the
+ * gate bank and w_up the up bank (out [T,k,N]); with w_up NULL the bank rows
+ * interleave gate/up (row 2i = gate_i, 2i+1 = up_i) and out is [T,k,N/2]. */
+typedef struct hq_act_args {
+  int32_t act;          /* HQ_ACT_* */
+  int32_t has_limit;    /* SWIGLU: clamp gate<=limit, |up|<=limit first */
+  float limit;          /* GPTOSS: L */
+  float alpha;          /* GPTOSS: alpha */
+} hq_act_args;
+#define HQ_ROWS_PER_TOKEN 0
+#define HQ_ROWS_PER_SLOT 1
+#define HQ_ROWS_SORTED 2
+int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const hq_act_args* act, const void* x,
+                              int32_t x_dtype, int32_t x_layout, int64_t n_tokens, int32_t top_k,
+                              const int32_t* expert_bounds, const int32_t* sorted_assign,
+                              const int32_t* sorted_token, const void* workspace, void* out, int32_t out_dtype,
+                              int32_t out_layout, int32_t* status_dev, void* stream);
+
+/* ---- combine: moe_weighted_reduce_flat -------------------------------------
+ * out[t, :] = sum_s w[t, s] * y[t, s, :] (+ addend[t, :]), f32 accumulation in
+ * slot order, no atomics.  Replaces launch_moe_weighted_reduce_flat{,_bf16}
+ * (hanzo-quant/src/gguf/ffi.rs:421-435, moe_grouped.cu:678-703) and
+ * moe_combine_kernel (hanzo-engine/src/cuda/moe_combine.cu:38-60).
+ * y [T*k, H] in y_dtype, w f32 [T, k], addend [T, H] in out_dtype or NULL.
+ * row_map int32 [T*k] gives the row of y that holds assignment (t, s) -- pass
+ * inv_perm from hq_moe_dispatch_build when y is expert-sorted, NULL when y is
+ * already in (token, slot) order. */
+int32_t hq_moe_weighted_reduce(const void* y, int32_t y_dtype, const float* w, const int32_t* row_map,
+                               const void* addend, void* out, int32_t out_dtype, int64_t n_tokens, int32_t top_k,
+                               int64_t hidden, void* stream);
+
+/* ---- FP8 quantizers ---------------------------------------------------------
+ * 1x128 groups along the last axis: scale = absmax/448 (1e-12 if zero),
+ * code = e4m3(clamp(v/scale, +-448)).  Replaces launch_quant_fp8_vector_kernel_*
+ * / launch_dequant_fp8_vector_kernel_* (hanzo-quant/src/vector_fp8/ffi.rs;
+ * CPU twin vector_fp8/ops.rs:235-287).  n_elems % 128 == 0. */
+int32_t hq_fp8_vector_quant(const void* x, int32_t x_dtype, int64_t n_elems, uint8_t* codes, float* scales,
+                            void* stream);
+int32_t hq_fp8_vector_dequant(const uint8_t* codes, const float* scales, int64_t n_elems, void* out,
+                              int32_t out_dtype, void* stream);
+/* 128x128 (by x bx) blocks over [rows, cols]: launch_{quant,dequant}_fp8_blockwise_kernel_*
+ * (hanzo-quant/src/blockwise_fp8/ffi.rs; CPU twin blockwise_fp8/ops.rs:11-59, :329-411). */
+int32_t hq_fp8_block_quant(const void* w, int32_t w_dtype, int64_t rows, int64_t cols, int32_t by, int32_t bx,
+                           uint8_t* codes, float* scales, void* stream);
+int32_t hq_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t rows, int64_t cols, int32_t by,
+                             int32_t bx, void* out, int32_t out_dtype, void* stream);
+
+/* ---- gated activations as stand-alone ops -----------------------------------
+ * out = act(gate, up) elementwise over n_elems; interleaved = 1 reads pairs
+ * (gate, up) from `gate` ([..., I, 2]) and ignores `up`.  Replaces fused_glu_*,
+ * gptoss_swiglu_* and gptoss_swiglu_interleaved_* (hanzo-quant/src/utils/ffi.rs,
+ * kernels/ops/ops.cu:335-360, :482-512, :845-858).  Math in f32, one rounding
+ * to `dtype` at the end. */
+int32_t hq_gated_act(const void* gate, const void* up, int32_t dtype, int64_t n_elems, int32_t interleaved,
+                     const hq_act_args* act, void* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HANZOQUANT_B200_H */
