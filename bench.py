@@ -1,0 +1,391 @@
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemv] [--impl reference]
+
+Workload `gemv` (default): the Q8_0 decode mat-vec sweep over Llama-3-8B layer shapes
+(4096->4096, 4096->14336, 14336->4096, 4096->128256) with M in {1, 2, 4, 8} bf16 activation rows.
+One step = one pass over all 16 (shape, M) launches; a "token" is one activation row carried through
+the four linears, so a step processes 15 tokens.  Weights are synthetic N(0, 0.02^2) quantized to Q8_0,
+activations N(0, 1) in bf16.  Every launch reads a weight copy that was last touched at least one
+full step (> 700 MB) earlier, so nothing is served from L2.
+
+One JSON line is printed by rank 0.  `value` is timed with inputs resident in HBM (CUDA-graph replay
+of the step, CUDA events); `e2e` times the same step through the public API with pinned host buffers
+(host->device copy of every activation, device->host copy of every result inside the timed region);
+`roofline` gives the mat-vec kernel's algorithmic bytes over its event-timed duration against the
+measured HBM copy peak; `cpu_baseline` is the C oracle on the host cores.
+`--impl reference` times the CPU restatement of the reference path alone (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096), (4096, 128256)]   # (K, N)
+MS = [1, 2, 4, 8]
+METRIC = "quant_linear_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def algorithmic_bytes(k, n, m, x_size=2, y_size=4):
+    return n * (k // 32) * 34 + m * k * x_size + m * n * y_size
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only query)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])), mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_q8_0_on_device(torch, n, k, gen, device):
+    """N(0, 0.02^2) weights quantized to GGUF Q8_0 blocks on the device (benchmark data only; the byte format
+    is the one tests/ checks against the oracle): d = absmax/127 (fp16), q = round(x/d)."""
+    out = torch.empty((n, k // 32, 34), dtype=torch.uint8, device=device)
+    rows_per = max(1, (1 << 26) // k)
+    for r0 in range(0, n, rows_per):
+        r1 = min(n, r0 + rows_per)
+        w = torch.randn((r1 - r0, k // 32, 32), generator=gen, device=device, dtype=torch.float32) * 0.02
+        d = w.abs().amax(dim=2, keepdim=True) / 127.0
+        q = torch.round(w / torch.where(d > 0, d, torch.ones_like(d))).clamp(-127, 127).to(torch.int8)
+        out[r0:r1, :, 0:2] = d.to(torch.float16).view(torch.uint8).reshape(r1 - r0, k // 32, 2)
+        out[r0:r1, :, 2:] = q.view(torch.uint8)
+    return out.reshape(n, -1)
+
+
+def cpu_reference_step(threads, sample_shapes, weights_host, xs_host):
+    """One pass of the sampled (shape, M) list through the C oracle; returns seconds."""
+    from oracle import cbuild
+    t0 = time.perf_counter()
+    for (k, n) in sample_shapes:
+        for m in MS:
+            cbuild.linear("Q8_0", weights_host[(k, n)], None, None, xs_host[(k, m)], threads)
+    return time.perf_counter() - t0
+
+
+def host_weights_for_cpu(shapes):
+    import numpy as np
+    from oracle import formats as F
+    rng = np.random.Generator(np.random.PCG64(2002))
+    ws, xs = {}, {}
+    for (k, n) in shapes:
+        # block bytes for the CPU leg: random valid Q8_0 blocks (d = small positive fp16, random int8 codes)
+        raw = rng.integers(0, 256, (n, k // 32, 34), dtype=np.uint8)
+        raw[:, :, 0:2] = np.frombuffer(np.float16(0.0005).tobytes(), np.uint8)
+        ws[(k, n)] = raw.reshape(n, -1)
+        for m in MS:
+            xs[(k, m)] = rng.standard_normal((m, k)).astype(np.float32)
+    return ws, xs
+
+
+def run_reference(args):
+    """CPU restatement of the reference path (the reference itself is Rust and cannot be built without a Rust
+    toolchain), all host threads, on the same workload: every step is the full 16-launch sweep."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cbuild
+    cbuild.build()
+    threads = os.cpu_count() or 1
+    ws, xs = host_weights_for_cpu(SHAPES)
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_reference_step(threads, SHAPES, ws, xs)
+    times = [cpu_reference_step(threads, SHAPES, ws, xs) for _ in range(args.steps)]
+    total = sum(times)
+    tokens = sum(MS) * args.steps
+    value = tokens / total
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg2_q8_0_decode_gemv_sweep", "shapes_k_to_n": SHAPES, "m": MS,
+                   "note": "CPU port of the reference's dequantize-then-dot path; reference Rust not buildable here"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": "full 16-launch sweep per step"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_gemv(args):
+    import torch
+    import engine_b200 as hq
+    from engine_b200 import _lib as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2000 + rank)
+    n_variants = 16                       # step variants, each reading a different weight copy
+    layers = {}
+    for (k, n) in SHAPES:
+        nbytes = n * (k // 32) * 34
+        copies = n_variants if nbytes < 128 * 2**20 else 2
+        base = make_q8_0_on_device(torch, n, k, gen, dev)
+        layers[(k, n)] = [hq.GgufMatMul(base if c == 0 else base.clone(), "Q8_0", k) for c in range(copies)]
+    xs = {(k, m): torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+          for (k, _) in SHAPES for m in MS}
+    ys = {(n, m): torch.empty((m, n), dtype=torch.float32, device=dev) for (_, n) in SHAPES for m in MS}
+    launches_per_step = len(SHAPES) * len(MS)
+
+    def step(variant: int):
+        for (k, n) in SHAPES:
+            ls = layers[(k, n)]
+            layer = ls[variant % len(ls)]
+            for m in MS:
+                w = layer._weight_struct()
+                rc = L.lib().hq_linear_forward(w, xs[(k, m)].data_ptr(), L.DT_BF16, k, ys[(n, m)].data_ptr(), L.DT_F32,
+                                               n, m, layer._status_buf(dev).data_ptr(),
+                                               torch.cuda.current_stream().cuda_stream)
+                L.check(rc, "hq_linear_forward")
+
+    # ---- warm-up (eager; also sets kernel attributes before any capture) ------------------------------
+    for w in range(max(args.warmup, 3)):
+        step(w)
+    torch.cuda.synchronize()
+
+    # ---- parity spot check of what is being timed (one launch against torch's f32 matmul of the dequantized
+    # weights: d * q) -------------------------------------------------------------------------------------
+    k0, n0 = SHAPES[0]
+    lay = layers[(k0, n0)][0]
+    blk = lay.data.reshape(n0, k0 // 32, 34)
+    deq = (blk[:, :, 0:2].contiguous().view(torch.float16).to(torch.float32) *
+           blk[:, :, 2:].contiguous().view(torch.int8).to(torch.float32)).reshape(n0, k0)
+    want = xs[(k0, 8)].to(torch.float32) @ deq.t()
+    got = lay.forward_raw(xs[(k0, 8)], torch.float32)
+    rel = float(torch.linalg.norm(got - want) / torch.linalg.norm(want))
+    assert rel < 1e-3, f"bench self-check failed: rel-L2 {rel}"
+    assert lay.device_status()[0] == 0
+    del deq, want, got
+
+    # ---- capture one CUDA graph per step variant ------------------------------------------------------------
+    graphs = []
+    side = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(side):
+        for v in range(n_variants):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                step(v)
+            graphs.append(g)
+    torch.cuda.synchronize()
+    for v in range(3):
+        graphs[v].replay()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- timed region: exactly K steps, device-resident inputs ----------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(args.steps):
+        graphs[s % n_variants].replay()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+
+    # ---- per-launch kernel durations (eager, one event pair per launch, rotating copies) ---------------------
+    reps = max(5, min(args.steps, 20))
+    per = {}
+    for (k, n) in SHAPES:
+        ls = layers[(k, n)]
+        for m in MS:
+            evs = []
+            for r in range(reps):
+                layer = ls[r % len(ls)]
+                w = layer._weight_struct()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                L.lib().hq_linear_forward(w, xs[(k, m)].data_ptr(), L.DT_BF16, k, ys[(n, m)].data_ptr(), L.DT_F32, n, m,
+                                          layer._status_buf(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                b.record()
+                evs.append((a, b))
+            torch.cuda.synchronize()
+            per[(k, n, m)] = statistics.median(a.elapsed_time(b) for a, b in evs)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the public API with pinned host buffers -------------------------------------------
+    hx = {key: t.cpu().pin_memory() for key, t in xs.items()}
+    hy = {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in ys.items()}
+    h2d = sum(t.numel() * t.element_size() for t in hx.values())
+    d2h = sum(t.numel() * t.element_size() for t in hy.values())
+
+    def e2e_step(variant: int):
+        for (k, n) in SHAPES:
+            ls = layers[(k, n)]
+            layer = ls[variant % len(ls)]
+            for m in MS:
+                xd = hx[(k, m)].to(dev, non_blocking=True)
+                y = layer.forward_raw(xd, torch.float32)
+                hy[(n, m)].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for v in range(3):
+        e2e_step(v)
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        e2e_step(s)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    # ---- reduce over ranks -------------------------------------------------------------------------------------
+    if dist is not None:
+        tt = torch.tensor([ms_total, e2e_s * 1e3], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms = float(tt[0]), float(tt[1])
+    else:
+        e2e_ms = e2e_s * 1e3
+    tokens_per_step = sum(MS)
+    value = world * tokens_per_step * args.steps / (ms_total / 1e3)
+    e2e_value = world * tokens_per_step * args.steps / (e2e_ms / 1e3)
+
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        step_bytes = sum(algorithmic_bytes(k, n, m) for (k, n) in SHAPES for m in MS)
+        kern_ms = sum(per.values())
+        achieved = step_bytes / (kern_ms / 1e3) / 1e9
+        by_shape = {}
+        for (k, n) in SHAPES:
+            for m in MS:
+                by_shape[f"{k}x{n}_m{m}"] = round(algorithmic_bytes(k, n, m) / (per[(k, n, m)] / 1e3) / 1e9, 1)
+        # CPU baseline: the C oracle on the three Llama layer shapes without the vocabulary projection
+        cpu = None
+        try:
+            from oracle import cbuild
+            cbuild.build()
+            sample = SHAPES[:3] if len(SHAPES) > 1 else SHAPES
+            ws, hxs = host_weights_for_cpu(sample)
+            threads = os.cpu_count() or 1
+            cpu_reference_step(threads, sample, ws, hxs)
+            dt = min(cpu_reference_step(threads, sample, ws, hxs) for _ in range(3))
+            sample_bytes = sum(algorithmic_bytes(k, n, m) for (k, n) in sample for m in MS)
+            # scaled to the full step by algorithmic bytes (the CPU path is bandwidth/dequant bound per weight)
+            cpu = {"value": tokens_per_step / (dt * step_bytes / sample_bytes), "unit": UNIT, "cores": threads,
+                   "kind": "port", "sample": "4096->4096, 4096->14336, 14336->4096 at M in {1,2,4,8}, scaled to the "
+                                            "full sweep by algorithmic bytes"}
+        except Exception as exc:  # the checker failing to build must not hide the GPU numbers
+            cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {exc}"}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "cfg2_q8_0_decode_gemv_sweep" if len(SHAPES) == 4 else "single_shape_profile_case",
+                       "shapes_k_to_n": SHAPES, "m": MS, "x_dtype": "bf16", "y_dtype": "f32", "multi_gpu": "replicas only (dense GEMV is not sharded)",
+                       "l2": "every launch reads a weight copy last touched >= 700 MB of traffic earlier",
+                       "timing": "CUDA-graph replay per step, CUDA events"},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "hq::gemv_kernel<Q8_0>", "launch_ms_sum": round(kern_ms, 4),
+                         "bytes_per_step": step_bytes, "by_launch_gbs": by_shape,
+                         "graph_step_gbs": round(step_bytes / (ms_total / args.steps / 1e3) / 1e9, 1)},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="gemv", choices=["gemv"])
+    ap.add_argument("--only", default=None, help="restrict the sweep to one KxN shape, e.g. 4096x128256 "
+                    "(profiling aid; the reported line is then not the headline workload)")
+    args = ap.parse_args()
+    if args.only:
+        k, n = (int(v) for v in args.only.lower().split("x"))
+        global SHAPES
+        SHAPES = [(k, n)]
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    run_gemv(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,175 @@
+/*
+ * CPU oracle in C: TEST INFRASTRUCTURE ONLY.  A plain restatement of the
+ * reference's CPU arithmetic for the quantized-linear / MoE path (per-block
+ * dequantize to f32, f32 dot products), used as the checker at sizes numpy is
+ * too slow for and as the timed CPU baseline ("port") of the benchmark.  The
+ * library never links or loads this file.
+ *
+ * Follows: Q8_0 / Q4_K block structs and value formulas
+ * (hanzo-quant/kernels/mmvq_gguf/mmvq_gguf.cu:134-137, :166-170, :385-404,
+ * :595-606); block-FP8 dequant (hanzo-quant/src/blockwise_fp8/ops.rs:11-59);
+ * MXFP4 LUT dequant and the blocked dot of forward_dequantize /
+ * gather_forward_dequantize (hanzo-quant/src/mxfp4/mod.rs:473-489, :550-726);
+ * per-expert grouping of the slow experts backend
+ * (hanzo-engine/src/moe/experts/backends.rs:900-959).
+ * Parity of this file is pinned by tests/test_oracle_c.py against the numpy
+ * oracle (itself pinned against gguf-py and the reference's golden vectors).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+enum { FMT_Q8_0 = 0, FMT_Q4_K = 1, FMT_FP8 = 2, FMT_MXFP4 = 3 };
+
+static float half_to_float(uint16_t h) {
+  uint32_t s = (uint32_t)(h >> 15) << 31, e = (h >> 10) & 31, m = h & 1023, b;
+  if (e == 0) {
+    if (m == 0) { b = s; }
+    else { int sh = 0; while (!(m & 1024)) { m <<= 1; ++sh; } b = s | ((uint32_t)(113 - sh) << 23) | ((m & 1023) << 13); }
+  } else if (e == 31) b = s | 0x7F800000u | (m << 13);
+  else b = s | ((e + 112) << 23) | (m << 13);
+  float f; memcpy(&f, &b, 4); return f;
+}
+
+static float e4m3_to_float(uint8_t c) {
+  int e = (c >> 3) & 15, m = c & 7;
+  float v;
+  if (e == 15 && m == 7) v = NAN;
+  else if (e == 0) v = ldexpf((float)m / 8.0f, -6);
+  else v = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+  return (c & 0x80) ? -v : v;
+}
+
+static const float FP4[16] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
+                              -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
+
+int64_t oracle_row_bytes(int fmt, int64_t k) {
+  switch (fmt) {
+    case FMT_Q8_0: return k / 32 * 34;
+    case FMT_Q4_K: return k / 256 * 144;
+    case FMT_FP8: return k;
+    default: return k / 2;
+  }
+}
+
+/* Dequantize one weight row to f32.  scales: FP8 -> f32 row of the scale grid for this row's 128-block,
+ * MXFP4 -> the row's e8m0 bytes. */
+static void dequant_row(int fmt, const uint8_t* row, const void* scales, int64_t k, float* out) {
+  if (fmt == FMT_Q8_0) {
+    for (int64_t b = 0; b < k / 32; ++b) {
+      const uint8_t* p = row + 34 * b;
+      uint16_t dh; memcpy(&dh, p, 2);
+      const float d = half_to_float(dh);
+      const int8_t* q = (const int8_t*)(p + 2);
+      for (int i = 0; i < 32; ++i) out[32 * b + i] = d * (float)q[i];
+    }
+  } else if (fmt == FMT_Q4_K) {
+    for (int64_t sb = 0; sb < k / 256; ++sb) {
+      const uint8_t* p = row + 144 * sb;
+      uint16_t dh, mh; memcpy(&dh, p, 2); memcpy(&mh, p + 2, 2);
+      const float d = half_to_float(dh), dmin = half_to_float(mh);
+      const uint8_t* sc = p + 4;
+      const uint8_t* qs = p + 16;
+      for (int j = 0; j < 8; ++j) {
+        int s, m;
+        if (j < 4) { s = sc[j] & 63; m = sc[j + 4] & 63; }
+        else { s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4); m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+        const float d1 = d * (float)s, m1 = dmin * (float)m;
+        const uint8_t* q = qs + 32 * (j / 2);
+        float* o = out + 256 * sb + 32 * j;
+        if (j & 1) for (int i = 0; i < 32; ++i) o[i] = d1 * (float)(q[i] >> 4) - m1;
+        else for (int i = 0; i < 32; ++i) o[i] = d1 * (float)(q[i] & 0xF) - m1;
+      }
+    }
+  } else if (fmt == FMT_FP8) {
+    const float* s = (const float*)scales;
+    for (int64_t i = 0; i < k; ++i) out[i] = e4m3_to_float(row[i]) * s[i / 128];
+  } else {
+    const uint8_t* s = (const uint8_t*)scales;
+    for (int64_t b = 0; b < k / 32; ++b) {
+      uint32_t bits = (uint32_t)s[b] << 23;
+      float sf; memcpy(&sf, &bits, 4);
+      for (int i = 0; i < 16; ++i) {
+        const uint8_t byte = row[16 * b + i];
+        out[32 * b + 2 * i] = FP4[byte & 0xF] * sf;
+        out[32 * b + 2 * i + 1] = FP4[byte >> 4] * sf;
+      }
+    }
+  }
+}
+
+static const void* row_scales(int fmt, const void* scales, int64_t n_row, int64_t k) {
+  if (fmt == FMT_FP8) return (const float*)scales + (n_row / 128) * ((k + 127) / 128);
+  if (fmt == FMT_MXFP4) return (const uint8_t*)scales + n_row * (k / 32);
+  return NULL;
+}
+
+/* y[m, n] = sum_k x[m, k] * dequant(W)[n, k] (+ bias[n]); f32 accumulation per row. */
+void oracle_linear(int fmt, const uint8_t* w, const void* scales, const float* bias, const float* x, float* y,
+                   int64_t n, int64_t k, int64_t m, int threads) {
+  const int64_t rb = oracle_row_bytes(fmt, k);
+#ifdef _OPENMP
+  if (threads > 0) omp_set_num_threads(threads);
+#endif
+#pragma omp parallel
+  {
+    float* wrow = (float*)malloc(sizeof(float) * (size_t)k);
+#pragma omp for schedule(static)
+    for (int64_t r = 0; r < n; ++r) {
+      dequant_row(fmt, w + r * rb, row_scales(fmt, scales, r, k), k, wrow);
+      for (int64_t j = 0; j < m; ++j) {
+        const float* xr = x + j * k;
+        float acc = 0.f;
+        for (int64_t i = 0; i < k; ++i) acc += xr[i] * wrow[i];
+        y[j * n + r] = acc + (bias ? bias[r] : 0.f);
+      }
+    }
+    free(wrow);
+  }
+}
+
+/* Per-assignment projection out of an expert bank, grouped by expert in stable (token, slot) order:
+ * out[rows[i], :] for every sorted position i of expert e uses x[xrows[i], :]. */
+void oracle_gather(int fmt, const uint8_t* w, const void* scales, const float* bias, const float* x, float* out,
+                   int64_t n, int64_t k, int n_experts, const int32_t* bounds, const int32_t* xrows,
+                   const int32_t* orows, int threads) {
+  const int64_t rb = oracle_row_bytes(fmt, k);
+#ifdef _OPENMP
+  if (threads > 0) omp_set_num_threads(threads);
+#endif
+#pragma omp parallel
+  {
+    float* wrow = (float*)malloc(sizeof(float) * (size_t)k);
+#pragma omp for schedule(dynamic, 16) collapse(2)
+    for (int e = 0; e < n_experts; ++e) {
+      for (int64_t r = 0; r < n; ++r) {
+        const int lo = bounds[e], hi = bounds[e + 1];
+        if (lo == hi) continue;
+        const int64_t gr = (int64_t)e * n + r;
+        const void* sc = NULL;
+        if (fmt == FMT_FP8) sc = (const float*)scales + ((int64_t)e * ((n + 127) / 128) + r / 128) * ((k + 127) / 128);
+        else if (fmt == FMT_MXFP4) sc = (const uint8_t*)scales + gr * (k / 32);
+        dequant_row(fmt, w + gr * rb, sc, k, wrow);
+        for (int i = lo; i < hi; ++i) {
+          const float* xr = x + (int64_t)xrows[i] * k;
+          float acc = 0.f;
+          for (int64_t c = 0; c < k; ++c) acc += xr[c] * wrow[c];
+          out[(int64_t)orows[i] * n + r] = acc + (bias ? bias[gr] : 0.f);
+        }
+      }
+    }
+    free(wrow);
+  }
+}
+
+int oracle_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
