@@ -16,12 +16,14 @@ SCORE_RAW, SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1, 2
 WEIGHT_SCORE, WEIGHT_SOFTMAX, WEIGHT_SIGMOID = 0, 1, 2
 ACT_NONE, ACT_SWIGLU, ACT_GPTOSS = 0, 1, 2
 ROWS_PER_TOKEN, ROWS_PER_SLOT, ROWS_SORTED = 0, 1, 2
+CFG_MOE_TENSOR_MIN_ROWS, CFG_DENSE_TENSOR_MIN_ROWS = 0, 1
 
 
 class HqWeight(C.Structure):
     _fields_ = [("format", C.c_int32), ("n_experts", C.c_int32), ("n", C.c_int64), ("k", C.c_int64),
                 ("data", C.c_void_p), ("scales", C.c_void_p), ("bias", C.c_void_p),
-                ("bias_dtype", C.c_int32), ("reserved", C.c_int32)]
+                ("bias_dtype", C.c_int32), ("reserved", C.c_int32),
+                ("fp8_tile_scale", C.c_void_p), ("fp8_rel_scale", C.c_void_p)]
 
 
 class HqRouterArgs(C.Structure):
@@ -53,6 +55,9 @@ SIGNATURES = {
     "hq_fp8_vector_dequant": (_I32, [_P, _P, _I64, _P, _I32, _P]),
     "hq_fp8_block_quant": (_I32, [_P, _I32, _I64, _I64, _I32, _I32, _P, _P, _P]),
     "hq_fp8_block_dequant": (_I32, [_P, _P, _I64, _I64, _I32, _I32, _P, _I32, _P]),
+    "hq_fp8_scale_prepare": (_I32, [_P, _I32, _I64, _I64, _P, _P, _P]),
+    "hq_config_set": (_I32, [_I32, _I64]),
+    "hq_config_get": (_I64, [_I32]),
     "hq_gated_act": (_I32, [_P, _P, _I32, _I64, _I32, C.POINTER(HqActArgs), _P, _P]),
 }
 

@@ -30,7 +30,7 @@ int32_t check_weight(const hq_weight* w) {
       if (w->k % 256 != 0) return HQ_ERR_SHAPE;
       break;
     case HQ_FMT_FP8_BLOCK:
-      if (w->k % 128 != 0 || w->k > 256 * 128) return HQ_ERR_SHAPE;
+      if (w->k % 128 != 0) return HQ_ERR_SHAPE;
       if (w->scales == nullptr) return HQ_ERR_NULL;
       break;
     case HQ_FMT_MXFP4:
@@ -44,6 +44,37 @@ int32_t check_weight(const hq_weight* w) {
   if (weight_row_bytes(w->format, w->k) % 16 != 0) return HQ_ERR_ALIGN;
   if (w->bias != nullptr && !valid_dtype(w->bias_dtype)) return HQ_ERR_FORMAT;
   return HQ_OK;
+}
+
+int64_t g_cfg[2] = {8, 9};
+
+void fill_grouped(GroupedParams& g, const hq_weight* w, const hq_weight* w_up) {
+  g.format = w->format;
+  g.n = (int)w->n;
+  g.k = (int)w->k;
+  g.w = w->data;
+  g.scales = w->scales;
+  g.bias = w->bias;
+  g.bias_dtype = w->bias_dtype;
+  g.w_up = w_up ? w_up->data : nullptr;
+  g.scales_up = w_up ? w_up->scales : nullptr;
+  g.bias_up = w_up ? w_up->bias : nullptr;
+  g.w_row_bytes = weight_row_bytes(w->format, w->k);
+  g.fp8_tile_scale = (const float*)w->fp8_tile_scale;
+  g.fp8_rel_scale = (const float*)w->fp8_rel_scale;
+  g.fp8_tile_scale_up = w_up ? (const float*)w_up->fp8_tile_scale : nullptr;
+  g.fp8_rel_scale_up = w_up ? (const float*)w_up->fp8_rel_scale : nullptr;
+  g.fp8_nb = (int)((w->n + 127) / 128);
+  g.fp8_kb = (int)((w->k + 127) / 128);
+}
+
+bool tensor_path_ok(const hq_weight* w, const hq_weight* w_up) {
+  if (!grouped_gemm_supported(w->format, w->n, w->k)) return false;
+  if (w->format == HQ_FMT_FP8_BLOCK) {
+    if (w->fp8_tile_scale == nullptr || w->fp8_rel_scale == nullptr) return false;
+    if (w_up != nullptr && (w_up->fp8_tile_scale == nullptr || w_up->fp8_rel_scale == nullptr)) return false;
+  }
+  return true;
 }
 
 void fill_weight(GemvParams& p, const hq_weight* w, const hq_weight* w_up) {
@@ -84,6 +115,14 @@ const char* hq_error_string(int32_t code) {
   }
 }
 
+int32_t hq_config_set(int32_t key, int64_t value) {
+  if (key < 0 || key > 1 || value < 0) return HQ_ERR_FORMAT;
+  g_cfg[key] = value;
+  return HQ_OK;
+}
+
+int64_t hq_config_get(int32_t key) { return (key < 0 || key > 1) ? -1 : g_cfg[key]; }
+
 int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* stream) {
   if (status_dev == nullptr || out_host == nullptr) return HQ_ERR_NULL;
   cudaStream_t s = (cudaStream_t)stream;
@@ -103,6 +142,16 @@ int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, in
   if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return HQ_ERR_FORMAT;
   if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
   if (x_stride < w->k || y_stride < w->n) return HQ_ERR_SHAPE;
+  if (m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS] && w->n_experts == 1 && tensor_path_ok(w, nullptr)) {
+    GroupedParams g{};
+    fill_grouped(g, w, nullptr);
+    g.m = (int)m;
+    g.x = x; g.x_dtype = x_dtype; g.x_stride = x_stride;
+    g.y = y; g.y_dtype = y_dtype; g.y_stride = y_stride;
+    g.act.act = HQ_ACT_NONE;
+    g.status = status_dev;
+    return launch_grouped_gemm(g, (int)((m + 127) / 128), (cudaStream_t)stream);
+  }
   GemvParams p{};
   fill_weight(p, w, nullptr);
   p.m = (int)m;
@@ -172,6 +221,24 @@ int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const h
   if (has_act && w_up == nullptr && (w->n % 2) != 0) return HQ_ERR_SHAPE;
   const DispatchLayout l = dispatch_layout(n_tokens, top_k, w->n_experts);
   const int32_t* ws = (const int32_t*)workspace;
+  const int32_t* x_rows =
+      x_layout == HQ_ROWS_PER_TOKEN ? sorted_token : (x_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr);
+  const int32_t* y_rows = out_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr;
+  if (n_tokens * top_k >= g_cfg[HQ_CFG_MOE_TENSOR_MIN_ROWS] * (int64_t)w->n_experts && tensor_path_ok(w, w_up)) {
+    GroupedParams g{};
+    fill_grouped(g, w, w_up);
+    g.x = x; g.x_dtype = x_dtype; g.x_stride = w->k;
+    g.y = out; g.y_dtype = out_dtype;
+    g.y_stride = (has_act && w_up == nullptr) ? w->n / 2 : w->n;
+    g.tiles = ws + l.off_tiles128;
+    g.tile_count = ws;
+    g.expert_bounds = expert_bounds;
+    g.x_rows = x_rows;
+    g.y_rows = y_rows;
+    if (has_act) g.act = *act; else g.act.act = HQ_ACT_NONE;
+    g.status = status_dev;
+    return launch_grouped_gemm(g, (int)l.max_tiles128, (cudaStream_t)stream);
+  }
   GemvParams p{};
   fill_weight(p, w, w_up);
   p.m = 0;
@@ -181,11 +248,10 @@ int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const h
   p.tiles = ws + l.off_tiles8;
   p.tile_count = ws;
   p.expert_bounds = expert_bounds;
-  p.x_rows = x_layout == HQ_ROWS_PER_TOKEN ? sorted_token : (x_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr);
-  p.y_rows = out_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr;
+  p.x_rows = x_rows;
+  p.y_rows = y_rows;
   if (has_act) p.act = *act; else p.act.act = HQ_ACT_NONE;
   p.status = status_dev;
-  if (l.max_tiles8 > 65535) return HQ_ERR_TOO_LARGE;
   return launch_gemv(p, (int)l.max_tiles8, (cudaStream_t)stream);
 }
 
@@ -237,6 +303,15 @@ int32_t hq_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t 
   if (codes == nullptr || scales == nullptr || out == nullptr) return HQ_ERR_NULL;
   if (!valid_dtype(out_dtype)) return HQ_ERR_FORMAT;
   return launch_fp8_block_dequant(codes, scales, rows, cols, by, bx, out, out_dtype, (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_scale_prepare(const float* scales, int32_t n_experts, int64_t n, int64_t k, float* tile_scale_out,
+                             float* rel_scale_out, void* stream) {
+  if (n_experts < 1 || n < 1 || k < 1) return HQ_ERR_SHAPE;
+  if (scales == nullptr || tile_scale_out == nullptr || rel_scale_out == nullptr) return HQ_ERR_NULL;
+  const int64_t groups = (int64_t)n_experts * ((n + 127) / 128);
+  return launch_fp8_scale_prepare(scales, groups, (int)((k + 127) / 128), tile_scale_out, rel_scale_out,
+                                  (cudaStream_t)stream);
 }
 
 int32_t hq_gated_act(const void* gate, const void* up, int32_t dtype, int64_t n_elems, int32_t interleaved,

@@ -1,0 +1,561 @@
+// Grouped expert GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), for
+// prefill-sized token counts: out[rows of expert e] = act( x_rows . dequant(W[e])^T ).
+//
+// One persistent CTA per SM walks (token tile, feature tile) work items of the
+// expert-sorted assignment list.  UMMA roles are swapped so the 128 TMEM lanes hold
+// output FEATURES and the columns hold TOKENS: D[feature, token] = W_tile[128, K] .
+// X_tile[128 tokens, K]^T.  Warp roles:
+//   warp 0        MMA issuer (one elected lane): tcgen05.mma kind::f16, 128x128x16 per
+//                 instruction, operands through shared-memory descriptors (K-major,
+//                 128-byte swizzle), f32 accumulators in tensor memory, double buffered
+//   warps 1-4     epilogue: tcgen05.ld the accumulators, bias, gated activation
+//                 (gate/up from two banks, or interleaved rows), store
+//   warps 5-12    producers: read the quantized weight tile straight from the
+//                 reference's byte layout, expand it to f16 in registers and write the
+//                 swizzled operand tile; gather the activation rows of the tile
+//                 (token order -> expert order), convert to f16, write them likewise
+// Stage hand-off is by mbarrier: producers arrive on full[s] after a proxy fence, the
+// MMA warp releases a stage with tcgen05.commit, accumulator buffers alternate
+// between MMA and epilogue through acc_full / acc_empty.  Every wait is bounded.
+//
+// Tensor-core bound for large token counts; algorithmic flops per launch =
+// 2 * rows * N * K (* 2 with a gate and an up bank).
+#include "hq_common.cuh"
+#include "hq_kernels.h"
+
+namespace hq {
+
+constexpr int kGgThreads = 13 * 32;
+constexpr int kGgProducerWarps = 8;
+constexpr int kGgProducerThreads = kGgProducerWarps * 32;
+constexpr int kTileM = 128;   // features per tile (TMEM lanes)
+constexpr int kTileN = 128;   // tokens per tile (TMEM columns)
+constexpr int kTileK = 64;    // k per stage: 64 f16 = one 128-byte swizzle row
+constexpr int kOperandBytes = 128 * kTileK * 2;  // 16 KiB per operand tile
+constexpr uint32_t kGgSpin = 1u << 22;
+
+// ---- tcgen05 wrappers -----------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle,
+// 8-row groups 1024 bytes apart, descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);         // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                              // descriptor version
+  d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+  return d;
+}
+// kind::f16 instruction descriptor: f32 accumulate, f16 x f16, both K-major, M = 128, N = 128
+__device__ __forceinline__ uint32_t make_idesc_f16() {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+}
+
+// byte offset of 16-byte chunk `c` (0..7) of row `r` inside a swizzled 128 x 64 f16 operand tile
+__device__ __forceinline__ uint32_t swz(int r, int c) {
+  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
+
+template <int NB>
+struct GgSmem {
+  static constexpr int NSTAGE = NB == 2 ? 4 : 6;
+  static constexpr int STAGE_BYTES = (NB + 1) * kOperandBytes;   // A bank(s) then B
+  static constexpr int OFF_BAR = NSTAGE * STAGE_BYTES;
+  static constexpr int TOTAL = OFF_BAR + (2 * NSTAGE + 4) * 8 + 16 + 1024;  // + alignment slack
+};
+
+// ---- weight tile expansion: 32 consecutive k of one row -> 32 f16 (4 chunks of 16 bytes) ----
+// Natural k order.  `out` receives 16 packed f16x2 words.
+__device__ __forceinline__ void expand_q4_k(const uint8_t* row_base, int k0, int half, uint32_t (&out)[16]) {
+  // super-block header {d, dmin, 12 scale bytes} and the 32 nibble bytes shared by sub-blocks 2c, 2c+1
+  const int sb = k0 >> 8, c = (k0 & 255) >> 6;
+  const uint8_t* blk = row_base + 144 * sb;
+  const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+  const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * c));
+  const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * c));
+  const int j = 2 * c + half;
+  uint32_t s, m;
+  if (j < 4) {
+    s = (hdr.y >> (8 * j)) & 63u;
+    m = (hdr.z >> (8 * j)) & 63u;
+  } else {
+    const int jj = j - 4;
+    s = ((hdr.w >> (8 * jj)) & 0xFu) | (((hdr.y >> (8 * jj + 6)) & 3u) << 4);
+    m = ((hdr.w >> (8 * jj + 4)) & 0xFu) | (((hdr.z >> (8 * jj + 6)) & 3u) << 4);
+  }
+  const float d1 = half_bits_to_float(hdr.x) * (float)s;
+  const float m1 = half_bits_to_float(hdr.x >> 16) * (float)m;
+  const __half2 d2 = __float2half2_rn(d1);
+  const __half2 m2 = __float2half2_rn(-m1);
+  const __half2 k1024 = __float2half2_rn(1024.f);
+  const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t v = half ? (qw[i] >> 4) : qw[i];
+    uint32_t p02 = (v & 0x000F000Fu) | 0x64006400u;          // 1024 + code of bytes 0 and 2
+    uint32_t p13 = ((v >> 8) & 0x000F000Fu) | 0x64006400u;   // bytes 1 and 3
+    __half2 h02 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&p02), k1024), d2, m2);
+    __half2 h13 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&p13), k1024), d2, m2);
+    const uint32_t a = *reinterpret_cast<uint32_t*>(&h02), b = *reinterpret_cast<uint32_t*>(&h13);
+    out[2 * i] = __byte_perm(a, b, 0x5410);       // elements 0, 1
+    out[2 * i + 1] = __byte_perm(a, b, 0x7632);   // elements 2, 3
+  }
+}
+
+// e4m3 -> f16 is exact; the block's scale relative to the largest scale of its 128-row block (<= 1) is folded
+// in here, the largest scale itself multiplies the accumulator in the epilogue.
+__device__ __forceinline__ void expand_fp8(const uint8_t* row_base, int k0, int half, float rel, uint32_t (&out)[16]) {
+  const uint4* src = reinterpret_cast<const uint4*>(row_base + k0 + 32 * half);
+  const uint4 a = __ldg(src), b = __ldg(src + 1);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  const __half2 r2 = __float2half2_rn(rel);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t lo, hi;
+    asm("{\n"
+        ".reg .b16 l, h;\n"
+        "mov.b32 {l, h}, %2;\n"
+        "cvt.rn.f16x2.e4m3x2 %0, l;\n"
+        "cvt.rn.f16x2.e4m3x2 %1, h;\n"
+        "}\n"
+        : "=r"(lo), "=r"(hi)
+        : "r"(w[i]));
+    __half2 l2 = __hmul2(*reinterpret_cast<__half2*>(&lo), r2);
+    __half2 h2 = __hmul2(*reinterpret_cast<__half2*>(&hi), r2);
+    out[2 * i] = *reinterpret_cast<uint32_t*>(&l2);
+    out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&h2);
+  }
+}
+
+// MXFP4 block of 32: e2m1 pairs -> f16x2 (hardware conversion, low nibble = even element = low half), times
+// 2^(e-127) as an exact f16 power of two.  e = 0 decodes to a zero scale (the reference's table builds the
+// scale from the bits e << 23); scales outside the f16 exponent range are reported by the caller.
+__device__ __forceinline__ bool expand_mxfp4(const uint8_t* row_base, const uint8_t* scale_row, int k0, int half,
+                                             uint32_t (&out)[16]) {
+  const int blk = (k0 >> 5) + half;
+  const uint4 q = __ldg(reinterpret_cast<const uint4*>(row_base + 16 * blk));
+  const uint32_t e = __ldg(scale_row + blk);
+  const bool in_range = (e == 0) || (e >= 113 && e <= 140);   // 2^-14 .. 2^13: products stay finite in f16
+  const uint32_t ef = (e >= 113 && e <= 140) ? (e - 112) : 0u;  // f16 exponent field of 2^(e-127)
+  const uint32_t sc16 = ef << 10;
+  const uint32_t sc2 = sc16 | (sc16 << 16);
+  const __half2 s2 = *reinterpret_cast<const __half2*>(&sc2);
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t h[4];
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}\n"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(w[i]));
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      __half2 v = __hmul2(*reinterpret_cast<__half2*>(&h[b]), s2);
+      out[4 * i + b] = *reinterpret_cast<uint32_t*>(&v);
+    }
+  }
+  return in_range;
+}
+
+// 32 activation values of one row -> f16 (natural order), optionally scaled
+__device__ __forceinline__ void load_x32(const void* x, int dtype, int64_t elem_off, float scale, uint32_t (&out)[16]) {
+  if (dtype == HQ_DT_F32) {
+    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + elem_off);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 f = __ldg(src + i);
+      out[2 * i] = pack_half2(f.x * scale, f.y * scale);
+      out[2 * i + 1] = pack_half2(f.z * scale, f.w * scale);
+    }
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + elem_off);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 r = __ldg(src + i);
+      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (dtype == HQ_DT_BF16) {
+          out[4 * i + j] = pack_half2(__uint_as_float(w[j] << 16) * scale, __uint_as_float(w[j] & 0xFFFF0000u) * scale);
+        } else if (scale != 1.f) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+          out[4 * i + j] = pack_half2(f.x * scale, f.y * scale);
+        } else {
+          out[4 * i + j] = w[j];
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void store_chunks(uint8_t* tile, int r, int c0, const uint32_t (&v)[16]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<uint4*>(tile + swz(r, c0 + c)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+}
+
+__device__ __forceinline__ float gg_gated(float g, float u, const hq_act_args& a) {
+  if (a.act == HQ_ACT_GPTOSS) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return (u + 1.f) * (g / (1.f + expf(-a.alpha * g)));
+  }
+  if (a.has_limit) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+  }
+  return (g / (1.f + expf(-g))) * u;
+}
+
+struct GgTile {
+  int expert, row_start, count, n0;
+};
+
+__device__ __forceinline__ GgTile gg_tile(const GroupedParams& p, int w, int n_nt) {
+  GgTile t;
+  const int tt = w / n_nt;
+  t.n0 = (w - tt * n_nt) * kTileM;
+  if (p.tiles != nullptr) {
+    t.expert = p.tiles[2 * tt];
+    t.row_start = p.tiles[2 * tt + 1];
+    t.count = min(kTileN, p.expert_bounds[t.expert + 1] - t.row_start);
+  } else {
+    t.expert = 0;
+    t.row_start = kTileN * tt;
+    t.count = min(kTileN, p.m - t.row_start);
+  }
+  return t;
+}
+
+template <int FMT, int NB>
+__global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const GroupedParams p) {
+  using L = GgSmem<NB>;
+  constexpr int NSTAGE = L::NSTAGE;
+  extern __shared__ uint8_t smem_raw[];
+  // operand tiles need 1024-byte alignment for the 128-byte swizzle
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* empty = full + NSTAGE;
+  uint64_t* acc_full = empty + NSTAGE;     // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_nt = (p.n + kTileM - 1) / kTileM;
+  const int n_tt = p.tiles != nullptr ? p.tile_count[1] : (p.m + kTileN - 1) / kTileN;
+  const int total = n_tt * n_nt;
+  const int n_ks = p.k / kTileK;
+
+  if (tid == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&full[s], kGgProducerWarps);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== MMA issuer ======================================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16();
+      uint32_t spin = kGgSpin;
+      int it = 0, tcount = 0;
+      for (int w = blockIdx.x; w < total; w += gridDim.x, ++tcount) {
+        const int buf = tcount & 1;
+        if (tcount >= 2) {
+          if (!mbar_wait(&acc_empty[buf], ((tcount >> 1) - 1) & 1, spin)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 300 + buf);
+            spin = 1;
+          }
+        }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + (uint32_t)(buf * NB * kTileN);
+        for (int ks = 0; ks < n_ks; ++ks, ++it) {
+          const int s = it % NSTAGE;
+          if (!mbar_wait(&full[s], (it / NSTAGE) & 1, spin)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + s);
+            spin = 1;
+          }
+          tc_fence_after();
+          const uint32_t stage = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint64_t bdesc = make_smem_desc(stage + NB * kOperandBytes);
+#pragma unroll
+          for (int bank = 0; bank < NB; ++bank) {
+            const uint64_t adesc = make_smem_desc(stage + bank * kOperandBytes);
+#pragma unroll
+            for (int kk = 0; kk < kTileK / 16; ++kk) {
+              // 16 k per instruction = 32 bytes along the swizzled row: advance the start address by 2 units
+              tc_mma_f16(d0 + bank * kTileN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            }
+          }
+          tc_commit(&empty[s]);     // stage is free once these MMAs have read it
+        }
+        tc_commit(&acc_full[buf]);  // accumulators complete
+      }
+    }
+    __syncwarp();
+  } else if (warp <= 4) {
+    // =========================== epilogue ========================================
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    uint32_t spin = kGgSpin;
+    int tcount = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x, ++tcount) {
+      const GgTile t = gg_tile(p, w, n_nt);
+      const int buf = tcount & 1;
+      if (!mbar_wait(&acc_full[buf], (tcount >> 1) & 1, spin)) {
+        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 400 + buf);
+        spin = 1;
+      }
+      tc_fence_after();
+      const int n = t.n0 + 32 * q + lane;       // feature owned by this thread
+      const bool n_ok = n < p.n;
+      float bias0 = 0.f, bias1 = 0.f;
+      if (n_ok && p.bias != nullptr) bias0 = load_as_float(p.bias, p.bias_dtype, (int64_t)t.expert * p.n + n);
+      if (NB == 2 && n_ok && p.bias_up != nullptr)
+        bias1 = load_as_float(p.bias_up, p.bias_dtype, (int64_t)t.expert * p.n + n);
+      float sc0 = 1.f, sc1 = 1.f;
+      if (FMT == HQ_FMT_FP8_BLOCK) {
+        sc0 = __ldg(p.fp8_tile_scale + (int64_t)t.expert * p.fp8_nb + t.n0 / 128);
+        if (NB == 2) sc1 = __ldg(p.fp8_tile_scale_up + (int64_t)t.expert * p.fp8_nb + t.n0 / 128);
+      }
+      const bool interleaved = NB == 1 && p.act.act != HQ_ACT_NONE;
+      const int64_t out_n = interleaved ? (n >> 1) : n;
+      const bool writer = n_ok && (!interleaved || (n & 1) == 0);
+      const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * NB * kTileN);
+#pragma unroll 1
+      for (int cc = 0; cc < kTileN / 32; ++cc) {
+        if (32 * cc >= t.count) break;          // warp-uniform: no tokens in this column group
+        uint32_t v0[32], v1[32];
+        tmem_ld32(taddr + 32 * cc, v0);
+        if (NB == 2) tmem_ld32(taddr + kTileN + 32 * cc, v1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float r = fmaf(__uint_as_float(v0[j]), sc0, bias0);
+          if (NB == 2) {
+            r = gg_gated(r, fmaf(__uint_as_float(v1[j]), sc1, bias1), p.act);
+          } else if (interleaved) {
+            const float partner = __shfl_xor_sync(0xffffffffu, r, 1);
+            r = gg_gated(r, partner, p.act);
+          }
+          const int col = 32 * cc + j;
+          if (writer && col < t.count) {
+            const int sp = t.row_start + col;
+            const int64_t orow = p.y_rows ? (int64_t)p.y_rows[sp] : (int64_t)sp;
+            store_from_float(p.y, p.y_dtype, orow * p.y_stride + out_n, r);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  } else {
+    // =========================== producers ========================================
+    const int ptid = tid - 5 * 32;            // 0..255
+    const int r = ptid >> 1, half = ptid & 1; // operand row and which 32-k half of the stage
+    uint32_t spin = kGgSpin;
+    int it = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x) {
+      const GgTile t = gg_tile(p, w, n_nt);
+      // weight row of this thread
+      const int n = t.n0 + r;
+      const bool n_ok = n < p.n;
+      const int64_t wrow = ((int64_t)t.expert * p.n + (n_ok ? n : 0));
+      const uint8_t* w0 = reinterpret_cast<const uint8_t*>(p.w) + wrow * p.w_row_bytes;
+      const uint8_t* w1 = NB == 2 ? reinterpret_cast<const uint8_t*>(p.w_up) + wrow * p.w_row_bytes : nullptr;
+      const uint8_t* s0 = nullptr;
+      const uint8_t* s1 = nullptr;
+      if (FMT == HQ_FMT_MXFP4) {
+        s0 = reinterpret_cast<const uint8_t*>(p.scales) + wrow * (p.k / 32);
+        if (NB == 2) s1 = reinterpret_cast<const uint8_t*>(p.scales_up) + wrow * (p.k / 32);
+      }
+      // activation row of this thread
+      const bool x_ok = r < t.count;
+      int64_t xrow = 0;
+      if (x_ok) {
+        const int sp = t.row_start + r;
+        xrow = p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp;
+      }
+      for (int ks = 0; ks < n_ks; ++ks, ++it) {
+        const int s = it % NSTAGE;
+        if (it >= NSTAGE) {
+          if (!mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
+            if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 500 + s);
+            spin = 1;
+          }
+        }
+        uint8_t* stage = smem + s * L::STAGE_BYTES;
+        const int k0 = ks * kTileK;
+        uint32_t v[16];
+        // ---- A: weight tile(s) --------------------------------------------------------
+#pragma unroll
+        for (int bank = 0; bank < NB; ++bank) {
+          const uint8_t* wb = bank == 0 ? w0 : w1;
+          if (n_ok) {
+            if (FMT == HQ_FMT_Q4_K) {
+              expand_q4_k(wb, k0, half, v);
+            } else if (FMT == HQ_FMT_FP8_BLOCK) {
+              const float* rel = bank == 0 ? p.fp8_rel_scale : p.fp8_rel_scale_up;
+              expand_fp8(wb, k0, half,
+                         __ldg(rel + ((int64_t)t.expert * p.fp8_nb + t.n0 / 128) * p.fp8_kb + k0 / 128), v);
+            } else {
+              if (!expand_mxfp4(wb, bank == 0 ? s0 : s1, k0, half, v))
+                report_status(p.status, HQ_DEV_BAD_INDEX, 600);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0u;
+          }
+          store_chunks(stage + bank * kOperandBytes, r, 4 * half, v);
+        }
+        // ---- B: activation rows (gathered into expert order) ----------------------------
+        if (x_ok) {
+          load_x32(p.x, p.x_dtype, xrow * p.x_stride + k0 + 32 * half, 1.f, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0u;
+        }
+        store_chunks(stage + NB * kOperandBytes, r, 4 * half, v);
+        fence_proxy_async_smem();     // generic-proxy writes -> visible to the tensor core (async proxy)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---- block-FP8 scale preparation (once per layer) -------------------------------------
+// scales [groups = E*NB][KB] -> tile_scale[group] = max_kb scale, rel_scale[group][kb] = scale / tile_scale.
+__global__ void __launch_bounds__(128) fp8_scale_prepare_kernel(const float* __restrict__ scales, int64_t n_groups,
+                                                                int kb, float* __restrict__ tile_scale,
+                                                                float* __restrict__ rel_scale) {
+  const int64_t grp = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (grp >= n_groups) return;
+  const int lane = threadIdx.x & 31;
+  float m = 0.f;
+  for (int i = lane; i < kb; i += 32) m = fmaxf(m, scales[grp * kb + i]);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  if (lane == 0) tile_scale[grp] = m;
+  for (int i = lane; i < kb; i += 32) rel_scale[grp * kb + i] = m > 0.f ? scales[grp * kb + i] / m : 0.f;
+}
+
+int32_t launch_fp8_scale_prepare(const float* scales, int64_t n_groups, int kb, float* tile_scale, float* rel_scale,
+                                 cudaStream_t stream) {
+  if (n_groups == 0) return HQ_OK;
+  fp8_scale_prepare_kernel<<<(unsigned)((n_groups + 3) / 4), 128, 0, stream>>>(scales, n_groups, kb, tile_scale,
+                                                                             rel_scale);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+// ---- host launcher -----------------------------------------------------------------
+template <int FMT, int NB>
+static int32_t launch_gg(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
+  using L = GgSmem<NB>;
+  static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
+  auto kern = grouped_gemm_kernel<FMT, NB>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
+  if (dev < 64 && !attr_done[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return HQ_ERR_CUDA;
+    attr_done[dev] = true;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  const int64_t items = (int64_t)max_tiles * ((p.n + kTileM - 1) / kTileM);
+  const int64_t grid = items < sms ? items : sms;
+  if (grid <= 0) return HQ_OK;
+  kern<<<(unsigned)grid, kGgThreads, L::TOTAL, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+bool grouped_gemm_supported(int format, int64_t n, int64_t k) {
+  if (format != HQ_FMT_Q4_K && format != HQ_FMT_FP8_BLOCK && format != HQ_FMT_MXFP4) return false;
+  if (k % kTileK != 0) return false;
+  if (format == HQ_FMT_FP8_BLOCK && (n % 128 != 0 || k % 128 != 0)) return false;
+  return true;
+}
+
+int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
+  const bool two = p.w_up != nullptr;
+  switch (p.format) {
+    case HQ_FMT_Q4_K:
+      return two ? launch_gg<HQ_FMT_Q4_K, 2>(p, max_tiles, stream) : launch_gg<HQ_FMT_Q4_K, 1>(p, max_tiles, stream);
+    case HQ_FMT_FP8_BLOCK:
+      return two ? launch_gg<HQ_FMT_FP8_BLOCK, 2>(p, max_tiles, stream)
+                 : launch_gg<HQ_FMT_FP8_BLOCK, 1>(p, max_tiles, stream);
+    case HQ_FMT_MXFP4:
+      return two ? launch_gg<HQ_FMT_MXFP4, 2>(p, max_tiles, stream) : launch_gg<HQ_FMT_MXFP4, 1>(p, max_tiles, stream);
+    default:
+      return HQ_ERR_FORMAT;
+  }
+}
+
+}  // namespace hq

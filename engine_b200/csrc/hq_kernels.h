@@ -38,6 +38,43 @@ struct GemvParams {
 };
 int32_t launch_gemv(const GemvParams& p, int grid_y, cudaStream_t stream);
 
+// ---- grouped expert GEMM on tcgen05 (hq_grouped_gemm.cu) -----------------------------
+struct GroupedParams {
+  int format;
+  int n, k, m;                 // m: dense rows (used when tiles == nullptr)
+  const void* w;
+  const void* w_up;            // second (up) bank for a fused gated activation, or nullptr
+  const void* scales;          // MXFP4: e8m0 bytes [E, N, K/32]
+  const void* scales_up;
+  const void* bias;
+  const void* bias_up;
+  int bias_dtype;
+  int64_t w_row_bytes;
+  // block-FP8: per (expert, 128-row block) largest scale, and every scale relative to it
+  const float* fp8_tile_scale;      // [E, NB]
+  const float* fp8_tile_scale_up;
+  const float* fp8_rel_scale;       // [E, NB, KB]
+  const float* fp8_rel_scale_up;
+  int fp8_nb, fp8_kb;
+  const void* x;
+  int x_dtype;
+  int64_t x_stride;
+  void* y;
+  int y_dtype;
+  int64_t y_stride;
+  const int32_t* tiles;         // [n_tiles][2] = (expert, first sorted row), tiles of <= 128 rows
+  const int32_t* tile_count;    // device words: [1] = n_tiles
+  const int32_t* expert_bounds;
+  const int32_t* x_rows;        // sorted row -> activation row (nullptr = identity)
+  const int32_t* y_rows;        // sorted row -> output row (nullptr = identity)
+  hq_act_args act;
+  int32_t* status;
+};
+bool grouped_gemm_supported(int format, int64_t n, int64_t k);
+int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t stream);
+int32_t launch_fp8_scale_prepare(const float* scales, int64_t n_groups, int kb, float* tile_scale, float* rel_scale,
+                                 cudaStream_t stream);
+
 // ---- dispatch tables (hq_dispatch.cu) -------------------------------------------
 constexpr int kDispatchChunk = 1024;  // flat assignments per block
 struct DispatchLayout {

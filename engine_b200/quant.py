@@ -244,11 +244,17 @@ class BlockwiseFP8Linear(QuantMethod):
         if tuple(self.scale.shape[-2:]) != want:
             raise L.HqError(f"scale grid {tuple(self.scale.shape)} does not match {want}")
         self.bias = bias
+        # tables for the tensor-core path, derived once from the scale grid
+        self.tile_scale = torch.empty(self.scale.shape[:-1], dtype=torch.float32, device=weight.device)
+        self.rel_scale = torch.empty_like(self.scale)
+        L.check(L.lib().hq_fp8_scale_prepare(_ptr(self.scale), self.n_experts, self.n, self.k, _ptr(self.tile_scale),
+                                             _ptr(self.rel_scale), _stream()), "hq_fp8_scale_prepare")
 
     def _weight_struct(self):
         return L.HqWeight(self.format, self.n_experts, self.n, self.k, self.weight.data_ptr(), self.scale.data_ptr(),
                           0 if self.bias is None else self.bias.data_ptr(),
-                          0 if self.bias is None else dt_code(self.bias.dtype), 0)
+                          0 if self.bias is None else dt_code(self.bias.dtype), 0, self.tile_scale.data_ptr(),
+                          self.rel_scale.data_ptr())
 
     def _device(self):
         return self.weight.device

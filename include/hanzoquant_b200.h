@@ -82,6 +82,10 @@ typedef struct hq_weight {
   const void* bias;    /* optional [E, N] in bias_dtype, or NULL */
   int32_t bias_dtype;  /* HQ_DT_* */
   int32_t reserved;
+  /* FP8 only, optional: tables written once per layer by hq_fp8_scale_prepare.  With them the
+   * prefill-sized calls run on the tensor cores; without them every call takes the decode kernel. */
+  const void* fp8_tile_scale;  /* f32 [E, ceil(N/128)] */
+  const void* fp8_rel_scale;   /* f32 [E, ceil(N/128), ceil(K/128)] */
 } hq_weight;
 
 /* ---- library ------------------------------------------------------------ */
@@ -90,6 +94,15 @@ const char* hq_error_string(int32_t code);
 /* Reads the 4-word device status buffer after synchronising `stream`
  * (test / debug helper; the hot path never calls it). */
 int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* stream);
+
+/* Tuning knobs (process-wide, read at call time).  HQ_CFG_MOE_TENSOR_MIN_ROWS: expert projections run on the
+ * tensor-core grouped GEMM when n_tokens*top_k >= value * n_experts (default 8; 0 = always when the shape
+ * allows, a huge value = never).  HQ_CFG_DENSE_TENSOR_MIN_ROWS: same switch for hq_linear_forward's m
+ * (default 9).  Shapes the grouped GEMM does not cover (Q8_0, K % 64 != 0) always take the decode kernel. */
+#define HQ_CFG_MOE_TENSOR_MIN_ROWS 0
+#define HQ_CFG_DENSE_TENSOR_MIN_ROWS 1
+int32_t hq_config_set(int32_t key, int64_t value);
+int64_t hq_config_get(int32_t key);
 
 /* ---- dense quantized linear: QuantMethod::forward ------------------------
  * y[m, n] = sum_k x[m, k] * dequant(W)[n, k] (+ bias[n]).
@@ -196,6 +209,13 @@ int32_t hq_fp8_block_quant(const void* w, int32_t w_dtype, int64_t rows, int64_t
                            uint8_t* codes, float* scales, void* stream);
 int32_t hq_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t rows, int64_t cols, int32_t by,
                              int32_t bx, void* out, int32_t out_dtype, void* stream);
+
+/* Derives the tables hq_weight.fp8_tile_scale / fp8_rel_scale from a layer's scale grid
+ * (f32 [E, ceil(N/128), ceil(K/128)]): the largest scale of every 128-row block and each scale
+ * divided by it.  No counterpart in the reference (its FP8 kernels multiply by the scale per
+ * element, hanzo-quant/kernels/blockwise_fp8/blockwise_fp8_gemm.cu:47-124). */
+int32_t hq_fp8_scale_prepare(const float* scales, int32_t n_experts, int64_t n, int64_t k, float* tile_scale_out,
+                             float* rel_scale_out, void* stream);
 
 /* ---- gated activations as stand-alone ops -----------------------------------
  * out = act(gate, up) elementwise over n_elems; interleaved = 1 reads pairs

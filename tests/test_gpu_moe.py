@@ -236,3 +236,63 @@ def test_fp8_quantizers_bit_exact():
     sc = torch.arange(9, dtype=torch.float32, device=DEV).reshape(3, 3)
     got = hq.fp8_blockwise_dequantize(ones, sc, (2, 2), torch.float32).cpu().tolist()
     assert got == [[0, 0, 1, 1, 2], [0, 0, 1, 1, 2], [3, 3, 4, 4, 5], [3, 3, 4, 4, 5], [6, 6, 7, 7, 8]]
+
+
+# ---- tensor-core (tcgen05) grouped GEMM: forced on, checked against the oracle and the decode kernel ----------
+
+@pytest.fixture
+def tensor_path():
+    lib = L.lib()
+    old = (lib.hq_config_get(L.CFG_MOE_TENSOR_MIN_ROWS), lib.hq_config_get(L.CFG_DENSE_TENSOR_MIN_ROWS))
+    lib.hq_config_set(L.CFG_MOE_TENSOR_MIN_ROWS, 0)
+    lib.hq_config_set(L.CFG_DENSE_TENSOR_MIN_ROWS, 1)
+    yield lib
+    lib.hq_config_set(L.CFG_MOE_TENSOR_MIN_ROWS, old[0])
+    lib.hq_config_set(L.CFG_DENSE_TENSOR_MIN_ROWS, old[1])
+
+
+@pytest.mark.parametrize("fmt,n,k,m", [("Q4_K", 256, 512, 128), ("Q4_K", 200, 256, 37), ("FP8", 256, 384, 130),
+                                       ("MXFP4", 192, 320, 64), ("MXFP4", 2880, 2880, 150), ("Q4_K", 4096, 4096, 16)])
+def test_tensor_path_dense(tensor_path, fmt, n, k, m):
+    rng = T.rng_for(5, n + k + m)
+    arrays, deq = T.make_weight(fmt, rng, n, k)
+    bd = T.to_dev(rng.normal(0, 0.02, n).astype(np.float32), torch.bfloat16, DEV) if fmt == "MXFP4" else None
+    layer = T.make_layer(fmt, arrays, k, DEV, bd)
+    xd = T.to_dev(rng.standard_normal((m, k)).astype(np.float32), torch.bfloat16, DEV)
+    got = layer.forward_raw(xd, torch.float32)
+    torch.cuda.synchronize()
+    assert layer.device_status()[0] == 0, layer.device_status()
+    want = M.dense_forward(xd.to(torch.float32).cpu().numpy(), deq,
+                           None if bd is None else bd.to(torch.float32).cpu().numpy())
+    assert T.rel_l2(got.cpu().numpy(), want) <= TOL[fmt]
+    # and it agrees with the decode kernel on the same inputs
+    tensor_path.hq_config_set(L.CFG_DENSE_TENSOR_MIN_ROWS, 1 << 40)
+    ref = layer.forward_raw(xd, torch.float32)
+    assert T.rel_l2(got.cpu().numpy(), ref.cpu().numpy()) <= TOL[fmt]
+
+
+@pytest.mark.parametrize("fmt,k,n", [("Q4_K", 512, 192), ("FP8", 256, 128), ("MXFP4", 128, 144)])
+def test_tensor_path_gather_forward(tensor_path, fmt, k, n):
+    rng = T.rng_for(5, k + n)
+    e, t, topk = 5, 300, 2          # expert 4 gets nothing, expert 0 gets several 128-row tiles
+    arrays, deq = T.make_weight(fmt, rng, n, k, experts=e)
+    layer = T.make_layer(fmt, arrays, k, DEV)
+    p = np.array([0.7, 0.15, 0.1, 0.05, 0.0])
+    ids = np.stack([rng.choice(e, size=topk, replace=False, p=p) for _ in range(t)]).astype(np.int32)
+    xd = T.to_dev(rng.standard_normal((t, k)).astype(np.float32), torch.bfloat16, DEV)
+    out = layer.gather_forward_raw(xd, T.to_dev(ids, torch.int32, DEV), torch.float32)
+    torch.cuda.synchronize()
+    assert layer.device_status()[0] == 0, layer.device_status()
+    want = M.gather_forward(xd.to(torch.float32).cpu().numpy(), ids.astype(np.uint32), deq)
+    assert T.rel_l2(out.cpu().numpy(), want) <= TOL[fmt]
+    again = layer.gather_forward_raw(xd, T.to_dev(ids, torch.int32, DEV), torch.float32)
+    assert torch.equal(out, again)            # no atomics anywhere: bit-reproducible
+
+
+def test_tensor_path_moe_blocks(tensor_path):
+    got, want = _moe_case("Q4_K", 200, 8, 4, 512, 256, False, L.ACT_SWIGLU, 21)
+    assert T.rel_l2(got, want) <= 1e-3
+    got, want = _moe_case("FP8", 150, 8, 4, 512, 256, False, L.ACT_SWIGLU, 22)
+    assert T.rel_l2(got, want) <= 2e-3
+    got, want = _moe_case("MXFP4", 140, 8, 4, 320, 320, True, L.ACT_GPTOSS, 23, limit=7.0)
+    assert T.rel_l2(got, want) <= 2e-3
