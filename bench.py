@@ -261,24 +261,37 @@ def run_gemv(args):
     barrier()
     ms_total = e0.elapsed_time(e1)
 
-    # ---- per-launch kernel durations (eager, one event pair per launch, rotating copies) ---------------------
-    reps = max(5, min(args.steps, 20))
+    # ---- per-launch kernel durations: one CUDA graph of back-to-back launches per (shape, M), each launch on
+    # a different weight copy, timed with CUDA events and divided by the launch count (a Python-driven launch
+    # costs more host time than these kernels run for, so eager event pairs would time the host) -----------
     per = {}
-    for (k, n) in SHAPES:
-        ls = layers[(k, n)]
-        for m in MS:
-            evs = []
-            for r in range(reps):
-                layer = ls[r % len(ls)]
-                w = layer._weight_struct()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                L.lib().hq_linear_forward(w, xs[(k, m)].data_ptr(), L.DT_BF16, k, ys[(n, m)].data_ptr(), L.DT_F32, n, m,
-                                          layer._status_buf(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
-                b.record()
-                evs.append((a, b))
+    with torch.cuda.stream(side):
+        for (k, n) in SHAPES:
+            ls = layers[(k, n)]
+            reps = len(ls) if len(ls) > 2 else 4
+            for m in MS:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for r in range(reps):
+                        layer = ls[r % len(ls)]
+                        L.check(L.lib().hq_linear_forward(layer._weight_struct(), xs[(k, m)].data_ptr(), L.DT_BF16, k,
+                                                          ys[(n, m)].data_ptr(), L.DT_F32, n, m,
+                                                          layer._status_buf(dev).data_ptr(),
+                                                          torch.cuda.current_stream().cuda_stream), "hq_linear_forward")
+                per[(k, n, m)] = (g, reps)
+    torch.cuda.synchronize()
+    for key, (g, reps) in list(per.items()):
+        g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
             torch.cuda.synchronize()
-            per[(k, n, m)] = statistics.median(a.elapsed_time(b) for a, b in evs)
+            ts.append(a.elapsed_time(b) / reps)
+        per[key] = statistics.median(ts)
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the public API with pinned host buffers -------------------------------------------

@@ -115,7 +115,7 @@ __device__ __forceinline__ void x_prefetch(XPrefetch& pf, const GemvParams& p, i
 
 template <bool PERM, bool XSUM, int XP>
 __device__ __forceinline__ void x_commit(const XPrefetch& pf, const GemvParams& p, int nrows, int k_len, int tid,
-                                         __half* xs, float* xsum) {
+                                         __half* xs, float* xsum, float xsum_scale) {
   const int esz = dtype_size(p.x_dtype);
   const int epg = 16 / esz;
   const int gpr = k_len / epg;
@@ -165,7 +165,7 @@ __device__ __forceinline__ void x_commit(const XPrefetch& pf, const GemvParams& 
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         if (lpb == 8) s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (ok && (tid % lpb) == 0) xsum[(kk / 32) * 8 + col] = s;
+        if (ok && (tid % lpb) == 0) xsum[(kk / 32) * 8 + col] = s * xsum_scale;
       }
       if (ok) {
         __half* dst = xs + col * XP + kk;
@@ -203,30 +203,33 @@ __device__ __forceinline__ void q8_load(Q8Regs& r, uint32_t rowA, uint32_t rowB,
   r.sh = (q & 3u) * 8u;
   r.dA = lds16(rowA + off);
   r.dB = lds16(rowB + off);
-  r.a[0] = lds32(rowA + al); r.a[1] = lds32(rowA + al + 4); r.a[2] = lds32(rowA + al + 16); r.a[3] = lds32(rowA + al + 20);
-  r.b[0] = lds32(rowB + al); r.b[1] = lds32(rowB + al + 4); r.b[2] = lds32(rowB + al + 16); r.b[3] = lds32(rowB + al + 20);
+  const uint32_t pa = rowA + al, pb = rowB + al;
+  r.a[0] = lds32<0>(pa); r.a[1] = lds32<4>(pa); r.a[2] = lds32<16>(pa); r.a[3] = lds32<20>(pa);
+  r.b[0] = lds32<0>(pb); r.b[1] = lds32<4>(pb); r.b[2] = lds32<16>(pb); r.b[3] = lds32<20>(pb);
   const uint32_t xo = xs_g + (32u * unit + 4u * t) * 2u;
-  r.x0 = lds64(xo);
-  r.x1 = lds64(xo + 32u);
+  r.x0 = lds64<0>(xo);
+  r.x1 = lds64<32>(xo);
   r.xs = lds64(xsum_t + 32u * unit);
 }
+// bytes 1 and 3 of v into the low bytes of the two halves: (v >> 8) & 0x00FF00FF in one permute
+__device__ __forceinline__ uint32_t odd_bytes(uint32_t v) { return __byte_perm(v, 0u, 0x4341); }
 __device__ __forceinline__ void q8_compute(float (&acc)[4], const Q8Regs& r) {
   const uint32_t a_lo = __funnelshift_r(r.a[0], r.a[1], r.sh) ^ 0x80808080u;
   const uint32_t a_hi = __funnelshift_r(r.a[2], r.a[3], r.sh) ^ 0x80808080u;
   const uint32_t b_lo = __funnelshift_r(r.b[0], r.b[1], r.sh) ^ 0x80808080u;
   const uint32_t b_hi = __funnelshift_r(r.b[2], r.b[3], r.sh) ^ 0x80808080u;
-  float b0[4] = {0.f, 0.f, 0.f, 0.f}, b1[4] = {0.f, 0.f, 0.f, 0.f};   // two independent MMAs
-  mma_f16_16816(b0, a_lo & 0x00FF00FFu, b_lo & 0x00FF00FFu, (a_lo >> 8) & 0x00FF00FFu, (b_lo >> 8) & 0x00FF00FFu,
-                r.x0.x, r.x0.y);
-  mma_f16_16816(b1, a_hi & 0x00FF00FFu, b_hi & 0x00FF00FFu, (a_hi >> 8) & 0x00FF00FFu, (b_hi >> 8) & 0x00FF00FFu,
-                r.x1.x, r.x1.y);
-  // codes were fed as (q+128) * 2^-24: value = (d * 2^24) * (blk - 128 * 2^-24 * sum(x))
-  const float c0 = -7.62939453125e-06f * __uint_as_float(r.xs.x), c1 = -7.62939453125e-06f * __uint_as_float(r.xs.y);
+  // codes are fed as (q+128) * 2^-24; the staged table holds -128 * 2^-24 * sum(x) per block and column and
+  // enters as the C operand, so blk = 2^-24 * sum(q*x)
+  const float c0 = __uint_as_float(r.xs.x), c1 = __uint_as_float(r.xs.y);
+  float blk[4];
+  mma_f16_16816_c(blk, a_lo & 0x00FF00FFu, b_lo & 0x00FF00FFu, odd_bytes(a_lo), odd_bytes(b_lo), r.x0.x, r.x0.y, c0,
+                  c1, c0, c1);
+  mma_f16_16816(blk, a_hi & 0x00FF00FFu, b_hi & 0x00FF00FFu, odd_bytes(a_hi), odd_bytes(b_hi), r.x1.x, r.x1.y);
   const float sA = half_bits_to_float(r.dA) * 16777216.f, sB = half_bits_to_float(r.dB) * 16777216.f;
-  acc[0] = fmaf(sA, (b0[0] + b1[0]) + c0, acc[0]);
-  acc[1] = fmaf(sA, (b0[1] + b1[1]) + c1, acc[1]);
-  acc[2] = fmaf(sB, (b0[2] + b1[2]) + c0, acc[2]);
-  acc[3] = fmaf(sB, (b0[3] + b1[3]) + c1, acc[3]);
+  acc[0] = fmaf(sA, blk[0], acc[0]);
+  acc[1] = fmaf(sA, blk[1], acc[1]);
+  acc[2] = fmaf(sB, blk[2], acc[2]);
+  acc[3] = fmaf(sB, blk[3], acc[3]);
 }
 
 // Q4_K: unit = 64 elements = sub-blocks (2c, 2c+1) of a super-block; they share 32 nibble bytes.
@@ -243,15 +246,16 @@ __device__ __forceinline__ void q4_load(Q4Regs& r, uint32_t rowA, uint32_t rowB,
   r.dmA = lds32(sbA);
   r.dmB = lds32(sbB);
   // 12 scale bytes at +4: 6-bit (scale, min) pairs, the GGML get_scale_min_k4 packing
-  r.scA[0] = lds32(sbA + 4); r.scA[1] = lds32(sbA + 8); r.scA[2] = lds32(sbA + 12);
-  r.scB[0] = lds32(sbB + 4); r.scB[1] = lds32(sbB + 8); r.scB[2] = lds32(sbB + 12);
+  r.scA[0] = lds32<4>(sbA); r.scA[1] = lds32<8>(sbA); r.scA[2] = lds32<12>(sbA);
+  r.scB[0] = lds32<4>(sbB); r.scB[1] = lds32<8>(sbB); r.scB[2] = lds32<12>(sbB);
   const uint32_t qo = 16u + 32u * c + 4u * t;
-  r.a0 = lds32(sbA + qo); r.a1 = lds32(sbA + qo + 16);
-  r.b0 = lds32(sbB + qo); r.b1 = lds32(sbB + qo + 16);
+  r.a0 = lds32<0>(sbA + qo); r.a1 = lds32<16>(sbA + qo);
+  r.b0 = lds32<0>(sbB + qo); r.b1 = lds32<16>(sbB + qo);
   const uint32_t xo = xs_g + (256u * sb + 64u * c + 4u * t) * 2u;
-  r.x[0] = lds64(xo); r.x[1] = lds64(xo + 32u); r.x[2] = lds64(xo + 64u); r.x[3] = lds64(xo + 96u);
-  r.xs[0] = lds64(xsum_t + 32u * (8u * sb + 2u * c));
-  r.xs[1] = lds64(xsum_t + 32u * (8u * sb + 2u * c + 1u));
+  r.x[0] = lds64<0>(xo); r.x[1] = lds64<32>(xo); r.x[2] = lds64<64>(xo); r.x[3] = lds64<96>(xo);
+  const uint32_t so = xsum_t + 32u * (8u * sb + 2u * c);
+  r.xs[0] = lds64<0>(so);
+  r.xs[1] = lds64<32>(so);
 }
 __device__ __forceinline__ void q4k_scale_min(const uint32_t (&w)[3], int j, float& sc, float& mn) {
   uint32_t s, m;
@@ -273,9 +277,10 @@ __device__ __forceinline__ void q4_compute(float (&acc)[4], const Q4Regs& r) {
   for (int hi = 0; hi < 2; ++hi) {
     // low nibbles -> sub-block 2c (codes * 2^-24), high nibbles -> 2c+1 (codes * 2^-20)
     const uint32_t mask = hi ? 0x00F000F0u : 0x000F000Fu;
-    float b0[4] = {0.f, 0.f, 0.f, 0.f}, b1[4] = {0.f, 0.f, 0.f, 0.f};
-    mma_f16_16816(b0, r.a0 & mask, r.b0 & mask, (r.a0 >> 8) & mask, (r.b0 >> 8) & mask, r.x[2 * hi].x, r.x[2 * hi].y);
-    mma_f16_16816(b1, r.a1 & mask, r.b1 & mask, (r.a1 >> 8) & mask, (r.b1 >> 8) & mask, r.x[2 * hi + 1].x,
+    float blk[4];
+    mma_f16_16816_c(blk, r.a0 & mask, r.b0 & mask, (r.a0 >> 8) & mask, (r.b0 >> 8) & mask, r.x[2 * hi].x,
+                    r.x[2 * hi].y, 0.f, 0.f, 0.f, 0.f);
+    mma_f16_16816(blk, r.a1 & mask, r.b1 & mask, (r.a1 >> 8) & mask, (r.b1 >> 8) & mask, r.x[2 * hi + 1].x,
                   r.x[2 * hi + 1].y);
     const int j = 2 * r.c + hi;
     float scA, mnA, scB, mnB;
@@ -285,10 +290,10 @@ __device__ __forceinline__ void q4_compute(float (&acc)[4], const Q4Regs& r) {
     const float sx0 = __uint_as_float(r.xs[hi].x), sx1 = __uint_as_float(r.xs[hi].y);
     const float fA = dA * scA * pw, fB = dB * scB * pw;
     const float gA = -(mA * mnA), gB = -(mB * mnB);
-    acc[0] = fmaf(fA, b0[0] + b1[0], fmaf(gA, sx0, acc[0]));
-    acc[1] = fmaf(fA, b0[1] + b1[1], fmaf(gA, sx1, acc[1]));
-    acc[2] = fmaf(fB, b0[2] + b1[2], fmaf(gB, sx0, acc[2]));
-    acc[3] = fmaf(fB, b0[3] + b1[3], fmaf(gB, sx1, acc[3]));
+    acc[0] = fmaf(fA, blk[0], fmaf(gA, sx0, acc[0]));
+    acc[1] = fmaf(fA, blk[1], fmaf(gA, sx1, acc[1]));
+    acc[2] = fmaf(fB, blk[2], fmaf(gB, sx0, acc[2]));
+    acc[3] = fmaf(fB, blk[3], fmaf(gB, sx1, acc[3]));
   }
 }
 
@@ -310,23 +315,23 @@ struct B32Regs {
 };
 __device__ __forceinline__ void fp8_load(B32Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, int unit, int t) {
   const uint32_t qo = 32u * unit + 4u * t;
-  r.a0 = lds32(rowA + qo); r.a1 = lds32(rowA + qo + 16);
-  r.b0 = lds32(rowB + qo); r.b1 = lds32(rowB + qo + 16);
+  r.a0 = lds32<0>(rowA + qo); r.a1 = lds32<16>(rowA + qo);
+  r.b0 = lds32<0>(rowB + qo); r.b1 = lds32<16>(rowB + qo);
   const uint32_t xo = xs_g + (32u * unit + 4u * t) * 2u;
-  r.x0 = lds64(xo);
-  r.x1 = lds64(xo + 32u);
+  r.x0 = lds64<0>(xo);
+  r.x1 = lds64<32>(xo);
 }
 __device__ __forceinline__ void fp8_compute(float (&acc)[4], const B32Regs& r, float scale) {
-  float k0[4] = {0.f, 0.f, 0.f, 0.f}, k1[4] = {0.f, 0.f, 0.f, 0.f};
+  float blk[4];
   uint32_t al, ah, bl, bh;
   e4m3x4_to_f16x4(r.a0, al, ah);
   e4m3x4_to_f16x4(r.b0, bl, bh);
-  mma_f16_16816(k0, al, bl, ah, bh, r.x0.x, r.x0.y);
+  mma_f16_16816_c(blk, al, bl, ah, bh, r.x0.x, r.x0.y, 0.f, 0.f, 0.f, 0.f);
   e4m3x4_to_f16x4(r.a1, al, ah);
   e4m3x4_to_f16x4(r.b1, bl, bh);
-  mma_f16_16816(k1, al, bl, ah, bh, r.x1.x, r.x1.y);
+  mma_f16_16816(blk, al, bl, ah, bh, r.x1.x, r.x1.y);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) acc[i] = fmaf(scale, k0[i] + k1[i], acc[i]);
+  for (int i = 0; i < 4; ++i) acc[i] = fmaf(scale, blk[i], acc[i]);
 }
 
 // e2m1 nibble pair (one byte: low nibble = even element) -> f16x2 holding value * 2^-14:
@@ -343,19 +348,19 @@ __device__ __forceinline__ void mx_load(B32Regs& r, uint32_t rowA, uint32_t rowB
   r.a0 = lds32(rowA + qo);
   r.b0 = lds32(rowB + qo);
   const uint32_t xo = xs_g + (32u * unit + 8u * t) * 2u;
-  r.x0 = lds64(xo);
-  r.x1 = lds64(xo + 8u);
+  r.x0 = lds64<0>(xo);
+  r.x1 = lds64<8>(xo);
 }
 __device__ __forceinline__ void mx_compute(float (&acc)[4], const B32Regs& r, float sA, float sB) {
-  float k0[4] = {0.f, 0.f, 0.f, 0.f}, k1[4] = {0.f, 0.f, 0.f, 0.f};
-  mma_f16_16816(k0, e2m1_byte_to_f16x2(r.a0), e2m1_byte_to_f16x2(r.b0), e2m1_byte_to_f16x2(r.a0 >> 8),
-                e2m1_byte_to_f16x2(r.b0 >> 8), r.x0.x, r.x0.y);
-  mma_f16_16816(k1, e2m1_byte_to_f16x2(r.a0 >> 16), e2m1_byte_to_f16x2(r.b0 >> 16), e2m1_byte_to_f16x2(r.a0 >> 24),
+  float blk[4];
+  mma_f16_16816_c(blk, e2m1_byte_to_f16x2(r.a0), e2m1_byte_to_f16x2(r.b0), e2m1_byte_to_f16x2(r.a0 >> 8),
+                  e2m1_byte_to_f16x2(r.b0 >> 8), r.x0.x, r.x0.y, 0.f, 0.f, 0.f, 0.f);
+  mma_f16_16816(blk, e2m1_byte_to_f16x2(r.a0 >> 16), e2m1_byte_to_f16x2(r.b0 >> 16), e2m1_byte_to_f16x2(r.a0 >> 24),
                 e2m1_byte_to_f16x2(r.b0 >> 24), r.x1.x, r.x1.y);
-  acc[0] = fmaf(sA, k0[0] + k1[0], acc[0]);
-  acc[1] = fmaf(sA, k0[1] + k1[1], acc[1]);
-  acc[2] = fmaf(sB, k0[2] + k1[2], acc[2]);
-  acc[3] = fmaf(sB, k0[3] + k1[3], acc[3]);
+  acc[0] = fmaf(sA, blk[0], acc[0]);
+  acc[1] = fmaf(sA, blk[1], acc[1]);
+  acc[2] = fmaf(sB, blk[2], acc[2]);
+  acc[3] = fmaf(sB, blk[3], acc[3]);
 }
 
 __device__ __forceinline__ float gated(float g, float u, const hq_act_args& a) {
@@ -402,6 +407,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   using F = FmtTraits<FMT>;
   constexpr int WK = kConsumerWarps;
   constexpr int RT = L::RT;
+  // per-block activation sums: Q8_0 wants them as the MMA's C operand (-128 * 2^-24 * sum), Q4_K plain
+  constexpr float kXsumScale = FMT == HQ_FMT_Q8_0 ? -7.62939453125e-06f : 1.f;
   extern __shared__ __align__(128) uint8_t smem[];
 
   const int n_rt = (p.n + RT - 1) / RT;
@@ -511,11 +518,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         for (int i = tid; i < (staged_rows - wi.nrows) * (L::XP / 8); i += kConsumerThreads)
           reinterpret_cast<uint4*>(xs + wi.nrows * L::XP)[i] = make_uint4(0, 0, 0, 0);
         staged_rows = wi.nrows;
-        x_commit<F::kPermX, F::kNeedXsum, L::XP>(pf, p, wi.nrows, min(xk_sub, k_len), tid, xs, xsum);
+        x_commit<F::kPermX, F::kNeedXsum, L::XP>(pf, p, wi.nrows, min(xk_sub, k_len), tid, xs, xsum, kXsumScale);
         for (int sub = xk_sub; sub < k_len; sub += xk_sub) {   // f32 input: second half, fetched now
           x_prefetch(pf, p, wi.row0, wi.nrows, k_base + sub, min(xk_sub, k_len - sub), tid);
           x_commit<F::kPermX, F::kNeedXsum, L::XP>(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xs + sub,
-                                                   xsum + (sub / 32) * 8);
+                                                   xsum + (sub / 32) * 8, kXsumScale);
         }
         staged_y = wi.y;
         pf_valid = false;

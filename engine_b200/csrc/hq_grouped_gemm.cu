@@ -124,8 +124,12 @@ __device__ __forceinline__ void expand_q4_k(const uint8_t* row_base, int k0, int
   }
   const float d1 = half_bits_to_float(hdr.x) * (float)s;
   const float m1 = half_bits_to_float(hdr.x >> 16) * (float)m;
-  const __half2 d2 = __float2half2_rn(d1);
-  const __half2 m2 = __float2half2_rn(-m1);
+  // f16 arithmetic with the scale and the min split into a leading f16 and its remainder, so the only
+  // rounding that matters is the final one of each weight: w = code * (dh + dl) - (mh + ml)
+  const __half dh = __float2half_rn(d1), mh = __float2half_rn(m1);
+  const __half2 dh2 = __half2half2(dh), nmh2 = __half2half2(__hneg(mh));
+  const __half2 dl2 = __float2half2_rn(d1 - __half2float(dh));
+  const __half2 nml2 = __float2half2_rn(__half2float(mh) - m1);
   const __half2 k1024 = __float2half2_rn(1024.f);
   const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
@@ -133,8 +137,10 @@ __device__ __forceinline__ void expand_q4_k(const uint8_t* row_base, int k0, int
     const uint32_t v = half ? (qw[i] >> 4) : qw[i];
     uint32_t p02 = (v & 0x000F000Fu) | 0x64006400u;          // 1024 + code of bytes 0 and 2
     uint32_t p13 = ((v >> 8) & 0x000F000Fu) | 0x64006400u;   // bytes 1 and 3
-    __half2 h02 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&p02), k1024), d2, m2);
-    __half2 h13 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&p13), k1024), d2, m2);
+    const __half2 c02 = __hsub2(*reinterpret_cast<__half2*>(&p02), k1024);
+    const __half2 c13 = __hsub2(*reinterpret_cast<__half2*>(&p13), k1024);
+    __half2 h02 = __hadd2(__hfma2(c02, dh2, nmh2), __hfma2(c02, dl2, nml2));
+    __half2 h13 = __hadd2(__hfma2(c13, dh2, nmh2), __hfma2(c13, dl2, nml2));
     const uint32_t a = *reinterpret_cast<uint32_t*>(&h02), b = *reinterpret_cast<uint32_t*>(&h13);
     out[2 * i] = __byte_perm(a, b, 0x5410);       // elements 0, 1
     out[2 * i + 1] = __byte_perm(a, b, 0x7632);   // elements 2, 3

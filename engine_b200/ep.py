@@ -1,0 +1,102 @@
+"""Expert-parallel MoE over the GPUs of one box: experts are sharded in contiguous ranges (E / world per rank),
+tokens stay data-parallel, and two all-to-all exchanges per layer move token rows to the ranks that own their
+experts and bring the expert outputs back (NCCL over NVLink through torch.distributed).
+
+The reference has no expert parallelism (its only MoE collective is the tensor-parallel all-reduce at
+hanzo-engine/src/moe/experts/mod.rs:260-263, hanzo-quant/src/distributed/mod.rs:360-411); this module is the
+exchange step the sharded path needs, built around the same local kernels.
+
+Per layer and rank:
+  1. assignments (t, s) are ordered by destination rank (stable), counts are exchanged (one small all-to-all);
+  2. token rows + local expert ids go out in one all-to-all-v each;
+  3. the local expert block runs on the received rows (one row per assignment, top_k = 1);
+  4. outputs return by the mirrored all-to-all-v;
+  5. the source rank un-permutes and takes the router-weighted sum over its k slots.
+Results equal the single-GPU result up to f32 summation order (none: every (t, s) output is computed once,
+by the rank that owns the expert, and summed in slot order at the source).
+
+`expert_fn` and `reduce_fn` are injectable so the protocol can be exercised with CPU ranks (gloo).
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+def _gpu_expert_fn(experts):
+    def run(rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
+        if rows.shape[0] == 0:
+            return torch.empty((0, experts.down.n), dtype=torch.float32, device=rows.device)
+        ones = torch.ones((rows.shape[0], 1), dtype=torch.float32, device=rows.device)
+        return experts.forward(rows, ones, local_ids.reshape(-1, 1).to(torch.int32), out_dtype=torch.float32)
+    return run
+
+
+def _gpu_reduce_fn(y_rows, weights, row_map, out_dtype, addend):
+    from .moe import moe_weighted_reduce
+    return moe_weighted_reduce(y_rows, weights, out_dtype, row_map, addend)
+
+
+class ExpertParallelMoE:
+    def __init__(self, n_experts_global: int, experts=None, group=None,
+                 expert_fn: Callable | None = None, reduce_fn: Callable | None = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if n_experts_global % self.world:
+            raise ValueError(f"{n_experts_global} experts do not split over {self.world} ranks")
+        self.n_experts = n_experts_global
+        self.e_local = n_experts_global // self.world
+        self.expert_fn = expert_fn or _gpu_expert_fn(experts)
+        self.reduce_fn = reduce_fn or _gpu_reduce_fn
+        self.last_counts = None      # (send_counts, recv_counts) of the last call, for traffic accounting
+
+    def local_expert_range(self):
+        return self.rank * self.e_local, (self.rank + 1) * self.e_local
+
+    def plan(self, topk_ids: torch.Tensor):
+        """Order the flat assignment list by destination rank (stable).  Returns (order, send_counts, local_ids,
+        row_map): order[i] = flat index t*k+s of the i-th row sent; row_map[t*k+s] = its position."""
+        flat = topk_ids.reshape(-1).to(torch.int64)
+        dest = torch.div(flat, self.e_local, rounding_mode="floor")
+        order = torch.argsort(dest, stable=True)
+        send_counts = torch.bincount(dest, minlength=self.world)
+        row_map = torch.empty_like(order)
+        row_map[order] = torch.arange(order.numel(), device=order.device)
+        local_ids = (flat - dest * self.e_local)[order]
+        return order, send_counts, local_ids, row_map.to(torch.int32)
+
+    def _exchange_counts(self, send_counts: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return send_counts.clone()
+        recv = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv, send_counts, group=self.group)
+        return recv
+
+    def _all_to_all_v(self, send: torch.Tensor, send_splits, recv_splits) -> torch.Tensor:
+        out = torch.empty((sum(recv_splits),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        if self.world == 1:
+            out.copy_(send)
+            return out
+        dist.all_to_all_single(out, send.contiguous(), recv_splits, send_splits, group=self.group)
+        return out
+
+    def forward(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        t, k = topk_ids.shape
+        x = xs.reshape(t, -1)
+        order, send_counts, local_ids, row_map = self.plan(topk_ids)
+        recv_counts = self._exchange_counts(send_counts)
+        # split sizes are needed on the host by the collective: one small device->host read per layer
+        send_splits = [int(v) for v in send_counts.tolist()]
+        recv_splits = [int(v) for v in recv_counts.tolist()]
+        self.last_counts = (send_splits, recv_splits)
+        rows = x.index_select(0, torch.div(order, k, rounding_mode="floor"))
+        got_rows = self._all_to_all_v(rows, send_splits, recv_splits)
+        got_ids = self._all_to_all_v(local_ids, send_splits, recv_splits)
+        y = self.expert_fn(got_rows, got_ids)
+        back = self._all_to_all_v(y, recv_splits, send_splits)
+        out = self.reduce_fn(back, topk_weights.to(torch.float32), row_map, out_dtype or xs.dtype, shared_out)
+        return out.reshape(*xs.shape[:-1], out.shape[-1])

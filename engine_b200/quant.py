@@ -171,9 +171,15 @@ class QuantMethod:
         dev = self._device()
         eye = torch.eye(self.k, dtype=torch.float16, device=dev)
         outs = []
-        for e in range(self.n_experts):
-            layer = self._expert_view(e)
-            outs.append(layer.forward_raw(eye, torch.float32).t().contiguous())
+        lib = L.lib()
+        old = lib.hq_config_get(L.CFG_DENSE_TENSOR_MIN_ROWS)
+        lib.hq_config_set(L.CFG_DENSE_TENSOR_MIN_ROWS, 1 << 40)   # the decode kernel is the exact one
+        try:
+            for e in range(self.n_experts):
+                layer = self._expert_view(e)
+                outs.append(layer.forward_raw(eye, torch.float32).t().contiguous())
+        finally:
+            lib.hq_config_set(L.CFG_DENSE_TENSOR_MIN_ROWS, old)
         return outs[0] if self.n_experts == 1 else torch.stack(outs)
 
     def _device(self):
