@@ -48,6 +48,7 @@ SIGNATURES = {
     "hq_router_topk": (_I32, [_P, _I32, _I64, C.POINTER(HqRouterArgs), _P, _P, _P]),
     "hq_moe_dispatch_workspace_bytes": (_I64, [_I64, _I32, _I32]),
     "hq_moe_dispatch_build": (_I32, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P, _I64, _P]),
+    "hq_moe_dispatch_build_noalloc": (_I32, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P]),
     "hq_moe_gather_forward": (_I32, [C.POINTER(HqWeight), C.POINTER(HqWeight), C.POINTER(HqActArgs), _P, _I32,
                                      _I32, _I64, _I32, _P, _P, _P, _P, _P, _I32, _I32, _P, _P]),
     "hq_moe_weighted_reduce": (_I32, [_P, _I32, _P, _P, _P, _P, _I32, _I64, _I32, _I64, _P]),

@@ -194,6 +194,17 @@ int32_t hq_moe_dispatch_build(const uint32_t* ids, int64_t n_tokens, int32_t top
                          (int32_t*)workspace, (cudaStream_t)stream);
 }
 
+int32_t hq_moe_dispatch_build_noalloc(const uint32_t* ids, int64_t n_tokens, int32_t top_k, int32_t n_experts,
+                                      int32_t* expert_bounds, int32_t* sorted_assign, int32_t* sorted_token,
+                                      int32_t* inv_perm, void* stream) {
+  if (n_tokens < 0 || top_k < 1 || top_k > 64 || n_experts < 1) return HQ_ERR_SHAPE;
+  if (expert_bounds == nullptr) return HQ_ERR_NULL;
+  if (n_tokens > 0 && (ids == nullptr || sorted_assign == nullptr || sorted_token == nullptr || inv_perm == nullptr))
+    return HQ_ERR_NULL;
+  return launch_dispatch_noalloc(ids, n_tokens, top_k, n_experts, expert_bounds, sorted_assign, sorted_token,
+                                 inv_perm, (cudaStream_t)stream);
+}
+
 int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const hq_act_args* act, const void* x,
                               int32_t x_dtype, int32_t x_layout, int64_t n_tokens, int32_t top_k,
                               const int32_t* expert_bounds, const int32_t* sorted_assign,

@@ -162,4 +162,40 @@ int32_t launch_dispatch(const uint32_t* ids, int64_t n_tokens, int top_k, int n_
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
+// ---- variant for callers that cannot allocate ------------------------------------------------------
+// Some hosts have no way to hand this library a workspace: every byte of device memory is already owned by
+// their own pool (a serving engine that sizes its KV cache to whatever is free), or the call is made from
+// a place where asking the CUDA runtime for memory is not allowed.  For them the chunk histograms and the
+// tile lists live in a fixed array inside the library image.  It is sized for kNoAllocMaxAssignments
+// assignments and kNoAllocMaxExperts experts (about 210 KB), exists once per GPU that loads the library
+// and is shared by every call: two calls that overlap on the GPU (different streams, or graphs replayed
+// concurrently) race on it.  Nothing in it has to start at zero -- every word that is read is written
+// first by the same call.
+constexpr int kNoAllocMaxAssignments = 65536;
+constexpr int kNoAllocMaxExperts = 512;
+constexpr int64_t kNoAllocWords = 4 + (int64_t)(kNoAllocMaxAssignments / kDispatchChunk) * kNoAllocMaxExperts +
+                                  2 * ((int64_t)kNoAllocMaxAssignments / 8 + kNoAllocMaxExperts) +
+                                  2 * ((int64_t)kNoAllocMaxAssignments / 128 + kNoAllocMaxExperts);
+static __device__ __align__(256) int32_t g_noalloc_scratch[kNoAllocWords];
+
+int32_t launch_dispatch_noalloc(const uint32_t* ids, int64_t n_tokens, int top_k, int n_experts, int32_t* bounds,
+                                int32_t* sorted_assign, int32_t* sorted_token, int32_t* inv_perm,
+                                cudaStream_t stream) {
+  if (n_tokens * top_k > kNoAllocMaxAssignments || n_experts > kNoAllocMaxExperts) return HQ_ERR_TOO_LARGE;
+  const DispatchLayout l = dispatch_layout(n_tokens, top_k, n_experts);
+  if (l.total_words > kNoAllocWords) return HQ_ERR_TOO_LARGE;
+  // The array's name is only a host-side handle; kernels need its device address, which differs per device.
+  // Looked up on the first call made with a given device current (a plain runtime query, no allocation).
+  static int32_t* dev_ptr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HQ_ERR_CUDA;
+  if (dev_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return HQ_ERR_CUDA;
+    dev_ptr[dev] = static_cast<int32_t*>(p);
+  }
+  return launch_dispatch(ids, n_tokens, top_k, n_experts, bounds, sorted_assign, sorted_token, inv_perm,
+                         dev_ptr[dev], stream);
+}
+
 }  // namespace hq

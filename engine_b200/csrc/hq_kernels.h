@@ -91,6 +91,10 @@ int32_t launch_dispatch(const uint32_t* ids, int64_t n_tokens, int top_k, int n_
                         int32_t* sorted_assign, int32_t* sorted_token, int32_t* inv_perm, int32_t* ws,
                         cudaStream_t stream);
 
+int32_t launch_dispatch_noalloc(const uint32_t* ids, int64_t n_tokens, int top_k, int n_experts, int32_t* bounds,
+                                int32_t* sorted_assign, int32_t* sorted_token, int32_t* inv_perm,
+                                cudaStream_t stream);
+
 // ---- router (hq_router.cu) --------------------------------------------------------
 int32_t launch_router(const void* logits, int dtype, int64_t n_rows, const hq_router_args& a, uint32_t* ids,
                       float* weights, cudaStream_t stream);

@@ -151,6 +151,20 @@ int32_t hq_moe_dispatch_build(const uint32_t* ids, int64_t n_tokens, int32_t top
                               int32_t* expert_bounds, int32_t* sorted_assign, int32_t* sorted_token,
                               int32_t* inv_perm, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Same tables for hosts that have no device memory to spare for a workspace and may not allocate any:
+ * engines whose own pool already owns all of HBM, or code that runs where the CUDA runtime must not be
+ * asked for memory.  This entry point has no counterpart in the reference.  The scratch it needs sits in a
+ * fixed array inside the library (about 210 KB per GPU, held until the process exits), so it only accepts
+ * n_tokens*top_k <= 65536 and n_experts <= 512 and answers HQ_ERR_TOO_LARGE beyond that.  It calls no
+ * allocator of any kind.  The first call on a device looks up the array's device address; make that
+ * first call outside any stream capture.  All calls share the one array: calls that run at the same time
+ * on one GPU corrupt each other, so keep them on one stream or order them yourself.  (The tile lists the
+ * expert projections consume stay inside that array; this variant is for callers that only need the
+ * four tables.) */
+int32_t hq_moe_dispatch_build_noalloc(const uint32_t* ids, int64_t n_tokens, int32_t top_k, int32_t n_experts,
+                                      int32_t* expert_bounds, int32_t* sorted_assign, int32_t* sorted_token,
+                                      int32_t* inv_perm, void* stream);
+
 /* ---- expert projection: QuantMethod::gather_forward ------------------------
  * out[t, s, :] = dequant(W[ids[t,s]]) . x_row (+ bias[ids[t,s]]), out [T, k, N].
  * x_layout: HQ_ROWS_PER_TOKEN = [T, K], one row per token shared by its k slots;
