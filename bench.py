@@ -380,13 +380,260 @@ def run_gemv(args):
         dist.destroy_process_group()
 
 
+# ======================================================================================================
+# MoE layer workloads (BASELINE configs 3-5): router -> dispatch tables -> gate/up projection with the gated
+# activation fused -> down projection -> weighted reduce.  Router logits are an input of the step, as they
+# are for the reference's moe_router_topk.
+# ======================================================================================================
+MOE_CFGS = {
+    # name: (format, experts, top_k, hidden, intermediate, tokens, router mode, interleaved gate/up + biases)
+    "moe_q4k": dict(fmt="Q4_K", e=128, k=8, h=2048, i=768, t=4096, router="softmax", inter=False,
+                    label="cfg3_qwen3_30b_a3b_q4k_moe"),
+    "moe_fp8": dict(fmt="FP8", e=256, k=8, h=7168, i=2048, t=4096, router="sigmoid_bias", inter=False,
+                    label="cfg4_deepseek_v3_block_fp8_moe"),
+    "moe_mxfp4": dict(fmt="MXFP4", e=128, k=4, h=2880, i=2880, t=8192, router="topk_softmax", inter=True,
+                      label="cfg5_gpt_oss_120b_mxfp4_moe"),
+}
+
+
+def _q4k_bank(torch, e, n, k, gen, dev):
+    """N(0, 0.02^2) weights -> GGUF Q4_K super-blocks with a plain min/max quantizer, on the device, one expert at a
+    time (benchmark data only): per 32-element sub-block scale = (max - min)/15 and min <= 0, both coded in 6 bits
+    against the super-block's d / dmin."""
+    out = torch.empty((e, n, k // 256, 144), dtype=torch.uint8, device=dev)
+    for ex in range(e):
+        w = torch.randn((n, k // 256, 8, 32), generator=gen, device=dev) * 0.02
+        mn = torch.clamp(w.amin(dim=3), max=0.0)
+        sc = (w.amax(dim=3) - mn) / 15.0
+        d = (sc.amax(dim=2, keepdim=True) / 63.0).to(torch.float16)
+        dmin = ((-mn).amax(dim=2, keepdim=True) / 63.0).to(torch.float16)
+        df, dmf = d.float().clamp_min(1e-12), dmin.float().clamp_min(1e-12)
+        ls = torch.clamp(torch.round(sc / df), 0, 63).to(torch.int32)
+        lm = torch.clamp(torch.round(-mn / dmf), 0, 63).to(torch.int32)
+        d1 = (d.float() * ls).unsqueeze(-1)
+        m1 = (dmin.float() * lm).unsqueeze(-1)
+        q = torch.clamp(torch.round((w + m1) / d1.clamp_min(1e-12)), 0, 15).to(torch.uint8)
+        blk = out[ex]
+        blk[:, :, 0:2] = d.view(torch.uint8).reshape(n, k // 256, 2)
+        blk[:, :, 2:4] = dmin.view(torch.uint8).reshape(n, k // 256, 2)
+        sb = torch.zeros((n, k // 256, 12), dtype=torch.int32, device=dev)
+        sb[:, :, 0:4] = ls[:, :, 0:4] | ((ls[:, :, 4:8] >> 4) << 6)
+        sb[:, :, 4:8] = lm[:, :, 0:4] | ((lm[:, :, 4:8] >> 4) << 6)
+        sb[:, :, 8:12] = (ls[:, :, 4:8] & 0xF) | ((lm[:, :, 4:8] & 0xF) << 4)
+        blk[:, :, 4:16] = sb.to(torch.uint8)
+        blk[:, :, 16:] = (q[:, :, 0::2, :] | (q[:, :, 1::2, :] << 4)).reshape(n, k // 256, 128)
+    return out.reshape(e, n, -1)
+
+
+def _fp8_bank(torch, e, n, k, gen, dev):
+    codes = torch.empty((e, n, k), dtype=torch.uint8, device=dev)
+    scales = torch.empty((e, n // 128, k // 128), dtype=torch.float32, device=dev)
+    for ex in range(e):
+        w = (torch.randn((n // 128, 128, k // 128, 128), generator=gen, device=dev) * 0.02)
+        s = w.abs().amax(dim=(1, 3)) / 448.0
+        q = (w / s[:, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+        codes[ex] = q.view(torch.uint8).reshape(n, k)
+        scales[ex] = s
+    return codes, scales
+
+
+def _mxfp4_bank(torch, e, n, k, gen, dev):
+    blocks = torch.empty((e, n, k // 2), dtype=torch.uint8, device=dev)
+    scales = torch.empty((e, n, k // 32), dtype=torch.uint8, device=dev)
+    for ex in range(e):
+        w = torch.randn((n, k // 32, 32), generator=gen, device=dev) * 0.02
+        amax = w.abs().amax(dim=2)
+        ee = torch.clamp(torch.floor(torch.log2(amax / 6.0)) + 127, 0, 254)
+        ee = torch.where(amax == 0, torch.full_like(ee, 127), ee)
+        v = (w / torch.exp2(ee - 127).unsqueeze(-1)).abs()
+        nib = ((v >= 0.25).int() + (v >= 0.75).int() + (v >= 1.25).int() + (v >= 1.75).int() + (v >= 2.5).int() +
+               (v >= 3.5).int() + (v >= 5.0).int())
+        nib = (nib | ((w < 0).int() << 3)).to(torch.uint8).reshape(n, k)
+        blocks[ex] = nib[:, 0::2] | (nib[:, 1::2] << 4)
+        scales[ex] = ee.to(torch.uint8)
+    return blocks, scales
+
+
+def build_moe_layer(torch, hq, cfg, gen, dev, e_local=None):
+    """Banks for experts [0, e_local) of the layer (all experts when e_local is None)."""
+    e = e_local or cfg["e"]
+    h, i, fmt = cfg["h"], cfg["i"], cfg["fmt"]
+    from engine_b200 import _lib as L
+
+    def bank(n, k, bias):
+        b = (torch.randn((e, n), generator=gen, device=dev) * 0.02).to(torch.bfloat16) if bias else None
+        if fmt == "Q4_K":
+            return hq.GgufMatMul(_q4k_bank(torch, e, n, k, gen, dev), "Q4_K", k, b)
+        if fmt == "FP8":
+            c, s = _fp8_bank(torch, e, n, k, gen, dev)
+            return hq.BlockwiseFP8Linear(c, s, b)
+        bl, sc = _mxfp4_bank(torch, e, n, k, gen, dev)
+        return hq.MXFP4Layer(bl, sc, b)
+
+    down = bank(h, i, cfg["inter"])
+    if cfg["inter"]:
+        return hq.MoEExperts(down, gate_up_proj=bank(2 * i, h, True), act=L.ACT_GPTOSS, limit=7.0, alpha=1.702)
+    return hq.MoEExperts(down, bank(i, h, False), bank(i, h, False), act=L.ACT_SWIGLU)
+
+
+def router_config(hq, cfg):
+    from engine_b200 import _lib as L
+    if cfg["router"] == "softmax":
+        return hq.MoeRouterTopKConfig(cfg["k"], L.SCORE_SOFTMAX, L.WEIGHT_SCORE, True)
+    if cfg["router"] == "sigmoid_bias":
+        return hq.MoeRouterTopKConfig(cfg["k"], L.SCORE_SIGMOID, L.WEIGHT_SCORE, True, 1e-20, 2.5)
+    return hq.MoeRouterTopKConfig(cfg["k"], L.SCORE_RAW, L.WEIGHT_SOFTMAX, False)
+
+
+def moe_flops(cfg, tokens):
+    return 2.0 * tokens * cfg["k"] * 3 * cfg["h"] * cfg["i"]
+
+
+def run_moe(args):
+    import torch
+    import engine_b200 as hq
+    from engine_b200 import _lib as L
+    from engine_b200.ep import ExpertParallelMoE
+
+    cfg = dict(MOE_CFGS[args.workload])
+    if args.tokens:
+        cfg["t"] = args.tokens
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3000 + rank)
+    e, k, h, t_global = cfg["e"], cfg["k"], cfg["h"], cfg["t"]
+    t_local = t_global // world                      # tokens are data-parallel, experts sharded E/world per rank
+    experts = build_moe_layer(torch, hq, cfg, gen, dev, e // world)
+    ep = ExpertParallelMoE(e, experts) if world > 1 else None
+    rcfg = router_config(hq, cfg)
+    sel_bias = (torch.randn(e, generator=gen, device=dev) * 0.01) if cfg["router"] == "sigmoid_bias" else None
+    n_in = 4                                          # rotate inputs; the expert bank itself exceeds L2
+    xs = [torch.randn((t_local, h), generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_in)]
+    logits = [torch.randn((t_local, e), generator=gen, device=dev) for _ in range(n_in)]
+    launches = [0]
+
+    def step(j, x=None, lg=None):
+        x = xs[j % n_in] if x is None else x
+        lg = logits[j % n_in] if lg is None else lg
+        top = hq.moe_router_topk(lg, rcfg, sel_bias)
+        if ep is not None:
+            return ep.forward(x, top.values, top.indices, out_dtype=torch.bfloat16)
+        return experts.forward(x, top.values, top.indices, out_dtype=torch.bfloat16)
+
+    for w in range(max(args.warmup, 3)):
+        out = step(w)
+    torch.cuda.synchronize()
+    status = experts.down.device_status()
+    assert status[0] == 0, f"device status {status}"
+    assert bool(torch.isfinite(out.float()).all())
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s_ in range(args.steps):
+        step(s_)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # dominant kernel: the two expert projections, timed on their own at this rank's share of the work
+    gemm_ms = None
+    if world == 1:
+        top = hq.moe_router_topk(logits[0], rcfg, sel_bias)
+        tables = hq.moe_dispatch_build(top.indices, e)
+        ts = []
+        for r in range(6):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            x = xs[r % n_in]
+            a.record()
+            experts.forward(x, top.values, top.indices, out_dtype=torch.bfloat16, tables=tables, _skip_reduce=True)
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        gemm_ms = statistics.median(ts[1:])
+
+    # end to end with pinned host buffers: activations + logits in, layer output back
+    hx = [x.cpu().pin_memory() for x in xs]
+    hl = [l_.cpu().pin_memory() for l_ in logits]
+    hy = torch.empty((t_local, h), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(j):
+        x = hx[j % n_in].to(dev, non_blocking=True)
+        lg = hl[j % n_in].to(dev, non_blocking=True)
+        hy.copy_(step(j, x, lg), non_blocking=True)
+        torch.cuda.synchronize()
+
+    for j in range(3):
+        e2e_step(j)
+    barrier()
+    t0 = time.perf_counter()
+    for j in range(args.steps):
+        e2e_step(j)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    if dist is not None:
+        tt = torch.tensor([ms_total, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms = float(tt[0]), float(tt[1])
+    value = t_global * args.steps / (ms_total / 1e3)
+    e2e_value = t_global * args.steps / (e2e_ms / 1e3)
+    if rank == 0:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+            os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+        peak_tf = float(peaks.get("bf16_tflops", 1590.0))
+        roof = None
+        if gemm_ms is not None:
+            ach = moe_flops(cfg, t_global) / (gemm_ms / 1e3) / 1e12
+            roof = {"bound": "tensor", "achieved": round(ach, 1), "peak": peak_tf, "unit": "TFLOP/s",
+                    "frac": round(ach / peak_tf, 4), "traffic": None,
+                    "peak_kind": "measured" if peaks else "fallback",
+                    "kernel": "hq::grouped_gemm_kernel (gate/up + down)", "launch_ms_sum": round(gemm_ms, 4),
+                    "note": "f16 operands: fraction of the measured dense 16-bit tensor peak"}
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": cfg["label"], "format": cfg["fmt"], "experts": e, "top_k": k, "hidden": h,
+                       "intermediate": cfg["i"], "tokens_global": t_global, "experts_per_gpu": e // world,
+                       "parallelism": f"ep{world}", "l2": "expert banks exceed L2; activations rotate over 4 buffers"},
+            "roofline": roof,
+            "cpu_baseline": None,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": t_local * (h * 2 + e * 4),
+                    "d2h_bytes_per_step": t_local * h * 2, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": args.steps * 7,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="gemv", choices=["gemv"])
+    ap.add_argument("--workload", default="gemv", choices=["gemv"] + list(MOE_CFGS))
+    ap.add_argument("--tokens", type=int, default=0, help="override the global token count of a MoE workload")
     ap.add_argument("--only", default=None, help="restrict the sweep to one KxN shape, e.g. 4096x128256 "
                     "(profiling aid; the reported line is then not the headline workload)")
     args = ap.parse_args()
@@ -396,6 +643,9 @@ def main():
         SHAPES = [(k, n)]
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload in MOE_CFGS:
+        run_moe(args)
         return
     run_gemv(args)
 

@@ -97,7 +97,7 @@ class MoEExperts:
 
     def forward(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                 shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-                tables: DispatchTables | None = None) -> torch.Tensor:
+                tables: DispatchTables | None = None, _skip_reduce: bool = False) -> torch.Tensor:
         _require_cuda(xs, "xs")
         lead = xs.shape[:-1]
         x = xs.reshape(-1, xs.shape[-1]).contiguous()
@@ -122,5 +122,7 @@ class MoEExperts:
                                               _ptr(tables.sorted_token), _ptr(tables.workspace), _ptr(y),
                                               dt_code(y.dtype), L.ROWS_SORTED, _ptr(status), _stream()),
                 "hq_moe_gather_forward(down)")
+        if _skip_reduce:       # measurement aid: the two projections only, output left expert-sorted
+            return y
         out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype or xs.dtype, tables.inv_perm, shared_out)
         return out.reshape(*lead, self.down.n)
