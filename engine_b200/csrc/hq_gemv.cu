@@ -24,7 +24,16 @@ constexpr int kConsumerWarps = 15;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kGemvThreads = kConsumerThreads + 32;
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kXK = 4096;  // activation columns staged in shared memory at a time (2048 for f32 input)
+
+// shared-memory plan of one launch (computed on the host)
+struct GemvLayout {
+  int nstage;       // ring stages
+  int xs_rows;      // activation rows staged (rows beyond read as zero)
+  int xk;           // activation columns per epoch
+  int xk_sub;       // columns per register prefetch
+  int x_bytes;
+  int off_x, off_xsum, off_red, off_bar, total;
+};
 
 // ---- per-format geometry ----------------------------------------------------
 template <int FMT>
@@ -68,22 +77,15 @@ __host__ __device__ constexpr int seg_pitch(int seg) {
   return ((seg / 4) % 8 == 4) ? seg : seg + 16;
 }
 
-template <int FMT, int KC, int NSTAGE>
-struct GemvSmem {
+template <int FMT, int KC>
+struct GemvStage {
   static constexpr int RT = 16;
   static constexpr int SEG = FmtTraits<FMT>::seg_bytes(KC);
   static constexpr int PITCH = seg_pitch(SEG);
   static constexpr int STAGE_BYTES = RT * PITCH;
-  static constexpr int XP = kXK + 16;  // f16 elements per activation row in shared memory
-  static constexpr int OFF_X = NSTAGE * STAGE_BYTES;
-  static constexpr int X_BYTES = 8 * XP * 2;
-  static constexpr int OFF_XSUM = OFF_X + X_BYTES;
-  static constexpr int XSUM_BYTES = FmtTraits<FMT>::kNeedXsum ? (kXK / 32) * 8 * 4 : 0;
-  static constexpr int OFF_RED = OFF_XSUM + XSUM_BYTES;
-  static constexpr int RED_BYTES = 2 * kConsumerWarps * 32 * 4 * 4 * 2;  // two buffers x two banks
-  static constexpr int OFF_BAR = OFF_RED + RED_BYTES;
-  static constexpr int TOTAL = OFF_BAR + (2 * NSTAGE + 4) * 8 + 16;
 };
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 227 * 1024;
 
 // ---- activation staging -----------------------------------------------------
 // The (<= 8) activation rows of a work item are staged as f16 in shared memory, kXK columns at a time, in
@@ -113,9 +115,9 @@ __device__ __forceinline__ void x_prefetch(XPrefetch& pf, const GemvParams& p, i
   }
 }
 
-template <bool PERM, bool XSUM, int XP>
+template <bool PERM, bool XSUM>
 __device__ __forceinline__ void x_commit(const XPrefetch& pf, const GemvParams& p, int nrows, int k_len, int tid,
-                                         __half* xs, float* xsum, float xsum_scale) {
+                                         __half* xs, int XP, float* xsum, float xsum_scale) {
   const int esz = dtype_size(p.x_dtype);
   const int epg = 16 / esz;
   const int gpr = k_len / epg;
@@ -196,7 +198,7 @@ struct Q8Regs {
   uint2 x0, x1, xs;
 };
 __device__ __forceinline__ void q8_load(Q8Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, uint32_t xsum_t,
-                                        int unit, int t) {
+                                        int unit, int t, bool xv) {
   const uint32_t off = 34u * unit;
   const uint32_t q = off + 2u + 4u * t;
   const uint32_t al = q & ~3u;
@@ -207,8 +209,8 @@ __device__ __forceinline__ void q8_load(Q8Regs& r, uint32_t rowA, uint32_t rowB,
   r.a[0] = lds32<0>(pa); r.a[1] = lds32<4>(pa); r.a[2] = lds32<16>(pa); r.a[3] = lds32<20>(pa);
   r.b[0] = lds32<0>(pb); r.b[1] = lds32<4>(pb); r.b[2] = lds32<16>(pb); r.b[3] = lds32<20>(pb);
   const uint32_t xo = xs_g + (32u * unit + 4u * t) * 2u;
-  r.x0 = lds64<0>(xo);
-  r.x1 = lds64<32>(xo);
+  r.x0 = xv ? lds64<0>(xo) : make_uint2(0u, 0u);
+  r.x1 = xv ? lds64<32>(xo) : make_uint2(0u, 0u);
   r.xs = lds64(xsum_t + 32u * unit);
 }
 // bytes 1 and 3 of v into the low bytes of the two halves: (v >> 8) & 0x00FF00FF in one permute
@@ -239,7 +241,7 @@ struct Q4Regs {
   int c;
 };
 __device__ __forceinline__ void q4_load(Q4Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, uint32_t xsum_t,
-                                        int unit, int t) {
+                                        int unit, int t, bool xv) {
   const int sb = unit >> 2, c = unit & 3;
   r.c = c;
   const uint32_t sbA = rowA + 144u * sb, sbB = rowB + 144u * sb;
@@ -252,7 +254,9 @@ __device__ __forceinline__ void q4_load(Q4Regs& r, uint32_t rowA, uint32_t rowB,
   r.a0 = lds32<0>(sbA + qo); r.a1 = lds32<16>(sbA + qo);
   r.b0 = lds32<0>(sbB + qo); r.b1 = lds32<16>(sbB + qo);
   const uint32_t xo = xs_g + (256u * sb + 64u * c + 4u * t) * 2u;
-  r.x[0] = lds64<0>(xo); r.x[1] = lds64<32>(xo); r.x[2] = lds64<64>(xo); r.x[3] = lds64<96>(xo);
+  const uint2 z = make_uint2(0u, 0u);
+  r.x[0] = xv ? lds64<0>(xo) : z; r.x[1] = xv ? lds64<32>(xo) : z;
+  r.x[2] = xv ? lds64<64>(xo) : z; r.x[3] = xv ? lds64<96>(xo) : z;
   const uint32_t so = xsum_t + 32u * (8u * sb + 2u * c);
   r.xs[0] = lds64<0>(so);
   r.xs[1] = lds64<32>(so);
@@ -313,13 +317,14 @@ struct B32Regs {
   uint32_t a0, a1, b0, b1;
   uint2 x0, x1;
 };
-__device__ __forceinline__ void fp8_load(B32Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, int unit, int t) {
+__device__ __forceinline__ void fp8_load(B32Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, int unit, int t,
+                                         bool xv) {
   const uint32_t qo = 32u * unit + 4u * t;
   r.a0 = lds32<0>(rowA + qo); r.a1 = lds32<16>(rowA + qo);
   r.b0 = lds32<0>(rowB + qo); r.b1 = lds32<16>(rowB + qo);
   const uint32_t xo = xs_g + (32u * unit + 4u * t) * 2u;
-  r.x0 = lds64<0>(xo);
-  r.x1 = lds64<32>(xo);
+  r.x0 = xv ? lds64<0>(xo) : make_uint2(0u, 0u);
+  r.x1 = xv ? lds64<32>(xo) : make_uint2(0u, 0u);
 }
 __device__ __forceinline__ void fp8_compute(float (&acc)[4], const B32Regs& r, float scale) {
   float blk[4];
@@ -343,13 +348,14 @@ __device__ __forceinline__ uint32_t e2m1_byte_to_f16x2(uint32_t byte) {
   return hl | (hh << 16);
 }
 // MXFP4: one 32-element block = 16 bytes; lane t owns bytes 4t..4t+3 (elements 8t..8t+7).
-__device__ __forceinline__ void mx_load(B32Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, int unit, int t) {
+__device__ __forceinline__ void mx_load(B32Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, int unit, int t,
+                                        bool xv) {
   const uint32_t qo = 16u * unit + 4u * t;
   r.a0 = lds32(rowA + qo);
   r.b0 = lds32(rowB + qo);
   const uint32_t xo = xs_g + (32u * unit + 8u * t) * 2u;
-  r.x0 = lds64<0>(xo);
-  r.x1 = lds64<8>(xo);
+  r.x0 = xv ? lds64<0>(xo) : make_uint2(0u, 0u);
+  r.x1 = xv ? lds64<8>(xo) : make_uint2(0u, 0u);
 }
 __device__ __forceinline__ void mx_compute(float (&acc)[4], const B32Regs& r, float sA, float sB) {
   float blk[4];
@@ -401,12 +407,13 @@ __device__ __forceinline__ WorkItem get_item(const GemvParams& p, int w, int n_r
 
 // Persistent: each CTA walks work items (activation-row group y, 16-row output tile) with a stride of
 // gridDim.x; the producer warp keeps the weight ring full across item boundaries.
-template <int FMT, int KC, int NSTAGE>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
-  using L = GemvSmem<FMT, KC, NSTAGE>;
+template <int FMT, int KC>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p, const GemvLayout lay) {
+  using L = GemvStage<FMT, KC>;
   using F = FmtTraits<FMT>;
   constexpr int WK = kConsumerWarps;
   constexpr int RT = L::RT;
+  const int NSTAGE = lay.nstage;
   // per-block activation sums: Q8_0 wants them as the MMA's C operand (-128 * 2^-24 * sum), Q4_K plain
   constexpr float kXsumScale = FMT == HQ_FMT_Q8_0 ? -7.62939453125e-06f : 1.f;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -415,12 +422,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   const int n_y = p.tiles != nullptr ? p.tile_count[0] : (p.m + 7) / 8;
   const int total = n_y * n_rt;
   if ((int)blockIdx.x >= total) return;
-  const int xk_sub = p.x_dtype == HQ_DT_F32 ? kXK / 2 : kXK;   // columns one register prefetch covers
+  const int kXK = lay.xk;          // activation columns staged per epoch (whole chunks)
+  const int xk_sub = lay.xk_sub;   // columns one register prefetch covers
   const int n_super = (p.k + kXK - 1) / kXK;
 
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-  uint64_t* empty = full + NSTAGE;
-  uint64_t* red_full = empty + NSTAGE;   // [2] partial sums of an item are all written
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar);
+  uint64_t* empty = full + kMaxStages;
+  uint64_t* red_full = empty + kMaxStages;   // [2] partial sums of an item are all written
   uint64_t* red_free = red_full + 2;     // [2] ... and have been consumed
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -437,8 +445,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     fence_barrier_init();
   }
   // zero the activation buffer once: rows beyond an item's row count must read as zero
-  for (int i = tid; i < L::X_BYTES / 16; i += kGemvThreads)
-    reinterpret_cast<uint4*>(smem + L::OFF_X)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < lay.x_bytes / 16; i += kGemvThreads)
+    reinterpret_cast<uint4*>(smem + lay.off_x)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
 
   const int64_t row_bytes = F::row_bytes(p.k);
@@ -483,10 +491,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   // ================= consumer warps ============================================
   const int wk = warp;
   const int g = lane >> 2, t = lane & 3;
-  __half* xs = reinterpret_cast<__half*>(smem + L::OFF_X);
-  float* xsum = reinterpret_cast<float*>(smem + L::OFF_XSUM);
-  float* red = reinterpret_cast<float*>(smem + L::OFF_RED);   // [2 buffers][2 banks][warps][4][32]
-  const uint32_t xs_g = smem_u32(xs) + (uint32_t)g * L::XP * 2u;
+  __half* xs = reinterpret_cast<__half*>(smem + lay.off_x);
+  float* xsum = reinterpret_cast<float*>(smem + lay.off_xsum);
+  float* red = reinterpret_cast<float*>(smem + lay.off_red);   // [2 buffers][banks][warps][4][32]
+  const int XP = lay.xk + 16;                 // f16 elements per staged activation row
+  const bool xv = g < lay.xs_rows;            // activation rows beyond the staged ones are zero
+  const uint32_t xs_g = smem_u32(xs) + (uint32_t)(xv ? g : 0) * XP * 2u;
   const uint32_t xsum_t = smem_u32(xsum) + 8u * t;
 
   XPrefetch pf;
@@ -515,14 +525,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         if (!pf_valid) x_prefetch(pf, p, wi.row0, wi.nrows, k_base, min(xk_sub, k_len), tid);
         named_bar_sync(1, kConsumerThreads);       // everyone is done reading the previous epoch
         // rows left over from an earlier item with more rows than this one must read as zero
-        for (int i = tid; i < (staged_rows - wi.nrows) * (L::XP / 8); i += kConsumerThreads)
-          reinterpret_cast<uint4*>(xs + wi.nrows * L::XP)[i] = make_uint4(0, 0, 0, 0);
+        for (int i = tid; i < (staged_rows - wi.nrows) * (XP / 8); i += kConsumerThreads)
+          reinterpret_cast<uint4*>(xs + wi.nrows * XP)[i] = make_uint4(0, 0, 0, 0);
         staged_rows = wi.nrows;
-        x_commit<F::kPermX, F::kNeedXsum, L::XP>(pf, p, wi.nrows, min(xk_sub, k_len), tid, xs, xsum, kXsumScale);
+        x_commit<F::kPermX, F::kNeedXsum>(pf, p, wi.nrows, min(xk_sub, k_len), tid, xs, XP, xsum, kXsumScale);
         for (int sub = xk_sub; sub < k_len; sub += xk_sub) {   // f32 input: second half, fetched now
           x_prefetch(pf, p, wi.row0, wi.nrows, k_base + sub, min(xk_sub, k_len - sub), tid);
-          x_commit<F::kPermX, F::kNeedXsum, L::XP>(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xs + sub,
-                                                   xsum + (sub / 32) * 8, kXsumScale);
+          x_commit<F::kPermX, F::kNeedXsum>(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xs + sub, XP,
+                                            xsum + (sub / 32) * 8, kXsumScale);
         }
         staged_y = wi.y;
         pf_valid = false;
@@ -563,14 +573,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             int u = wk;
             for (; u + WK < nunits; u += 2 * WK) {
               Q8Regs r0, r1;
-              q8_load(r0, rowA, rowB, xs_c, xsum_c, u, t);
-              q8_load(r1, rowA, rowB, xs_c, xsum_c, u + WK, t);
+              q8_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
+              q8_load(r1, rowA, rowB, xs_c, xsum_c, u + WK, t, xv);
               q8_compute(a, r0);
               q8_compute(a, r1);
             }
             if (u < nunits) {
               Q8Regs r0;
-              q8_load(r0, rowA, rowB, xs_c, xsum_c, u, t);
+              q8_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
               q8_compute(a, r0);
             }
           } else if (FMT == HQ_FMT_Q4_K) {
@@ -578,14 +588,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             int u = wk;
             for (; u + WK < nunits; u += 2 * WK) {
               Q4Regs r0, r1;
-              q4_load(r0, rowA, rowB, xs_c, xsum_c, u, t);
-              q4_load(r1, rowA, rowB, xs_c, xsum_c, u + WK, t);
+              q4_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
+              q4_load(r1, rowA, rowB, xs_c, xsum_c, u + WK, t, xv);
               q4_compute(a, r0);
               q4_compute(a, r1);
             }
             if (u < nunits) {
               Q4Regs r0;
-              q4_load(r0, rowA, rowB, xs_c, xsum_c, u, t);
+              q4_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
               q4_compute(a, r0);
             }
           } else if (FMT == HQ_FMT_FP8_BLOCK) {
@@ -596,8 +606,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             int u = wk;
             for (; u + WK < nunits; u += 2 * WK) {
               B32Regs r0, r1;
-              fp8_load(r0, rowA, rowB, xs_c, u, t);
-              fp8_load(r1, rowA, rowB, xs_c, u + WK, t);
+              fp8_load(r0, rowA, rowB, xs_c, u, t, xv);
+              fp8_load(r1, rowA, rowB, xs_c, u + WK, t, xv);
               const float s0 = __ldg(fsc + (chunk * KC + 32 * u) / 128);
               const float s1 = __ldg(fsc + (chunk * KC + 32 * (u + WK)) / 128);
               fp8_compute(a, r0, s0);
@@ -605,7 +615,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             }
             if (u < nunits) {
               B32Regs r0;
-              fp8_load(r0, rowA, rowB, xs_c, u, t);
+              fp8_load(r0, rowA, rowB, xs_c, u, t, xv);
               fp8_compute(a, r0, __ldg(fsc + (chunk * KC + 32 * u) / 128));
             }
           } else {
@@ -617,7 +627,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             const uint8_t* mB = msc + (int64_t)min(wi.n0 + g + 8, p.n - 1) * kb_row;
             for (int u = wk; u < nunits; u += WK) {
               B32Regs r0;
-              mx_load(r0, rowA, rowB, xs_c, u, t);
+              mx_load(r0, rowA, rowB, xs_c, u, t, xv);
               // 2^(e-127) with the reference's bit trick (e = 0 decodes to 0), times 2^14 for the nibble encoding
               const float sA = __uint_as_float((uint32_t)__ldg(mA + u) << 23) * 16384.f;
               const float sB = __uint_as_float((uint32_t)__ldg(mB + u) << 23) * 16384.f;
@@ -632,7 +642,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 
     // ---- hand the K-split partials to one warp (rotating), which adds them in warp order ------------
     const int rb = item & 1;
-    float* rbuf = red + rb * (2 * kConsumerWarps * 4 * 32);
+    float* rbuf = red + rb * (p.n_banks * kConsumerWarps * 4 * 32);
     if (item >= 2) {
       if (!mbar_wait(&red_free[rb], ((item >> 1) - 1) & 1, spin)) {
         if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 300 + rb);
@@ -641,8 +651,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     }
 #pragma unroll
     for (int b = 0; b < 2; ++b)
+      if (b < p.n_banks) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) rbuf[((b * kConsumerWarps + warp) * 4 + i) * 32 + lane] = acc[b][i];
+        for (int i = 0; i < 4; ++i) rbuf[((b * kConsumerWarps + warp) * 4 + i) * 32 + lane] = acc[b][i];
+      }
     __syncwarp();
     if (lane == 0) mbar_arrive(&red_full[rb]);
     if (warp == (item % kConsumerWarps)) {
@@ -652,12 +664,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
       }
 #pragma unroll
       for (int b = 0; b < 2; ++b)
+        if (b < p.n_banks) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float s = 0.f;
+          for (int i = 0; i < 4; ++i) {
+            float s = 0.f;
 #pragma unroll
-          for (int j = 0; j < kConsumerWarps; ++j) s += rbuf[((b * kConsumerWarps + j) * 4 + i) * 32 + lane];
-          acc[b][i] = s;
+            for (int j = 0; j < kConsumerWarps; ++j) s += rbuf[((b * kConsumerWarps + j) * 4 + i) * 32 + lane];
+            acc[b][i] = s;
+          }
         }
       __syncwarp();
       if (lane == 0) mbar_arrive(&red_free[rb]);
@@ -721,36 +735,65 @@ static int sm_count() {
   return cached[dev];
 }
 
-template <int FMT, int KC, int NSTAGE>
-static int32_t launch_cfg(const GemvParams& p, int n_y_max, cudaStream_t stream) {
-  using L = GemvSmem<FMT, KC, NSTAGE>;
-  static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
+template <int FMT, int KC>
+static int32_t launch_cfg(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
+  using L = GemvStage<FMT, KC>;
+  using F = FmtTraits<FMT>;
   static_assert((L::PITCH / 4) % 8 == 4, "row pitch must spread banks");
-  static_assert(kXK % KC == 0, "activation epochs must hold whole chunks");
-  static_assert(FmtTraits<FMT>::seg_bytes(KC) >= 2048, "bulk copies below 2 KiB cannot saturate HBM");
-  auto kern = gemv_kernel<FMT, KC, NSTAGE>;
+  static_assert(F::seg_bytes(KC) >= 2048, "bulk copies below 2 KiB cannot saturate HBM");
+  // Shared-memory plan: stage as many activation columns as leave at least four ring stages (the whole K when
+  // it fits -- then a persistent CTA converts its activations once), give every remaining byte to the ring.
+  GemvLayout lay{};
+  const int esz = dtype_size(p.x_dtype);
+  const int k_round = (p.k + KC - 1) / KC * KC;
+  const int candidates[3] = {k_round, 8192 < k_round ? (8192 / KC * KC) : k_round, 4096 < k_round ? 4096 : k_round};
+  for (int c = 0; c < 3; ++c) {
+    lay.xk = candidates[c];
+    lay.xs_rows = max_rows;
+    lay.x_bytes = lay.xs_rows * (lay.xk + 16) * 2;
+    const int xsum_bytes = F::kNeedXsum ? (lay.xk / 32) * 8 * 4 : 0;
+    const int red_bytes = 2 * p.n_banks * kConsumerWarps * 4 * 32 * 4;
+    const int bar_bytes = (2 * kMaxStages + 4) * 8 + 16;
+    const int fixed = lay.x_bytes + xsum_bytes + red_bytes + bar_bytes;
+    int nst = (kSmemBudget - fixed) / L::STAGE_BYTES;
+    if (nst > kMaxStages) nst = kMaxStages;
+    lay.nstage = nst;
+    lay.off_x = nst * L::STAGE_BYTES;
+    lay.off_xsum = lay.off_x + lay.x_bytes;
+    lay.off_red = lay.off_xsum + xsum_bytes;
+    lay.off_bar = lay.off_red + red_bytes;
+    lay.total = lay.off_bar + bar_bytes;
+    if (nst >= 4) break;
+  }
+  if (lay.nstage < 2) return HQ_ERR_SHAPE;
+  // columns one register prefetch can hold (kMaxXGroups groups of 16 bytes per thread), in whole 256-column steps
+  int sub = (kMaxXGroups * kConsumerThreads * 16) / (lay.xs_rows * esz) / 256 * 256;
+  lay.xk_sub = sub < lay.xk ? sub : lay.xk;
+  auto kern = gemv_kernel<FMT, KC>;
   static bool attr_done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
   if (dev < 64 && !attr_done[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess)
       return HQ_ERR_CUDA;
     attr_done[dev] = true;
   }
   const int64_t items = (int64_t)n_y_max * ((p.n + L::RT - 1) / L::RT);
   const int64_t grid = items < sm_count() ? items : sm_count();
   if (grid <= 0) return HQ_OK;
-  kern<<<(unsigned)grid, kGemvThreads, L::TOTAL, stream>>>(p);
+  kern<<<(unsigned)grid, kGemvThreads, lay.total, stream>>>(p, lay);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
 int32_t launch_gemv(const GemvParams& p, int n_y_max, cudaStream_t stream) {
+  // most activation rows any work item of this launch can have
+  const int max_rows = p.tiles != nullptr ? 8 : (p.m < 8 ? p.m : 8);
   // chunk sizes keep every bulk copy (one row segment) at 2 KiB or more
   switch (p.format) {
-    case HQ_FMT_Q8_0: return launch_cfg<HQ_FMT_Q8_0, 2048, 3>(p, n_y_max, stream);
-    case HQ_FMT_Q4_K: return launch_cfg<HQ_FMT_Q4_K, 4096, 3>(p, n_y_max, stream);
-    case HQ_FMT_FP8_BLOCK: return launch_cfg<HQ_FMT_FP8_BLOCK, 2048, 4>(p, n_y_max, stream);
-    case HQ_FMT_MXFP4: return launch_cfg<HQ_FMT_MXFP4, 4096, 4>(p, n_y_max, stream);
+    case HQ_FMT_Q8_0: return launch_cfg<HQ_FMT_Q8_0, 2048>(p, n_y_max, max_rows, stream);
+    case HQ_FMT_Q4_K: return launch_cfg<HQ_FMT_Q4_K, 4096>(p, n_y_max, max_rows, stream);
+    case HQ_FMT_FP8_BLOCK: return launch_cfg<HQ_FMT_FP8_BLOCK, 2048>(p, n_y_max, max_rows, stream);
+    case HQ_FMT_MXFP4: return launch_cfg<HQ_FMT_MXFP4, 4096>(p, n_y_max, max_rows, stream);
     default: return HQ_ERR_FORMAT;
   }
 }

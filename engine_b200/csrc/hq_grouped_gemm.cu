@@ -27,7 +27,6 @@ namespace hq {
 
 constexpr int kGgThreads = 13 * 32;
 constexpr int kGgProducerWarps = 8;
-constexpr int kGgProducerThreads = kGgProducerWarps * 32;
 constexpr int kTileM = 128;   // features per tile (TMEM lanes)
 constexpr int kTileN = 128;   // tokens per tile (TMEM columns)
 constexpr int kTileK = 64;    // k per stage: 64 f16 = one 128-byte swizzle row
@@ -86,6 +85,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return d;
 }
 // kind::f16 instruction descriptor: f32 accumulate, f16 x f16, both K-major, M = 128, N = 128
+// (both operands must have the same 16-bit format: f16 weights beside bf16 activations in one instruction
+// raise an illegal-instruction error on B200, so bf16 activations are converted while their tile is written)
 __device__ __forceinline__ uint32_t make_idesc_f16() {
   return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
 }
@@ -103,57 +104,79 @@ struct GgSmem {
   static constexpr int TOTAL = OFF_BAR + (2 * NSTAGE + 4) * 8 + 16 + 1024;  // + alignment slack
 };
 
-// ---- weight tile expansion: 32 consecutive k of one row -> 32 f16 (4 chunks of 16 bytes) ----
-// Natural k order.  `out` receives 16 packed f16x2 words.
-__device__ __forceinline__ void expand_q4_k(const uint8_t* row_base, int k0, int half, uint32_t (&out)[16]) {
-  // super-block header {d, dmin, 12 scale bytes} and the 32 nibble bytes shared by sub-blocks 2c, 2c+1
-  const int sb = k0 >> 8, c = (k0 & 255) >> 6;
-  const uint8_t* blk = row_base + 144 * sb;
-  const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-  const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * c));
-  const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * c));
+// ---- operand production, split in two halves so the global loads of the next stage are in flight while
+// this stage is converted: fetch_* issues the loads into registers, emit_* converts and writes shared memory.
+// A thread owns 32 consecutive k of one operand row per stage (natural k order, 4 chunks of 16 bytes).
+struct RawA {
+  uint4 a, b, c;      // Q4_K: header, nibble bytes 0-15, 16-31; FP8: codes 0-15, 16-31; MXFP4: 16 nibble bytes
+  uint32_t aux;       // FP8: relative block scale (f32 bits); MXFP4: e8m0 byte
+};
+struct RawB {
+  uint4 v[4];         // 32 x 16-bit activations
+};
+
+template <int FMT>
+__device__ __forceinline__ void fetch_a(RawA& r, const uint8_t* row_base, const uint8_t* scale_row, const float* rel,
+                                        int k0, int half) {
+  if (FMT == HQ_FMT_Q4_K) {
+    const int sb = k0 >> 8, c = (k0 & 255) >> 6;
+    const uint8_t* blk = row_base + 144 * sb;
+    r.a = __ldg(reinterpret_cast<const uint4*>(blk));
+    r.b = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * c));
+    r.c = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * c));
+  } else if (FMT == HQ_FMT_FP8_BLOCK) {
+    const uint4* src = reinterpret_cast<const uint4*>(row_base + k0 + 32 * half);
+    r.a = __ldg(src);
+    r.b = __ldg(src + 1);
+    r.aux = __float_as_uint(__ldg(rel + k0 / 128));
+  } else {
+    const int blk = (k0 >> 5) + half;
+    r.a = __ldg(reinterpret_cast<const uint4*>(row_base + 16 * blk));
+    r.aux = __ldg(scale_row + blk);
+  }
+}
+
+// Q4_K sub-block of 32: w = code * d1 - m1 with d1 = d * sc, m1 = dmin * m.  Codes are extracted as the f16
+// pair (1024 + e0, 1024 + e1) with one permute (bytes {code, 0x64}); the offset and the min go into one
+// constant C = -(m1 + 1024 * d1).  d1 and C are each split into a leading f16 and its remainder, so
+// w = fma(p, dh, Ch) + fma(p, dl, Cl) carries only the final roundings of weight-sized quantities.
+__device__ __forceinline__ void emit_q4_k(const RawA& r, int k0, int half, uint32_t (&out)[16]) {
+  const int c = (k0 & 255) >> 6;
   const int j = 2 * c + half;
   uint32_t s, m;
   if (j < 4) {
-    s = (hdr.y >> (8 * j)) & 63u;
-    m = (hdr.z >> (8 * j)) & 63u;
+    s = (r.a.y >> (8 * j)) & 63u;
+    m = (r.a.z >> (8 * j)) & 63u;
   } else {
     const int jj = j - 4;
-    s = ((hdr.w >> (8 * jj)) & 0xFu) | (((hdr.y >> (8 * jj + 6)) & 3u) << 4);
-    m = ((hdr.w >> (8 * jj + 4)) & 0xFu) | (((hdr.z >> (8 * jj + 6)) & 3u) << 4);
+    s = ((r.a.w >> (8 * jj)) & 0xFu) | (((r.a.y >> (8 * jj + 6)) & 3u) << 4);
+    m = ((r.a.w >> (8 * jj + 4)) & 0xFu) | (((r.a.z >> (8 * jj + 6)) & 3u) << 4);
   }
-  const float d1 = half_bits_to_float(hdr.x) * (float)s;
-  const float m1 = half_bits_to_float(hdr.x >> 16) * (float)m;
-  // f16 arithmetic with the scale and the min split into a leading f16 and its remainder, so the only
-  // rounding that matters is the final one of each weight: w = code * (dh + dl) - (mh + ml)
-  const __half dh = __float2half_rn(d1), mh = __float2half_rn(m1);
-  const __half2 dh2 = __half2half2(dh), nmh2 = __half2half2(__hneg(mh));
+  const float d1 = half_bits_to_float(r.a.x) * (float)s;
+  const float cc = -fmaf(1024.f, d1, half_bits_to_float(r.a.x >> 16) * (float)m);
+  const __half dh = __float2half_rn(d1), ch = __float2half_rn(cc);
+  const __half2 dh2 = __half2half2(dh), ch2 = __half2half2(ch);
   const __half2 dl2 = __float2half2_rn(d1 - __half2float(dh));
-  const __half2 nml2 = __float2half2_rn(__half2float(mh) - m1);
-  const __half2 k1024 = __float2half2_rn(1024.f);
-  const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+  const __half2 cl2 = __float2half2_rn(cc - __half2float(ch));
+  const uint32_t qw[8] = {r.b.x, r.b.y, r.b.z, r.b.w, r.c.x, r.c.y, r.c.z, r.c.w};
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const uint32_t v = half ? (qw[i] >> 4) : qw[i];
-    uint32_t p02 = (v & 0x000F000Fu) | 0x64006400u;          // 1024 + code of bytes 0 and 2
-    uint32_t p13 = ((v >> 8) & 0x000F000Fu) | 0x64006400u;   // bytes 1 and 3
-    const __half2 c02 = __hsub2(*reinterpret_cast<__half2*>(&p02), k1024);
-    const __half2 c13 = __hsub2(*reinterpret_cast<__half2*>(&p13), k1024);
-    __half2 h02 = __hadd2(__hfma2(c02, dh2, nmh2), __hfma2(c02, dl2, nml2));
-    __half2 h13 = __hadd2(__hfma2(c13, dh2, nmh2), __hfma2(c13, dl2, nml2));
-    const uint32_t a = *reinterpret_cast<uint32_t*>(&h02), b = *reinterpret_cast<uint32_t*>(&h13);
-    out[2 * i] = __byte_perm(a, b, 0x5410);       // elements 0, 1
-    out[2 * i + 1] = __byte_perm(a, b, 0x7632);   // elements 2, 3
+    const uint32_t vm = (half ? (qw[i] >> 4) : qw[i]) & 0x0F0F0F0Fu;
+    uint32_t p01 = __byte_perm(vm, 0x64646464u, 0x4140);   // f16 pair (1024 + e0, 1024 + e1)
+    uint32_t p23 = __byte_perm(vm, 0x64646464u, 0x4342);
+    const __half2 h01 = *reinterpret_cast<__half2*>(&p01), h23 = *reinterpret_cast<__half2*>(&p23);
+    __half2 w01 = __hadd2(__hfma2(h01, dh2, ch2), __hfma2(h01, dl2, cl2));
+    __half2 w23 = __hadd2(__hfma2(h23, dh2, ch2), __hfma2(h23, dl2, cl2));
+    out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
+    out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
   }
 }
 
 // e4m3 -> f16 is exact; the block's scale relative to the largest scale of its 128-row block (<= 1) is folded
 // in here, the largest scale itself multiplies the accumulator in the epilogue.
-__device__ __forceinline__ void expand_fp8(const uint8_t* row_base, int k0, int half, float rel, uint32_t (&out)[16]) {
-  const uint4* src = reinterpret_cast<const uint4*>(row_base + k0 + 32 * half);
-  const uint4 a = __ldg(src), b = __ldg(src + 1);
-  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-  const __half2 r2 = __float2half2_rn(rel);
+__device__ __forceinline__ void emit_fp8(const RawA& r, uint32_t (&out)[16]) {
+  const uint32_t w[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
+  const __half2 r2 = __float2half2_rn(__uint_as_float(r.aux));
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     uint32_t lo, hi;
@@ -175,17 +198,14 @@ __device__ __forceinline__ void expand_fp8(const uint8_t* row_base, int k0, int 
 // MXFP4 block of 32: e2m1 pairs -> f16x2 (hardware conversion, low nibble = even element = low half), times
 // 2^(e-127) as an exact f16 power of two.  e = 0 decodes to a zero scale (the reference's table builds the
 // scale from the bits e << 23); scales outside the f16 exponent range are reported by the caller.
-__device__ __forceinline__ bool expand_mxfp4(const uint8_t* row_base, const uint8_t* scale_row, int k0, int half,
-                                             uint32_t (&out)[16]) {
-  const int blk = (k0 >> 5) + half;
-  const uint4 q = __ldg(reinterpret_cast<const uint4*>(row_base + 16 * blk));
-  const uint32_t e = __ldg(scale_row + blk);
+__device__ __forceinline__ bool emit_mxfp4(const RawA& r, uint32_t (&out)[16]) {
+  const uint32_t e = r.aux;
   const bool in_range = (e == 0) || (e >= 113 && e <= 140);   // 2^-14 .. 2^13: products stay finite in f16
   const uint32_t ef = (e >= 113 && e <= 140) ? (e - 112) : 0u;  // f16 exponent field of 2^(e-127)
   const uint32_t sc16 = ef << 10;
   const uint32_t sc2 = sc16 | (sc16 << 16);
   const __half2 s2 = *reinterpret_cast<const __half2*>(&sc2);
-  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     uint32_t h[4];
@@ -208,34 +228,30 @@ __device__ __forceinline__ bool expand_mxfp4(const uint8_t* row_base, const uint
   return in_range;
 }
 
-// 32 activation values of one row -> f16 (natural order), optionally scaled
-__device__ __forceinline__ void load_x32(const void* x, int dtype, int64_t elem_off, float scale, uint32_t (&out)[16]) {
-  if (dtype == HQ_DT_F32) {
-    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + elem_off);
+__device__ __forceinline__ void fetch_b(RawB& r, const void* x, int64_t elem_off) {
+  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + elem_off);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float4 f = __ldg(src + i);
-      out[2 * i] = pack_half2(f.x * scale, f.y * scale);
-      out[2 * i + 1] = pack_half2(f.z * scale, f.w * scale);
-    }
-  } else {
-    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + elem_off);
+  for (int i = 0; i < 4; ++i) r.v[i] = __ldg(src + i);
+}
+// 16-bit activations -> f16 words; bf16 goes through f32 (exact in the f16 normal range), f16 is copied
+__device__ __forceinline__ void emit_b(const RawB& r, bool convert_bf16, uint32_t (&out)[16]) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 r = __ldg(src + i);
-      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t w[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (dtype == HQ_DT_BF16) {
-          out[4 * i + j] = pack_half2(__uint_as_float(w[j] << 16) * scale, __uint_as_float(w[j] & 0xFFFF0000u) * scale);
-        } else if (scale != 1.f) {
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-          out[4 * i + j] = pack_half2(f.x * scale, f.y * scale);
-        } else {
-          out[4 * i + j] = w[j];
-        }
-      }
-    }
+    for (int j = 0; j < 4; ++j)
+      out[4 * i + j] = convert_bf16 ? pack_half2(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xFFFF0000u))
+                                    : w[j];
+  }
+}
+// f32 activations: loaded and converted in one go (only the dense path sees them)
+__device__ __forceinline__ void load_x32_f32(const void* x, int64_t elem_off, uint32_t (&out)[16]) {
+  const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + elem_off);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 f = __ldg(src + i);
+    out[2 * i] = pack_half2(f.x, f.y);
+    out[2 * i + 1] = pack_half2(f.z, f.w);
   }
 }
 
@@ -417,73 +433,120 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
     // =========================== producers ========================================
     const int ptid = tid - 5 * 32;            // 0..255
     const int r = ptid >> 1, half = ptid & 1; // operand row and which 32-k half of the stage
+    const bool x_f32 = p.x_dtype == HQ_DT_F32;
+    const bool x_conv = p.x_dtype == HQ_DT_BF16;
     uint32_t spin = kGgSpin;
-    int it = 0;
-    for (int w = blockIdx.x; w < total; w += gridDim.x) {
-      const GgTile t = gg_tile(p, w, n_nt);
-      // weight row of this thread
+
+    // cursor over the flattened (tile, k stage) sequence of this CTA
+    struct Cursor {
+      int w, ks;
+      const uint8_t *w0, *w1, *s0, *s1;
+      const float *rel0, *rel1;
+      int64_t xoff;
+      bool n_ok, x_ok;
+    };
+    auto open_tile = [&](Cursor& c) {
+      const GgTile t = gg_tile(p, c.w, n_nt);
       const int n = t.n0 + r;
-      const bool n_ok = n < p.n;
-      const int64_t wrow = ((int64_t)t.expert * p.n + (n_ok ? n : 0));
-      const uint8_t* w0 = reinterpret_cast<const uint8_t*>(p.w) + wrow * p.w_row_bytes;
-      const uint8_t* w1 = NB == 2 ? reinterpret_cast<const uint8_t*>(p.w_up) + wrow * p.w_row_bytes : nullptr;
-      const uint8_t* s0 = nullptr;
-      const uint8_t* s1 = nullptr;
+      c.n_ok = n < p.n;
+      const int64_t wrow = (int64_t)t.expert * p.n + (c.n_ok ? n : 0);
+      c.w0 = reinterpret_cast<const uint8_t*>(p.w) + wrow * p.w_row_bytes;
+      c.w1 = NB == 2 ? reinterpret_cast<const uint8_t*>(p.w_up) + wrow * p.w_row_bytes : nullptr;
+      c.s0 = c.s1 = nullptr;
+      c.rel0 = c.rel1 = nullptr;
       if (FMT == HQ_FMT_MXFP4) {
-        s0 = reinterpret_cast<const uint8_t*>(p.scales) + wrow * (p.k / 32);
-        if (NB == 2) s1 = reinterpret_cast<const uint8_t*>(p.scales_up) + wrow * (p.k / 32);
+        c.s0 = reinterpret_cast<const uint8_t*>(p.scales) + wrow * (p.k / 32);
+        if (NB == 2) c.s1 = reinterpret_cast<const uint8_t*>(p.scales_up) + wrow * (p.k / 32);
       }
-      // activation row of this thread
-      const bool x_ok = r < t.count;
-      int64_t xrow = 0;
-      if (x_ok) {
+      if (FMT == HQ_FMT_FP8_BLOCK) {
+        const int64_t g = ((int64_t)t.expert * p.fp8_nb + t.n0 / 128) * p.fp8_kb;
+        c.rel0 = p.fp8_rel_scale + g;
+        if (NB == 2) c.rel1 = p.fp8_rel_scale_up + g;
+      }
+      c.x_ok = r < t.count;
+      c.xoff = 0;
+      if (c.x_ok) {
         const int sp = t.row_start + r;
-        xrow = p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp;
+        c.xoff = (p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp) * p.x_stride + 32 * half;
       }
-      for (int ks = 0; ks < n_ks; ++ks, ++it) {
-        const int s = it % NSTAGE;
-        if (it >= NSTAGE) {
-          if (!mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
-            if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 500 + s);
-            spin = 1;
-          }
+    };
+    auto fetch = [&](const Cursor& c, RawA (&ra)[NB], RawB& rb) {
+      const int k0 = c.ks * kTileK;
+      if (c.n_ok) {
+        fetch_a<FMT>(ra[0], c.w0, c.s0, c.rel0, k0, half);
+        if (NB == 2) fetch_a<FMT>(ra[NB - 1], c.w1, c.s1, c.rel1, k0, half);
+      }
+      if (c.x_ok && !x_f32) fetch_b(rb, p.x, c.xoff + k0);
+    };
+
+    Cursor cur;
+    cur.w = blockIdx.x;
+    cur.ks = 0;
+    RawA ra[NB], ra_next[NB];
+    RawB rb, rb_next;
+    bool live = cur.w < total;
+    if (live) {
+      open_tile(cur);
+      fetch(cur, ra, rb);
+    }
+    int it = 0;
+    while (live) {
+      // issue the next stage's loads before converting this one
+      Cursor nxt = cur;
+      bool next_live = true;
+      if (cur.ks + 1 < n_ks) {
+        nxt.ks = cur.ks + 1;
+      } else {
+        nxt.w = cur.w + gridDim.x;
+        nxt.ks = 0;
+        next_live = nxt.w < total;
+        if (next_live) open_tile(nxt);
+      }
+      if (next_live) fetch(nxt, ra_next, rb_next);
+
+      const int s = it % NSTAGE;
+      if (it >= NSTAGE) {
+        if (!mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
+          if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 500 + s);
+          spin = 1;
         }
-        uint8_t* stage = smem + s * L::STAGE_BYTES;
-        const int k0 = ks * kTileK;
-        uint32_t v[16];
-        // ---- A: weight tile(s) --------------------------------------------------------
+      }
+      uint8_t* stage = smem + s * L::STAGE_BYTES;
+      const int k0 = cur.ks * kTileK;
+      uint32_t v[16];
 #pragma unroll
-        for (int bank = 0; bank < NB; ++bank) {
-          const uint8_t* wb = bank == 0 ? w0 : w1;
-          if (n_ok) {
-            if (FMT == HQ_FMT_Q4_K) {
-              expand_q4_k(wb, k0, half, v);
-            } else if (FMT == HQ_FMT_FP8_BLOCK) {
-              const float* rel = bank == 0 ? p.fp8_rel_scale : p.fp8_rel_scale_up;
-              expand_fp8(wb, k0, half,
-                         __ldg(rel + ((int64_t)t.expert * p.fp8_nb + t.n0 / 128) * p.fp8_kb + k0 / 128), v);
-            } else {
-              if (!expand_mxfp4(wb, bank == 0 ? s0 : s1, k0, half, v))
-                report_status(p.status, HQ_DEV_BAD_INDEX, 600);
-            }
+      for (int bank = 0; bank < NB; ++bank) {
+        if (cur.n_ok) {
+          if (FMT == HQ_FMT_Q4_K) {
+            emit_q4_k(ra[bank], k0, half, v);
+          } else if (FMT == HQ_FMT_FP8_BLOCK) {
+            emit_fp8(ra[bank], v);
           } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = 0u;
+            if (!emit_mxfp4(ra[bank], v)) report_status(p.status, HQ_DEV_BAD_INDEX, 600);
           }
-          store_chunks(stage + bank * kOperandBytes, r, 4 * half, v);
-        }
-        // ---- B: activation rows (gathered into expert order) ----------------------------
-        if (x_ok) {
-          load_x32(p.x, p.x_dtype, xrow * p.x_stride + k0 + 32 * half, 1.f, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0u;
         }
-        store_chunks(stage + NB * kOperandBytes, r, 4 * half, v);
-        fence_proxy_async_smem();     // generic-proxy writes -> visible to the tensor core (async proxy)
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
+        store_chunks(stage + bank * kOperandBytes, r, 4 * half, v);
       }
+      if (cur.x_ok) {
+        if (x_f32) load_x32_f32(p.x, cur.xoff + k0, v);
+        else emit_b(rb, x_conv, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0u;
+      }
+      store_chunks(stage + NB * kOperandBytes, r, 4 * half, v);
+      fence_proxy_async_smem();     // generic-proxy writes -> visible to the tensor core (async proxy)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[s]);
+      ++it;
+      cur = nxt;
+      live = next_live;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) ra[b] = ra_next[b];
+      rb = rb_next;
     }
   }
 

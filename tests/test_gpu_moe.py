@@ -296,3 +296,4 @@ def test_tensor_path_moe_blocks(tensor_path):
     assert T.rel_l2(got, want) <= 2e-3
     got, want = _moe_case("MXFP4", 140, 8, 4, 320, 320, True, L.ACT_GPTOSS, 23, limit=7.0)
     assert T.rel_l2(got, want) <= 2e-3
+
