@@ -150,7 +150,9 @@ int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, in
     g.y = y; g.y_dtype = y_dtype; g.y_stride = y_stride;
     g.act.act = HQ_ACT_NONE;
     g.status = status_dev;
-    return launch_grouped_gemm(g, (int)((m + 127) / 128), (cudaStream_t)stream);
+    g.x_is_f16_copy = x_dtype == HQ_DT_F16 && (x_stride % 8) == 0;
+    g.tile_rows = (g.x_is_f16_copy && m >= 512) ? 256 : 128;
+    return launch_grouped_gemm(g, (int)((m + g.tile_rows - 1) / g.tile_rows), (cudaStream_t)stream);
   }
   GemvParams p{};
   fill_weight(p, w, nullptr);
@@ -241,14 +243,18 @@ int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const h
     g.x = x; g.x_dtype = x_dtype; g.x_stride = w->k;
     g.y = out; g.y_dtype = out_dtype;
     g.y_stride = (has_act && w_up == nullptr) ? w->n / 2 : w->n;
-    g.tiles = ws + l.off_tiles128;
-    g.tile_count = ws;
+    // 256-token tiles when experts hold enough rows on average to fill them, the rows can be copied as is, and
+    // a single bank leaves tensor memory for two accumulator buffers
+    g.x_is_f16_copy = x_dtype == HQ_DT_F16;
+    g.tile_rows = (g.x_is_f16_copy && w_up == nullptr && n_tokens * top_k >= 192 * (int64_t)w->n_experts) ? 256 : 128;
+    g.tiles = ws + (g.tile_rows == 256 ? l.off_tiles256 : l.off_tiles128);
+    g.tile_count = ws + (g.tile_rows == 256 ? 3 : 1);
     g.expert_bounds = expert_bounds;
     g.x_rows = x_rows;
     g.y_rows = y_rows;
     if (has_act) g.act = *act; else g.act.act = HQ_ACT_NONE;
     g.status = status_dev;
-    return launch_grouped_gemm(g, (int)l.max_tiles128, (cudaStream_t)stream);
+    return launch_grouped_gemm(g, (int)(g.tile_rows == 256 ? l.max_tiles256 : l.max_tiles128), (cudaStream_t)stream);
   }
   GemvParams p{};
   fill_weight(p, w, w_up);

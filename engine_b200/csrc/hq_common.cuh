@@ -64,6 +64,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return false;
 }
 
+// Same bounded wait for warps that only hand work over (MMA issuer, epilogue, reducers): they back off
+// between polls so their polling does not take issue slots from the warps doing the arithmetic.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, uint32_t spin_limit) {
+  for (uint32_t i = 0; i < spin_limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(i < 8 ? 32 : 128);
+  }
+  return false;
+}
+
 // ---- bulk async copy global -> shared (TMA, untiled) ----------------------
 // Both addresses 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {

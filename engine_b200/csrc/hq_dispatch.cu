@@ -6,7 +6,7 @@
 //
 //   pass 1  per-chunk expert histograms (1024 assignments per block)
 //   pass 2  one block: per-expert exclusive prefix over chunks, expert bounds,
-//           tile lists (work items of <= 8 and <= 128 sorted rows per expert)
+//           tile lists (work items of <= 8, <= 128 and <= 256 sorted rows per expert)
 //   pass 3  stable scatter: warps take their 32 assignments in turn; inside a
 //           warp the rank among equal experts comes from a match mask + popcount
 //
@@ -25,8 +25,10 @@ DispatchLayout dispatch_layout(int64_t n_tokens, int top_k, int n_experts) {
   l.max_tiles8 = (total + 7) / 8 + n_experts;
   l.max_tiles128 = (total + 127) / 128 + n_experts;
   l.off_tiles8 = l.off_counts + l.n_blocks * n_experts;
+  l.max_tiles256 = (total + 255) / 256 + n_experts;
   l.off_tiles128 = l.off_tiles8 + 2 * l.max_tiles8;
-  l.total_words = l.off_tiles128 + 2 * l.max_tiles128;
+  l.off_tiles256 = l.off_tiles128 + 2 * l.max_tiles128;
+  l.total_words = l.off_tiles256 + 2 * l.max_tiles256;
   return l;
 }
 
@@ -49,11 +51,13 @@ __global__ void __launch_bounds__(1024) dispatch_scan_kernel(int32_t* __restrict
                                                              int n_experts, int32_t* __restrict__ bounds,
                                                              int32_t* __restrict__ header,
                                                              int32_t* __restrict__ tiles8,
-                                                             int32_t* __restrict__ tiles128) {
+                                                             int32_t* __restrict__ tiles128,
+                                                             int32_t* __restrict__ tiles256) {
   extern __shared__ int32_t sm[];
   int32_t* tot = sm;                    // [E] expert totals, then exclusive bounds
   int32_t* t8 = sm + n_experts;         // [E] tile8 offsets
   int32_t* t128 = sm + 2 * n_experts;   // [E] tile128 offsets
+  int32_t* t256 = sm + 3 * n_experts;   // [E] tile256 offsets
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
     int32_t run = 0;
     for (int b = 0; b < n_blocks; ++b) {
@@ -66,34 +70,37 @@ __global__ void __launch_bounds__(1024) dispatch_scan_kernel(int32_t* __restrict
   __syncthreads();
   if (threadIdx.x < 32) {
     // warp scan over experts, 32 at a time, carrying the running totals
-    int32_t carry = 0, c8 = 0, c128 = 0;
+    int32_t carry = 0, c8 = 0, c128 = 0, c256 = 0;
     for (int base = 0; base < n_experts; base += 32) {
       const int e = base + threadIdx.x;
       const int32_t cnt = e < n_experts ? tot[e] : 0;
-      int32_t v = cnt, v8 = (cnt + 7) / 8, v128 = (cnt + 127) / 128;
+      int32_t v = cnt, v8 = (cnt + 7) / 8, v128 = (cnt + 127) / 128, v256 = (cnt + 255) / 256;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const int32_t o = __shfl_up_sync(0xffffffffu, v, d);
         const int32_t o8 = __shfl_up_sync(0xffffffffu, v8, d);
         const int32_t o128 = __shfl_up_sync(0xffffffffu, v128, d);
-        if ((int)threadIdx.x >= d) { v += o; v8 += o8; v128 += o128; }
+        const int32_t o256 = __shfl_up_sync(0xffffffffu, v256, d);
+        if ((int)threadIdx.x >= d) { v += o; v8 += o8; v128 += o128; v256 += o256; }
       }
       if (e < n_experts) {
         bounds[e] = carry + v - cnt;
         tot[e] = carry + v - cnt;
         t8[e] = c8 + v8 - (cnt + 7) / 8;
         t128[e] = c128 + v128 - (cnt + 127) / 128;
+        t256[e] = c256 + v256 - (cnt + 255) / 256;
       }
       carry += __shfl_sync(0xffffffffu, v, 31);
       c8 += __shfl_sync(0xffffffffu, v8, 31);
       c128 += __shfl_sync(0xffffffffu, v128, 31);
+      c256 += __shfl_sync(0xffffffffu, v256, 31);
     }
     if (threadIdx.x == 0) {
       bounds[n_experts] = carry;
       header[0] = c8;
       header[1] = c128;
       header[2] = carry;
-      header[3] = 0;
+      header[3] = c256;
     }
   }
   __syncthreads();
@@ -110,6 +117,10 @@ __global__ void __launch_bounds__(1024) dispatch_scan_kernel(int32_t* __restrict
     for (int i = threadIdx.x; i < (cnt + 127) / 128; i += blockDim.x) {
       tiles128[2 * (t128[e] + i)] = e;
       tiles128[2 * (t128[e] + i) + 1] = start + 128 * i;
+    }
+    for (int i = threadIdx.x; i < (cnt + 255) / 256; i += blockDim.x) {
+      tiles256[2 * (t256[e] + i)] = e;
+      tiles256[2 * (t256[e] + i) + 1] = start + 256 * i;
     }
   }
 }
@@ -155,8 +166,8 @@ int32_t launch_dispatch(const uint32_t* ids, int64_t n_tokens, int top_k, int n_
   int32_t* counts = ws + l.off_counts;
   const size_t sm1 = (size_t)n_experts * 4;
   dispatch_count_kernel<<<(unsigned)l.n_blocks, 1024, sm1, stream>>>(ids, total, n_experts, counts);
-  dispatch_scan_kernel<<<1, 1024, 3 * sm1, stream>>>(counts, (int)l.n_blocks, n_experts, bounds, ws,
-                                                    ws + l.off_tiles8, ws + l.off_tiles128);
+  dispatch_scan_kernel<<<1, 1024, 4 * sm1, stream>>>(counts, (int)l.n_blocks, n_experts, bounds, ws,
+                                                    ws + l.off_tiles8, ws + l.off_tiles128, ws + l.off_tiles256);
   dispatch_scatter_kernel<<<(unsigned)l.n_blocks, 1024, sm1, stream>>>(ids, total, top_k, n_experts, counts,
                                                                       sorted_assign, sorted_token, inv_perm);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
@@ -167,7 +178,7 @@ int32_t launch_dispatch(const uint32_t* ids, int64_t n_tokens, int top_k, int n_
 // their own pool (a serving engine that sizes its KV cache to whatever is free), or the call is made from
 // a place where asking the CUDA runtime for memory is not allowed.  For them the chunk histograms and the
 // tile lists live in a fixed array inside the library image.  It is sized for kNoAllocMaxAssignments
-// assignments and kNoAllocMaxExperts experts (about 210 KB), exists once per GPU that loads the library
+// assignments and kNoAllocMaxExperts experts (about 220 KB), exists once per GPU that loads the library
 // and is shared by every call: two calls that overlap on the GPU (different streams, or graphs replayed
 // concurrently) race on it.  Nothing in it has to start at zero -- every word that is read is written
 // first by the same call.
@@ -175,7 +186,8 @@ constexpr int kNoAllocMaxAssignments = 65536;
 constexpr int kNoAllocMaxExperts = 512;
 constexpr int64_t kNoAllocWords = 4 + (int64_t)(kNoAllocMaxAssignments / kDispatchChunk) * kNoAllocMaxExperts +
                                   2 * ((int64_t)kNoAllocMaxAssignments / 8 + kNoAllocMaxExperts) +
-                                  2 * ((int64_t)kNoAllocMaxAssignments / 128 + kNoAllocMaxExperts);
+                                  2 * ((int64_t)kNoAllocMaxAssignments / 128 + kNoAllocMaxExperts) +
+                                  2 * ((int64_t)kNoAllocMaxAssignments / 256 + kNoAllocMaxExperts);
 static __device__ __align__(256) int32_t g_noalloc_scratch[kNoAllocWords];
 
 int32_t launch_dispatch_noalloc(const uint32_t* ids, int64_t n_tokens, int top_k, int n_experts, int32_t* bounds,

@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         for (int bank = 0; bank < p.n_banks; ++bank, ++it) {
           const int s = it % NSTAGE;
           if (it >= NSTAGE) {
-            if (!mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
+            if (!mbar_wait_backoff(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
               // give up waiting but keep the control flow intact: results are invalid and flagged
               if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 100 + s);
               spin = 1;
@@ -658,7 +658,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     __syncwarp();
     if (lane == 0) mbar_arrive(&red_full[rb]);
     if (warp == (item % kConsumerWarps)) {
-      if (!mbar_wait(&red_full[rb], (item >> 1) & 1, spin)) {
+      if (!mbar_wait_backoff(&red_full[rb], (item >> 1) & 1, spin)) {
         if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + rb);
         spin = 1;
       }

@@ -28,7 +28,6 @@ namespace hq {
 constexpr int kGgThreads = 13 * 32;
 constexpr int kGgProducerWarps = 8;
 constexpr int kTileM = 128;   // features per tile (TMEM lanes)
-constexpr int kTileN = 128;   // tokens per tile (TMEM columns)
 constexpr int kTileK = 64;    // k per stage: 64 f16 = one 128-byte swizzle row
 constexpr int kOperandBytes = 128 * kTileK * 2;  // 16 KiB per operand tile
 constexpr uint32_t kGgSpin = 1u << 22;
@@ -87,8 +86,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 // kind::f16 instruction descriptor: f32 accumulate, f16 x f16, both K-major, M = 128, N = 128
 // (both operands must have the same 16-bit format: f16 weights beside bf16 activations in one instruction
 // raise an illegal-instruction error on B200, so bf16 activations are converted while their tile is written)
-__device__ __forceinline__ uint32_t make_idesc_f16() {
-  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+__device__ __forceinline__ uint32_t make_idesc_f16(int tile_n) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(tile_n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
 }
 
 // byte offset of 16-byte chunk `c` (0..7) of row `r` inside a swizzled 128 x 64 f16 operand tile
@@ -96,10 +95,13 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
 }
 
-template <int NB>
+// TN = tokens per tile (TMEM columns per accumulator): 128, or 256 when experts hold enough rows to fill it
+template <int NB, int TN>
 struct GgSmem {
-  static constexpr int NSTAGE = NB == 2 ? 4 : 6;
-  static constexpr int STAGE_BYTES = (NB + 1) * kOperandBytes;   // A bank(s) then B
+  static constexpr int B_BYTES = TN * kTileK * 2;
+  static constexpr int STAGE_BYTES = NB * kOperandBytes + B_BYTES;   // A bank(s) then B
+  static constexpr int NSTAGE = (220 * 1024) / STAGE_BYTES > 6 ? 6 : (220 * 1024) / STAGE_BYTES;
+  static constexpr int NBUF = (2 * NB * TN <= 512) ? 2 : 1;          // accumulator buffers in tensor memory
   static constexpr int OFF_BAR = NSTAGE * STAGE_BYTES;
   static constexpr int TOTAL = OFF_BAR + (2 * NSTAGE + 4) * 8 + 16 + 1024;  // + alignment slack
 };
@@ -278,7 +280,9 @@ struct GgTile {
   int expert, row_start, count, n0;
 };
 
+template <int TN>
 __device__ __forceinline__ GgTile gg_tile(const GroupedParams& p, int w, int n_nt) {
+  constexpr int kTileN = TN;
   GgTile t;
   const int tt = w / n_nt;
   t.n0 = (w - tt * n_nt) * kTileM;
@@ -294,10 +298,12 @@ __device__ __forceinline__ GgTile gg_tile(const GroupedParams& p, int w, int n_n
   return t;
 }
 
-template <int FMT, int NB>
+template <int FMT, int NB, int TN>
 __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const GroupedParams p) {
-  using L = GgSmem<NB>;
+  using L = GgSmem<NB, TN>;
   constexpr int NSTAGE = L::NSTAGE;
+  constexpr int NBUF = L::NBUF;
+  constexpr int kTileN = TN;
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -309,7 +315,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_nt = (p.n + kTileM - 1) / kTileM;
-  const int n_tt = p.tiles != nullptr ? p.tile_count[1] : (p.m + kTileN - 1) / kTileN;
+  const int n_tt = p.tiles != nullptr ? p.tile_count[0] : (p.m + kTileN - 1) / kTileN;
   const int total = n_tt * n_nt;
   const int n_ks = p.k / kTileK;
 
@@ -336,13 +342,13 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
   if (warp == 0) {
     // =========================== MMA issuer ======================================
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16();
+      const uint32_t idesc = make_idesc_f16(TN);
       uint32_t spin = kGgSpin;
       int it = 0, tcount = 0;
       for (int w = blockIdx.x; w < total; w += gridDim.x, ++tcount) {
-        const int buf = tcount & 1;
-        if (tcount >= 2) {
-          if (!mbar_wait(&acc_empty[buf], ((tcount >> 1) - 1) & 1, spin)) {
+        const int buf = tcount % NBUF;
+        if (tcount >= NBUF) {
+          if (!mbar_wait_backoff(&acc_empty[buf], ((tcount / NBUF) - 1) & 1, spin)) {
             report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 300 + buf);
             spin = 1;
           }
@@ -351,7 +357,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         const uint32_t d0 = tmem_base + (uint32_t)(buf * NB * kTileN);
         for (int ks = 0; ks < n_ks; ++ks, ++it) {
           const int s = it % NSTAGE;
-          if (!mbar_wait(&full[s], (it / NSTAGE) & 1, spin)) {
+          if (!mbar_wait_backoff(&full[s], (it / NSTAGE) & 1, spin)) {
             report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + s);
             spin = 1;
           }
@@ -379,9 +385,9 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
     uint32_t spin = kGgSpin;
     int tcount = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++tcount) {
-      const GgTile t = gg_tile(p, w, n_nt);
-      const int buf = tcount & 1;
-      if (!mbar_wait(&acc_full[buf], (tcount >> 1) & 1, spin)) {
+      const GgTile t = gg_tile<TN>(p, w, n_nt);
+      const int buf = tcount % NBUF;
+      if (!mbar_wait_backoff(&acc_full[buf], (tcount / NBUF) & 1, spin)) {
         if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 400 + buf);
         spin = 1;
       }
@@ -435,6 +441,8 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
     const int r = ptid >> 1, half = ptid & 1; // operand row and which 32-k half of the stage
     const bool x_f32 = p.x_dtype == HQ_DT_F32;
     const bool x_conv = p.x_dtype == HQ_DT_BF16;
+    const bool b_copy = p.x_is_f16_copy != 0; // f16 activations: rows go global -> shared with cp.async
+    constexpr int BROWS = TN / 32;            // activation rows per thread in copy mode (one 16-byte chunk each)
     uint32_t spin = kGgSpin;
 
     // cursor over the flattened (tile, k stage) sequence of this CTA
@@ -444,9 +452,10 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
       const float *rel0, *rel1;
       int64_t xoff;
       bool n_ok, x_ok;
+      int64_t boff[BROWS];    // copy mode: element offset of this thread's chunk in each of its rows, -1 = no row
     };
     auto open_tile = [&](Cursor& c) {
-      const GgTile t = gg_tile(p, c.w, n_nt);
+      const GgTile t = gg_tile<TN>(p, c.w, n_nt);
       const int n = t.n0 + r;
       c.n_ok = n < p.n;
       const int64_t wrow = (int64_t)t.expert * p.n + (c.n_ok ? n : 0);
@@ -463,11 +472,24 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         c.rel0 = p.fp8_rel_scale + g;
         if (NB == 2) c.rel1 = p.fp8_rel_scale_up + g;
       }
-      c.x_ok = r < t.count;
+      c.x_ok = false;
       c.xoff = 0;
-      if (c.x_ok) {
-        const int sp = t.row_start + r;
-        c.xoff = (p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp) * p.x_stride + 32 * half;
+      if (b_copy) {
+#pragma unroll
+        for (int j = 0; j < BROWS; ++j) {
+          const int row = (ptid >> 3) + 32 * j;
+          c.boff[j] = -1;
+          if (row < t.count) {
+            const int sp = t.row_start + row;
+            c.boff[j] = (p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp) * p.x_stride + 8 * (ptid & 7);
+          }
+        }
+      } else {
+        c.x_ok = r < t.count;
+        if (c.x_ok) {
+          const int sp = t.row_start + r;
+          c.xoff = (p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp) * p.x_stride + 32 * half;
+        }
       }
     };
     auto fetch = [&](const Cursor& c, RawA (&ra)[NB], RawB& rb) {
@@ -476,7 +498,32 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         fetch_a<FMT>(ra[0], c.w0, c.s0, c.rel0, k0, half);
         if (NB == 2) fetch_a<FMT>(ra[NB - 1], c.w1, c.s1, c.rel1, k0, half);
       }
-      if (c.x_ok && !x_f32) fetch_b(rb, p.x, c.xoff + k0);
+      if (!b_copy && c.x_ok && !x_f32) fetch_b(rb, p.x, c.xoff + k0);
+    };
+    int waited = NSTAGE - 1;                  // stages up to this index are known to be free
+    auto ensure_empty = [&](int j) {
+      if (j > waited) {
+        if (!mbar_wait(&empty[j % NSTAGE], ((j / NSTAGE) - 1) & 1, spin)) {
+          if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 500 + j % NSTAGE);
+          spin = 1;
+        }
+        waited = j;
+      }
+    };
+    auto copy_b = [&](const Cursor& c, int stage_index) {
+      uint8_t* btile = smem + (stage_index % NSTAGE) * L::STAGE_BYTES + NB * kOperandBytes;
+      const int k0 = c.ks * kTileK;
+#pragma unroll
+      for (int j = 0; j < BROWS; ++j) {
+        const int row = (ptid >> 3) + 32 * j;
+        const uint32_t dst = smem_u32(btile + swz(row, ptid & 7));
+        const bool ok = c.boff[j] >= 0;
+        const void* src = ok ? reinterpret_cast<const void*>(reinterpret_cast<const uint16_t*>(p.x) + c.boff[j] + k0)
+                             : p.x;
+        // 16 bytes global -> shared without passing through registers; a missing row is zero-filled
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     Cursor cur;
@@ -488,6 +535,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
     if (live) {
       open_tile(cur);
       fetch(cur, ra, rb);
+      if (b_copy) copy_b(cur, 0);
     }
     int it = 0;
     while (live) {
@@ -502,15 +550,15 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         next_live = nxt.w < total;
         if (next_live) open_tile(nxt);
       }
-      if (next_live) fetch(nxt, ra_next, rb_next);
-
-      const int s = it % NSTAGE;
-      if (it >= NSTAGE) {
-        if (!mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
-          if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 500 + s);
-          spin = 1;
+      if (next_live) {
+        fetch(nxt, ra_next, rb_next);
+        if (b_copy) {
+          ensure_empty(it + 1);
+          copy_b(nxt, it + 1);
         }
       }
+      ensure_empty(it);
+      const int s = it % NSTAGE;
       uint8_t* stage = smem + s * L::STAGE_BYTES;
       const int k0 = cur.ks * kTileK;
       uint32_t v[16];
@@ -530,14 +578,20 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         }
         store_chunks(stage + bank * kOperandBytes, r, 4 * half, v);
       }
-      if (cur.x_ok) {
-        if (x_f32) load_x32_f32(p.x, cur.xoff + k0, v);
-        else emit_b(rb, x_conv, v);
+      if (b_copy) {
+        // this stage's activation copies were issued one iteration ago; the next stage's may stay in flight
+        if (next_live) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
       } else {
+        if (cur.x_ok) {
+          if (x_f32) load_x32_f32(p.x, cur.xoff + k0, v);
+          else emit_b(rb, x_conv, v);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = 0u;
+          for (int i = 0; i < 16; ++i) v[i] = 0u;
+        }
+        store_chunks(stage + NB * kOperandBytes, r, 4 * half, v);
       }
-      store_chunks(stage + NB * kOperandBytes, r, 4 * half, v);
       fence_proxy_async_smem();     // generic-proxy writes -> visible to the tensor core (async proxy)
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);
@@ -583,11 +637,12 @@ int32_t launch_fp8_scale_prepare(const float* scales, int64_t n_groups, int kb, 
 }
 
 // ---- host launcher -----------------------------------------------------------------
-template <int FMT, int NB>
+template <int FMT, int NB, int TN>
 static int32_t launch_gg(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
-  using L = GgSmem<NB>;
+  using L = GgSmem<NB, TN>;
   static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
-  auto kern = grouped_gemm_kernel<FMT, NB>;
+  static_assert(L::NSTAGE >= 3, "pipeline depth");
+  auto kern = grouped_gemm_kernel<FMT, NB, TN>;
   static bool attr_done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
@@ -605,6 +660,15 @@ static int32_t launch_gg(const GroupedParams& p, int max_tiles, cudaStream_t str
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
+template <int FMT>
+static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
+  const bool two = p.w_up != nullptr;
+  if (p.tile_rows == 256) {
+    return two ? launch_gg<FMT, 2, 256>(p, max_tiles, stream) : launch_gg<FMT, 1, 256>(p, max_tiles, stream);
+  }
+  return two ? launch_gg<FMT, 2, 128>(p, max_tiles, stream) : launch_gg<FMT, 1, 128>(p, max_tiles, stream);
+}
+
 bool grouped_gemm_supported(int format, int64_t n, int64_t k) {
   if (format != HQ_FMT_Q4_K && format != HQ_FMT_FP8_BLOCK && format != HQ_FMT_MXFP4) return false;
   if (k % kTileK != 0) return false;
@@ -613,17 +677,13 @@ bool grouped_gemm_supported(int format, int64_t n, int64_t k) {
 }
 
 int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
-  const bool two = p.w_up != nullptr;
+  if (p.tile_rows != 128 && p.tile_rows != 256) return HQ_ERR_SHAPE;
+  if (p.tile_rows == 256 && !p.x_is_f16_copy) return HQ_ERR_FORMAT;   // wide tiles take f16 activations only
   switch (p.format) {
-    case HQ_FMT_Q4_K:
-      return two ? launch_gg<HQ_FMT_Q4_K, 2>(p, max_tiles, stream) : launch_gg<HQ_FMT_Q4_K, 1>(p, max_tiles, stream);
-    case HQ_FMT_FP8_BLOCK:
-      return two ? launch_gg<HQ_FMT_FP8_BLOCK, 2>(p, max_tiles, stream)
-                 : launch_gg<HQ_FMT_FP8_BLOCK, 1>(p, max_tiles, stream);
-    case HQ_FMT_MXFP4:
-      return two ? launch_gg<HQ_FMT_MXFP4, 2>(p, max_tiles, stream) : launch_gg<HQ_FMT_MXFP4, 1>(p, max_tiles, stream);
-    default:
-      return HQ_ERR_FORMAT;
+    case HQ_FMT_Q4_K: return launch_gg_fmt<HQ_FMT_Q4_K>(p, max_tiles, stream);
+    case HQ_FMT_FP8_BLOCK: return launch_gg_fmt<HQ_FMT_FP8_BLOCK>(p, max_tiles, stream);
+    case HQ_FMT_MXFP4: return launch_gg_fmt<HQ_FMT_MXFP4>(p, max_tiles, stream);
+    default: return HQ_ERR_FORMAT;
   }
 }
 

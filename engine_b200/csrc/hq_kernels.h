@@ -62,8 +62,10 @@ struct GroupedParams {
   void* y;
   int y_dtype;
   int64_t y_stride;
-  const int32_t* tiles;         // [n_tiles][2] = (expert, first sorted row), tiles of <= 128 rows
-  const int32_t* tile_count;    // device words: [1] = n_tiles
+  const int32_t* tiles;         // [n_tiles][2] = (expert, first sorted row), tiles of <= tile_rows rows
+  const int32_t* tile_count;    // device word holding n_tiles
+  int tile_rows;                // 128 or 256 tokens per tile
+  int x_is_f16_copy;            // activations are f16 already: rows are copied with cp.async, no conversion
   const int32_t* expert_bounds;
   const int32_t* x_rows;        // sorted row -> activation row (nullptr = identity)
   const int32_t* y_rows;        // sorted row -> output row (nullptr = identity)
@@ -84,6 +86,8 @@ struct DispatchLayout {
   int64_t max_tiles8;
   int64_t off_tiles128;  // int32 words, [max128][2]
   int64_t max_tiles128;
+  int64_t off_tiles256;  // int32 words, [max256][2]
+  int64_t max_tiles256;
   int64_t total_words;
 };
 DispatchLayout dispatch_layout(int64_t n_tokens, int top_k, int n_experts);

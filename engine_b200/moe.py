@@ -10,7 +10,8 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib as L
-from .quant import (DispatchTables, QuantMethod, _ptr, _require_cuda, _stream, dt_code, moe_dispatch_build)
+from .quant import (DispatchTables, QuantMethod, _ptr, _require_cuda, _stream, dt_code, moe_dispatch_build,
+                    tensor_path_expected)
 
 
 @dataclass
@@ -104,6 +105,8 @@ class MoEExperts:
         t, k = topk_ids.shape
         tables = tables or moe_dispatch_build(topk_ids, self.n_experts)
         first = self.gate_up if self.gate_up is not None else self.gate
+        if x.dtype != torch.float16 and tensor_path_expected(first, t * k, dense=False):
+            x = x.to(torch.float16)     # one cast per token instead of one conversion per (token, slot) in the kernel
         inter = first.n // 2 if self.gate_up is not None else first.n
         h = torch.empty((t * k, inter), dtype=self.inter_dtype, device=x.device)
         w0 = first._weight_struct()

@@ -73,6 +73,20 @@ def moe_dispatch_build(ids: torch.Tensor, n_experts: int) -> DispatchTables:
     return DispatchTables(t, k, n_experts, bounds, sa, st, inv, ws)
 
 
+def tensor_path_expected(layer, n_rows_total: int, dense: bool) -> bool:
+    """Mirror of the C-side rule that sends a call to the tensor-core grouped GEMM (prefill-sized row counts,
+    Q4_K / FP8 / MXFP4, K % 64 == 0).  Used only to decide whether to hand activations over as f16, which that
+    kernel copies into its operand tiles without a conversion pass."""
+    if layer.format == L.FMT_Q8_0 or layer.k % 64:
+        return False
+    if layer.format == L.FMT_FP8_BLOCK and (layer.n % 128 or layer.k % 128):
+        return False
+    lib = L.lib()
+    if dense:
+        return n_rows_total >= lib.hq_config_get(L.CFG_DENSE_TENSOR_MIN_ROWS)
+    return n_rows_total >= lib.hq_config_get(L.CFG_MOE_TENSOR_MIN_ROWS) * layer.n_experts
+
+
 class QuantMethod:
     """Base of the quantized layers; weights are [N, K] (dense) or [E, N, K] (expert bank)."""
 
@@ -123,6 +137,8 @@ class QuantMethod:
             x = x.contiguous()
         m = x.shape[0]
         out_dtype = out_dtype or a.dtype
+        if x.dtype != torch.float16 and tensor_path_expected(self, m, dense=True):
+            x = x.to(torch.float16)     # the tensor-core kernel multiplies in f16 either way
         y = torch.empty((m, self.n), dtype=out_dtype, device=a.device)
         w = self._weight_struct()
         L.check(L.lib().hq_linear_forward(C.byref(w), _ptr(x), dt_code(x.dtype), x.stride(0) if m > 1 else self.k,
@@ -150,6 +166,8 @@ class QuantMethod:
         if a.shape[0] != t or a.shape[-1] != self.k:
             raise L.HqError("gather_forward: input / indices / weight shapes disagree")
         x = a.contiguous()
+        if x.dtype != torch.float16 and tensor_path_expected(self, t * k, dense=False):
+            x = x.to(torch.float16)
         tables = tables or moe_dispatch_build(indices, self.n_experts)
         out_dtype = out_dtype or a.dtype
         out = torch.empty((t, k, self.n), dtype=out_dtype, device=a.device)

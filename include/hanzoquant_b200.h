@@ -154,7 +154,7 @@ int32_t hq_moe_dispatch_build(const uint32_t* ids, int64_t n_tokens, int32_t top
 /* Same tables for hosts that have no device memory to spare for a workspace and may not allocate any:
  * engines whose own pool already owns all of HBM, or code that runs where the CUDA runtime must not be
  * asked for memory.  This entry point has no counterpart in the reference.  The scratch it needs sits in a
- * fixed array inside the library (about 210 KB per GPU, held until the process exits), so it only accepts
+ * fixed array inside the library (about 220 KB per GPU, held until the process exits), so it only accepts
  * n_tokens*top_k <= 65536 and n_experts <= 512 and answers HQ_ERR_TOO_LARGE beyond that.  It calls no
  * allocator of any kind.  The first call on a device looks up the array's device address; make that
  * first call outside any stream capture.  All calls share the one array: calls that run at the same time

@@ -297,3 +297,24 @@ def test_tensor_path_moe_blocks(tensor_path):
     got, want = _moe_case("MXFP4", 140, 8, 4, 320, 320, True, L.ACT_GPTOSS, 23, limit=7.0)
     assert T.rel_l2(got, want) <= 2e-3
 
+
+def test_tensor_path_wide_token_tiles(tensor_path):
+    # enough rows per expert on average for the 256-token tiles (f16 rows copied with cp.async)
+    rng = T.rng_for(5, 91)
+    e, t, topk, k, n = 4, 700, 2, 256, 192
+    arrays, deq = T.make_weight("Q4_K", rng, n, k, experts=e)
+    layer = T.make_layer("Q4_K", arrays, k, DEV)
+    p = np.array([0.55, 0.3, 0.15, 0.0])
+    ids = np.stack([rng.choice(e, size=topk, replace=False, p=p) for _ in range(t)]).astype(np.int32)
+    xd = T.to_dev(rng.standard_normal((t, k)).astype(np.float32), torch.bfloat16, DEV)
+    out = layer.gather_forward_raw(xd, T.to_dev(ids, torch.int32, DEV), torch.float32)
+    torch.cuda.synchronize()
+    assert layer.device_status()[0] == 0, layer.device_status()
+    want = M.gather_forward(xd.to(torch.float32).cpu().numpy(), ids.astype(np.uint32), deq)
+    assert T.rel_l2(out.cpu().numpy(), want) <= 1e-3
+    got, want = _moe_case("Q4_K", 450, 8, 4, 512, 256, False, L.ACT_SWIGLU, 31)
+    assert T.rel_l2(got, want) <= 1e-3
+    got, want = _moe_case("MXFP4", 450, 8, 4, 320, 320, True, L.ACT_GPTOSS, 32, limit=7.0)
+    assert T.rel_l2(got, want) <= 2e-3
+    got, want = _moe_case("FP8", 450, 8, 4, 512, 256, False, L.ACT_SWIGLU, 33)
+    assert T.rel_l2(got, want) <= 2e-3
