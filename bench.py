@@ -390,7 +390,7 @@ MOE_CFGS = {
     "moe_q4k": dict(fmt="Q4_K", e=128, k=8, h=2048, i=768, t=4096, router="softmax", inter=False,
                     label="cfg3_qwen3_30b_a3b_q4k_moe"),
     "moe_fp8": dict(fmt="FP8", e=256, k=8, h=7168, i=2048, t=4096, router="sigmoid_bias", inter=False,
-                    label="cfg4_deepseek_v3_block_fp8_moe"),
+                    shared=True, act_fp8=True, label="cfg4_deepseek_v3_block_fp8_moe"),
     "moe_mxfp4": dict(fmt="MXFP4", e=128, k=4, h=2880, i=2880, t=8192, router="topk_softmax", inter=True,
                       label="cfg5_gpt_oss_120b_mxfp4_moe"),
 }
@@ -485,8 +485,9 @@ def router_config(hq, cfg):
     return hq.MoeRouterTopKConfig(cfg["k"], L.SCORE_RAW, L.WEIGHT_SOFTMAX, False)
 
 
-def moe_flops(cfg, tokens):
-    return 2.0 * tokens * cfg["k"] * 3 * cfg["h"] * cfg["i"]
+def moe_flops(cfg, tokens, with_shared=False):
+    per_expert = 2.0 * 3 * cfg["h"] * cfg["i"]
+    return tokens * per_expert * (cfg["k"] + (1 if with_shared and cfg.get("shared") else 0))
 
 
 def run_moe(args):
@@ -513,6 +514,12 @@ def run_moe(args):
     t_local = t_global // world                      # tokens are data-parallel, experts sharded E/world per rank
     experts = build_moe_layer(torch, hq, cfg, gen, dev, e // world)
     ep = ExpertParallelMoE(e, experts) if world > 1 else None
+    shared = None
+    if cfg.get("shared"):
+        # the always-on shared expert: the same three projections as a one-expert bank over this rank's tokens
+        shared = build_moe_layer(torch, hq, cfg, gen, dev, 1)
+        shared_ids = torch.zeros((t_local, 1), dtype=torch.int32, device=dev)
+        shared_w = torch.ones((t_local, 1), dtype=torch.float32, device=dev)
     rcfg = router_config(hq, cfg)
     sel_bias = (torch.randn(e, generator=gen, device=dev) * 0.01) if cfg["router"] == "sigmoid_bias" else None
     n_in = 4                                          # rotate inputs; the expert bank itself exceeds L2
@@ -524,9 +531,17 @@ def run_moe(args):
         x = xs[j % n_in] if x is None else x
         lg = logits[j % n_in] if lg is None else lg
         top = hq.moe_router_topk(lg, rcfg, sel_bias)
+        if cfg.get("act_fp8"):
+            # per-token 1x128 dynamic FP8 quantization of the activations (the values the experts see are the
+            # dequantized codes; the MMA itself runs on f16 operands)
+            codes, scales = hq.fp8_vector_quantize(x)
+            x = hq.fp8_vector_dequantize(codes, scales, torch.float16)
+        add = None
+        if shared is not None:
+            add = shared.forward(x, shared_w[:x.shape[0]], shared_ids[:x.shape[0]], out_dtype=torch.bfloat16)
         if ep is not None:
-            return ep.forward(x, top.values, top.indices, out_dtype=torch.bfloat16)
-        return experts.forward(x, top.values, top.indices, out_dtype=torch.bfloat16)
+            return ep.forward(x, top.values, top.indices, shared_out=add, out_dtype=torch.bfloat16)
+        return experts.forward(x, top.values, top.indices, shared_out=add, out_dtype=torch.bfloat16)
 
     for w in range(max(args.warmup, 3)):
         out = step(w)
@@ -534,6 +549,21 @@ def run_moe(args):
     status = experts.down.device_status()
     assert status[0] == 0, f"device status {status}"
     assert bool(torch.isfinite(out.float()).all())
+    # what is timed is checked against the decode kernel (itself pinned to the CPU oracle by the tests): same step,
+    # tensor-core path switched off, first 64 tokens
+    parity = None
+    if world == 1:
+        lib = L.lib()
+        old = lib.hq_config_get(L.CFG_MOE_TENSOR_MIN_ROWS)
+        n_chk = min(64, t_local)
+        a = step(0)[:n_chk].float()
+        lib.hq_config_set(L.CFG_MOE_TENSOR_MIN_ROWS, 1 << 40)
+        try:
+            b = step(0, xs[0][:n_chk].contiguous(), logits[0][:n_chk].contiguous()).float()
+        finally:
+            lib.hq_config_set(L.CFG_MOE_TENSOR_MIN_ROWS, old)
+        parity = float(torch.linalg.norm(a - b) / torch.linalg.norm(b))
+        assert parity < 1e-2, f"tensor-core path disagrees with the decode kernel: rel-L2 {parity}"
 
     def barrier():
         if dist is not None:
@@ -615,6 +645,7 @@ def run_moe(args):
                        "intermediate": cfg["i"], "tokens_global": t_global, "experts_per_gpu": e // world,
                        "parallelism": f"ep{world}", "l2": "expert banks exceed L2; activations rotate over 4 buffers"},
             "roofline": roof,
+            "parity_vs_decode_kernel_rel_l2_bf16_out": parity,
             "cpu_baseline": None,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": t_local * (h * 2 + e * 4),
                     "d2h_bytes_per_step": t_local * h * 2, "ms_per_step": e2e_ms / args.steps},

@@ -59,6 +59,7 @@ SIGNATURES = {
     "hq_fp8_scale_prepare": (_I32, [_P, _I32, _I64, _I64, _P, _P, _P]),
     "hq_config_set": (_I32, [_I32, _I64]),
     "hq_config_get": (_I64, [_I32]),
+    "hq_convert": (_I32, [_P, _I32, _P, _I32, _I64, _P]),
     "hq_gated_act": (_I32, [_P, _P, _I32, _I64, _I32, C.POINTER(HqActArgs), _P, _P]),
 }
 

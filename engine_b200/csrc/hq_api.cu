@@ -68,7 +68,10 @@ void fill_grouped(GroupedParams& g, const hq_weight* w, const hq_weight* w_up) {
   g.fp8_kb = (int)((w->k + 127) / 128);
 }
 
-bool tensor_path_ok(const hq_weight* w, const hq_weight* w_up) {
+// the tensor-core kernel takes f16 activation rows (it copies them into its operand tiles); hosts holding bf16 or
+// f32 activations cast once per call (cheaper than converting every gathered copy of a row)
+bool tensor_path_ok(const hq_weight* w, const hq_weight* w_up, int x_dtype, int64_t x_stride) {
+  if (x_dtype != HQ_DT_F16 || (x_stride % 8) != 0) return false;
   if (!grouped_gemm_supported(w->format, w->n, w->k)) return false;
   if (w->format == HQ_FMT_FP8_BLOCK) {
     if (w->fp8_tile_scale == nullptr || w->fp8_rel_scale == nullptr) return false;
@@ -142,7 +145,7 @@ int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, in
   if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return HQ_ERR_FORMAT;
   if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
   if (x_stride < w->k || y_stride < w->n) return HQ_ERR_SHAPE;
-  if (m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS] && w->n_experts == 1 && tensor_path_ok(w, nullptr)) {
+  if (m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS] && w->n_experts == 1 && tensor_path_ok(w, nullptr, x_dtype, x_stride)) {
     GroupedParams g{};
     fill_grouped(g, w, nullptr);
     g.m = (int)m;
@@ -150,8 +153,7 @@ int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, in
     g.y = y; g.y_dtype = y_dtype; g.y_stride = y_stride;
     g.act.act = HQ_ACT_NONE;
     g.status = status_dev;
-    g.x_is_f16_copy = x_dtype == HQ_DT_F16 && (x_stride % 8) == 0;
-    g.tile_rows = (g.x_is_f16_copy && m >= 512) ? 256 : 128;
+    g.tile_rows = m >= 512 ? 256 : 128;
     return launch_grouped_gemm(g, (int)((m + g.tile_rows - 1) / g.tile_rows), (cudaStream_t)stream);
   }
   GemvParams p{};
@@ -237,16 +239,15 @@ int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const h
   const int32_t* x_rows =
       x_layout == HQ_ROWS_PER_TOKEN ? sorted_token : (x_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr);
   const int32_t* y_rows = out_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr;
-  if (n_tokens * top_k >= g_cfg[HQ_CFG_MOE_TENSOR_MIN_ROWS] * (int64_t)w->n_experts && tensor_path_ok(w, w_up)) {
+  if (n_tokens * top_k >= g_cfg[HQ_CFG_MOE_TENSOR_MIN_ROWS] * (int64_t)w->n_experts && tensor_path_ok(w, w_up, x_dtype, w->k)) {
     GroupedParams g{};
     fill_grouped(g, w, w_up);
     g.x = x; g.x_dtype = x_dtype; g.x_stride = w->k;
     g.y = out; g.y_dtype = out_dtype;
     g.y_stride = (has_act && w_up == nullptr) ? w->n / 2 : w->n;
-    // 256-token tiles when experts hold enough rows on average to fill them, the rows can be copied as is, and
-    // a single bank leaves tensor memory for two accumulator buffers
-    g.x_is_f16_copy = x_dtype == HQ_DT_F16;
-    g.tile_rows = (g.x_is_f16_copy && w_up == nullptr && n_tokens * top_k >= 192 * (int64_t)w->n_experts) ? 256 : 128;
+    // 256-token tiles when experts hold enough rows on average to fill them and a single bank leaves tensor
+    // memory for two accumulator buffers
+    g.tile_rows = (w_up == nullptr && n_tokens * top_k >= 192 * (int64_t)w->n_experts) ? 256 : 128;
     g.tiles = ws + (g.tile_rows == 256 ? l.off_tiles256 : l.off_tiles128);
     g.tile_count = ws + (g.tile_rows == 256 ? 3 : 1);
     g.expert_bounds = expert_bounds;
@@ -329,6 +330,14 @@ int32_t hq_fp8_scale_prepare(const float* scales, int32_t n_experts, int64_t n, 
   const int64_t groups = (int64_t)n_experts * ((n + 127) / 128);
   return launch_fp8_scale_prepare(scales, groups, (int)((k + 127) / 128), tile_scale_out, rel_scale_out,
                                   (cudaStream_t)stream);
+}
+
+int32_t hq_convert(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int64_t n_elems, void* stream) {
+  if (n_elems < 0) return HQ_ERR_SHAPE;
+  if (n_elems == 0) return HQ_OK;
+  if (src == nullptr || dst == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(src_dtype) || !valid_dtype(dst_dtype)) return HQ_ERR_FORMAT;
+  return launch_convert(src, src_dtype, dst, dst_dtype, n_elems, (cudaStream_t)stream);
 }
 
 int32_t hq_gated_act(const void* gate, const void* up, int32_t dtype, int64_t n_elems, int32_t interleaved,

@@ -193,6 +193,19 @@ int32_t launch_fp8_block_dequant(const uint8_t* codes, const float* scales, int6
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
+// ---- dtype conversion (hosts holding bf16 / f32 activations cast once before a prefill-sized call) -------
+__global__ void __launch_bounds__(256) convert_kernel(const void* __restrict__ src, int src_dtype,
+                                                      void* __restrict__ dst, int dst_dtype, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) store_from_float(dst, dst_dtype, i, load_as_float(src, src_dtype, i));
+}
+
+int32_t launch_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, cudaStream_t stream) {
+  if (n == 0) return HQ_OK;
+  convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(src, src_dtype, dst, dst_dtype, n);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
 // ---- gated activations --------------------------------------------------------------
 __device__ __forceinline__ float gated_act(float g, float u, const hq_act_args& a) {
   if (a.act == HQ_ACT_GPTOSS) {

@@ -563,6 +563,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             spin = 1;
           }
           ++it;
+          // the units of a stage do not divide evenly among the warps: rotate who gets the extra one
+          const int wrot = (wk + it) % WK;
           const uint32_t rowA = smem_u32(smem + s * L::STAGE_BYTES) + (uint32_t)g * L::PITCH;
           const uint32_t rowB = rowA + 8u * L::PITCH;
           const uint32_t xs_c = xs_g + 2u * kx;
@@ -570,7 +572,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
           float(&a)[4] = acc[bank];
           if (FMT == HQ_FMT_Q8_0) {
             const int nunits = kc_len / 32;
-            int u = wk;
+            int u = wrot;
             for (; u + WK < nunits; u += 2 * WK) {
               Q8Regs r0, r1;
               q8_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
@@ -585,7 +587,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             }
           } else if (FMT == HQ_FMT_Q4_K) {
             const int nunits = kc_len / 64;
-            int u = wk;
+            int u = wrot;
             for (; u + WK < nunits; u += 2 * WK) {
               Q4Regs r0, r1;
               q4_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
@@ -603,7 +605,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             const float* fsc = reinterpret_cast<const float*>(bank == 0 ? p.scales : p.scales_up) +
                                (int64_t)wi.expert * p.scale_expert_stride +
                                (int64_t)(wi.n0 / 128) * ((p.k + 127) / 128);
-            int u = wk;
+            int u = wrot;
             for (; u + WK < nunits; u += 2 * WK) {
               B32Regs r0, r1;
               fp8_load(r0, rowA, rowB, xs_c, u, t, xv);
@@ -625,7 +627,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                                  (int64_t)wi.expert * p.scale_expert_stride + chunk * (KC / 32);
             const uint8_t* mA = msc + (int64_t)min(wi.n0 + g, p.n - 1) * kb_row;
             const uint8_t* mB = msc + (int64_t)min(wi.n0 + g + 8, p.n - 1) * kb_row;
-            for (int u = wk; u < nunits; u += WK) {
+            for (int u = wrot; u < nunits; u += WK) {
               B32Regs r0;
               mx_load(r0, rowA, rowB, xs_c, u, t, xv);
               // 2^(e-127) with the reference's bit trick (e = 0 decodes to 0), times 2^14 for the nibble encoding

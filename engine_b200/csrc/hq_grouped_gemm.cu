@@ -10,10 +10,10 @@
 //                 128-byte swizzle), f32 accumulators in tensor memory, double buffered
 //   warps 1-4     epilogue: tcgen05.ld the accumulators, bias, gated activation
 //                 (gate/up from two banks, or interleaved rows), store
-//   warps 5-12    producers: read the quantized weight tile straight from the
+//   warps 5-20    producers: read the quantized weight tile straight from the
 //                 reference's byte layout, expand it to f16 in registers and write the
-//                 swizzled operand tile; gather the activation rows of the tile
-//                 (token order -> expert order), convert to f16, write them likewise
+//                 swizzled operand tile; gather the tile's f16 activation rows (token order
+//                 -> expert order) straight into the second operand tile with cp.async
 // Stage hand-off is by mbarrier: producers arrive on full[s] after a proxy fence, the
 // MMA warp releases a stage with tcgen05.commit, accumulator buffers alternate
 // between MMA and epilogue through acc_full / acc_empty.  Every wait is bounded.
@@ -25,8 +25,8 @@
 
 namespace hq {
 
-constexpr int kGgThreads = 13 * 32;
-constexpr int kGgProducerWarps = 8;
+constexpr int kGgProducerWarps = 16;
+constexpr int kGgThreads = (5 + kGgProducerWarps) * 32;
 constexpr int kTileM = 128;   // features per tile (TMEM lanes)
 constexpr int kTileK = 64;    // k per stage: 64 f16 = one 128-byte swizzle row
 constexpr int kOperandBytes = 128 * kTileK * 2;  // 16 KiB per operand tile
@@ -107,63 +107,62 @@ struct GgSmem {
 };
 
 // ---- operand production, split in two halves so the global loads of the next stage are in flight while
-// this stage is converted: fetch_* issues the loads into registers, emit_* converts and writes shared memory.
-// A thread owns 32 consecutive k of one operand row per stage (natural k order, 4 chunks of 16 bytes).
+// this stage is converted: fetch_a issues the loads into registers, emit_* converts to f16.  A thread owns 16
+// consecutive k (quarter `q` of the stage's 64) of one weight row: two 16-byte chunks, natural k order.
 struct RawA {
-  uint4 a, b, c;      // Q4_K: header, nibble bytes 0-15, 16-31; FP8: codes 0-15, 16-31; MXFP4: 16 nibble bytes
+  uint4 hdr;          // Q4_K: super-block header {d, dmin, 12 scale bytes}
+  uint4 q;            // Q4_K: 16 nibble bytes; FP8: 16 codes; MXFP4: .x/.y = 8 nibble bytes
   uint32_t aux;       // FP8: relative block scale (f32 bits); MXFP4: e8m0 byte
-};
-struct RawB {
-  uint4 v[4];         // 32 x 16-bit activations
 };
 
 template <int FMT>
 __device__ __forceinline__ void fetch_a(RawA& r, const uint8_t* row_base, const uint8_t* scale_row, const float* rel,
-                                        int k0, int half) {
+                                        int k0, int q) {
   if (FMT == HQ_FMT_Q4_K) {
+    // sub-blocks 2c and 2c+1 share 32 nibble bytes; quarters 0,1 are the low nibbles, 2,3 the high nibbles
     const int sb = k0 >> 8, c = (k0 & 255) >> 6;
     const uint8_t* blk = row_base + 144 * sb;
-    r.a = __ldg(reinterpret_cast<const uint4*>(blk));
-    r.b = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * c));
-    r.c = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * c));
+    r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+    r.q = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * c + 16 * (q & 1)));
   } else if (FMT == HQ_FMT_FP8_BLOCK) {
-    const uint4* src = reinterpret_cast<const uint4*>(row_base + k0 + 32 * half);
-    r.a = __ldg(src);
-    r.b = __ldg(src + 1);
+    r.q = __ldg(reinterpret_cast<const uint4*>(row_base + k0 + 16 * q));
     r.aux = __float_as_uint(__ldg(rel + k0 / 128));
   } else {
-    const int blk = (k0 >> 5) + half;
-    r.a = __ldg(reinterpret_cast<const uint4*>(row_base + 16 * blk));
+    const int blk = (k0 >> 5) + (q >> 1);
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(row_base + 16 * blk + 8 * (q & 1)));
+    r.q.x = v.x;
+    r.q.y = v.y;
     r.aux = __ldg(scale_row + blk);
   }
 }
 
-// Q4_K sub-block of 32: w = code * d1 - m1 with d1 = d * sc, m1 = dmin * m.  Codes are extracted as the f16
-// pair (1024 + e0, 1024 + e1) with one permute (bytes {code, 0x64}); the offset and the min go into one
-// constant C = -(m1 + 1024 * d1).  d1 and C are each split into a leading f16 and its remainder, so
+// Q4_K: w = code * d1 - m1 with d1 = d * sc, m1 = dmin * m.  Codes are extracted as the f16 pair
+// (1024 + e0, 1024 + e1) with one permute (bytes {code, 0x64}); the offset and the min go into one constant
+// C = -(m1 + 1024 * d1).  d1 and C are each split into a leading f16 and its remainder, so
 // w = fma(p, dh, Ch) + fma(p, dl, Cl) carries only the final roundings of weight-sized quantities.
-__device__ __forceinline__ void emit_q4_k(const RawA& r, int k0, int half, uint32_t (&out)[16]) {
+__device__ __forceinline__ void emit_q4_k(const RawA& r, int k0, int q, uint32_t (&out)[8]) {
   const int c = (k0 & 255) >> 6;
-  const int j = 2 * c + half;
+  const int hi = q >> 1;
+  const int j = 2 * c + hi;
   uint32_t s, m;
   if (j < 4) {
-    s = (r.a.y >> (8 * j)) & 63u;
-    m = (r.a.z >> (8 * j)) & 63u;
+    s = (r.hdr.y >> (8 * j)) & 63u;
+    m = (r.hdr.z >> (8 * j)) & 63u;
   } else {
     const int jj = j - 4;
-    s = ((r.a.w >> (8 * jj)) & 0xFu) | (((r.a.y >> (8 * jj + 6)) & 3u) << 4);
-    m = ((r.a.w >> (8 * jj + 4)) & 0xFu) | (((r.a.z >> (8 * jj + 6)) & 3u) << 4);
+    s = ((r.hdr.w >> (8 * jj)) & 0xFu) | (((r.hdr.y >> (8 * jj + 6)) & 3u) << 4);
+    m = ((r.hdr.w >> (8 * jj + 4)) & 0xFu) | (((r.hdr.z >> (8 * jj + 6)) & 3u) << 4);
   }
-  const float d1 = half_bits_to_float(r.a.x) * (float)s;
-  const float cc = -fmaf(1024.f, d1, half_bits_to_float(r.a.x >> 16) * (float)m);
+  const float d1 = half_bits_to_float(r.hdr.x) * (float)s;
+  const float cc = -fmaf(1024.f, d1, half_bits_to_float(r.hdr.x >> 16) * (float)m);
   const __half dh = __float2half_rn(d1), ch = __float2half_rn(cc);
   const __half2 dh2 = __half2half2(dh), ch2 = __half2half2(ch);
   const __half2 dl2 = __float2half2_rn(d1 - __half2float(dh));
   const __half2 cl2 = __float2half2_rn(cc - __half2float(ch));
-  const uint32_t qw[8] = {r.b.x, r.b.y, r.b.z, r.b.w, r.c.x, r.c.y, r.c.z, r.c.w};
+  const uint32_t qw[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t vm = (half ? (qw[i] >> 4) : qw[i]) & 0x0F0F0F0Fu;
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t vm = (hi ? (qw[i] >> 4) : qw[i]) & 0x0F0F0F0Fu;
     uint32_t p01 = __byte_perm(vm, 0x64646464u, 0x4140);   // f16 pair (1024 + e0, 1024 + e1)
     uint32_t p23 = __byte_perm(vm, 0x64646464u, 0x4342);
     const __half2 h01 = *reinterpret_cast<__half2*>(&p01), h23 = *reinterpret_cast<__half2*>(&p23);
@@ -176,11 +175,11 @@ __device__ __forceinline__ void emit_q4_k(const RawA& r, int k0, int half, uint3
 
 // e4m3 -> f16 is exact; the block's scale relative to the largest scale of its 128-row block (<= 1) is folded
 // in here, the largest scale itself multiplies the accumulator in the epilogue.
-__device__ __forceinline__ void emit_fp8(const RawA& r, uint32_t (&out)[16]) {
-  const uint32_t w[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
+__device__ __forceinline__ void emit_fp8(const RawA& r, uint32_t (&out)[8]) {
+  const uint32_t w[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
   const __half2 r2 = __float2half2_rn(__uint_as_float(r.aux));
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 4; ++i) {
     uint32_t lo, hi;
     asm("{\n"
         ".reg .b16 l, h;\n"
@@ -197,19 +196,19 @@ __device__ __forceinline__ void emit_fp8(const RawA& r, uint32_t (&out)[16]) {
   }
 }
 
-// MXFP4 block of 32: e2m1 pairs -> f16x2 (hardware conversion, low nibble = even element = low half), times
-// 2^(e-127) as an exact f16 power of two.  e = 0 decodes to a zero scale (the reference's table builds the
-// scale from the bits e << 23); scales outside the f16 exponent range are reported by the caller.
-__device__ __forceinline__ bool emit_mxfp4(const RawA& r, uint32_t (&out)[16]) {
+// MXFP4: e2m1 pairs -> f16x2 (hardware conversion, low nibble = even element = low half), times 2^(e-127) as
+// an exact f16 power of two.  e = 0 decodes to a zero scale (the reference's table builds the scale from the
+// bits e << 23); scales outside the f16 exponent range are reported by the caller.
+__device__ __forceinline__ bool emit_mxfp4(const RawA& r, uint32_t (&out)[8]) {
   const uint32_t e = r.aux;
   const bool in_range = (e == 0) || (e >= 113 && e <= 140);   // 2^-14 .. 2^13: products stay finite in f16
   const uint32_t ef = (e >= 113 && e <= 140) ? (e - 112) : 0u;  // f16 exponent field of 2^(e-127)
   const uint32_t sc16 = ef << 10;
   const uint32_t sc2 = sc16 | (sc16 << 16);
   const __half2 s2 = *reinterpret_cast<const __half2*>(&sc2);
-  const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+  const uint32_t w[2] = {r.q.x, r.q.y};
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 2; ++i) {
     uint32_t h[4];
     asm("{\n"
         ".reg .b8 b0, b1, b2, b3;\n"
@@ -230,36 +229,9 @@ __device__ __forceinline__ bool emit_mxfp4(const RawA& r, uint32_t (&out)[16]) {
   return in_range;
 }
 
-__device__ __forceinline__ void fetch_b(RawB& r, const void* x, int64_t elem_off) {
-  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + elem_off);
+__device__ __forceinline__ void store_chunks(uint8_t* tile, int r, int c0, const uint32_t (&v)[8]) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) r.v[i] = __ldg(src + i);
-}
-// 16-bit activations -> f16 words; bf16 goes through f32 (exact in the f16 normal range), f16 is copied
-__device__ __forceinline__ void emit_b(const RawB& r, bool convert_bf16, uint32_t (&out)[16]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t w[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      out[4 * i + j] = convert_bf16 ? pack_half2(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xFFFF0000u))
-                                    : w[j];
-  }
-}
-// f32 activations: loaded and converted in one go (only the dense path sees them)
-__device__ __forceinline__ void load_x32_f32(const void* x, int64_t elem_off, uint32_t (&out)[16]) {
-  const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + elem_off);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float4 f = __ldg(src + i);
-    out[2 * i] = pack_half2(f.x, f.y);
-    out[2 * i + 1] = pack_half2(f.z, f.w);
-  }
-}
-
-__device__ __forceinline__ void store_chunks(uint8_t* tile, int r, int c0, const uint32_t (&v)[16]) {
-#pragma unroll
-  for (int c = 0; c < 4; ++c)
+  for (int c = 0; c < 2; ++c)
     *reinterpret_cast<uint4*>(tile + swz(r, c0 + c)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
 }
 
@@ -437,12 +409,9 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
     }
   } else {
     // =========================== producers ========================================
-    const int ptid = tid - 5 * 32;            // 0..255
-    const int r = ptid >> 1, half = ptid & 1; // operand row and which 32-k half of the stage
-    const bool x_f32 = p.x_dtype == HQ_DT_F32;
-    const bool x_conv = p.x_dtype == HQ_DT_BF16;
-    const bool b_copy = p.x_is_f16_copy != 0; // f16 activations: rows go global -> shared with cp.async
-    constexpr int BROWS = TN / 32;            // activation rows per thread in copy mode (one 16-byte chunk each)
+    const int ptid = tid - 5 * 32;            // 0..511
+    const int r = ptid >> 2, q = ptid & 3;    // weight row and which 16-k quarter of the stage
+    constexpr int BROWS = TN / 64;            // activation rows per thread (one 16-byte chunk of each)
     uint32_t spin = kGgSpin;
 
     // cursor over the flattened (tile, k stage) sequence of this CTA
@@ -450,9 +419,8 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
       int w, ks;
       const uint8_t *w0, *w1, *s0, *s1;
       const float *rel0, *rel1;
-      int64_t xoff;
-      bool n_ok, x_ok;
-      int64_t boff[BROWS];    // copy mode: element offset of this thread's chunk in each of its rows, -1 = no row
+      bool n_ok;
+      int64_t boff[BROWS];    // element offset of this thread's chunk in each of its activation rows, -1 = no row
     };
     auto open_tile = [&](Cursor& c) {
       const GgTile t = gg_tile<TN>(p, c.w, n_nt);
@@ -472,33 +440,22 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         c.rel0 = p.fp8_rel_scale + g;
         if (NB == 2) c.rel1 = p.fp8_rel_scale_up + g;
       }
-      c.x_ok = false;
-      c.xoff = 0;
-      if (b_copy) {
 #pragma unroll
-        for (int j = 0; j < BROWS; ++j) {
-          const int row = (ptid >> 3) + 32 * j;
-          c.boff[j] = -1;
-          if (row < t.count) {
-            const int sp = t.row_start + row;
-            c.boff[j] = (p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp) * p.x_stride + 8 * (ptid & 7);
-          }
-        }
-      } else {
-        c.x_ok = r < t.count;
-        if (c.x_ok) {
-          const int sp = t.row_start + r;
-          c.xoff = (p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp) * p.x_stride + 32 * half;
+      for (int j = 0; j < BROWS; ++j) {
+        const int row = (ptid >> 3) + 64 * j;
+        c.boff[j] = -1;
+        if (row < t.count) {
+          const int sp = t.row_start + row;
+          c.boff[j] = (p.x_rows ? (int64_t)p.x_rows[sp] : (int64_t)sp) * p.x_stride + 8 * (ptid & 7);
         }
       }
     };
-    auto fetch = [&](const Cursor& c, RawA (&ra)[NB], RawB& rb) {
+    auto fetch = [&](const Cursor& c, RawA (&ra)[NB]) {
       const int k0 = c.ks * kTileK;
       if (c.n_ok) {
-        fetch_a<FMT>(ra[0], c.w0, c.s0, c.rel0, k0, half);
-        if (NB == 2) fetch_a<FMT>(ra[NB - 1], c.w1, c.s1, c.rel1, k0, half);
+        fetch_a<FMT>(ra[0], c.w0, c.s0, c.rel0, k0, q);
+        if (NB == 2) fetch_a<FMT>(ra[NB - 1], c.w1, c.s1, c.rel1, k0, q);
       }
-      if (!b_copy && c.x_ok && !x_f32) fetch_b(rb, p.x, c.xoff + k0);
     };
     int waited = NSTAGE - 1;                  // stages up to this index are known to be free
     auto ensure_empty = [&](int j) {
@@ -510,17 +467,18 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         waited = j;
       }
     };
+    // activation rows (f16, gathered token order -> expert order): 16 bytes global -> shared per chunk without
+    // passing through registers; a missing row is zero-filled
     auto copy_b = [&](const Cursor& c, int stage_index) {
       uint8_t* btile = smem + (stage_index % NSTAGE) * L::STAGE_BYTES + NB * kOperandBytes;
       const int k0 = c.ks * kTileK;
 #pragma unroll
       for (int j = 0; j < BROWS; ++j) {
-        const int row = (ptid >> 3) + 32 * j;
+        const int row = (ptid >> 3) + 64 * j;
         const uint32_t dst = smem_u32(btile + swz(row, ptid & 7));
         const bool ok = c.boff[j] >= 0;
         const void* src = ok ? reinterpret_cast<const void*>(reinterpret_cast<const uint16_t*>(p.x) + c.boff[j] + k0)
                              : p.x;
-        // 16 bytes global -> shared without passing through registers; a missing row is zero-filled
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0) : "memory");
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
@@ -530,12 +488,11 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
     cur.w = blockIdx.x;
     cur.ks = 0;
     RawA ra[NB], ra_next[NB];
-    RawB rb, rb_next;
     bool live = cur.w < total;
     if (live) {
       open_tile(cur);
-      fetch(cur, ra, rb);
-      if (b_copy) copy_b(cur, 0);
+      fetch(cur, ra);
+      copy_b(cur, 0);
     }
     int it = 0;
     while (live) {
@@ -551,22 +508,20 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         if (next_live) open_tile(nxt);
       }
       if (next_live) {
-        fetch(nxt, ra_next, rb_next);
-        if (b_copy) {
-          ensure_empty(it + 1);
-          copy_b(nxt, it + 1);
-        }
+        fetch(nxt, ra_next);
+        ensure_empty(it + 1);
+        copy_b(nxt, it + 1);
       }
       ensure_empty(it);
       const int s = it % NSTAGE;
       uint8_t* stage = smem + s * L::STAGE_BYTES;
       const int k0 = cur.ks * kTileK;
-      uint32_t v[16];
+      uint32_t v[8];
 #pragma unroll
       for (int bank = 0; bank < NB; ++bank) {
         if (cur.n_ok) {
           if (FMT == HQ_FMT_Q4_K) {
-            emit_q4_k(ra[bank], k0, half, v);
+            emit_q4_k(ra[bank], k0, q, v);
           } else if (FMT == HQ_FMT_FP8_BLOCK) {
             emit_fp8(ra[bank], v);
           } else {
@@ -574,24 +529,13 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = 0u;
+          for (int i = 0; i < 8; ++i) v[i] = 0u;
         }
-        store_chunks(stage + bank * kOperandBytes, r, 4 * half, v);
+        store_chunks(stage + bank * kOperandBytes, r, 2 * q, v);
       }
-      if (b_copy) {
-        // this stage's activation copies were issued one iteration ago; the next stage's may stay in flight
-        if (next_live) asm volatile("cp.async.wait_group 1;" ::: "memory");
-        else asm volatile("cp.async.wait_group 0;" ::: "memory");
-      } else {
-        if (cur.x_ok) {
-          if (x_f32) load_x32_f32(p.x, cur.xoff + k0, v);
-          else emit_b(rb, x_conv, v);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = 0u;
-        }
-        store_chunks(stage + NB * kOperandBytes, r, 4 * half, v);
-      }
+      // this stage's activation copies were issued one iteration ago; the next stage's may stay in flight
+      if (next_live) asm volatile("cp.async.wait_group 1;" ::: "memory");
+      else asm volatile("cp.async.wait_group 0;" ::: "memory");
       fence_proxy_async_smem();     // generic-proxy writes -> visible to the tensor core (async proxy)
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);
@@ -600,7 +544,6 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
       live = next_live;
 #pragma unroll
       for (int b = 0; b < NB; ++b) ra[b] = ra_next[b];
-      rb = rb_next;
     }
   }
 
@@ -678,7 +621,7 @@ bool grouped_gemm_supported(int format, int64_t n, int64_t k) {
 
 int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
   if (p.tile_rows != 128 && p.tile_rows != 256) return HQ_ERR_SHAPE;
-  if (p.tile_rows == 256 && !p.x_is_f16_copy) return HQ_ERR_FORMAT;   // wide tiles take f16 activations only
+  if (p.x_dtype != HQ_DT_F16) return HQ_ERR_FORMAT;   // activations are copied into the operand tiles as f16
   switch (p.format) {
     case HQ_FMT_Q4_K: return launch_gg_fmt<HQ_FMT_Q4_K>(p, max_tiles, stream);
     case HQ_FMT_FP8_BLOCK: return launch_gg_fmt<HQ_FMT_FP8_BLOCK>(p, max_tiles, stream);

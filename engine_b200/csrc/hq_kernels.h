@@ -65,7 +65,6 @@ struct GroupedParams {
   const int32_t* tiles;         // [n_tiles][2] = (expert, first sorted row), tiles of <= tile_rows rows
   const int32_t* tile_count;    // device word holding n_tiles
   int tile_rows;                // 128 or 256 tokens per tile
-  int x_is_f16_copy;            // activations are f16 already: rows are copied with cp.async, no conversion
   const int32_t* expert_bounds;
   const int32_t* x_rows;        // sorted row -> activation row (nullptr = identity)
   const int32_t* y_rows;        // sorted row -> output row (nullptr = identity)
@@ -115,6 +114,7 @@ int32_t launch_fp8_block_quant(const void* w, int w_dtype, int64_t rows, int64_t
                                uint8_t* codes, float* scales, cudaStream_t stream);
 int32_t launch_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t rows, int64_t cols, int by,
                                  int bx, void* out, int out_dtype, cudaStream_t stream);
+int32_t launch_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, cudaStream_t stream);
 int32_t launch_gated_act(const void* gate, const void* up, int dtype, int64_t n, int interleaved,
                          const hq_act_args& act, void* out, cudaStream_t stream);
 

@@ -231,6 +231,12 @@ int32_t hq_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t 
 int32_t hq_fp8_scale_prepare(const float* scales, int32_t n_experts, int64_t n, int64_t k, float* tile_scale_out,
                              float* rel_scale_out, void* stream);
 
+/* Elementwise dtype conversion (f32 / f16 / bf16).  The prefill-sized calls run on the tensor cores only
+ * when the activations are f16 (their rows are copied straight into the operand tiles); a host holding
+ * bf16 or f32 activations converts once with this call -- the reference's Tensor::to_dtype
+ * (e.g. hanzo-quant/src/gguf/mod.rs:196-209). */
+int32_t hq_convert(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int64_t n_elems, void* stream);
+
 /* ---- gated activations as stand-alone ops -----------------------------------
  * out = act(gate, up) elementwise over n_elems; interleaved = 1 reads pairs
  * (gate, up) from `gate` ([..., I, 2]) and ignores `up`.  Replaces fused_glu_*,
