@@ -487,16 +487,18 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
     Cursor cur;
     cur.w = blockIdx.x;
     cur.ks = 0;
-    RawA ra[NB], ra_next[NB];
+    // two register sets used alternately: the set being loaded for the next stage is never copied, so nothing
+    // waits on those loads until the stage after is converted
+    RawA ra0[NB], ra1[NB];
     bool live = cur.w < total;
     if (live) {
       open_tile(cur);
-      fetch(cur, ra);
+      fetch(cur, ra0);
       copy_b(cur, 0);
     }
     int it = 0;
-    while (live) {
-      // issue the next stage's loads before converting this one
+    // one stage: start the next stage's loads into `ld`, convert this stage from `use`
+    auto step = [&](RawA (&use)[NB], RawA (&ld)[NB]) {
       Cursor nxt = cur;
       bool next_live = true;
       if (cur.ks + 1 < n_ks) {
@@ -508,7 +510,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
         if (next_live) open_tile(nxt);
       }
       if (next_live) {
-        fetch(nxt, ra_next);
+        fetch(nxt, ld);
         ensure_empty(it + 1);
         copy_b(nxt, it + 1);
       }
@@ -521,11 +523,11 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
       for (int bank = 0; bank < NB; ++bank) {
         if (cur.n_ok) {
           if (FMT == HQ_FMT_Q4_K) {
-            emit_q4_k(ra[bank], k0, q, v);
+            emit_q4_k(use[bank], k0, q, v);
           } else if (FMT == HQ_FMT_FP8_BLOCK) {
-            emit_fp8(ra[bank], v);
+            emit_fp8(use[bank], v);
           } else {
-            if (!emit_mxfp4(ra[bank], v)) report_status(p.status, HQ_DEV_BAD_INDEX, 600);
+            if (!emit_mxfp4(use[bank], v)) report_status(p.status, HQ_DEV_BAD_INDEX, 600);
           }
         } else {
 #pragma unroll
@@ -542,8 +544,11 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
       ++it;
       cur = nxt;
       live = next_live;
-#pragma unroll
-      for (int b = 0; b < NB; ++b) ra[b] = ra_next[b];
+    };
+    while (live) {
+      step(ra0, ra1);
+      if (!live) break;
+      step(ra1, ra0);
     }
   }
 
