@@ -239,13 +239,13 @@ __device__ __forceinline__ float gg_gated(float g, float u, const hq_act_args& a
   if (a.act == HQ_ACT_GPTOSS) {
     g = fminf(g, a.limit);
     u = fminf(fmaxf(u, -a.limit), a.limit);
-    return (u + 1.f) * (g / (1.f + expf(-a.alpha * g)));
+    return (u + 1.f) * __fdividef(g, 1.f + __expf(-a.alpha * g));
   }
   if (a.has_limit) {
     g = fminf(g, a.limit);
     u = fminf(fmaxf(u, -a.limit), a.limit);
   }
-  return (g / (1.f + expf(-g))) * u;
+  return __fdividef(g, 1.f + __expf(-g)) * u;
 }
 
 struct GgTile {
@@ -379,12 +379,27 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
       const int64_t out_n = interleaved ? (n >> 1) : n;
       const bool writer = n_ok && (!interleaved || (n & 1) == 0);
       const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * NB * kTileN);
+      // Output row of the token in column 32*cc + lane (-1 past the tile's tokens).  One coalesced load per
+      // column group, issued a group ahead, then broadcast by shuffle: a load per stored element would
+      // serialise the stores behind the load latency, since the compiler must assume y aliases y_rows.
+      const int* __restrict__ yrows = p.y_rows;
+      auto row_of = [&](int cc) -> int {
+        const int col = 32 * cc + lane;
+        if (cc >= kTileN / 32 || col >= t.count) return -1;
+        const int sp = t.row_start + col;
+        return yrows != nullptr ? __ldg(yrows + sp) : sp;
+      };
+      const int esz = dtype_size(p.y_dtype);
+      char* const ybase = reinterpret_cast<char*>(p.y) + out_n * esz;
+      const int64_t ystride_b = (int64_t)p.y_stride * esz;
+      int myrow = row_of(0);
 #pragma unroll 1
       for (int cc = 0; cc < kTileN / 32; ++cc) {
         if (32 * cc >= t.count) break;          // warp-uniform: no tokens in this column group
         uint32_t v0[32], v1[32];
         tmem_ld32(taddr + 32 * cc, v0);
         if (NB == 2) tmem_ld32(taddr + kTileN + 32 * cc, v1);
+        const int nextrow = row_of(cc + 1);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -395,13 +410,22 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
             const float partner = __shfl_xor_sync(0xffffffffu, r, 1);
             r = gg_gated(r, partner, p.act);
           }
-          const int col = 32 * cc + j;
-          if (writer && col < t.count) {
-            const int sp = t.row_start + col;
-            const int64_t orow = p.y_rows ? (int64_t)p.y_rows[sp] : (int64_t)sp;
-            store_from_float(p.y, p.y_dtype, orow * p.y_stride + out_n, r);
-          }
+          v0[j] = __float_as_uint(r);
         }
+        auto store_group = [&](auto cvt) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int orow = __shfl_sync(0xffffffffu, myrow, j);
+            if (writer && orow >= 0) {
+              using T = decltype(cvt(0.f));
+              *reinterpret_cast<T*>(ybase + orow * ystride_b) = cvt(__uint_as_float(v0[j]));
+            }
+          }
+        };
+        if (p.y_dtype == HQ_DT_BF16) store_group([](float f) { return __float2bfloat16_rn(f); });
+        else if (p.y_dtype == HQ_DT_F16) store_group([](float f) { return __float2half_rn(f); });
+        else store_group([](float f) { return f; });
+        myrow = nextrow;
       }
       tc_fence_before();
       __syncwarp();
