@@ -15,8 +15,7 @@
 // a fixed order and writes the outputs, so results are bit-reproducible.
 //
 // Algorithmic bytes per launch: N*K*bits/8 (weights) + M*K*sizeof(x) + M*N*sizeof(y).
-#include "hq_common.cuh"
-#include "hq_kernels.h"
+#include "hq_gemv_shared.cuh"
 
 namespace hq {
 
@@ -369,42 +368,7 @@ __device__ __forceinline__ void mx_compute(float (&acc)[4], const B32Regs& r, fl
   acc[3] = fmaf(sB, blk[3], acc[3]);
 }
 
-__device__ __forceinline__ float gated(float g, float u, const hq_act_args& a) {
-  if (a.act == HQ_ACT_GPTOSS) {
-    g = fminf(g, a.limit);
-    u = fminf(fmaxf(u, -a.limit), a.limit);
-    const float glu = g / (1.f + expf(-a.alpha * g));
-    return (u + 1.f) * glu;
-  }
-  if (a.has_limit) {
-    g = fminf(g, a.limit);
-    u = fminf(fmaxf(u, -a.limit), a.limit);
-  }
-  return (g / (1.f + expf(-g))) * u;
-}
-
 // ---- the kernel --------------------------------------------------------------
-struct WorkItem {
-  int expert, row0, nrows, n0, y;
-};
-
-template <int RT>
-__device__ __forceinline__ WorkItem get_item(const GemvParams& p, int w, int n_rt) {
-  WorkItem it;
-  it.y = w / n_rt;
-  it.n0 = (w - it.y * n_rt) * RT;
-  if (p.tiles != nullptr) {
-    it.expert = p.tiles[2 * it.y];
-    it.row0 = p.tiles[2 * it.y + 1];
-    it.nrows = min(8, p.expert_bounds[it.expert + 1] - it.row0);
-  } else {
-    it.expert = 0;
-    it.row0 = 8 * it.y;
-    it.nrows = min(8, p.m - it.row0);
-  }
-  return it;
-}
-
 // Persistent: each CTA walks work items (activation-row group y, 16-row output tile) with a stride of
 // gridDim.x; the producer warp keeps the weight ring full across item boundaries.
 template <int FMT, int KC>
@@ -678,65 +642,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(&red_free[rb]);
       // rows of this lane: n0 + g (+8); columns 2t, 2t+1
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int n = wi.n0 + g + 8 * half;
-        const bool n_ok = n < p.n;
-        float v0 = acc[0][2 * half], v1 = acc[0][2 * half + 1];
-        float u0 = acc[1][2 * half], u1 = acc[1][2 * half + 1];
-        if (n_ok && p.bias != nullptr) {
-          const float bv = load_as_float(p.bias, p.bias_dtype, (int64_t)wi.expert * p.n + n);
-          v0 += bv; v1 += bv;
-        }
-        if (n_ok && p.n_banks == 2 && p.bias_up != nullptr) {
-          const float bv = load_as_float(p.bias_up, p.bias_dtype, (int64_t)wi.expert * p.n + n);
-          u0 += bv; u1 += bv;
-        }
-        int64_t out_n = n;
-        bool write = n_ok;
-        if (p.act.act != HQ_ACT_NONE) {
-          if (p.n_banks == 2) {
-            v0 = gated(v0, u0, p.act);
-            v1 = gated(v1, u1, p.act);
-          } else {
-            // interleaved bank: even row = gate, odd row = up (the neighbour lane group g+1)
-            const float p0 = __shfl_down_sync(0xffffffffu, v0, 4);
-            const float p1 = __shfl_down_sync(0xffffffffu, v1, 4);
-            v0 = gated(v0, p0, p.act);
-            v1 = gated(v1, p1, p.act);
-            write = n_ok && (n & 1) == 0;
-            out_n = n >> 1;
-          }
-        }
-        if (write) {
-#pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
-            const int col = 2 * t + cc;
-            if (col < wi.nrows) {
-              const int64_t yr = p.y_rows ? (int64_t)p.y_rows[wi.row0 + col] : (int64_t)(wi.row0 + col);
-              store_from_float(p.y, p.y_dtype, yr * p.y_stride + out_n, cc ? v1 : v0);
-            }
-          }
-        }
-      }
+      gemv_store_item(p, wi, g, 2 * t, true, acc);
     }
     ++item;
   }
 }
 
 // ---- host launcher ------------------------------------------------------------
-static int sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
 template <int FMT, int KC>
 static int32_t launch_cfg(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
   using L = GemvStage<FMT, KC>;
@@ -792,7 +704,7 @@ int32_t launch_gemv(const GemvParams& p, int n_y_max, cudaStream_t stream) {
   const int max_rows = p.tiles != nullptr ? 8 : (p.m < 8 ? p.m : 8);
   // chunk sizes keep every bulk copy (one row segment) at 2 KiB or more
   switch (p.format) {
-    case HQ_FMT_Q8_0: return launch_cfg<HQ_FMT_Q8_0, 2048>(p, n_y_max, max_rows, stream);
+    case HQ_FMT_Q8_0: return launch_gemv_q8(p, n_y_max, max_rows, stream);
     case HQ_FMT_Q4_K: return launch_cfg<HQ_FMT_Q4_K, 4096>(p, n_y_max, max_rows, stream);
     case HQ_FMT_FP8_BLOCK: return launch_cfg<HQ_FMT_FP8_BLOCK, 2048>(p, n_y_max, max_rows, stream);
     case HQ_FMT_MXFP4: return launch_cfg<HQ_FMT_MXFP4, 4096>(p, n_y_max, max_rows, stream);

@@ -1,0 +1,529 @@
+// Decode-regime mat-vec for GGUF Q8_0 weights (1..8 activation rows per work item), dense and
+// expert-indexed.
+//
+// HBM-bound: every weight byte is read once, straight from the 34-byte blocks {f16 d, int8 q[32]}.
+// What limits such a kernel on the SM side is the number of instructions spent per weight byte, so the
+// int8 codes are never converted: they go into the integer warp MMA (m16n8k32, s8 x s8 -> s32) exactly as
+// they lie in the block.  The activations are made to fit instead: each 128-element group of an
+// activation row is written as x ~= s * (h + l / 254) with int8 h and l (s a power of two, h = rint(x / s), l the
+// rounded remainder; the error is below max|x| / 32000 per element), and h and l occupy separate MMA columns.
+// One MMA then yields the exact integer dot products of one block for all rows and columns; they leave
+// the accumulator as floats through a bias constant (no conversion instruction), are multiplied by the
+// block's d, summed over the four blocks of a group and scaled once by the group's activation scale.
+//
+// Layout of the work: persistent CTAs (one per SM) walk items of 16 output rows.  A producer warp streams
+// the item's row segments (2176 bytes = 64 blocks per bulk async copy; copies below 2 KiB cannot keep HBM
+// busy) into a shared-memory ring with mbarrier completion.  Sixteen consumer warps each take one group of
+// four blocks (136 bytes, 8-byte aligned) of every stage, so the misaligned block payloads are fetched
+// with a fixed pattern of 8- and 4-byte loads and four funnel shifts per row.  Within an MMA the k order
+// is free as long as both operands agree: lane t owns payload bytes 8t..8t+7 of a block, and reads the
+// same eight positions of the staged activations with one 8-byte load.  Partial sums of the sixteen K
+// slices meet in shared memory and are added in warp order by one (rotating) warp: results are
+// bit-reproducible.
+//
+// Algorithmic bytes per launch: N*K*34/32 (weights) + M*K*sizeof(x) + M*N*sizeof(y).
+#include "hq_gemv_shared.cuh"
+
+namespace hq {
+
+#ifndef HQ_Q8_GROUPS_PER_WARP
+#define HQ_Q8_GROUPS_PER_WARP 2
+#endif
+constexpr int kQ8GroupsPerWarp = HQ_Q8_GROUPS_PER_WARP;   // 128-element groups a warp takes from every stage
+constexpr int kQ8Warps = 16 / kQ8GroupsPerWarp;  // consumer warps
+constexpr int kQ8Consumers = kQ8Warps * 32;
+constexpr int kQ8Threads = kQ8Consumers + 32;    // + producer warp
+constexpr int kQ8KC = 2048;                      // k per stage
+constexpr int kQ8Seg = kQ8KC / 32 * 34;          // bytes of one row segment (one bulk copy)
+constexpr int kQ8Pitch = kQ8Seg + 32;            // row pitch in a stage: = 32 (mod 128), 8-byte loads of 4 rows
+                                                 // x 4 lanes cover all banks
+constexpr int kQ8RT = 16;
+constexpr int kQ8StageBytes = kQ8RT * kQ8Pitch;
+constexpr int kQ8MaxStages = 8;
+constexpr int kQ8SmemBudget = 227 * 1024;
+constexpr int kQ8XGroups = 8;                    // 16-byte activation groups a thread prefetches per epoch
+constexpr uint32_t kQ8Spin = 1u << 22;
+constexpr int kQ8Magic = 0x4B400000;             // 1.5 * 2^23 as f32 bits: magic + n reads as 12582912.f + n
+static_assert(kQ8Seg >= 2048 && kQ8Seg % 16 == 0, "bulk copy size");
+static_assert(kQ8Pitch % 128 == 32, "row pitch must spread banks");
+
+// shared-memory plan of one launch (computed on the host)
+struct Q8Layout {
+  int nstage;
+  int ncols;        // staged int8 columns: 8 = (h, l) of <= 4 activation rows, 16 = (h, l) of <= 8
+  int xk;           // activation columns staged per epoch (whole stages)
+  int xk_sub;       // columns one register prefetch covers
+  int xpitch;       // bytes between staged columns, = 32 (mod 128)
+  int x_bytes;
+  int off_x, off_sx, off_red, off_bar, total;
+};
+
+__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1, int c) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+}
+
+// ---- activation staging ---------------------------------------------------------------------
+// Raw activation bytes are fetched one epoch ahead into registers (16 bytes per group), then every
+// 128-element group of a row is quantized by the 16 (or, for f32 input, 32) lanes that hold it.
+struct Q8XPrefetch {
+  uint4 v[kQ8XGroups];
+};
+
+__device__ __forceinline__ void q8_x_prefetch(Q8XPrefetch& pf, const GemvParams& p, int row0, int nrows, int k0,
+                                              int k_len, int tid) {
+  const int esz = dtype_size(p.x_dtype);
+  const int epg = 16 / esz;              // elements per 16-byte group
+  const int gpr = k_len / epg;           // groups per activation row in this epoch
+  const int ngroups = nrows * gpr;
+#pragma unroll
+  for (int i = 0; i < kQ8XGroups; ++i) {
+    const int it = i * kQ8Consumers + tid;
+    if (it < ngroups) {
+      const int col = it / gpr;
+      const int kk = (it - col * gpr) * epg;
+      const int64_t xr = p.x_rows ? (int64_t)p.x_rows[row0 + col] : (int64_t)(row0 + col);
+      const char* src = (const char*)p.x + (xr * p.x_stride + k0 + kk) * esz;
+      pf.v[i] = __ldg(reinterpret_cast<const uint4*>(src));
+    }
+  }
+}
+
+// k_len is a multiple of 256, so a warp never straddles two activation rows and is valid or idle as a whole.
+// xq: staged int8 columns of this epoch (column c at xq + c * xpitch), already offset to the sub-range;
+// sx: scale table [group][ncols] f32, likewise offset.
+__device__ __forceinline__ void q8_x_commit(const Q8XPrefetch& pf, const GemvParams& p, int nrows, int k_len, int tid,
+                                            uint8_t* xq, int xpitch, float* sx, int ncols) {
+  const int esz = dtype_size(p.x_dtype);
+  const int epg = 16 / esz;
+  const int gpr = k_len / epg;
+  const int ngroups = nrows * gpr;
+  const int l_off = ncols >> 1;          // column of the remainder term relative to the leading term
+#pragma unroll
+  for (int i = 0; i < kQ8XGroups; ++i) {
+    const int it = i * kQ8Consumers + tid;
+    if (it < ngroups) {                  // uniform across the warp
+      const int col = it / gpr;
+      const int kk = (it - col * gpr) * epg;
+      const uint4 raw = pf.v[i];
+      float f[8];
+      if (p.x_dtype == HQ_DT_F32) {
+        f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y);
+        f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+        f[4] = f[5] = f[6] = f[7] = 0.f;
+      } else if (p.x_dtype == HQ_DT_BF16) {
+        f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+        f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+        f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xFFFF0000u);
+        f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xFFFF0000u);
+      } else {
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = __half22float2(h[j]);
+          f[2 * j] = t.x; f[2 * j + 1] = t.y;
+        }
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {      // a NaN or an infinity makes the whole group's scale non-finite
+        const float a = fabsf(f[j]);
+        amax = (a <= 3.0e38f) ? fmaxf(amax, a) : __int_as_float(0x7f800000);
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+      if (epg == 4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+      // The step s is the power of two at or above amax / 127 (not below 2^-100), so x / s and the products
+      // with s are exact: an activation that is a small multiple of s (a one-hot row, say) passes through
+      // without any rounding.  Non-finite input must not turn into a finite output: its step is a NaN.
+      const bool finite = amax <= 3.0e38f;
+      const uint32_t tb = __float_as_uint(fmaxf(amax / 127.f, 7.888609052e-31f));
+      const float s = finite ? __uint_as_float((tb + 0x007FFFFFu) & 0x7F800000u) : __int_as_float(0x7fc00000);
+      const float inv = (finite && amax > 0.f) ? 1.f / s : 0.f;
+      uint32_t hq[2] = {0u, 0u}, lq[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float v = f[j] * inv;
+        const float h = rintf(v);
+        const float l = rintf((v - h) * 254.f);
+        hq[j >> 2] |= ((uint32_t)(int)h & 0xFFu) << (8 * (j & 3));
+        lq[j >> 2] |= ((uint32_t)(int)l & 0xFFu) << (8 * (j & 3));
+      }
+      uint8_t* dh = xq + col * xpitch + kk;
+      uint8_t* dl = dh + l_off * xpitch;
+      if (epg == 8) {
+        *reinterpret_cast<uint2*>(dh) = make_uint2(hq[0], hq[1]);
+        *reinterpret_cast<uint2*>(dl) = make_uint2(lq[0], lq[1]);
+      } else {
+        *reinterpret_cast<uint32_t*>(dh) = hq[0];
+        *reinterpret_cast<uint32_t*>(dl) = lq[0];
+      }
+      if ((kk & 127) == 0) {
+        float* d = sx + (kk >> 7) * ncols + col;
+        d[0] = s;
+        d[l_off] = s * (1.f / 254.f);
+      }
+    }
+  }
+}
+
+// ---- one group: four blocks x 16 weight rows x NCS column sets --------------------------------
+// Fragment ownership: lane = 4*g + t.  A rows g and g+8; B column g of each column set; accumulator
+// element 0, 1 = (row g, columns 2t, 2t+1), element 2, 3 = row g+8.
+//   pa, pb : shared addresses of the group in rows g and g+8, plus 8t
+//   da, db : the same without the 8t (block headers)
+//   xq     : shared address of staged column g at this group's first element, plus 8t
+//   cs_stride : bytes between column sets (8 staged columns)
+//   sx     : shared address of this group's scale-table row, plus 8t bytes (columns 2t, 2t+1)
+template <int NCS>
+__device__ __forceinline__ void q8_group(float (&acc)[NCS][4], uint32_t pa, uint32_t pb, uint32_t da, uint32_t db,
+                                         uint32_t xq, uint32_t cs_stride, uint32_t sx) {
+  // ---- all shared loads first ----
+  const uint2 a0 = lds64<0>(pa);   const uint32_t a0x = lds32<8>(pa);
+  const uint32_t a1l = lds32<36>(pa), a1h = lds32<40>(pa);
+  const uint32_t a2x = lds32<68>(pa); const uint2 a2 = lds64<72>(pa);
+  const uint2 a3 = lds64<104>(pa);
+  const uint2 b0 = lds64<0>(pb);   const uint32_t b0x = lds32<8>(pb);
+  const uint32_t b1l = lds32<36>(pb), b1h = lds32<40>(pb);
+  const uint32_t b2x = lds32<68>(pb); const uint2 b2 = lds64<72>(pb);
+  const uint2 b3 = lds64<104>(pb);
+  uint2 xb[NCS][4];
+  uint2 sxv[NCS];
+#pragma unroll
+  for (int c = 0; c < NCS; ++c) {
+    const uint32_t xc = xq + c * cs_stride;
+    xb[c][0] = lds64<0>(xc); xb[c][1] = lds64<32>(xc); xb[c][2] = lds64<64>(xc); xb[c][3] = lds64<96>(xc);
+    sxv[c] = lds64(sx + 32u * c);
+  }
+  uint32_t dA[4], dB[4];
+  dA[0] = lds16<0>(da); dA[1] = lds16<34>(da); dA[2] = lds16<68>(da); dA[3] = lds16<102>(da);
+  dB[0] = lds16<0>(db); dB[1] = lds16<34>(db); dB[2] = lds16<68>(db); dB[3] = lds16<102>(db);
+
+  // ---- block payloads: lane t owns bytes 8t..8t+7 of each block (payloads start at 2, 36, 70, 104) ----
+  uint32_t alo[4], ahi[4], blo[4], bhi[4];
+  alo[0] = __funnelshift_r(a0.x, a0.y, 16); ahi[0] = __funnelshift_r(a0.y, a0x, 16);
+  alo[1] = a1l;                             ahi[1] = a1h;
+  alo[2] = __funnelshift_r(a2x, a2.x, 16);  ahi[2] = __funnelshift_r(a2.x, a2.y, 16);
+  alo[3] = a3.x;                            ahi[3] = a3.y;
+  blo[0] = __funnelshift_r(b0.x, b0.y, 16); bhi[0] = __funnelshift_r(b0.y, b0x, 16);
+  blo[1] = b1l;                             bhi[1] = b1h;
+  blo[2] = __funnelshift_r(b2x, b2.x, 16);  bhi[2] = __funnelshift_r(b2.x, b2.y, 16);
+  blo[3] = b3.x;                            bhi[3] = b3.y;
+  float fA[4], fB[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    fA[j] = half_bits_to_float(dA[j]);
+    fB[j] = half_bits_to_float(dB[j]);
+  }
+#pragma unroll
+  for (int c = 0; c < NCS; ++c) {
+    float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int d[4];
+      mma_s8_16832(d, alo[j], blo[j], ahi[j], bhi[j], xb[c][j].x, xb[c][j].y, kQ8Magic);
+      // |sum| <= 32 * 128 * 127 < 2^22, so the biased word is an exact float
+      tmp[0] = fmaf(fA[j], __int_as_float(d[0]) - 12582912.f, tmp[0]);
+      tmp[1] = fmaf(fA[j], __int_as_float(d[1]) - 12582912.f, tmp[1]);
+      tmp[2] = fmaf(fB[j], __int_as_float(d[2]) - 12582912.f, tmp[2]);
+      tmp[3] = fmaf(fB[j], __int_as_float(d[3]) - 12582912.f, tmp[3]);
+    }
+    const float s0 = __uint_as_float(sxv[c].x), s1 = __uint_as_float(sxv[c].y);
+    acc[c][0] = fmaf(tmp[0], s0, acc[c][0]);
+    acc[c][1] = fmaf(tmp[1], s1, acc[c][1]);
+    acc[c][2] = fmaf(tmp[2], s0, acc[c][2]);
+    acc[c][3] = fmaf(tmp[3], s1, acc[c][3]);
+  }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------
+// NCS = column sets per block: 1 when every work item has at most 4 activation rows (columns 0-3 hold the
+// leading terms, 4-7 the remainders), 2 for up to 8 rows (set 0 = leading terms, set 1 = remainders).
+template <int NCS>
+__global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams p, const Q8Layout lay) {
+  constexpr int WK = kQ8Warps;
+  constexpr int RT = kQ8RT;
+  constexpr int KC = kQ8KC;
+  const int NSTAGE = lay.nstage;
+  extern __shared__ __align__(128) uint8_t smem[];
+
+  const int n_rt = (p.n + RT - 1) / RT;
+  const int n_y = p.tiles != nullptr ? p.tile_count[0] : (p.m + 7) / 8;
+  const int total = n_y * n_rt;
+  if ((int)blockIdx.x >= total) return;
+  const int kXK = lay.xk;
+  const int xk_sub = lay.xk_sub;
+  const int n_super = (p.k + kXK - 1) / kXK;
+
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar);
+  uint64_t* empty = full + kQ8MaxStages;
+  uint64_t* red_full = empty + kQ8MaxStages;   // [2] partial sums of an item are all written
+  uint64_t* red_free = red_full + 2;           // [2] ... and have been consumed
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], WK);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&red_full[b], WK);
+      mbar_init(&red_free[b], 1);
+    }
+    fence_barrier_init();
+  }
+  // zero the staged activations once: columns beyond an item's row count must read as zero
+  for (int i = tid; i < lay.x_bytes / 16; i += kQ8Threads)
+    reinterpret_cast<uint4*>(smem + lay.off_x)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+
+  const int64_t row_bytes = (int64_t)p.k / 32 * 34;
+  const int nchunk = (p.k + KC - 1) / KC;
+
+  if (warp == WK) {
+    // ================= producer warp: stream weight row segments =================================
+    uint32_t spin = kQ8Spin;
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    int it = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x) {
+      const WorkItem wi = get_item<RT>(p, w, n_rt);
+      if (wi.nrows <= 0) continue;
+      const int rows_valid = min(RT, p.n - wi.n0);
+      for (int chunk = 0; chunk < nchunk; ++chunk) {
+        const int kc_len = min(KC, p.k - chunk * KC);
+        const uint32_t bytes = (uint32_t)(kc_len / 32 * 34);
+        for (int bank = 0; bank < p.n_banks; ++bank, ++it) {
+          const int s = it % NSTAGE;
+          if (it >= NSTAGE) {
+            if (!mbar_wait_backoff(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
+              // give up waiting but keep the control flow intact: results are invalid and flagged
+              if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 100 + s);
+              spin = 1;
+            }
+          }
+          const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(bank == 0 ? p.w : p.w_up) +
+                                (int64_t)wi.expert * p.w_expert_stride + (int64_t)wi.n0 * row_bytes +
+                                (int64_t)chunk * kQ8Seg;
+          if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * (uint32_t)rows_valid);
+          __syncwarp();
+          uint8_t* dst = smem + s * kQ8StageBytes;
+          if (lane < rows_valid)
+            bulk_g2s_hint(dst + lane * kQ8Pitch, wsrc + (int64_t)lane * row_bytes, bytes, &full[s], policy);
+        }
+      }
+    }
+    return;
+  }
+
+  // ================= consumer warps ================================================================
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* xq = smem + lay.off_x;
+  float* sx = reinterpret_cast<float*>(smem + lay.off_sx);
+  float* red = reinterpret_cast<float*>(smem + lay.off_red);   // [2 buffers][banks][warps][4][32]
+  const int xpitch = lay.xpitch;
+  const int ncols = lay.ncols;
+  const uint32_t cs_stride = 8u * (uint32_t)xpitch;
+  // this lane's staged column (column g of every set), its group within a stage, its scale-table columns
+  const uint32_t xq_lane = smem_u32(xq) + (uint32_t)g * xpitch + 128u * warp + 8u * t;
+  const uint32_t sx_lane = smem_u32(sx) + (uint32_t)warp * ncols * 4u + 8u * t;
+
+  Q8XPrefetch pf;
+  bool pf_valid = false;
+  int staged_y = -1;        // activation rows currently staged (valid when n_super == 1)
+  int staged_rows = 0;
+  {
+    const WorkItem w0 = get_item<RT>(p, blockIdx.x, n_rt);
+    if (w0.nrows > 0) {
+      q8_x_prefetch(pf, p, w0.row0, w0.nrows, 0, min(xk_sub, p.k), tid);
+      pf_valid = true;
+    }
+  }
+
+  uint32_t spin = kQ8Spin;
+  int it = 0, item = 0;
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    const WorkItem wi = get_item<RT>(p, w, n_rt);
+    if (wi.nrows <= 0) continue;
+    float acc[2][NCS][4];
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+#pragma unroll
+      for (int c = 0; c < NCS; ++c)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[b][c][i] = 0.f;
+    for (int sc = 0; sc < n_super; ++sc) {
+      const int k_base = sc * kXK;
+      const int k_len = min(kXK, p.k - k_base);
+      if (n_super > 1 || wi.y != staged_y) {
+        // ---- stage this epoch's activations (all consumer warps) ----------------------------------
+        if (!pf_valid) q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base, min(xk_sub, k_len), tid);
+        named_bar_sync(1, kQ8Consumers);       // everyone is done reading the previous epoch
+        // columns left over from an earlier item with more rows than this one must read as zero
+        if (staged_rows > wi.nrows) {
+          const int per_col = xpitch / 16;
+          const int stale = staged_rows - wi.nrows;
+          for (int i = tid; i < 2 * stale * per_col; i += kQ8Consumers) {
+            const int half = i / (stale * per_col);
+            const int j = i - half * (stale * per_col);
+            const int col = wi.nrows + j / per_col + half * (ncols >> 1);
+            reinterpret_cast<uint4*>(xq + col * xpitch)[j % per_col] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        staged_rows = wi.nrows;
+        q8_x_commit(pf, p, wi.nrows, min(xk_sub, k_len), tid, xq, xpitch, sx, ncols);
+        for (int sub = xk_sub; sub < k_len; sub += xk_sub) {   // wide input: the rest is fetched now
+          q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base + sub, min(xk_sub, k_len - sub), tid);
+          q8_x_commit(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xq + sub, xpitch, sx + (sub >> 7) * ncols,
+                      ncols);
+        }
+        staged_y = wi.y;
+        pf_valid = false;
+        // fetch the next epoch's activations while this one is being consumed
+        if (sc + 1 < n_super) {
+          q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base + kXK, min(xk_sub, p.k - k_base - kXK), tid);
+          pf_valid = true;
+        } else if (w + (int)gridDim.x < total) {
+          const WorkItem nx = get_item<RT>(p, w + gridDim.x, n_rt);
+          if (nx.nrows > 0 && (n_super > 1 || nx.y != wi.y)) {
+            q8_x_prefetch(pf, p, nx.row0, nx.nrows, 0, min(xk_sub, p.k), tid);
+            pf_valid = true;
+          }
+        }
+        named_bar_sync(1, kQ8Consumers);
+      }
+      const int c0 = k_base / KC, c1 = (k_base + k_len + KC - 1) / KC;
+      for (int chunk = c0; chunk < c1; ++chunk) {
+        const int ngroups = min(KC, p.k - chunk * KC) >> 7;   // 128-element groups in this stage
+        const uint32_t kx = (uint32_t)(chunk * KC - k_base);  // offset of the stage inside the staged activations
+#pragma unroll
+        for (int bank = 0; bank < 2; ++bank) {
+          if (bank >= p.n_banks) break;
+          const int s = it % NSTAGE;
+          if (!mbar_wait(&full[s], (it / NSTAGE) & 1, spin)) {
+            // bounded wait ran out: flag it and carry on (every warp still reaches every barrier)
+            if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 200 + s);
+            spin = 1;
+          }
+          ++it;
+#pragma unroll
+          for (int gi = 0; gi < kQ8GroupsPerWarp; ++gi) {
+            const int grp = warp + gi * WK;
+            if (grp < ngroups) {
+              const uint32_t da = smem_u32(smem + s * kQ8StageBytes) + (uint32_t)g * kQ8Pitch + 136u * grp;
+              const uint32_t db = da + 8u * kQ8Pitch;
+              q8_group<NCS>(acc[bank], da + 8u * t, db + 8u * t, da, db, xq_lane + kx + 128u * (gi * WK), cs_stride,
+                            sx_lane + ((kx >> 7) + gi * WK) * (uint32_t)ncols * 4u);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[s]);
+        }
+      }
+    }
+
+    // ---- hand the K-split partials to one warp (rotating), which adds them in warp order ------------
+    const int rb = item & 1;
+    float* rbuf = red + rb * (p.n_banks * WK * 4 * 32);
+    if (item >= 2) {
+      if (!mbar_wait(&red_free[rb], ((item >> 1) - 1) & 1, spin)) {
+        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 300 + rb);
+        spin = 1;
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+      if (b < p.n_banks) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          rbuf[((b * WK + warp) * 4 + i) * 32 + lane] = NCS == 2 ? acc[b][0][i] + acc[b][NCS - 1][i] : acc[b][0][i];
+      }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&red_full[rb]);
+    if (warp == (item % WK)) {
+      if (!mbar_wait_backoff(&red_full[rb], (item >> 1) & 1, spin)) {
+        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + rb);
+        spin = 1;
+      }
+      float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+        if (b < p.n_banks) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < WK; ++j) sum += rbuf[((b * WK + j) * 4 + i) * 32 + lane];
+            // four-row layout: the remainder columns 4..7 sit two lanes further on
+            if (NCS == 1) sum += __shfl_down_sync(0xffffffffu, sum, 2);
+            v[b][i] = sum;
+          }
+        }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_free[rb]);
+      gemv_store_item(p, wi, g, 2 * t, NCS == 2 || t < 2, v);
+    }
+    ++item;
+  }
+}
+
+// ---- host launcher -----------------------------------------------------------------------------
+template <int NCS>
+static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
+  // Shared-memory plan: stage as many activation columns as leave at least four ring stages (the whole K when
+  // it fits -- then a persistent CTA quantizes its activations once), give every remaining byte to the ring.
+  Q8Layout lay{};
+  lay.ncols = 8 * NCS;
+  const int esz = dtype_size(p.x_dtype);
+  const int k_round = (p.k + kQ8KC - 1) / kQ8KC * kQ8KC;
+  const int candidates[3] = {k_round, 8192 < k_round ? 8192 : k_round, 4096 < k_round ? 4096 : k_round};
+  for (int c = 0; c < 3; ++c) {
+    lay.xk = candidates[c];
+    lay.xpitch = lay.xk + 32;
+    lay.x_bytes = lay.ncols * lay.xpitch;
+    const int sx_bytes = (lay.xk / 128) * lay.ncols * 4;
+    const int red_bytes = 2 * p.n_banks * kQ8Warps * 4 * 32 * 4;
+    const int bar_bytes = (2 * kQ8MaxStages + 4) * 8 + 16;
+    const int fixed = lay.x_bytes + sx_bytes + red_bytes + bar_bytes;
+    int nst = (kQ8SmemBudget - fixed) / kQ8StageBytes;
+    if (nst > kQ8MaxStages) nst = kQ8MaxStages;
+    lay.nstage = nst;
+    lay.off_x = nst * kQ8StageBytes;
+    lay.off_sx = lay.off_x + lay.x_bytes;
+    lay.off_red = lay.off_sx + sx_bytes;
+    lay.off_bar = lay.off_red + red_bytes;
+    lay.total = lay.off_bar + bar_bytes;
+    if (nst >= 4) break;
+  }
+  if (lay.nstage < 2) return HQ_ERR_SHAPE;
+  // columns one register prefetch can hold, in whole 256-column steps
+  const int sub = (kQ8XGroups * kQ8Consumers * 16) / (max_rows * esz) / 256 * 256;
+  lay.xk_sub = sub < lay.xk ? sub : lay.xk;
+  auto kern = gemv_q8_kernel<NCS>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
+  if (dev < 64 && !attr_done[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kQ8SmemBudget) != cudaSuccess)
+      return HQ_ERR_CUDA;
+    attr_done[dev] = true;
+  }
+  const int64_t items = (int64_t)n_y_max * ((p.n + kQ8RT - 1) / kQ8RT);
+  const int64_t grid = items < sm_count() ? items : sm_count();
+  if (grid <= 0) return HQ_OK;
+  kern<<<(unsigned)grid, kQ8Threads, lay.total, stream>>>(p, lay);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+int32_t launch_gemv_q8(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
+  if (p.k % 256 != 0) return HQ_ERR_SHAPE;   // row segments must stay 16-byte aligned for the bulk copies
+  return max_rows > 4 ? launch_q8_cfg<2>(p, n_y_max, max_rows, stream)
+                      : launch_q8_cfg<1>(p, n_y_max, max_rows, stream);
+}
+
+}  // namespace hq
