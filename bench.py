@@ -198,16 +198,23 @@ def run_gemv(args):
     ys = {(n, m): torch.empty((m, n), dtype=torch.float32, device=dev) for (_, n) in SHAPES for m in MS}
     launches_per_step = len(SHAPES) * len(MS)
 
+    # one scratch for every launch: they all run on one stream, and each call leaves the scratch zero-filled
+    ws_bytes = max(int(L.lib().hq_linear_workspace_bytes(layers[(k, n)][0]._weight_struct(), m))
+                   for (k, n) in SHAPES for m in MS)
+    ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+
+    def launch(layer, k, n, m):
+        rc = L.lib().hq_linear_forward_ws(layer._weight_struct(), xs[(k, m)].data_ptr(), L.DT_BF16, k,
+                                          ys[(n, m)].data_ptr(), L.DT_F32, n, m, ws.data_ptr(), ws.numel(),
+                                          layer._status_buf(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        L.check(rc, "hq_linear_forward_ws")
+
     def step(variant: int):
         for (k, n) in SHAPES:
             ls = layers[(k, n)]
             layer = ls[variant % len(ls)]
             for m in MS:
-                w = layer._weight_struct()
-                rc = L.lib().hq_linear_forward(w, xs[(k, m)].data_ptr(), L.DT_BF16, k, ys[(n, m)].data_ptr(), L.DT_F32,
-                                               n, m, layer._status_buf(dev).data_ptr(),
-                                               torch.cuda.current_stream().cuda_stream)
-                L.check(rc, "hq_linear_forward")
+                launch(layer, k, n, m)
 
     # ---- warm-up (eager; also sets kernel attributes before any capture) ------------------------------
     for w in range(max(args.warmup, 3)):
@@ -273,11 +280,7 @@ def run_gemv(args):
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=side):
                     for r in range(reps):
-                        layer = ls[r % len(ls)]
-                        L.check(L.lib().hq_linear_forward(layer._weight_struct(), xs[(k, m)].data_ptr(), L.DT_BF16, k,
-                                                          ys[(n, m)].data_ptr(), L.DT_F32, n, m,
-                                                          layer._status_buf(dev).data_ptr(),
-                                                          torch.cuda.current_stream().cuda_stream), "hq_linear_forward")
+                        launch(ls[r % len(ls)], k, n, m)
                 per[(k, n, m)] = (g, reps)
     torch.cuda.synchronize()
     for key, (g, reps) in list(per.items()):
@@ -366,7 +369,7 @@ def run_gemv(args):
                        "timing": "CUDA-graph replay per step, CUDA events"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "hq::gemv_kernel<Q8_0>", "launch_ms_sum": round(kern_ms, 4),
+                         "kernel": "hq::gemv_q8_kernel", "launch_ms_sum": round(kern_ms, 4),
                          "bytes_per_step": step_bytes, "by_launch_gbs": by_shape,
                          "graph_step_gbs": round(step_bytes / (ms_total / args.steps / 1e3) / 1e9, 1)},
             "cpu_baseline": cpu,

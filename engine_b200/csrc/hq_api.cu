@@ -135,8 +135,15 @@ int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* str
   return HQ_OK;
 }
 
-int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, int64_t x_stride, void* y,
-                          int32_t y_dtype, int64_t y_stride, int64_t m, int32_t* status_dev, void* stream) {
+int64_t hq_linear_workspace_bytes(const hq_weight* w, int64_t m) {
+  if (check_weight(w) != HQ_OK || m <= 0) return 0;
+  if (w->format != HQ_FMT_Q8_0 || w->n_experts != 1) return 0;
+  return gemv_q8_workspace_bytes(w->n, w->k, m);
+}
+
+int32_t hq_linear_forward_ws(const hq_weight* w, const void* x, int32_t x_dtype, int64_t x_stride, void* y,
+                             int32_t y_dtype, int64_t y_stride, int64_t m, void* workspace, int64_t workspace_bytes,
+                             int32_t* status_dev, void* stream) {
   int32_t rc = check_weight(w);
   if (rc != HQ_OK) return rc;
   if (m < 0 || m > (1 << 24)) return HQ_ERR_SHAPE;
@@ -145,6 +152,7 @@ int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, in
   if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return HQ_ERR_FORMAT;
   if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
   if (x_stride < w->k || y_stride < w->n) return HQ_ERR_SHAPE;
+  if (workspace != nullptr && (workspace_bytes < 0 || ((uintptr_t)workspace & 255u) != 0)) return HQ_ERR_ALIGN;
   if (m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS] && w->n_experts == 1 && tensor_path_ok(w, nullptr, x_dtype, x_stride)) {
     GroupedParams g{};
     fill_grouped(g, w, nullptr);
@@ -163,7 +171,14 @@ int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, in
   p.y = y; p.y_dtype = y_dtype; p.y_stride = y_stride;
   p.act.act = HQ_ACT_NONE;
   p.status = status_dev;
+  p.workspace = workspace;
+  p.workspace_bytes = workspace != nullptr ? workspace_bytes : 0;
   return launch_gemv(p, (int)((m + 7) / 8), (cudaStream_t)stream);
+}
+
+int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, int64_t x_stride, void* y,
+                          int32_t y_dtype, int64_t y_stride, int64_t m, int32_t* status_dev, void* stream) {
+  return hq_linear_forward_ws(w, x, x_dtype, x_stride, y, y_dtype, y_stride, m, nullptr, 0, status_dev, stream);
 }
 
 int32_t hq_router_topk(const void* logits, int32_t logits_dtype, int64_t n_rows, const hq_router_args* args,

@@ -11,14 +11,14 @@
 // the accumulator as floats through a bias constant (no conversion instruction), are multiplied by the
 // block's d, summed over the four blocks of a group and scaled once by the group's activation scale.
 //
-// Layout of the work: persistent CTAs (one per SM) walk items of 16 output rows.  A producer warp streams
+// Layout of the work: persistent CTAs (one per SM) walk items of 16 output rows.  Two producer warps stream
 // the item's row segments (2176 bytes = 64 blocks per bulk async copy; copies below 2 KiB cannot keep HBM
-// busy) into a shared-memory ring with mbarrier completion.  Sixteen consumer warps each take one group of
+// busy) into a shared-memory ring with mbarrier completion.  The consumer warps each take groups of
 // four blocks (136 bytes, 8-byte aligned) of every stage, so the misaligned block payloads are fetched
 // with a fixed pattern of 8- and 4-byte loads and four funnel shifts per row.  Within an MMA the k order
 // is free as long as both operands agree: lane t owns payload bytes 8t..8t+7 of a block, and reads the
-// same eight positions of the staged activations with one 8-byte load.  Partial sums of the sixteen K
-// slices meet in shared memory and are added in warp order by one (rotating) warp: results are
+// same eight positions of the staged activations with one 8-byte load.  Partial sums of the K slices
+// meet in shared memory and are added in warp order by a warp of their own: results are
 // bit-reproducible.
 //
 // Algorithmic bytes per launch: N*K*34/32 (weights) + M*K*sizeof(x) + M*N*sizeof(y).
@@ -32,7 +32,10 @@ namespace hq {
 constexpr int kQ8GroupsPerWarp = HQ_Q8_GROUPS_PER_WARP;   // 128-element groups a warp takes from every stage
 constexpr int kQ8Warps = 16 / kQ8GroupsPerWarp;  // consumer warps
 constexpr int kQ8Consumers = kQ8Warps * 32;
-constexpr int kQ8Threads = kQ8Consumers + 32;    // + producer warp
+constexpr int kQ8Producers = 2;                  // producer warps: a bulk-copy instruction holds its warp for ~50
+                                                 // cycles per active lane, so the 16 row copies of a stage are
+                                                 // split over two warps
+constexpr int kQ8Threads = kQ8Consumers + 32 * (kQ8Producers + 1);   // + producers + the reducing warp
 constexpr int kQ8KC = 2048;                      // k per stage
 constexpr int kQ8Seg = kQ8KC / 32 * 34;          // bytes of one row segment (one bulk copy)
 constexpr int kQ8Pitch = kQ8Seg + 32;            // row pitch in a stage: = 32 (mod 128), 8-byte loads of 4 rows
@@ -40,7 +43,7 @@ constexpr int kQ8Pitch = kQ8Seg + 32;            // row pitch in a stage: = 32 (
 constexpr int kQ8RT = 16;
 constexpr int kQ8StageBytes = kQ8RT * kQ8Pitch;
 constexpr int kQ8MaxStages = 8;
-constexpr int kQ8SmemBudget = 227 * 1024;
+constexpr int kQ8SmemBudget = 227 * 1024 - 256;   // dynamic part; a few static words come on top
 constexpr int kQ8XGroups = 8;                    // 16-byte activation groups a thread prefetches per epoch
 constexpr uint32_t kQ8Spin = 1u << 22;
 constexpr int kQ8Magic = 0x4B400000;             // 1.5 * 2^23 as f32 bits: magic + n reads as 12582912.f + n
@@ -56,6 +59,10 @@ struct Q8Layout {
   int xpitch;       // bytes between staged columns, = 32 (mod 128)
   int x_bytes;
   int off_x, off_sx, off_red, off_bar, total;
+  int kslices;            // K slices worked by different CTAs (1 = a CTA covers the whole K)
+  int chunks_per_slice;   // stages of kQ8KC columns per slice
+  int32_t* counters;      // split K: arrivals per item stream (zero between launches)
+  float* partials;        // split K: [item][slice][bank][4][32] partial sums
 };
 
 __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -63,6 +70,31 @@ __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t 
   asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+}
+
+// two f32 lanes per instruction (sm_100): the accumulator pairs of one weight row share every factor
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_pack_bits(int lo, int hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
 }
 
 // ---- activation staging ---------------------------------------------------------------------
@@ -213,30 +245,31 @@ __device__ __forceinline__ void q8_group(float (&acc)[NCS][4], uint32_t pa, uint
   blo[1] = b1l;                             bhi[1] = b1h;
   blo[2] = __funnelshift_r(b2x, b2.x, 16);  bhi[2] = __funnelshift_r(b2.x, b2.y, 16);
   blo[3] = b3.x;                            bhi[3] = b3.y;
-  float fA[4], fB[4];
+  uint64_t fA[4], fB[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    fA[j] = half_bits_to_float(dA[j]);
-    fB[j] = half_bits_to_float(dB[j]);
+    const float a = half_bits_to_float(dA[j]), b = half_bits_to_float(dB[j]);
+    fA[j] = f2_pack(a, a);
+    fB[j] = f2_pack(b, b);
   }
+  const uint64_t unbias = f2_pack(-12582912.f, -12582912.f);
 #pragma unroll
   for (int c = 0; c < NCS; ++c) {
-    float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+    uint64_t tmpA = 0ull, tmpB = 0ull;     // (row g, columns 2t, 2t+1) and (row g+8, ...)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       int d[4];
       mma_s8_16832(d, alo[j], blo[j], ahi[j], bhi[j], xb[c][j].x, xb[c][j].y, kQ8Magic);
       // |sum| <= 32 * 128 * 127 < 2^22, so the biased word is an exact float
-      tmp[0] = fmaf(fA[j], __int_as_float(d[0]) - 12582912.f, tmp[0]);
-      tmp[1] = fmaf(fA[j], __int_as_float(d[1]) - 12582912.f, tmp[1]);
-      tmp[2] = fmaf(fB[j], __int_as_float(d[2]) - 12582912.f, tmp[2]);
-      tmp[3] = fmaf(fB[j], __int_as_float(d[3]) - 12582912.f, tmp[3]);
+      tmpA = f2_fma(fA[j], f2_add(f2_pack_bits(d[0], d[1]), unbias), tmpA);
+      tmpB = f2_fma(fB[j], f2_add(f2_pack_bits(d[2], d[3]), unbias), tmpB);
     }
-    const float s0 = __uint_as_float(sxv[c].x), s1 = __uint_as_float(sxv[c].y);
-    acc[c][0] = fmaf(tmp[0], s0, acc[c][0]);
-    acc[c][1] = fmaf(tmp[1], s1, acc[c][1]);
-    acc[c][2] = fmaf(tmp[2], s0, acc[c][2]);
-    acc[c][3] = fmaf(tmp[3], s1, acc[c][3]);
+    const uint64_t s01 = f2_pack_bits((int)sxv[c].x, (int)sxv[c].y);
+    uint64_t accA = f2_pack(acc[c][0], acc[c][1]), accB = f2_pack(acc[c][2], acc[c][3]);
+    accA = f2_fma(tmpA, s01, accA);
+    accB = f2_fma(tmpB, s01, accB);
+    f2_unpack(accA, acc[c][0], acc[c][1]);
+    f2_unpack(accB, acc[c][2], acc[c][3]);
   }
 }
 
@@ -254,10 +287,20 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
   const int n_rt = (p.n + RT - 1) / RT;
   const int n_y = p.tiles != nullptr ? p.tile_count[0] : (p.m + 7) / 8;
   const int total = n_y * n_rt;
-  if ((int)blockIdx.x >= total) return;
+  // Split K: neighbouring CTAs take the K slices of one item, so each keeps only its slice of the activations
+  // staged (once, for every item it meets) and the slices of an item finish at about the same time.
+  const int S = lay.kslices;
+  const int R = gridDim.x / S;                 // item streams
+  const int r0 = blockIdx.x / S;
+  const int slice = blockIdx.x - r0 * S;
+  if (r0 >= total || r0 >= R) return;
+  const int nchunk = (p.k + KC - 1) / KC;
+  const int ck_lo = slice * lay.chunks_per_slice;
+  const int ck_hi = min(nchunk, ck_lo + lay.chunks_per_slice);
+  const int k_lo = ck_lo * KC, k_hi = min(p.k, ck_hi * KC);
   const int kXK = lay.xk;
   const int xk_sub = lay.xk_sub;
-  const int n_super = (p.k + kXK - 1) / kXK;
+  const int n_super = (k_hi - k_lo + kXK - 1) / kXK;
 
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + lay.off_bar);
   uint64_t* empty = full + kQ8MaxStages;
@@ -268,7 +311,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
 
   if (tid == 0) {
     for (int s = 0; s < NSTAGE; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], kQ8Producers);
       mbar_init(&empty[s], WK);
     }
     for (int b = 0; b < 2; ++b) {
@@ -283,49 +326,101 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
   __syncthreads();
 
   const int64_t row_bytes = (int64_t)p.k / 32 * 34;
-  const int nchunk = (p.k + KC - 1) / KC;
 
-  if (warp == WK) {
-    // ================= producer warp: stream weight row segments =================================
+  if (warp >= WK && warp < WK + kQ8Producers) {
+    // ================= producer warps: stream weight row segments ================================
+    const int pw = warp - WK;
+    constexpr int RPP = RT / kQ8Producers;      // rows per producer warp
     uint32_t spin = kQ8Spin;
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-    int it = 0;
-    for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    int s = 0, round = 0;
+    for (int w = r0; w < total; w += R) {
       const WorkItem wi = get_item<RT>(p, w, n_rt);
       if (wi.nrows <= 0) continue;
       const int rows_valid = min(RT, p.n - wi.n0);
-      for (int chunk = 0; chunk < nchunk; ++chunk) {
+      const int my_rows = max(0, min(RPP, rows_valid - pw * RPP));
+      for (int chunk = ck_lo; chunk < ck_hi; ++chunk) {
         const int kc_len = min(KC, p.k - chunk * KC);
         const uint32_t bytes = (uint32_t)(kc_len / 32 * 34);
-        for (int bank = 0; bank < p.n_banks; ++bank, ++it) {
-          const int s = it % NSTAGE;
-          if (it >= NSTAGE) {
-            if (!mbar_wait_backoff(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
+        for (int bank = 0; bank < p.n_banks; ++bank) {
+          if (round > 0) {
+            if (!mbar_wait_backoff(&empty[s], (round - 1) & 1, spin)) {
               // give up waiting but keep the control flow intact: results are invalid and flagged
               if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 100 + s);
               spin = 1;
             }
           }
           const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(bank == 0 ? p.w : p.w_up) +
-                                (int64_t)wi.expert * p.w_expert_stride + (int64_t)wi.n0 * row_bytes +
+                                (int64_t)wi.expert * p.w_expert_stride + (int64_t)(wi.n0 + pw * RPP) * row_bytes +
                                 (int64_t)chunk * kQ8Seg;
-          if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * (uint32_t)rows_valid);
+          if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * (uint32_t)my_rows);
           __syncwarp();
-          uint8_t* dst = smem + s * kQ8StageBytes;
-          if (lane < rows_valid)
+          uint8_t* dst = smem + s * kQ8StageBytes + pw * RPP * kQ8Pitch;
+          if (lane < my_rows)
             bulk_g2s_hint(dst + lane * kQ8Pitch, wsrc + (int64_t)lane * row_bytes, bytes, &full[s], policy);
+          if (++s == NSTAGE) {
+            s = 0;
+            ++round;
+          }
         }
       }
     }
-    return;
   }
 
-  // ================= consumer warps ================================================================
+  float* red = reinterpret_cast<float*>(smem + lay.off_red);   // [2 buffers][banks][warps][4][32]
   const int g = lane >> 2, t = lane & 3;
+
+  if (warp == WK + kQ8Producers) {
+    // ================= reducing warp: adds the K-split partial sums in warp order and writes ======
+    uint32_t spin = kQ8Spin;
+    int item = 0;
+    for (int w = r0; w < total; w += R) {
+      const WorkItem wi = get_item<RT>(p, w, n_rt);
+      if (wi.nrows <= 0) continue;
+      const int rb = item & 1;
+      const float* rbuf = red + rb * (p.n_banks * WK * 4 * 32);
+      if (!mbar_wait_backoff(&red_full[rb], (item >> 1) & 1, spin)) {
+        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + rb);
+        spin = 1;
+      }
+      float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+        if (b < p.n_banks) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < WK; ++j) sum += rbuf[((b * WK + j) * 4 + i) * 32 + lane];
+            // four-row layout: the remainder columns 4..7 sit two lanes further on
+            if (NCS == 1) sum += __shfl_down_sync(0xffffffffu, sum, 2);
+            v[b][i] = sum;
+          }
+        }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_free[rb]);
+      if (S > 1) {
+        // split K: the slice sums of an item meet in global memory and are added when the kernel ends
+        const int nb = p.n_banks;
+        float* mine = lay.partials + ((int64_t)w * S + slice) * (nb * 128);
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+          if (b < nb) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) __stcg(mine + (b * 4 + i) * 32 + lane, v[b][i]);
+          }
+      } else {
+        gemv_store_item(p, wi, g, 2 * t, NCS == 2 || t < 2, v);
+      }
+      ++item;
+    }
+  }
+
+  if (warp < WK) {
+  // ================= consumer warps ================================================================
   uint8_t* xq = smem + lay.off_x;
   float* sx = reinterpret_cast<float*>(smem + lay.off_sx);
-  float* red = reinterpret_cast<float*>(smem + lay.off_red);   // [2 buffers][banks][warps][4][32]
   const int xpitch = lay.xpitch;
   const int ncols = lay.ncols;
   const uint32_t cs_stride = 8u * (uint32_t)xpitch;
@@ -338,16 +433,17 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
   int staged_y = -1;        // activation rows currently staged (valid when n_super == 1)
   int staged_rows = 0;
   {
-    const WorkItem w0 = get_item<RT>(p, blockIdx.x, n_rt);
+    const WorkItem w0 = get_item<RT>(p, r0, n_rt);
     if (w0.nrows > 0) {
-      q8_x_prefetch(pf, p, w0.row0, w0.nrows, 0, min(xk_sub, p.k), tid);
+      q8_x_prefetch(pf, p, w0.row0, w0.nrows, k_lo, min(xk_sub, k_hi - k_lo), tid);
       pf_valid = true;
     }
   }
 
   uint32_t spin = kQ8Spin;
-  int it = 0, item = 0;
-  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+  int s = 0, item = 0;
+  uint32_t phase = 0;
+  for (int w = r0; w < total; w += R) {
     const WorkItem wi = get_item<RT>(p, w, n_rt);
     if (wi.nrows <= 0) continue;
     float acc[2][NCS][4];
@@ -358,8 +454,8 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[b][c][i] = 0.f;
     for (int sc = 0; sc < n_super; ++sc) {
-      const int k_base = sc * kXK;
-      const int k_len = min(kXK, p.k - k_base);
+      const int k_base = k_lo + sc * kXK;
+      const int k_len = min(kXK, k_hi - k_base);
       if (n_super > 1 || wi.y != staged_y) {
         // ---- stage this epoch's activations (all consumer warps) ----------------------------------
         if (!pf_valid) q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base, min(xk_sub, k_len), tid);
@@ -386,12 +482,12 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
         pf_valid = false;
         // fetch the next epoch's activations while this one is being consumed
         if (sc + 1 < n_super) {
-          q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base + kXK, min(xk_sub, p.k - k_base - kXK), tid);
+          q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base + kXK, min(xk_sub, k_hi - k_base - kXK), tid);
           pf_valid = true;
-        } else if (w + (int)gridDim.x < total) {
-          const WorkItem nx = get_item<RT>(p, w + gridDim.x, n_rt);
+        } else if (w + R < total) {
+          const WorkItem nx = get_item<RT>(p, w + R, n_rt);
           if (nx.nrows > 0 && (n_super > 1 || nx.y != wi.y)) {
-            q8_x_prefetch(pf, p, nx.row0, nx.nrows, 0, min(xk_sub, p.k), tid);
+            q8_x_prefetch(pf, p, nx.row0, nx.nrows, k_lo, min(xk_sub, k_hi - k_lo), tid);
             pf_valid = true;
           }
         }
@@ -404,13 +500,11 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
 #pragma unroll
         for (int bank = 0; bank < 2; ++bank) {
           if (bank >= p.n_banks) break;
-          const int s = it % NSTAGE;
-          if (!mbar_wait(&full[s], (it / NSTAGE) & 1, spin)) {
+          if (!mbar_wait(&full[s], phase, spin)) {
             // bounded wait ran out: flag it and carry on (every warp still reaches every barrier)
             if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 200 + s);
             spin = 1;
           }
-          ++it;
 #pragma unroll
           for (int gi = 0; gi < kQ8GroupsPerWarp; ++gi) {
             const int grp = warp + gi * WK;
@@ -423,11 +517,15 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty[s]);
+          if (++s == NSTAGE) {
+            s = 0;
+            phase ^= 1u;
+          }
         }
       }
     }
 
-    // ---- hand the K-split partials to one warp (rotating), which adds them in warp order ------------
+    // ---- hand the K-split partials to the reducing warp (two buffers) ----------------------------------
     const int rb = item & 1;
     float* rbuf = red + rb * (p.n_banks * WK * 4 * 32);
     if (item >= 2) {
@@ -445,42 +543,99 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
       }
     __syncwarp();
     if (lane == 0) mbar_arrive(&red_full[rb]);
-    if (warp == (item % WK)) {
-      if (!mbar_wait_backoff(&red_full[rb], (item >> 1) & 1, spin)) {
-        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + rb);
-        spin = 1;
-      }
-      float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-      for (int b = 0; b < 2; ++b)
-        if (b < p.n_banks) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float sum = 0.f;
-#pragma unroll
-            for (int j = 0; j < WK; ++j) sum += rbuf[((b * WK + j) * 4 + i) * 32 + lane];
-            // four-row layout: the remainder columns 4..7 sit two lanes further on
-            if (NCS == 1) sum += __shfl_down_sync(0xffffffffu, sum, 2);
-            v[b][i] = sum;
-          }
-        }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&red_free[rb]);
-      gemv_store_item(p, wi, g, 2 * t, NCS == 2 || t < 2, v);
-    }
     ++item;
+  }
+  }   // consumer warps
+
+  if (S > 1) {
+    // ---- split K: whichever CTA of an item stream finishes last adds the slice sums of the stream's items, in
+    // slice order (so the result does not depend on who that is), and leaves the counter at zero ---------------
+    __shared__ int last_flag;
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      const int old = atomicAdd(lay.counters + r0, 1);
+      last_flag = old == S - 1;
+      if (last_flag) lay.counters[r0] = 0;
+    }
+    __syncthreads();
+    if (last_flag) {
+      __threadfence();
+      const int nb = p.n_banks;
+      int idx = 0;
+      for (int w = r0; w < total; w += R, ++idx) {
+        if (idx % (kQ8Threads / 32) != warp) continue;
+        const WorkItem wi = get_item<RT>(p, w, n_rt);
+        if (wi.nrows <= 0) continue;
+        const float* all = lay.partials + (int64_t)w * S * (nb * 128);
+        float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+          if (b < nb) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float sum = 0.f;
+              for (int sl = 0; sl < S; ++sl) sum += __ldcg(all + (sl * nb + b) * 128 + i * 32 + lane);
+              v[b][i] = sum;
+            }
+          }
+        gemv_store_item(p, wi, g, 2 * t, NCS == 2 || t < 2, v);
+      }
+    }
   }
 }
 
 // ---- host launcher -----------------------------------------------------------------------------
+// Split K (up to eight slices of whole stages) when K is too long for a CTA to keep its activations staged
+// beside at least four ring stages: a CTA that covers the whole K would then have to stage them again for
+// every item.  Shorter K stays unsplit -- the meeting of the slice sums costs a few microseconds.
+struct Q8Split {
+  int kslices, chunks_per_slice;
+  int64_t counter_bytes, bytes;
+};
+static int q8_ring_stages(int ncols, int xk, int n_banks) {
+  const int fixed = ncols * (xk + 32) + (xk / 128) * ncols * 4 + 2 * n_banks * kQ8Warps * 4 * 32 * 4 +
+                    (2 * kQ8MaxStages + 4) * 8 + 16;
+  return (kQ8SmemBudget - fixed) / kQ8StageBytes;
+}
+static Q8Split q8_split_plan(int64_t n, int64_t k, int64_t n_y, int n_banks, bool expert_indexed, int ncols) {
+  Q8Split sp{};
+  const int nchunk = (int)((k + kQ8KC - 1) / kQ8KC);
+  const int64_t items = n_y * ((n + kQ8RT - 1) / kQ8RT);
+  sp.kslices = 1;
+  sp.chunks_per_slice = nchunk;
+  if (expert_indexed || nchunk < 2 || q8_ring_stages(ncols, nchunk * kQ8KC, n_banks) >= 4) return sp;
+  sp.chunks_per_slice = (nchunk + 7) / 8;
+  sp.kslices = (nchunk + sp.chunks_per_slice - 1) / sp.chunks_per_slice;
+  sp.counter_bytes = 1024;     // one arrival counter per item stream (at most one stream per SM)
+  sp.bytes = sp.counter_bytes + items * sp.kslices * n_banks * 512;
+  return sp;
+}
+
+int64_t gemv_q8_workspace_bytes(int64_t n, int64_t k, int64_t m) {
+  return q8_split_plan(n, k, (m + 7) / 8, 1, false, m > 4 ? 16 : 8).bytes;
+}
+
 template <int NCS>
 static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
-  // Shared-memory plan: stage as many activation columns as leave at least four ring stages (the whole K when
-  // it fits -- then a persistent CTA quantizes its activations once), give every remaining byte to the ring.
   Q8Layout lay{};
   lay.ncols = 8 * NCS;
+  Q8Split sp = q8_split_plan(p.n, p.k, n_y_max, p.n_banks, p.tiles != nullptr, lay.ncols);
+  if (sp.kslices > 1 && (p.workspace == nullptr || p.workspace_bytes < sp.bytes)) {
+    sp.kslices = 1;                      // no scratch from the caller: every CTA covers the whole K
+    sp.chunks_per_slice = (p.k + kQ8KC - 1) / kQ8KC;
+  }
+  lay.kslices = sp.kslices;
+  lay.chunks_per_slice = sp.chunks_per_slice;
+  if (sp.kslices > 1) {
+    lay.counters = reinterpret_cast<int32_t*>(p.workspace);
+    lay.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.workspace) + sp.counter_bytes);
+  }
+  // Shared-memory plan: stage as many activation columns as leave at least four ring stages (the CTA's whole
+  // K range when it fits -- then a persistent CTA quantizes its activations once), give every remaining byte
+  // to the ring.
   const int esz = dtype_size(p.x_dtype);
-  const int k_round = (p.k + kQ8KC - 1) / kQ8KC * kQ8KC;
+  const int k_round = sp.chunks_per_slice * kQ8KC;
   const int candidates[3] = {k_round, 8192 < k_round ? 8192 : k_round, 4096 < k_round ? 4096 : k_round};
   for (int c = 0; c < 3; ++c) {
     lay.xk = candidates[c];
@@ -514,7 +669,10 @@ static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cud
     attr_done[dev] = true;
   }
   const int64_t items = (int64_t)n_y_max * ((p.n + kQ8RT - 1) / kQ8RT);
-  const int64_t grid = items < sm_count() ? items : sm_count();
+  int64_t streams = sm_count() / sp.kslices;
+  if (streams < 1) streams = 1;
+  if (streams > items) streams = items;
+  const int64_t grid = streams * sp.kslices;
   if (grid <= 0) return HQ_OK;
   kern<<<(unsigned)grid, kQ8Threads, lay.total, stream>>>(p, lay);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;

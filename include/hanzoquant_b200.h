@@ -109,14 +109,29 @@ int64_t hq_config_get(int32_t key);
  * Replaces launch_mmvq_gguf_quantize_q8_1_* + launch_mmvq_gguf_{q4_k,q8_0}_*_plain
  * (hanzo-quant/src/gguf/fast_mmvq.rs:107-148, :343-368), launch_fp8_matmul_*
  * (blockwise_fp8/ffi.rs) and launch_mxfp4_matmul_* (mxfp4/ffi.rs).  Activations
- * are NOT quantized to int8 (the reference's Q8_1 step): x is used at 16-bit
- * precision, products accumulate in f32.
+ * do not go through the reference's single int8 term (its Q8_1 step): for Q4_K,
+ * FP8 and MXFP4 x is used at 16-bit precision; for Q8_0 every 128-element group
+ * of x is split into two int8 terms (error below max|x| / 32000 per element) so
+ * the block codes can enter the integer MMA unconverted.  Products accumulate in
+ * f32.
  * x: [m, k] with row stride x_stride elements; y: [m, n] with row stride y_stride.
  * Requires K % 256 == 0 for Q8_0/Q4_K, K % 128 == 0 for FP8, K % 32 == 0 for
  * MXFP4; x rows 16-byte aligned.  Any m >= 0 (rows are processed 8 at a time
  * on the decode path). */
 int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, int64_t x_stride, void* y,
                           int32_t y_dtype, int64_t y_stride, int64_t m, int32_t* status_dev, void* stream);
+
+/* The same call with caller-owned scratch, the counterpart of the Q8_1 activation buffer the reference's
+ * host side allocates for launch_mmvq_gguf_quantize_q8_1_* (hanzo-quant/src/gguf/fast_mmvq.rs:107-148).
+ * With it the Q8_0 decode kernel splits K across CTAs when an output has few rows or K is long (partial sums
+ * meet in the scratch and are added in a fixed order: results stay bit-reproducible).
+ * hq_linear_workspace_bytes gives the size for (w, m), 0 when the call would not use any.  The scratch must be
+ * 256-byte aligned and zero-filled once before its first use; every call leaves it zero-filled again.  One
+ * scratch serves one stream at a time.  workspace == NULL is allowed and equals hq_linear_forward. */
+int64_t hq_linear_workspace_bytes(const hq_weight* w, int64_t m);
+int32_t hq_linear_forward_ws(const hq_weight* w, const void* x, int32_t x_dtype, int64_t x_stride, void* y,
+                             int32_t y_dtype, int64_t y_stride, int64_t m, void* workspace, int64_t workspace_bytes,
+                             int32_t* status_dev, void* stream);
 
 /* ---- router: moe_router_topk ---------------------------------------------
  * Replaces moe_router_topk_{f32,bf16,f16} (hanzo-engine/src/cuda/ffi.rs:466-520,
