@@ -1,5 +1,6 @@
 // Decode-regime quantized mat-vec (1..8 activation rows per work item), dense
-// and expert-indexed, for Q8_0, Q4_K, block-FP8 and MXFP4 weights.
+// and expert-indexed, for Q4_K, block-FP8 and MXFP4 weights (Q8_0 has a kernel of
+// its own in hq_gemv_q8.cu and is only dispatched from here).
 //
 // HBM-bound: every weight byte is read once, straight from the reference's
 // device layout.  Persistent CTAs (one per SM) walk work items of 16 output rows.
@@ -37,14 +38,6 @@ struct GemvLayout {
 // ---- per-format geometry ----------------------------------------------------
 template <int FMT>
 struct FmtTraits;
-template <>
-struct FmtTraits<HQ_FMT_Q8_0> {
-  static constexpr int kGran = 256;  // K granularity that keeps row segments 16-byte aligned
-  static constexpr bool kPermX = true;
-  static constexpr bool kNeedXsum = true;
-  __host__ __device__ static constexpr int seg_bytes(int kc) { return kc / 32 * 34; }
-  __host__ __device__ static int64_t row_bytes(int64_t k) { return k / 32 * 34; }
-};
 template <>
 struct FmtTraits<HQ_FMT_Q4_K> {
   static constexpr int kGran = 256;
@@ -191,48 +184,6 @@ __device__ __forceinline__ void x_commit(const XPrefetch& pf, const GemvParams& 
 // back to back for several units) and a compute half, so the reads of the
 // next unit are in flight while the MMAs of this one run.
 
-// Q8_0: unit = one 32-element block (34 bytes, 2-byte aligned in the ring).
-struct Q8Regs {
-  uint32_t dA, dB, a[4], b[4], sh;
-  uint2 x0, x1, xs;
-};
-__device__ __forceinline__ void q8_load(Q8Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, uint32_t xsum_t,
-                                        int unit, int t, bool xv) {
-  const uint32_t off = 34u * unit;
-  const uint32_t q = off + 2u + 4u * t;
-  const uint32_t al = q & ~3u;
-  r.sh = (q & 3u) * 8u;
-  r.dA = lds16(rowA + off);
-  r.dB = lds16(rowB + off);
-  const uint32_t pa = rowA + al, pb = rowB + al;
-  r.a[0] = lds32<0>(pa); r.a[1] = lds32<4>(pa); r.a[2] = lds32<16>(pa); r.a[3] = lds32<20>(pa);
-  r.b[0] = lds32<0>(pb); r.b[1] = lds32<4>(pb); r.b[2] = lds32<16>(pb); r.b[3] = lds32<20>(pb);
-  const uint32_t xo = xs_g + (32u * unit + 4u * t) * 2u;
-  r.x0 = xv ? lds64<0>(xo) : make_uint2(0u, 0u);
-  r.x1 = xv ? lds64<32>(xo) : make_uint2(0u, 0u);
-  r.xs = lds64(xsum_t + 32u * unit);
-}
-// bytes 1 and 3 of v into the low bytes of the two halves: (v >> 8) & 0x00FF00FF in one permute
-__device__ __forceinline__ uint32_t odd_bytes(uint32_t v) { return __byte_perm(v, 0u, 0x4341); }
-__device__ __forceinline__ void q8_compute(float (&acc)[4], const Q8Regs& r) {
-  const uint32_t a_lo = __funnelshift_r(r.a[0], r.a[1], r.sh) ^ 0x80808080u;
-  const uint32_t a_hi = __funnelshift_r(r.a[2], r.a[3], r.sh) ^ 0x80808080u;
-  const uint32_t b_lo = __funnelshift_r(r.b[0], r.b[1], r.sh) ^ 0x80808080u;
-  const uint32_t b_hi = __funnelshift_r(r.b[2], r.b[3], r.sh) ^ 0x80808080u;
-  // codes are fed as (q+128) * 2^-24; the staged table holds -128 * 2^-24 * sum(x) per block and column and
-  // enters as the C operand, so blk = 2^-24 * sum(q*x)
-  const float c0 = __uint_as_float(r.xs.x), c1 = __uint_as_float(r.xs.y);
-  float blk[4];
-  mma_f16_16816_c(blk, a_lo & 0x00FF00FFu, b_lo & 0x00FF00FFu, odd_bytes(a_lo), odd_bytes(b_lo), r.x0.x, r.x0.y, c0,
-                  c1, c0, c1);
-  mma_f16_16816(blk, a_hi & 0x00FF00FFu, b_hi & 0x00FF00FFu, odd_bytes(a_hi), odd_bytes(b_hi), r.x1.x, r.x1.y);
-  const float sA = half_bits_to_float(r.dA) * 16777216.f, sB = half_bits_to_float(r.dB) * 16777216.f;
-  acc[0] = fmaf(sA, blk[0], acc[0]);
-  acc[1] = fmaf(sA, blk[1], acc[1]);
-  acc[2] = fmaf(sB, blk[2], acc[2]);
-  acc[3] = fmaf(sB, blk[3], acc[3]);
-}
-
 // Q4_K: unit = 64 elements = sub-blocks (2c, 2c+1) of a super-block; they share 32 nibble bytes.
 struct Q4Regs {
   uint32_t dmA, dmB, scA[3], scB[3], a0, a1, b0, b1;
@@ -378,8 +329,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   constexpr int WK = kConsumerWarps;
   constexpr int RT = L::RT;
   const int NSTAGE = lay.nstage;
-  // per-block activation sums: Q8_0 wants them as the MMA's C operand (-128 * 2^-24 * sum), Q4_K plain
-  constexpr float kXsumScale = FMT == HQ_FMT_Q8_0 ? -7.62939453125e-06f : 1.f;
+  constexpr float kXsumScale = 1.f;   // per-block activation sums (Q4_K's min term)
   extern __shared__ __align__(128) uint8_t smem[];
 
   const int n_rt = (p.n + RT - 1) / RT;
@@ -534,22 +484,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
           const uint32_t xs_c = xs_g + 2u * kx;
           const uint32_t xsum_c = xsum_t + 32u * (kx / 32);
           float(&a)[4] = acc[bank];
-          if (FMT == HQ_FMT_Q8_0) {
-            const int nunits = kc_len / 32;
-            int u = wrot;
-            for (; u + WK < nunits; u += 2 * WK) {
-              Q8Regs r0, r1;
-              q8_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
-              q8_load(r1, rowA, rowB, xs_c, xsum_c, u + WK, t, xv);
-              q8_compute(a, r0);
-              q8_compute(a, r1);
-            }
-            if (u < nunits) {
-              Q8Regs r0;
-              q8_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
-              q8_compute(a, r0);
-            }
-          } else if (FMT == HQ_FMT_Q4_K) {
+          if (FMT == HQ_FMT_Q4_K) {
             const int nunits = kc_len / 64;
             int u = wrot;
             for (; u + WK < nunits; u += 2 * WK) {

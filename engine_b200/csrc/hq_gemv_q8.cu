@@ -5,8 +5,8 @@
 // What limits such a kernel on the SM side is the number of instructions spent per weight byte, so the
 // int8 codes are never converted: they go into the integer warp MMA (m16n8k32, s8 x s8 -> s32) exactly as
 // they lie in the block.  The activations are made to fit instead: each 128-element group of an
-// activation row is written as x ~= s * (h + l / 254) with int8 h and l (s a power of two, h = rint(x / s), l the
-// rounded remainder; the error is below max|x| / 32000 per element), and h and l occupy separate MMA columns.
+// activation row is written as x ~= s * (h + l / 256) with int8 h and l (s a power of two; 256 h + l is x / s
+// rounded to 16-bit fixed point, so the error is below max|x| / 32000 per element), and h and l occupy separate MMA columns.
 // One MMA then yields the exact integer dot products of one block for all rows and columns; they leave
 // the accumulator as floats through a bias constant (no conversion instruction), are multiplied by the
 // block's d, summed over the four blocks of a group and scaled once by the group's activation scale.
@@ -158,32 +158,36 @@ __device__ __forceinline__ void q8_x_commit(const Q8XPrefetch& pf, const GemvPar
           f[2 * j] = t.x; f[2 * j + 1] = t.y;
         }
       }
-      float amax = 0.f;
+      // largest magnitude as an integer maximum of the sign-cleared bits: NaN and infinity order above every
+      // finite value, so either makes the group's step non-finite instead of vanishing in an fmax
+      uint32_t abits = 0u;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {      // a NaN or an infinity makes the whole group's scale non-finite
-        const float a = fabsf(f[j]);
-        amax = (a <= 3.0e38f) ? fmaxf(amax, a) : __int_as_float(0x7f800000);
-      }
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
-      if (epg == 4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+      for (int j = 0; j < 8; ++j) abits = max(abits, __float_as_uint(f[j]) & 0x7FFFFFFFu);
+      abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 1));
+      abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 2));
+      abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 4));
+      abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 8));
+      if (epg == 4) abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 16));
+      const float amax = __uint_as_float(abits);
       // The step s is the power of two at or above amax / 127 (not below 2^-100), so x / s and the products
       // with s are exact: an activation that is a small multiple of s (a one-hot row, say) passes through
       // without any rounding.  Non-finite input must not turn into a finite output: its step is a NaN.
-      const bool finite = amax <= 3.0e38f;
+      const bool finite = abits < 0x7F800000u;
       const uint32_t tb = __float_as_uint(fmaxf(amax / 127.f, 7.888609052e-31f));
       const float s = finite ? __uint_as_float((tb + 0x007FFFFFu) & 0x7F800000u) : __int_as_float(0x7fc00000);
-      const float inv = (finite && amax > 0.f) ? 1.f / s : 0.f;
-      uint32_t hq[2] = {0u, 0u}, lq[2] = {0u, 0u};
+      const float inv256 = (finite && abits != 0u) ? 256.f / s : 0.f;
+      // x / s as 16-bit fixed point u = rint(256 x / s) + 128 = 256 h + (l + 128): h is the high byte, the low
+      // byte is l in offset binary
+      uint32_t u[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float v = f[j] * inv;
-        const float h = rintf(v);
-        const float l = rintf((v - h) * 254.f);
-        hq[j >> 2] |= ((uint32_t)(int)h & 0xFFu) << (8 * (j & 3));
-        lq[j >> 2] |= ((uint32_t)(int)l & 0xFFu) << (8 * (j & 3));
+      for (int j = 0; j < 8; ++j) u[j] = (uint32_t)__float2int_rn(fmaf(f[j], inv256, 128.f));
+      uint32_t hq[2], lq[2];
+#pragma unroll
+      for (int w2 = 0; w2 < 2; ++w2) {
+        const uint32_t p01 = __byte_perm(u[4 * w2], u[4 * w2 + 1], 0x5140);      // bytes l0 l1 h0 h1
+        const uint32_t p23 = __byte_perm(u[4 * w2 + 2], u[4 * w2 + 3], 0x5140);
+        hq[w2] = __byte_perm(p01, p23, 0x7632);
+        lq[w2] = __byte_perm(p01, p23, 0x5410) ^ 0x80808080u;
       }
       uint8_t* dh = xq + col * xpitch + kk;
       uint8_t* dl = dh + l_off * xpitch;
@@ -197,7 +201,7 @@ __device__ __forceinline__ void q8_x_commit(const Q8XPrefetch& pf, const GemvPar
       if ((kk & 127) == 0) {
         float* d = sx + (kk >> 7) * ncols + col;
         d[0] = s;
-        d[l_off] = s * (1.f / 254.f);
+        d[l_off] = s * (1.f / 256.f);
       }
     }
   }
