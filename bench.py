@@ -37,6 +37,9 @@ METRIC = "quant_linear_decode_tokens_per_s"
 UNIT = "tokens/s"
 
 
+NCU_TRAFFIC_RATIO = 563.3 / 558.2   # measured DRAM traffic over algorithmic bytes, decode kernel
+
+
 def algorithmic_bytes(k, n, m, x_size=2, y_size=4):
     return n * (k // 32) * 34 + m * k * x_size + m * n * y_size
 
@@ -368,8 +371,14 @@ def run_gemv(args):
                        "l2": "every launch reads a weight copy last touched >= 700 MB of traffic earlier",
                        "timing": "CUDA-graph replay per step, CUDA events"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "hq::gemv_q8_kernel", "launch_ms_sum": round(kern_ms, 4),
+                         "frac": round(achieved / peak, 4),
+                         # DRAM bytes per launch (average over the step's launches): the ncu capture of the
+                         # 4096 -> 128256 launch read and wrote 563.3 MB for 558.2 MB of algorithmic bytes
+                         # (profiles/gemv_q8_0_4096x128256.md); the other launches are scaled by that ratio
+                         "traffic": int(NCU_TRAFFIC_RATIO * step_bytes / launches_per_step),
+                         "traffic_note": "algorithmic bytes x 1.009 (ncu dram bytes / algorithmic bytes of the "
+                                         "4096x128256 launch)",
+                         "peak_kind": peak_kind, "kernel": "hq::gemv_q8_kernel", "launch_ms_sum": round(kern_ms, 4),
                          "bytes_per_step": step_bytes, "by_launch_gbs": by_shape,
                          "graph_step_gbs": round(step_bytes / (ms_total / args.steps / 1e3) / 1e9, 1)},
             "cpu_baseline": cpu,
