@@ -4,25 +4,26 @@
 //
 // HBM-bound: every weight byte is read once, straight from the reference's
 // device layout.  Persistent CTAs (one per SM) walk work items of 16 output rows.
-// A producer warp streams each item's row segments (>= 2 KiB per bulk async
+// Two producer warps stream each item's row segments (>= 2 KiB per bulk async
 // copy -- smaller copies cannot keep HBM busy) into a shared-memory ring with
-// mbarrier completion; fifteen consumer warps split K fifteen ways, decode the
+// mbarrier completion; thirteen consumer warps split K thirteen ways, decode the
 // blocks in registers into f16 MMA fragments -- integer codes become f16
 // *subnormals* with a couple of logic ops, the power-of-two factor is folded
 // into the block scale -- and multiply them against the (<= 8) activation rows
 // with m16n8k16 warp MMAs, f32 accumulation, one scale FMA per 32-element block.
-// The fifteen partial sums of an item are handed through shared memory (two
-// buffers, mbarrier hand-off, no CTA-wide barrier) to one warp that adds them in
-// a fixed order and writes the outputs, so results are bit-reproducible.
+// The thirteen partial sums of an item are handed through shared memory (two
+// buffers, mbarrier hand-off, no CTA-wide barrier) to a warp of its own that adds
+// them in a fixed order and writes the outputs, so results are bit-reproducible.
 //
 // Algorithmic bytes per launch: N*K*bits/8 (weights) + M*K*sizeof(x) + M*N*sizeof(y).
 #include "hq_gemv_shared.cuh"
 
 namespace hq {
 
-constexpr int kConsumerWarps = 15;
+constexpr int kConsumerWarps = 13;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kGemvThreads = kConsumerThreads + 32;
+constexpr int kProducerWarps = 2;   // a bulk-copy instruction holds its warp ~50 cycles per active lane: split the rows
+constexpr int kGemvThreads = kConsumerThreads + 32 * (kProducerWarps + 1);   // + producers + the reducing warp
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 // shared-memory plan of one launch (computed on the host)
@@ -349,7 +350,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 
   if (tid == 0) {
     for (int s = 0; s < NSTAGE; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], kProducerWarps);
       mbar_init(&empty[s], kConsumerWarps);
     }
     for (int b = 0; b < 2; ++b) {
@@ -366,48 +367,89 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   const int64_t row_bytes = F::row_bytes(p.k);
   const int nchunk = (p.k + KC - 1) / KC;
 
-  if (warp == kConsumerWarps) {
-    // ================= producer warp: stream weight row segments ===============
+  if (warp >= kConsumerWarps && warp < kConsumerWarps + kProducerWarps) {
+    // ================= producer warps: stream weight row segments ===============
+    const int pw = warp - kConsumerWarps;
+    constexpr int RPP = RT / kProducerWarps;    // rows per producer warp
     uint32_t spin = kSpinLimit;
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-    int it = 0;
+    int s = 0, round = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x) {
       const WorkItem wi = get_item<RT>(p, w, n_rt);
       if (wi.nrows <= 0) continue;
       const int rows_valid = min(RT, p.n - wi.n0);
+      const int my_rows = max(0, min(RPP, rows_valid - pw * RPP));
       for (int chunk = 0; chunk < nchunk; ++chunk) {
         const int kc_len = min(KC, p.k - chunk * KC);
         const uint32_t bytes = (uint32_t)F::seg_bytes(kc_len);
-        for (int bank = 0; bank < p.n_banks; ++bank, ++it) {
-          const int s = it % NSTAGE;
-          if (it >= NSTAGE) {
-            if (!mbar_wait_backoff(&empty[s], ((it / NSTAGE) - 1) & 1, spin)) {
+        for (int bank = 0; bank < p.n_banks; ++bank) {
+          if (round > 0) {
+            if (!mbar_wait_backoff(&empty[s], (round - 1) & 1, spin)) {
               // give up waiting but keep the control flow intact: results are invalid and flagged
               if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 100 + s);
               spin = 1;
             }
           }
           const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(bank == 0 ? p.w : p.w_up) +
-                                (int64_t)wi.expert * p.w_expert_stride + (int64_t)wi.n0 * row_bytes +
+                                (int64_t)wi.expert * p.w_expert_stride + (int64_t)(wi.n0 + pw * RPP) * row_bytes +
                                 (int64_t)F::seg_bytes(chunk * KC);
-          if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * (uint32_t)rows_valid);
+          if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * (uint32_t)my_rows);
           __syncwarp();
-          uint8_t* dst = smem + s * L::STAGE_BYTES;
-          if (lane < rows_valid)
+          uint8_t* dst = smem + s * L::STAGE_BYTES + pw * RPP * L::PITCH;
+          if (lane < my_rows)
             bulk_g2s_hint(dst + lane * L::PITCH, wsrc + (int64_t)lane * row_bytes, bytes, &full[s], policy);
+          if (++s == NSTAGE) {
+            s = 0;
+            ++round;
+          }
         }
       }
     }
     return;
   }
 
+  const int g = lane >> 2, t = lane & 3;
+  float* red = reinterpret_cast<float*>(smem + lay.off_red);   // [2 buffers][banks][warps][4][32]
+
+  if (warp == kConsumerWarps + kProducerWarps) {
+    // ================= reducing warp: adds the K-split partial sums in warp order and writes ==========
+    uint32_t spin = kSpinLimit;
+    int item = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x) {
+      const WorkItem wi = get_item<RT>(p, w, n_rt);
+      if (wi.nrows <= 0) continue;
+      const int rb = item & 1;
+      const float* rbuf = red + rb * (p.n_banks * kConsumerWarps * 4 * 32);
+      if (!mbar_wait_backoff(&red_full[rb], (item >> 1) & 1, spin)) {
+        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + rb);
+        spin = 1;
+      }
+      float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+        if (b < p.n_banks) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < kConsumerWarps; ++j) sum += rbuf[((b * kConsumerWarps + j) * 4 + i) * 32 + lane];
+            v[b][i] = sum;
+          }
+        }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_free[rb]);
+      // rows of this lane: n0 + g (+8); columns 2t, 2t+1
+      gemv_store_item(p, wi, g, 2 * t, true, v);
+      ++item;
+    }
+    return;
+  }
+
   // ================= consumer warps ============================================
   const int wk = warp;
-  const int g = lane >> 2, t = lane & 3;
   __half* xs = reinterpret_cast<__half*>(smem + lay.off_x);
   float* xsum = reinterpret_cast<float*>(smem + lay.off_xsum);
-  float* red = reinterpret_cast<float*>(smem + lay.off_red);   // [2 buffers][banks][warps][4][32]
   const int XP = lay.xk + 16;                 // f16 elements per staged activation row
   const bool xv = g < lay.xs_rows;            // activation rows beyond the staged ones are zero
   const uint32_t xs_g = smem_u32(xs) + (uint32_t)(xv ? g : 0) * XP * 2u;
@@ -426,7 +468,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   }
 
   uint32_t spin = kSpinLimit;
-  int it = 0, item = 0;
+  int s = 0, it = 0, item = 0;
+  uint32_t phase = 0;
   for (int w = blockIdx.x; w < total; w += gridDim.x) {
     const WorkItem wi = get_item<RT>(p, w, n_rt);
     if (wi.nrows <= 0) continue;
@@ -470,8 +513,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 #pragma unroll
         for (int bank = 0; bank < 2; ++bank) {
           if (bank >= p.n_banks) break;
-          const int s = it % NSTAGE;
-          if (!mbar_wait(&full[s], (it / NSTAGE) & 1, spin)) {
+          if (!mbar_wait(&full[s], phase, spin)) {
             // bounded wait ran out: flag it and carry on (every warp still reaches every barrier)
             if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 200 + s);
             spin = 1;
@@ -537,11 +579,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty[s]);
+          if (++s == NSTAGE) {
+            s = 0;
+            phase ^= 1u;
+          }
         }
       }
     }
 
-    // ---- hand the K-split partials to one warp (rotating), which adds them in warp order ------------
+    // ---- hand the K-split partials to the reducing warp (two buffers) ----------------------------------
     const int rb = item & 1;
     float* rbuf = red + rb * (p.n_banks * kConsumerWarps * 4 * 32);
     if (item >= 2) {
@@ -558,27 +604,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
       }
     __syncwarp();
     if (lane == 0) mbar_arrive(&red_full[rb]);
-    if (warp == (item % kConsumerWarps)) {
-      if (!mbar_wait_backoff(&red_full[rb], (item >> 1) & 1, spin)) {
-        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + rb);
-        spin = 1;
-      }
-#pragma unroll
-      for (int b = 0; b < 2; ++b)
-        if (b < p.n_banks) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float s = 0.f;
-#pragma unroll
-            for (int j = 0; j < kConsumerWarps; ++j) s += rbuf[((b * kConsumerWarps + j) * 4 + i) * 32 + lane];
-            acc[b][i] = s;
-          }
-        }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&red_free[rb]);
-      // rows of this lane: n0 + g (+8); columns 2t, 2t+1
-      gemv_store_item(p, wi, g, 2 * t, true, acc);
-    }
     ++item;
   }
 }
