@@ -1,16 +1,16 @@
 // Decode-regime quantized mat-vec (1..8 activation rows per work item), dense
-// and expert-indexed, for Q4_K, block-FP8 and MXFP4 weights (Q8_0 has a kernel of
-// its own in hq_gemv_q8.cu and is only dispatched from here).
+// and expert-indexed, for block-FP8 and MXFP4 weights (Q8_0 and Q4_K have a kernel
+// of their own in hq_gemv_int8.cu and are only dispatched from here).
 //
 // HBM-bound: every weight byte is read once, straight from the reference's
 // device layout.  Persistent CTAs (one per SM) walk work items of 16 output rows.
 // Two producer warps stream each item's row segments (>= 2 KiB per bulk async
 // copy -- smaller copies cannot keep HBM busy) into a shared-memory ring with
 // mbarrier completion; thirteen consumer warps split K thirteen ways, decode the
-// blocks in registers into f16 MMA fragments -- integer codes become f16
-// *subnormals* with a couple of logic ops, the power-of-two factor is folded
-// into the block scale -- and multiply them against the (<= 8) activation rows
-// with m16n8k16 warp MMAs, f32 accumulation, one scale FMA per 32-element block.
+// blocks in registers into f16 MMA fragments (e4m3 by hardware conversion, e2m1
+// codes as f16 bit patterns with the power of two folded into the block scale)
+// and multiply them against the (<= 8) activation rows with m16n8k16 warp MMAs,
+// f32 accumulation, one scale FMA per 32-element block.
 // The thirteen partial sums of an item are handed through shared memory (two
 // buffers, mbarrier hand-off, no CTA-wide barrier) to a warp of its own that adds
 // them in a fixed order and writes the outputs, so results are bit-reproducible.
@@ -33,33 +33,21 @@ struct GemvLayout {
   int xk;           // activation columns per epoch
   int xk_sub;       // columns per register prefetch
   int x_bytes;
-  int off_x, off_xsum, off_red, off_bar, total;
+  int off_x, off_red, off_bar, total;
 };
 
 // ---- per-format geometry ----------------------------------------------------
 template <int FMT>
 struct FmtTraits;
 template <>
-struct FmtTraits<HQ_FMT_Q4_K> {
-  static constexpr int kGran = 256;
-  static constexpr bool kPermX = true;
-  static constexpr bool kNeedXsum = true;
-  __host__ __device__ static constexpr int seg_bytes(int kc) { return kc / 256 * 144; }
-  __host__ __device__ static int64_t row_bytes(int64_t k) { return k / 256 * 144; }
-};
-template <>
 struct FmtTraits<HQ_FMT_FP8_BLOCK> {
   static constexpr int kGran = 128;
-  static constexpr bool kPermX = false;
-  static constexpr bool kNeedXsum = false;
   __host__ __device__ static constexpr int seg_bytes(int kc) { return kc; }
   __host__ __device__ static int64_t row_bytes(int64_t k) { return k; }
 };
 template <>
 struct FmtTraits<HQ_FMT_MXFP4> {
   static constexpr int kGran = 32;
-  static constexpr bool kPermX = false;
-  static constexpr bool kNeedXsum = false;
   __host__ __device__ static constexpr int seg_bytes(int kc) { return kc / 2; }
   __host__ __device__ static int64_t row_bytes(int64_t k) { return k / 2; }
 };
@@ -108,14 +96,12 @@ __device__ __forceinline__ void x_prefetch(XPrefetch& pf, const GemvParams& p, i
   }
 }
 
-template <bool PERM, bool XSUM>
 __device__ __forceinline__ void x_commit(const XPrefetch& pf, const GemvParams& p, int nrows, int k_len, int tid,
-                                         __half* xs, int XP, float* xsum, float xsum_scale) {
+                                         __half* xs, int XP) {
   const int esz = dtype_size(p.x_dtype);
   const int epg = 16 / esz;
   const int gpr = k_len / epg;
   const int ngroups = nrows * gpr;
-  const int lpb = 32 / epg;  // lanes that share one 32-element block
 #pragma unroll
   for (int i = 0; i < kMaxXGroups; ++i) {
     const int it0 = i * kConsumerThreads;
@@ -149,25 +135,12 @@ __device__ __forceinline__ void x_commit(const XPrefetch& pf, const GemvParams& 
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = 0.f;
       }
-      // round to f16 (what the MMA sees); sums below use the rounded values
+      // round to f16 (what the MMA sees)
       __half hv[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) hv[j] = __float2half_rn(f[j]);
-      if (XSUM) {
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) s += __half2float(hv[j]);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        if (lpb == 8) s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (ok && (tid % lpb) == 0) xsum[(kk / 32) * 8 + col] = s * xsum_scale;
-      }
       if (ok) {
         __half* dst = xs + col * XP + kk;
-        if (PERM) {  // within each group of four: order 0,2,1,3 (fragment pairs are (b0,b2),(b1,b3))
-          __half t1 = hv[1]; hv[1] = hv[2]; hv[2] = t1;
-          __half t5 = hv[5]; hv[5] = hv[6]; hv[6] = t5;
-        }
         if (epg == 8) {
           *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hv);
         } else {
@@ -184,73 +157,6 @@ __device__ __forceinline__ void x_commit(const XPrefetch& pf, const GemvParams& 
 // Every decoder is split into a load half (shared-memory reads only, issued
 // back to back for several units) and a compute half, so the reads of the
 // next unit are in flight while the MMAs of this one run.
-
-// Q4_K: unit = 64 elements = sub-blocks (2c, 2c+1) of a super-block; they share 32 nibble bytes.
-struct Q4Regs {
-  uint32_t dmA, dmB, scA[3], scB[3], a0, a1, b0, b1;
-  uint2 x[4], xs[2];
-  int c;
-};
-__device__ __forceinline__ void q4_load(Q4Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, uint32_t xsum_t,
-                                        int unit, int t, bool xv) {
-  const int sb = unit >> 2, c = unit & 3;
-  r.c = c;
-  const uint32_t sbA = rowA + 144u * sb, sbB = rowB + 144u * sb;
-  r.dmA = lds32(sbA);
-  r.dmB = lds32(sbB);
-  // 12 scale bytes at +4: 6-bit (scale, min) pairs, the GGML get_scale_min_k4 packing
-  r.scA[0] = lds32<4>(sbA); r.scA[1] = lds32<8>(sbA); r.scA[2] = lds32<12>(sbA);
-  r.scB[0] = lds32<4>(sbB); r.scB[1] = lds32<8>(sbB); r.scB[2] = lds32<12>(sbB);
-  const uint32_t qo = 16u + 32u * c + 4u * t;
-  r.a0 = lds32<0>(sbA + qo); r.a1 = lds32<16>(sbA + qo);
-  r.b0 = lds32<0>(sbB + qo); r.b1 = lds32<16>(sbB + qo);
-  const uint32_t xo = xs_g + (256u * sb + 64u * c + 4u * t) * 2u;
-  const uint2 z = make_uint2(0u, 0u);
-  r.x[0] = xv ? lds64<0>(xo) : z; r.x[1] = xv ? lds64<32>(xo) : z;
-  r.x[2] = xv ? lds64<64>(xo) : z; r.x[3] = xv ? lds64<96>(xo) : z;
-  const uint32_t so = xsum_t + 32u * (8u * sb + 2u * c);
-  r.xs[0] = lds64<0>(so);
-  r.xs[1] = lds64<32>(so);
-}
-__device__ __forceinline__ void q4k_scale_min(const uint32_t (&w)[3], int j, float& sc, float& mn) {
-  uint32_t s, m;
-  if (j < 4) {
-    s = (w[0] >> (8 * j)) & 63u;
-    m = (w[1] >> (8 * j)) & 63u;
-  } else {
-    const int jj = j - 4;
-    s = ((w[2] >> (8 * jj)) & 0xFu) | (((w[0] >> (8 * jj + 6)) & 3u) << 4);
-    m = ((w[2] >> (8 * jj + 4)) & 0xFu) | (((w[1] >> (8 * jj + 6)) & 3u) << 4);
-  }
-  sc = (float)s;
-  mn = (float)m;
-}
-__device__ __forceinline__ void q4_compute(float (&acc)[4], const Q4Regs& r) {
-  const float dA = half_bits_to_float(r.dmA), mA = half_bits_to_float(r.dmA >> 16);
-  const float dB = half_bits_to_float(r.dmB), mB = half_bits_to_float(r.dmB >> 16);
-#pragma unroll
-  for (int hi = 0; hi < 2; ++hi) {
-    // low nibbles -> sub-block 2c (codes * 2^-24), high nibbles -> 2c+1 (codes * 2^-20)
-    const uint32_t mask = hi ? 0x00F000F0u : 0x000F000Fu;
-    float blk[4];
-    mma_f16_16816_c(blk, r.a0 & mask, r.b0 & mask, (r.a0 >> 8) & mask, (r.b0 >> 8) & mask, r.x[2 * hi].x,
-                    r.x[2 * hi].y, 0.f, 0.f, 0.f, 0.f);
-    mma_f16_16816(blk, r.a1 & mask, r.b1 & mask, (r.a1 >> 8) & mask, (r.b1 >> 8) & mask, r.x[2 * hi + 1].x,
-                  r.x[2 * hi + 1].y);
-    const int j = 2 * r.c + hi;
-    float scA, mnA, scB, mnB;
-    q4k_scale_min(r.scA, j, scA, mnA);
-    q4k_scale_min(r.scB, j, scB, mnB);
-    const float pw = hi ? 1048576.f : 16777216.f;
-    const float sx0 = __uint_as_float(r.xs[hi].x), sx1 = __uint_as_float(r.xs[hi].y);
-    const float fA = dA * scA * pw, fB = dB * scB * pw;
-    const float gA = -(mA * mnA), gB = -(mB * mnB);
-    acc[0] = fmaf(fA, blk[0], fmaf(gA, sx0, acc[0]));
-    acc[1] = fmaf(fA, blk[1], fmaf(gA, sx1, acc[1]));
-    acc[2] = fmaf(fB, blk[2], fmaf(gB, sx0, acc[2]));
-    acc[3] = fmaf(fB, blk[3], fmaf(gB, sx1, acc[3]));
-  }
-}
 
 __device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t v, uint32_t& lo, uint32_t& hi) {
   asm("{\n"
@@ -330,7 +236,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   constexpr int WK = kConsumerWarps;
   constexpr int RT = L::RT;
   const int NSTAGE = lay.nstage;
-  constexpr float kXsumScale = 1.f;   // per-block activation sums (Q4_K's min term)
   extern __shared__ __align__(128) uint8_t smem[];
 
   const int n_rt = (p.n + RT - 1) / RT;
@@ -449,11 +354,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   // ================= consumer warps ============================================
   const int wk = warp;
   __half* xs = reinterpret_cast<__half*>(smem + lay.off_x);
-  float* xsum = reinterpret_cast<float*>(smem + lay.off_xsum);
   const int XP = lay.xk + 16;                 // f16 elements per staged activation row
   const bool xv = g < lay.xs_rows;            // activation rows beyond the staged ones are zero
   const uint32_t xs_g = smem_u32(xs) + (uint32_t)(xv ? g : 0) * XP * 2u;
-  const uint32_t xsum_t = smem_u32(xsum) + 8u * t;
 
   XPrefetch pf;
   bool pf_valid = false;
@@ -485,11 +388,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         for (int i = tid; i < (staged_rows - wi.nrows) * (XP / 8); i += kConsumerThreads)
           reinterpret_cast<uint4*>(xs + wi.nrows * XP)[i] = make_uint4(0, 0, 0, 0);
         staged_rows = wi.nrows;
-        x_commit<F::kPermX, F::kNeedXsum>(pf, p, wi.nrows, min(xk_sub, k_len), tid, xs, XP, xsum, kXsumScale);
+        x_commit(pf, p, wi.nrows, min(xk_sub, k_len), tid, xs, XP);
         for (int sub = xk_sub; sub < k_len; sub += xk_sub) {   // f32 input: second half, fetched now
           x_prefetch(pf, p, wi.row0, wi.nrows, k_base + sub, min(xk_sub, k_len - sub), tid);
-          x_commit<F::kPermX, F::kNeedXsum>(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xs + sub, XP,
-                                            xsum + (sub / 32) * 8, kXsumScale);
+          x_commit(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xs + sub, XP);
         }
         staged_y = wi.y;
         pf_valid = false;
@@ -524,24 +426,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
           const uint32_t rowA = smem_u32(smem + s * L::STAGE_BYTES) + (uint32_t)g * L::PITCH;
           const uint32_t rowB = rowA + 8u * L::PITCH;
           const uint32_t xs_c = xs_g + 2u * kx;
-          const uint32_t xsum_c = xsum_t + 32u * (kx / 32);
           float(&a)[4] = acc[bank];
-          if (FMT == HQ_FMT_Q4_K) {
-            const int nunits = kc_len / 64;
-            int u = wrot;
-            for (; u + WK < nunits; u += 2 * WK) {
-              Q4Regs r0, r1;
-              q4_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
-              q4_load(r1, rowA, rowB, xs_c, xsum_c, u + WK, t, xv);
-              q4_compute(a, r0);
-              q4_compute(a, r1);
-            }
-            if (u < nunits) {
-              Q4Regs r0;
-              q4_load(r0, rowA, rowB, xs_c, xsum_c, u, t, xv);
-              q4_compute(a, r0);
-            }
-          } else if (FMT == HQ_FMT_FP8_BLOCK) {
+          if (FMT == HQ_FMT_FP8_BLOCK) {
             const int nunits = kc_len / 32;
             const float* fsc = reinterpret_cast<const float*>(bank == 0 ? p.scales : p.scales_up) +
                                (int64_t)wi.expert * p.scale_expert_stride +
@@ -625,16 +511,14 @@ static int32_t launch_cfg(const GemvParams& p, int n_y_max, int max_rows, cudaSt
     lay.xk = candidates[c];
     lay.xs_rows = max_rows;
     lay.x_bytes = lay.xs_rows * (lay.xk + 16) * 2;
-    const int xsum_bytes = F::kNeedXsum ? (lay.xk / 32) * 8 * 4 : 0;
     const int red_bytes = 2 * p.n_banks * kConsumerWarps * 4 * 32 * 4;
     const int bar_bytes = (2 * kMaxStages + 4) * 8 + 16;
-    const int fixed = lay.x_bytes + xsum_bytes + red_bytes + bar_bytes;
+    const int fixed = lay.x_bytes + red_bytes + bar_bytes;
     int nst = (kSmemBudget - fixed) / L::STAGE_BYTES;
     if (nst > kMaxStages) nst = kMaxStages;
     lay.nstage = nst;
     lay.off_x = nst * L::STAGE_BYTES;
-    lay.off_xsum = lay.off_x + lay.x_bytes;
-    lay.off_red = lay.off_xsum + xsum_bytes;
+    lay.off_red = lay.off_x + lay.x_bytes;
     lay.off_bar = lay.off_red + red_bytes;
     lay.total = lay.off_bar + bar_bytes;
     if (nst >= 4) break;
@@ -664,8 +548,8 @@ int32_t launch_gemv(const GemvParams& p, int n_y_max, cudaStream_t stream) {
   const int max_rows = p.tiles != nullptr ? 8 : (p.m < 8 ? p.m : 8);
   // chunk sizes keep every bulk copy (one row segment) at 2 KiB or more
   switch (p.format) {
-    case HQ_FMT_Q8_0: return launch_gemv_q8(p, n_y_max, max_rows, stream);
-    case HQ_FMT_Q4_K: return launch_cfg<HQ_FMT_Q4_K, 4096>(p, n_y_max, max_rows, stream);
+    case HQ_FMT_Q8_0:
+    case HQ_FMT_Q4_K: return launch_gemv_int8(p, n_y_max, max_rows, stream);   // integer-MMA kernel
     case HQ_FMT_FP8_BLOCK: return launch_cfg<HQ_FMT_FP8_BLOCK, 2048>(p, n_y_max, max_rows, stream);
     case HQ_FMT_MXFP4: return launch_cfg<HQ_FMT_MXFP4, 4096>(p, n_y_max, max_rows, stream);
     default: return HQ_ERR_FORMAT;

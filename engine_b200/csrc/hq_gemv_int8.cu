@@ -36,19 +36,37 @@ constexpr int kQ8Producers = 2;                  // producer warps: a bulk-copy 
                                                  // cycles per active lane, so the 16 row copies of a stage are
                                                  // split over two warps
 constexpr int kQ8Threads = kQ8Consumers + 32 * (kQ8Producers + 1);   // + producers + the reducing warp
-constexpr int kQ8KC = 2048;                      // k per stage
-constexpr int kQ8Seg = kQ8KC / 32 * 34;          // bytes of one row segment (one bulk copy)
-constexpr int kQ8Pitch = kQ8Seg + 32;            // row pitch in a stage: = 32 (mod 128), 8-byte loads of 4 rows
-                                                 // x 4 lanes cover all banks
 constexpr int kQ8RT = 16;
-constexpr int kQ8StageBytes = kQ8RT * kQ8Pitch;
+
+// Stage geometry per format.  A stage holds KC columns of 16 weight rows = 16 groups of GK columns; a group is
+// the unit a consumer warp works on (Q8_0: four 34-byte blocks = 136 bytes; Q4_K: one 144-byte super-block)
+// and the unit that shares one activation step.  Row segments (one bulk copy each) are >= 2 KiB; the row
+// pitch in a stage is = 32 (mod 128) so 8-byte loads of 4 rows x 4 lanes cover all banks.
+template <int FMT>
+struct I8Traits;
+template <>
+struct I8Traits<HQ_FMT_Q8_0> {
+  static constexpr int KC = 2048, GK = 128, GROUP_BYTES = 136;
+  static constexpr int SEG = KC / 32 * 34, PITCH = SEG + 32, STAGE_BYTES = kQ8RT * PITCH;
+  __host__ __device__ static constexpr int64_t row_bytes(int64_t k) { return k / 32 * 34; }
+  static constexpr bool kSubSums = false;
+};
+template <>
+struct I8Traits<HQ_FMT_Q4_K> {
+  static constexpr int KC = 4096, GK = 256, GROUP_BYTES = 144;
+  static constexpr int SEG = KC / 256 * 144, PITCH = SEG + 32, STAGE_BYTES = kQ8RT * PITCH;
+  __host__ __device__ static constexpr int64_t row_bytes(int64_t k) { return k / 256 * 144; }
+  static constexpr bool kSubSums = true;     // per 32-element sub-block sums of the staged bytes (the min term)
+};
 constexpr int kQ8MaxStages = 8;
 constexpr int kQ8SmemBudget = 227 * 1024 - 256;   // dynamic part; a few static words come on top
-constexpr int kQ8XGroups = 8;                    // 16-byte activation groups a thread prefetches per epoch
+constexpr int kQ8XGroups = 8;                    // 16-byte registers a thread prefetches activations into
 constexpr uint32_t kQ8Spin = 1u << 22;
 constexpr int kQ8Magic = 0x4B400000;             // 1.5 * 2^23 as f32 bits: magic + n reads as 12582912.f + n
-static_assert(kQ8Seg >= 2048 && kQ8Seg % 16 == 0, "bulk copy size");
-static_assert(kQ8Pitch % 128 == 32, "row pitch must spread banks");
+static_assert(I8Traits<HQ_FMT_Q8_0>::SEG >= 2048 && I8Traits<HQ_FMT_Q8_0>::SEG % 16 == 0, "bulk copy size");
+static_assert(I8Traits<HQ_FMT_Q4_K>::SEG >= 2048 && I8Traits<HQ_FMT_Q4_K>::SEG % 16 == 0, "bulk copy size");
+static_assert(I8Traits<HQ_FMT_Q8_0>::PITCH % 128 == 32 && I8Traits<HQ_FMT_Q4_K>::PITCH % 128 == 32, "row pitch");
+static_assert(I8Traits<HQ_FMT_Q8_0>::KC / I8Traits<HQ_FMT_Q8_0>::GK == 16 && I8Traits<HQ_FMT_Q4_K>::KC / I8Traits<HQ_FMT_Q4_K>::GK == 16, "16 groups per stage");
 
 // shared-memory plan of one launch (computed on the host)
 struct Q8Layout {
@@ -58,9 +76,9 @@ struct Q8Layout {
   int xk_sub;       // columns one register prefetch covers
   int xpitch;       // bytes between staged columns, = 32 (mod 128)
   int x_bytes;
-  int off_x, off_sx, off_red, off_bar, total;
+  int off_x, off_sx, off_xs, off_red, off_bar, total;   // off_xs: Q4_K sub-block sums [group][column][16]
   int kslices;            // K slices worked by different CTAs (1 = a CTA covers the whole K)
-  int chunks_per_slice;   // stages of kQ8KC columns per slice
+  int chunks_per_slice;   // stages per slice
   int32_t* counters;      // split K: arrivals per item stream (zero between launches)
   float* partials;        // split K: [item][slice][bank][4][32] partial sums
 };
@@ -98,59 +116,68 @@ __device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
 }
 
 // ---- activation staging ---------------------------------------------------------------------
-// Raw activation bytes are fetched one epoch ahead into registers (16 bytes per group), then every
-// 128-element group of a row is quantized by the 16 (or, for f32 input, 32) lanes that hold it.
+// Raw activations are fetched one epoch ahead into registers, eight elements per item (16 bytes of f16 / bf16,
+// 32 bytes of f32), then every GK-element group of a row is quantized by the GK/8 lanes that hold it.
 struct Q8XPrefetch {
   uint4 v[kQ8XGroups];
 };
 
 __device__ __forceinline__ void q8_x_prefetch(Q8XPrefetch& pf, const GemvParams& p, int row0, int nrows, int k0,
                                               int k_len, int tid) {
-  const int esz = dtype_size(p.x_dtype);
-  const int epg = 16 / esz;              // elements per 16-byte group
-  const int gpr = k_len / epg;           // groups per activation row in this epoch
-  const int ngroups = nrows * gpr;
+  const bool wide = p.x_dtype == HQ_DT_F32;
+  const int ipr = k_len >> 3;            // items per activation row in this epoch
+  const int nitems = nrows * ipr;
+  const int per_thread = wide ? kQ8XGroups / 2 : kQ8XGroups;
 #pragma unroll
   for (int i = 0; i < kQ8XGroups; ++i) {
     const int it = i * kQ8Consumers + tid;
-    if (it < ngroups) {
-      const int col = it / gpr;
-      const int kk = (it - col * gpr) * epg;
+    if (i < per_thread && it < nitems) {
+      const int col = it / ipr;
+      const int kk = (it - col * ipr) << 3;
       const int64_t xr = p.x_rows ? (int64_t)p.x_rows[row0 + col] : (int64_t)(row0 + col);
-      const char* src = (const char*)p.x + (xr * p.x_stride + k0 + kk) * esz;
-      pf.v[i] = __ldg(reinterpret_cast<const uint4*>(src));
+      const char* src = (const char*)p.x + (xr * p.x_stride + k0 + kk) * (wide ? 4 : 2);
+      if (wide) {
+        pf.v[(2 * i) % kQ8XGroups] = __ldg(reinterpret_cast<const uint4*>(src));
+        pf.v[(2 * i + 1) % kQ8XGroups] = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+      } else {
+        pf.v[i] = __ldg(reinterpret_cast<const uint4*>(src));
+      }
     }
   }
 }
 
 // k_len is a multiple of 256, so a warp never straddles two activation rows and is valid or idle as a whole.
 // xq: staged int8 columns of this epoch (column c at xq + c * xpitch), already offset to the sub-range;
-// sx: scale table [group][ncols] f32, likewise offset.
+// sx: step table [group][ncols] f32, xs: sub-block sums [group][ncols][16] bytes, likewise offset.
+template <int GK, bool SUBSUMS>
 __device__ __forceinline__ void q8_x_commit(const Q8XPrefetch& pf, const GemvParams& p, int nrows, int k_len, int tid,
-                                            uint8_t* xq, int xpitch, float* sx, int ncols) {
-  const int esz = dtype_size(p.x_dtype);
-  const int epg = 16 / esz;
-  const int gpr = k_len / epg;
-  const int ngroups = nrows * gpr;
-  const int l_off = ncols >> 1;          // column of the remainder term relative to the leading term
+                                            uint8_t* xq, int xpitch, float* sx, uint8_t* xs, int ncols) {
+  const bool wide = p.x_dtype == HQ_DT_F32;
+  const int ipr = k_len >> 3;
+  const int nitems = nrows * ipr;
+  const int per_thread = wide ? kQ8XGroups / 2 : kQ8XGroups;
+  const int l_off = ncols >> 1;          // column of the low byte relative to the high byte
 #pragma unroll
   for (int i = 0; i < kQ8XGroups; ++i) {
     const int it = i * kQ8Consumers + tid;
-    if (it < ngroups) {                  // uniform across the warp
-      const int col = it / gpr;
-      const int kk = (it - col * gpr) * epg;
-      const uint4 raw = pf.v[i];
+    if (i < per_thread && it < nitems) {   // uniform across the warp
+      const int col = it / ipr;
+      const int kk = (it - col * ipr) << 3;
       float f[8];
-      if (p.x_dtype == HQ_DT_F32) {
-        f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y);
-        f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
-        f[4] = f[5] = f[6] = f[7] = 0.f;
+      if (wide) {
+        const uint4 r0 = pf.v[(2 * i) % kQ8XGroups], r1 = pf.v[(2 * i + 1) % kQ8XGroups];
+        f[0] = __uint_as_float(r0.x); f[1] = __uint_as_float(r0.y);
+        f[2] = __uint_as_float(r0.z); f[3] = __uint_as_float(r0.w);
+        f[4] = __uint_as_float(r1.x); f[5] = __uint_as_float(r1.y);
+        f[6] = __uint_as_float(r1.z); f[7] = __uint_as_float(r1.w);
       } else if (p.x_dtype == HQ_DT_BF16) {
+        const uint4 raw = pf.v[i];
         f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xFFFF0000u);
         f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xFFFF0000u);
         f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xFFFF0000u);
         f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xFFFF0000u);
       } else {
+        const uint4 raw = pf.v[i];
         const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -167,7 +194,7 @@ __device__ __forceinline__ void q8_x_commit(const Q8XPrefetch& pf, const GemvPar
       abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 2));
       abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 4));
       abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 8));
-      if (epg == 4) abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 16));
+      if (GK == 256) abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 16));
       const float amax = __uint_as_float(abits);
       // The step s is the power of two at or above amax / 127 (not below 2^-100), so x / s and the products
       // with s are exact: an activation that is a small multiple of s (a one-hot row, say) passes through
@@ -191,17 +218,34 @@ __device__ __forceinline__ void q8_x_commit(const Q8XPrefetch& pf, const GemvPar
       }
       uint8_t* dh = xq + col * xpitch + kk;
       uint8_t* dl = dh + l_off * xpitch;
-      if (epg == 8) {
-        *reinterpret_cast<uint2*>(dh) = make_uint2(hq[0], hq[1]);
-        *reinterpret_cast<uint2*>(dl) = make_uint2(lq[0], lq[1]);
-      } else {
-        *reinterpret_cast<uint32_t*>(dh) = hq[0];
-        *reinterpret_cast<uint32_t*>(dl) = lq[0];
-      }
-      if ((kk & 127) == 0) {
-        float* d = sx + (kk >> 7) * ncols + col;
+      *reinterpret_cast<uint2*>(dh) = make_uint2(hq[0], hq[1]);
+      *reinterpret_cast<uint2*>(dl) = make_uint2(lq[0], lq[1]);
+      if ((kk & (GK - 1)) == 0) {
+        float* d = sx + (kk / GK) * ncols + col;
         d[0] = s;
         d[l_off] = s * (1.f / 256.f);
+      }
+      if (SUBSUMS) {
+        // sums of the staged bytes over each 32-element sub-block (4 lanes), written as 32 a + b with int8 a
+        // and b in 0..31, for the integer dot product with the sub-block minima
+        int sh = 0, sl = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          sh += (int)u[j] >> 8;
+          sl += (int)(u[j] & 0xFFu) - 128;
+        }
+        sh += __shfl_xor_sync(0xffffffffu, sh, 1);
+        sl += __shfl_xor_sync(0xffffffffu, sl, 1);
+        sh += __shfl_xor_sync(0xffffffffu, sh, 2);
+        sl += __shfl_xor_sync(0xffffffffu, sl, 2);
+        if ((kk & 31) == 0) {
+          const int j = (kk & 255) >> 5;
+          uint8_t* e = xs + ((kk >> 8) * ncols + col) * 16 + j;
+          e[0] = (uint8_t)(sh >> 5);
+          e[8] = (uint8_t)(sh & 31);
+          e[l_off * 16] = (uint8_t)(sl >> 5);
+          e[l_off * 16 + 8] = (uint8_t)(sl & 31);
+        }
       }
     }
   }
@@ -277,14 +321,113 @@ __device__ __forceinline__ void q8_group(float (&acc)[NCS][4], uint32_t pa, uint
   }
 }
 
+// ---- Q4_K: one super-block (256 weights) x 16 weight rows x NCS column sets ---------------------------
+// y = d * sum_j sc_j * (q_j . x_j) - dmin * sum_j m_j * sum(x_j) over the eight 32-element sub-blocks j.  The
+// 4-bit codes enter the integer MMA as bytes 0..15 (a mask and a shift, no conversion); the 6-bit sub-block
+// scales multiply the integer block sums with integer multiply-adds, so one conversion to float per output
+// serves the whole super-block; the minima meet the staged sub-block sums of the activations in two more MMAs
+// (k = sub-block index).  Nibble bytes 32c..32c+31 hold sub-block 2c in their low and 2c+1 in their high
+// nibbles; lane t owns bytes 8t..8t+7 of each 32-byte chunk.
+//   pa, pb : shared addresses of the super-block in rows g and g+8, plus 8t;  da, db : the same without 8t
+//   xq     : shared address of staged column g at this group's first element, plus 8t
+//   sx     : shared address of this group's step-table row, plus 8t bytes (columns 2t, 2t+1)
+//   xs     : shared address of this group's sub-block sums for column g, plus 4 (t & 1)
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void mma_s8_16832_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NCS>
+__device__ __forceinline__ void q4k_group(float (&acc)[NCS][4], uint32_t pa, uint32_t pb, uint32_t da, uint32_t db,
+                                          uint32_t xq, uint32_t cs_stride, uint32_t sx, uint32_t xs,
+                                          uint32_t xs_cs_stride, int t) {
+  // ---- all shared loads first ----
+  const uint4 hA = lds128(da), hB = lds128(db);     // {d | dmin, 12 bytes of 6-bit scales and minima}
+  uint2 qA[4], qB[4];
+  qA[0] = lds64<16>(pa); qA[1] = lds64<48>(pa); qA[2] = lds64<80>(pa); qA[3] = lds64<112>(pa);
+  qB[0] = lds64<16>(pb); qB[1] = lds64<48>(pb); qB[2] = lds64<80>(pb); qB[3] = lds64<112>(pb);
+  uint2 xb[NCS][8];
+  uint2 sxv[NCS];
+  uint32_t xsa[NCS], xsb[NCS];
+#pragma unroll
+  for (int c = 0; c < NCS; ++c) {
+    const uint32_t xc = xq + c * cs_stride;
+    xb[c][0] = lds64<0>(xc);   xb[c][1] = lds64<32>(xc);  xb[c][2] = lds64<64>(xc);  xb[c][3] = lds64<96>(xc);
+    xb[c][4] = lds64<128>(xc); xb[c][5] = lds64<160>(xc); xb[c][6] = lds64<192>(xc); xb[c][7] = lds64<224>(xc);
+    sxv[c] = lds64(sx + 32u * c);
+    xsa[c] = lds32<0>(xs + c * xs_cs_stride);
+    xsb[c] = lds32<8>(xs + c * xs_cs_stride);
+  }
+  // ---- 6-bit scales and minima, four to a word (sub-blocks 0-3 and 4-7) ----
+  uint32_t scA[2], scB[2], mnA[2], mnB[2];
+  scA[0] = hA.y & 0x3F3F3F3Fu; mnA[0] = hA.z & 0x3F3F3F3Fu;
+  scA[1] = (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u);
+  mnA[1] = ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u);
+  scB[0] = hB.y & 0x3F3F3F3Fu; mnB[0] = hB.z & 0x3F3F3F3Fu;
+  scB[1] = (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u);
+  mnB[1] = ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u);
+  // ---- nibbles to bytes ----
+  uint32_t aL[4][2], aH[4][2], bL[4][2], bH[4][2];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    aL[c][0] = qA[c].x & 0x0F0F0F0Fu; aL[c][1] = qA[c].y & 0x0F0F0F0Fu;
+    aH[c][0] = (qA[c].x >> 4) & 0x0F0F0F0Fu; aH[c][1] = (qA[c].y >> 4) & 0x0F0F0F0Fu;
+    bL[c][0] = qB[c].x & 0x0F0F0F0Fu; bL[c][1] = qB[c].y & 0x0F0F0F0Fu;
+    bH[c][0] = (qB[c].x >> 4) & 0x0F0F0F0Fu; bH[c][1] = (qB[c].y >> 4) & 0x0F0F0F0Fu;
+  }
+  const float dA = half_bits_to_float(hA.x), nA = half_bits_to_float(hA.x >> 16);
+  const float dB = half_bits_to_float(hB.x), nB = half_bits_to_float(hB.x >> 16);
+  // the minima as the A operand of the sub-block-sum MMAs: k = sub-block index (8 of the 32 k slots used)
+  const uint32_t mA = t == 0 ? mnA[0] : (t == 1 ? mnA[1] : 0u);
+  const uint32_t mB = t == 0 ? mnB[0] : (t == 1 ? mnB[1] : 0u);
+#pragma unroll
+  for (int c = 0; c < NCS; ++c) {
+    int isum[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int ch = j >> 1;
+      int d[4];
+      if (j & 1) mma_s8_16832(d, aH[ch][0], bH[ch][0], aH[ch][1], bH[ch][1], xb[c][j].x, xb[c][j].y, 0);
+      else       mma_s8_16832(d, aL[ch][0], bL[ch][0], aL[ch][1], bL[ch][1], xb[c][j].x, xb[c][j].y, 0);
+      const int sa = (int)((scA[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+      const int sb = (int)((scB[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+      isum[0] += sa * d[0];
+      isum[1] += sa * d[1];
+      isum[2] += sb * d[2];
+      isum[3] += sb * d[3];
+    }
+    // |isum| <= 8 * 63 * 32 * 15 * 128 < 2^31
+    int ma[4] = {0, 0, 0, 0}, mb[4] = {0, 0, 0, 0};
+    mma_s8_16832_acc(ma, mA, mB, 0u, 0u, xsa[c], 0u);
+    mma_s8_16832_acc(mb, mA, mB, 0u, 0u, xsb[c], 0u);
+    const float s0 = __uint_as_float(sxv[c].x), s1 = __uint_as_float(sxv[c].y);
+    const float v0 = dA * (float)isum[0] - nA * (float)(32 * ma[0] + mb[0]);
+    const float v1 = dA * (float)isum[1] - nA * (float)(32 * ma[1] + mb[1]);
+    const float v2 = dB * (float)isum[2] - nB * (float)(32 * ma[2] + mb[2]);
+    const float v3 = dB * (float)isum[3] - nB * (float)(32 * ma[3] + mb[3]);
+    acc[c][0] = fmaf(v0, s0, acc[c][0]);
+    acc[c][1] = fmaf(v1, s1, acc[c][1]);
+    acc[c][2] = fmaf(v2, s0, acc[c][2]);
+    acc[c][3] = fmaf(v3, s1, acc[c][3]);
+  }
+}
+
 // ---- the kernel ------------------------------------------------------------------------------------
 // NCS = column sets per block: 1 when every work item has at most 4 activation rows (columns 0-3 hold the
 // leading terms, 4-7 the remainders), 2 for up to 8 rows (set 0 = leading terms, set 1 = remainders).
-template <int NCS>
-__global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams p, const Q8Layout lay) {
+template <int FMT, int NCS>
+__global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvParams p, const Q8Layout lay) {
+  using T = I8Traits<FMT>;
   constexpr int WK = kQ8Warps;
   constexpr int RT = kQ8RT;
-  constexpr int KC = kQ8KC;
+  constexpr int KC = T::KC;
   const int NSTAGE = lay.nstage;
   extern __shared__ __align__(128) uint8_t smem[];
 
@@ -329,7 +472,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
     reinterpret_cast<uint4*>(smem + lay.off_x)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
 
-  const int64_t row_bytes = (int64_t)p.k / 32 * 34;
+  const int64_t row_bytes = T::row_bytes(p.k);
 
   if (warp >= WK && warp < WK + kQ8Producers) {
     // ================= producer warps: stream weight row segments ================================
@@ -346,7 +489,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
       const int my_rows = max(0, min(RPP, rows_valid - pw * RPP));
       for (int chunk = ck_lo; chunk < ck_hi; ++chunk) {
         const int kc_len = min(KC, p.k - chunk * KC);
-        const uint32_t bytes = (uint32_t)(kc_len / 32 * 34);
+        const uint32_t bytes = (uint32_t)T::row_bytes(kc_len);
         for (int bank = 0; bank < p.n_banks; ++bank) {
           if (round > 0) {
             if (!mbar_wait_backoff(&empty[s], (round - 1) & 1, spin)) {
@@ -357,12 +500,12 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
           }
           const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(bank == 0 ? p.w : p.w_up) +
                                 (int64_t)wi.expert * p.w_expert_stride + (int64_t)(wi.n0 + pw * RPP) * row_bytes +
-                                (int64_t)chunk * kQ8Seg;
+                                (int64_t)chunk * T::SEG;
           if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * (uint32_t)my_rows);
           __syncwarp();
-          uint8_t* dst = smem + s * kQ8StageBytes + pw * RPP * kQ8Pitch;
+          uint8_t* dst = smem + s * T::STAGE_BYTES + pw * RPP * T::PITCH;
           if (lane < my_rows)
-            bulk_g2s_hint(dst + lane * kQ8Pitch, wsrc + (int64_t)lane * row_bytes, bytes, &full[s], policy);
+            bulk_g2s_hint(dst + lane * T::PITCH, wsrc + (int64_t)lane * row_bytes, bytes, &full[s], policy);
           if (++s == NSTAGE) {
             s = 0;
             ++round;
@@ -429,8 +572,10 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
   const int ncols = lay.ncols;
   const uint32_t cs_stride = 8u * (uint32_t)xpitch;
   // this lane's staged column (column g of every set), its group within a stage, its scale-table columns
-  const uint32_t xq_lane = smem_u32(xq) + (uint32_t)g * xpitch + 128u * warp + 8u * t;
+  const uint32_t xq_lane = smem_u32(xq) + (uint32_t)g * xpitch + (uint32_t)T::GK * warp + 8u * t;
   const uint32_t sx_lane = smem_u32(sx) + (uint32_t)warp * ncols * 4u + 8u * t;
+  uint8_t* xsub = smem + lay.off_xs;     // Q4_K: sub-block sums [group][column][16]
+  const uint32_t xs_lane = smem_u32(xsub) + ((uint32_t)warp * ncols + g) * 16u + 4u * (t & 1);
 
   Q8XPrefetch pf;
   bool pf_valid = false;
@@ -476,11 +621,11 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
           }
         }
         staged_rows = wi.nrows;
-        q8_x_commit(pf, p, wi.nrows, min(xk_sub, k_len), tid, xq, xpitch, sx, ncols);
+        q8_x_commit<T::GK, T::kSubSums>(pf, p, wi.nrows, min(xk_sub, k_len), tid, xq, xpitch, sx, xsub, ncols);
         for (int sub = xk_sub; sub < k_len; sub += xk_sub) {   // wide input: the rest is fetched now
           q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base + sub, min(xk_sub, k_len - sub), tid);
-          q8_x_commit(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xq + sub, xpitch, sx + (sub >> 7) * ncols,
-                      ncols);
+          q8_x_commit<T::GK, T::kSubSums>(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xq + sub, xpitch,
+                                          sx + (sub / T::GK) * ncols, xsub + (sub / T::GK) * ncols * 16, ncols);
         }
         staged_y = wi.y;
         pf_valid = false;
@@ -499,7 +644,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
       }
       const int c0 = k_base / KC, c1 = (k_base + k_len + KC - 1) / KC;
       for (int chunk = c0; chunk < c1; ++chunk) {
-        const int ngroups = min(KC, p.k - chunk * KC) >> 7;   // 128-element groups in this stage
+        const int ngroups = min(KC, p.k - chunk * KC) / T::GK;   // groups in this stage
         const uint32_t kx = (uint32_t)(chunk * KC - k_base);  // offset of the stage inside the staged activations
 #pragma unroll
         for (int bank = 0; bank < 2; ++bank) {
@@ -513,10 +658,17 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_q8_kernel(const GemvParams
           for (int gi = 0; gi < kQ8GroupsPerWarp; ++gi) {
             const int grp = warp + gi * WK;
             if (grp < ngroups) {
-              const uint32_t da = smem_u32(smem + s * kQ8StageBytes) + (uint32_t)g * kQ8Pitch + 136u * grp;
-              const uint32_t db = da + 8u * kQ8Pitch;
-              q8_group<NCS>(acc[bank], da + 8u * t, db + 8u * t, da, db, xq_lane + kx + 128u * (gi * WK), cs_stride,
-                            sx_lane + ((kx >> 7) + gi * WK) * (uint32_t)ncols * 4u);
+              const uint32_t da = smem_u32(smem + s * T::STAGE_BYTES) + (uint32_t)g * T::PITCH +
+                                  (uint32_t)T::GROUP_BYTES * grp;
+              const uint32_t db = da + 8u * T::PITCH;
+              const uint32_t gq = kx / T::GK + gi * WK;      // group index inside the staged activations, less `warp`
+              if (FMT == HQ_FMT_Q8_0) {
+                q8_group<NCS>(acc[bank], da + 8u * t, db + 8u * t, da, db, xq_lane + gq * T::GK, cs_stride,
+                              sx_lane + gq * (uint32_t)ncols * 4u);
+              } else {
+                q4k_group<NCS>(acc[bank], da + 8u * t, db + 8u * t, da, db, xq_lane + gq * T::GK, cs_stride,
+                               sx_lane + gq * (uint32_t)ncols * 4u, xs_lane + gq * (uint32_t)ncols * 16u, 128u, t);
+              }
             }
           }
           __syncwarp();
@@ -597,18 +749,25 @@ struct Q8Split {
   int kslices, chunks_per_slice;
   int64_t counter_bytes, bytes;
 };
-static int q8_ring_stages(int ncols, int xk, int n_banks) {
-  const int fixed = ncols * (xk + 32) + (xk / 128) * ncols * 4 + 2 * n_banks * kQ8Warps * 4 * 32 * 4 +
-                    (2 * kQ8MaxStages + 4) * 8 + 16;
-  return (kQ8SmemBudget - fixed) / kQ8StageBytes;
+template <int FMT>
+static int q8_fixed_bytes(int ncols, int xk, int n_banks) {
+  using T = I8Traits<FMT>;
+  return ncols * (xk + 32) + (xk / T::GK) * ncols * 4 + (T::kSubSums ? (xk / T::GK) * ncols * 16 : 0) +
+         2 * n_banks * kQ8Warps * 4 * 32 * 4 + (2 * kQ8MaxStages + 4) * 8 + 16;
 }
+template <int FMT>
+static int q8_ring_stages(int ncols, int xk, int n_banks) {
+  return (kQ8SmemBudget - q8_fixed_bytes<FMT>(ncols, xk, n_banks)) / I8Traits<FMT>::STAGE_BYTES;
+}
+template <int FMT>
 static Q8Split q8_split_plan(int64_t n, int64_t k, int64_t n_y, int n_banks, bool expert_indexed, int ncols) {
+  constexpr int KC = I8Traits<FMT>::KC;
   Q8Split sp{};
-  const int nchunk = (int)((k + kQ8KC - 1) / kQ8KC);
+  const int nchunk = (int)((k + KC - 1) / KC);
   const int64_t items = n_y * ((n + kQ8RT - 1) / kQ8RT);
   sp.kslices = 1;
   sp.chunks_per_slice = nchunk;
-  if (expert_indexed || nchunk < 2 || q8_ring_stages(ncols, nchunk * kQ8KC, n_banks) >= 4) return sp;
+  if (expert_indexed || nchunk < 2 || q8_ring_stages<FMT>(ncols, nchunk * KC, n_banks) >= 4) return sp;
   sp.chunks_per_slice = (nchunk + 7) / 8;
   sp.kslices = (nchunk + sp.chunks_per_slice - 1) / sp.chunks_per_slice;
   sp.counter_bytes = 1024;     // one arrival counter per item stream (at most one stream per SM)
@@ -616,18 +775,21 @@ static Q8Split q8_split_plan(int64_t n, int64_t k, int64_t n_y, int n_banks, boo
   return sp;
 }
 
-int64_t gemv_q8_workspace_bytes(int64_t n, int64_t k, int64_t m) {
-  return q8_split_plan(n, k, (m + 7) / 8, 1, false, m > 4 ? 16 : 8).bytes;
+int64_t gemv_int8_workspace_bytes(int format, int64_t n, int64_t k, int64_t m) {
+  if (format == HQ_FMT_Q8_0) return q8_split_plan<HQ_FMT_Q8_0>(n, k, (m + 7) / 8, 1, false, m > 4 ? 16 : 8).bytes;
+  if (format == HQ_FMT_Q4_K) return q8_split_plan<HQ_FMT_Q4_K>(n, k, (m + 7) / 8, 1, false, m > 4 ? 16 : 8).bytes;
+  return 0;
 }
 
-template <int NCS>
+template <int FMT, int NCS>
 static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
+  using T = I8Traits<FMT>;
   Q8Layout lay{};
   lay.ncols = 8 * NCS;
-  Q8Split sp = q8_split_plan(p.n, p.k, n_y_max, p.n_banks, p.tiles != nullptr, lay.ncols);
+  Q8Split sp = q8_split_plan<FMT>(p.n, p.k, n_y_max, p.n_banks, p.tiles != nullptr, lay.ncols);
   if (sp.kslices > 1 && (p.workspace == nullptr || p.workspace_bytes < sp.bytes)) {
     sp.kslices = 1;                      // no scratch from the caller: every CTA covers the whole K
-    sp.chunks_per_slice = (p.k + kQ8KC - 1) / kQ8KC;
+    sp.chunks_per_slice = (p.k + T::KC - 1) / T::KC;
   }
   lay.kslices = sp.kslices;
   lay.chunks_per_slice = sp.chunks_per_slice;
@@ -639,31 +801,33 @@ static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cud
   // K range when it fits -- then a persistent CTA quantizes its activations once), give every remaining byte
   // to the ring.
   const int esz = dtype_size(p.x_dtype);
-  const int k_round = sp.chunks_per_slice * kQ8KC;
+  const int k_round = sp.chunks_per_slice * T::KC;
   const int candidates[3] = {k_round, 8192 < k_round ? 8192 : k_round, 4096 < k_round ? 4096 : k_round};
   for (int c = 0; c < 3; ++c) {
     lay.xk = candidates[c];
     lay.xpitch = lay.xk + 32;
     lay.x_bytes = lay.ncols * lay.xpitch;
-    const int sx_bytes = (lay.xk / 128) * lay.ncols * 4;
+    const int sx_bytes = (lay.xk / T::GK) * lay.ncols * 4;
+    const int xs_bytes = T::kSubSums ? (lay.xk / T::GK) * lay.ncols * 16 : 0;
     const int red_bytes = 2 * p.n_banks * kQ8Warps * 4 * 32 * 4;
     const int bar_bytes = (2 * kQ8MaxStages + 4) * 8 + 16;
-    const int fixed = lay.x_bytes + sx_bytes + red_bytes + bar_bytes;
-    int nst = (kQ8SmemBudget - fixed) / kQ8StageBytes;
+    const int fixed = lay.x_bytes + sx_bytes + xs_bytes + red_bytes + bar_bytes;
+    int nst = (kQ8SmemBudget - fixed) / T::STAGE_BYTES;
     if (nst > kQ8MaxStages) nst = kQ8MaxStages;
     lay.nstage = nst;
-    lay.off_x = nst * kQ8StageBytes;
+    lay.off_x = nst * T::STAGE_BYTES;
     lay.off_sx = lay.off_x + lay.x_bytes;
-    lay.off_red = lay.off_sx + sx_bytes;
+    lay.off_xs = lay.off_sx + sx_bytes;
+    lay.off_red = lay.off_xs + xs_bytes;
     lay.off_bar = lay.off_red + red_bytes;
     lay.total = lay.off_bar + bar_bytes;
     if (nst >= 4) break;
   }
   if (lay.nstage < 2) return HQ_ERR_SHAPE;
   // columns one register prefetch can hold, in whole 256-column steps
-  const int sub = (kQ8XGroups * kQ8Consumers * 16) / (max_rows * esz) / 256 * 256;
+  const int sub = (kQ8XGroups * kQ8Consumers * 16) / (max_rows * esz) / 256 * 256;   // 16 bytes per register
   lay.xk_sub = sub < lay.xk ? sub : lay.xk;
-  auto kern = gemv_q8_kernel<NCS>;
+  auto kern = gemv_int8_kernel<FMT, NCS>;
   static bool attr_done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
@@ -682,10 +846,15 @@ static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cud
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
-int32_t launch_gemv_q8(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
+int32_t launch_gemv_int8(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
   if (p.k % 256 != 0) return HQ_ERR_SHAPE;   // row segments must stay 16-byte aligned for the bulk copies
-  return max_rows > 4 ? launch_q8_cfg<2>(p, n_y_max, max_rows, stream)
-                      : launch_q8_cfg<1>(p, n_y_max, max_rows, stream);
+  if (p.format == HQ_FMT_Q8_0)
+    return max_rows > 4 ? launch_q8_cfg<HQ_FMT_Q8_0, 2>(p, n_y_max, max_rows, stream)
+                        : launch_q8_cfg<HQ_FMT_Q8_0, 1>(p, n_y_max, max_rows, stream);
+  if (p.format == HQ_FMT_Q4_K)
+    return max_rows > 4 ? launch_q8_cfg<HQ_FMT_Q4_K, 2>(p, n_y_max, max_rows, stream)
+                        : launch_q8_cfg<HQ_FMT_Q4_K, 1>(p, n_y_max, max_rows, stream);
+  return HQ_ERR_FORMAT;
 }
 
 }  // namespace hq

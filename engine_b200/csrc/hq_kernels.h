@@ -35,12 +35,12 @@ struct GemvParams {
   const int32_t* y_rows;        // sorted row -> output row (nullptr = identity)
   hq_act_args act;
   int32_t* status;
-  void* workspace;              // optional caller scratch for split-K partial sums (Q8_0), zero between calls
+  void* workspace;              // optional caller scratch for split-K partial sums (Q8_0, Q4_K), zero between calls
   int64_t workspace_bytes;
 };
 int32_t launch_gemv(const GemvParams& p, int grid_y, cudaStream_t stream);
-// scratch bytes the Q8_0 decode kernel wants for a dense [m, k] x [n, k] call (0 = none)
-int64_t gemv_q8_workspace_bytes(int64_t n, int64_t k, int64_t m);
+// scratch bytes the Q8_0 / Q4_K decode kernel wants for a dense [m, k] x [n, k] call (0 = none)
+int64_t gemv_int8_workspace_bytes(int format, int64_t n, int64_t k, int64_t m);
 
 // ---- grouped expert GEMM on tcgen05 (hq_grouped_gemm.cu) -----------------------------
 struct GroupedParams {
