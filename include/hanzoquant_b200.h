@@ -123,11 +123,12 @@ int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, in
 
 /* The same call with caller-owned scratch, the counterpart of the Q8_1 activation buffer the reference's
  * host side allocates for launch_mmvq_gguf_quantize_q8_1_* (hanzo-quant/src/gguf/fast_mmvq.rs:107-148).
- * With it the Q8_0 decode kernel splits K across CTAs when an output has few rows or K is long (partial sums
- * meet in the scratch and are added in a fixed order: results stay bit-reproducible).
- * hq_linear_workspace_bytes gives the size for (w, m), 0 when the call would not use any.  The scratch must be
- * 256-byte aligned and zero-filled once before its first use; every call leaves it zero-filled again.  One
- * scratch serves one stream at a time.  workspace == NULL is allowed and equals hq_linear_forward. */
+ * With it the Q8_0 / Q4_K decode kernel splits K across CTAs when K is too long for a CTA to keep its
+ * activations staged (partial sums meet in the scratch and are added in a fixed order: results stay
+ * bit-reproducible).  hq_linear_workspace_bytes gives the size for (w, m), 0 when the call would not use
+ * any.  The scratch must be 256-byte aligned and zero-filled once before its first use; every call leaves
+ * its arrival counters (the first 1024 bytes) at zero again and overwrites the rest.  One scratch serves
+ * one stream at a time.  workspace == NULL is allowed and equals hq_linear_forward. */
 int64_t hq_linear_workspace_bytes(const hq_weight* w, int64_t m);
 int32_t hq_linear_forward_ws(const hq_weight* w, const void* x, int32_t x_dtype, int64_t x_stride, void* y,
                              int32_t y_dtype, int64_t y_stride, int64_t m, void* workspace, int64_t workspace_bytes,
