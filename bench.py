@@ -523,9 +523,13 @@ def run_moe(args):
     gen = torch.Generator(device=dev)
     gen.manual_seed(3000 + rank)
     e, k, h, t_global = cfg["e"], cfg["k"], cfg["h"], cfg["t"]
-    t_local = t_global // world                      # tokens are data-parallel, experts sharded E/world per rank
+    # tokens are data-parallel, experts sharded E/world per rank.  Weak scaling (default): every rank brings the
+    # configuration's token count; strong: the global count is split.
+    weak = args.ep_scaling == "weak"
+    t_local = t_global if weak else t_global // world
+    t_global = t_local * world
     experts = build_moe_layer(torch, hq, cfg, gen, dev, e // world)
-    ep = ExpertParallelMoE(e, experts) if world > 1 else None
+    ep = ExpertParallelMoE(e, experts, wire_dtype=torch.float16) if world > 1 else None
     shared = None
     if cfg.get("shared"):
         # the always-on shared expert: the same three projections as a one-expert bank over this rank's tokens
@@ -652,7 +656,7 @@ def run_moe(args):
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "scaling": "weak" if weak else "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": cfg["label"], "format": cfg["fmt"], "experts": e, "top_k": k, "hidden": h,
                        "intermediate": cfg["i"], "tokens_global": t_global, "experts_per_gpu": e // world,
                        "parallelism": f"ep{world}", "l2": "expert banks exceed L2; activations rotate over 4 buffers"},
@@ -676,7 +680,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="gemv", choices=["gemv"] + list(MOE_CFGS))
-    ap.add_argument("--tokens", type=int, default=0, help="override the global token count of a MoE workload")
+    ap.add_argument("--tokens", type=int, default=0, help="override the token count of a MoE workload")
+    ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"],
+                    help="MoE workloads on several GPUs: tokens per GPU fixed (weak) or global count split (strong)")
     ap.add_argument("--only", default=None, help="restrict the sweep to one KxN shape, e.g. 4096x128256 "
                     "(profiling aid; the reported line is then not the headline workload)")
     args = ap.parse_args()

@@ -82,6 +82,8 @@ int32_t launch_weighted_reduce(const void* y, int y_dtype, const float* w, const
   HQ_WR(HQ_DT_BF16, __nv_bfloat16, HQ_DT_BF16, __nv_bfloat16)
   HQ_WR(HQ_DT_F16, __half, HQ_DT_F32, float)
   HQ_WR(HQ_DT_F16, __half, HQ_DT_F16, __half)
+  HQ_WR(HQ_DT_F16, __half, HQ_DT_BF16, __nv_bfloat16)
+  HQ_WR(HQ_DT_BF16, __nv_bfloat16, HQ_DT_F16, __half)
 #undef HQ_WR
   return HQ_ERR_FORMAT;
 }
