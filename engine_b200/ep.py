@@ -62,7 +62,18 @@ class ExpertParallelMoE:
 
     def plan(self, topk_ids: torch.Tensor):
         """Order the flat assignment list by destination rank (stable).  Returns (order, send_counts, local_ids,
-        row_map): order[i] = flat index t*k+s of the i-th row sent; row_map[t*k+s] = its position."""
+        row_map): order[i] = flat index t*k+s of the i-th row sent; row_map[t*k+s] = its position.
+        On the GPU the ordering is the library's own stable dispatch build with ranks in the place of experts
+        (three small kernels instead of a sort)."""
+        if topk_ids.is_cuda:
+            from .quant import moe_dispatch_build
+            ids32 = topk_ids.to(torch.int32)
+            dest = torch.div(ids32, self.e_local, rounding_mode="floor")
+            tab = moe_dispatch_build(dest, self.world)
+            order = tab.sorted_assign
+            send_counts = (tab.expert_bounds[1:] - tab.expert_bounds[:-1]).to(torch.int64)
+            local_ids = (ids32 - dest * self.e_local).reshape(-1).index_select(0, order)
+            return order, send_counts, local_ids, tab.inv_perm
         flat = topk_ids.reshape(-1).to(torch.int64)
         dest = torch.div(flat, self.e_local, rounding_mode="floor")
         order = torch.argsort(dest, stable=True)
@@ -94,8 +105,9 @@ class ExpertParallelMoE:
         order, send_counts, local_ids, row_map = self.plan(topk_ids)
         recv_counts = self._exchange_counts(send_counts)
         # split sizes are needed on the host by the collective: one small device->host read per layer
-        send_splits = [int(v) for v in send_counts.tolist()]
-        recv_splits = [int(v) for v in recv_counts.tolist()]
+        both = torch.stack([send_counts, recv_counts]).tolist()
+        send_splits = [int(v) for v in both[0]]
+        recv_splits = [int(v) for v in both[1]]
         self.last_counts = (send_splits, recv_splits)
         rows = x.index_select(0, torch.div(order, k, rounding_mode="floor"))
         got_rows = self._all_to_all_v(rows, send_splits, recv_splits)
