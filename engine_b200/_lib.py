@@ -45,6 +45,11 @@ SIGNATURES = {
     "hq_error_string": (C.c_char_p, [_I32]),
     "hq_status_read": (_I32, [_P, C.POINTER(_I32 * 4), _P]),
     "hq_linear_forward": (_I32, [C.POINTER(HqWeight), _P, _I32, _I64, _P, _I32, _I64, _I64, _P, _P]),
+    "hq_fp8_quant_rows": (_I32, [_P, _I32, _I64, _P, _I64, _I64, _P, _P, _P]),
+    "hq_fp8_gated_quant_rows": (_I32, [_P, _I32, _I64, _I64, C.POINTER(HqActArgs), _P, _P, _P]),
+    "hq_fp8_linear_forward": (_I32, [C.POINTER(HqWeight), _P, _P, _I64, _P, _I32, _I64, _P, _P]),
+    "hq_moe_fp8_gather_forward": (_I32, [C.POINTER(HqWeight), _P, _P, _I64, _I32, _P, _P, _P, _P, _I32, _I64, _I32,
+                                         _P, _P]),
     "hq_linear_workspace_bytes": (_I64, [C.POINTER(HqWeight), _I64]),
     "hq_linear_forward_ws": (_I32, [C.POINTER(HqWeight), _P, _I32, _I64, _P, _I32, _I64, _I64, _P, _I64, _P, _P]),
     "hq_router_topk": (_I32, [_P, _I32, _I64, C.POINTER(HqRouterArgs), _P, _P, _P]),

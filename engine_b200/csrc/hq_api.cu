@@ -289,6 +289,90 @@ int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const h
   return launch_gemv(p, (int)l.max_tiles8, (cudaStream_t)stream);
 }
 
+// ---- block-FP8 layers with FP8 activations (codes + 1 x 128 scales) ------------------------------------
+static int32_t check_fp8_native(const hq_weight* w) {
+  int32_t rc = check_weight(w);
+  if (rc != HQ_OK) return rc;
+  if (w->format != HQ_FMT_FP8_BLOCK) return HQ_ERR_FORMAT;
+  if (!fp8_grouped_supported(w->n, w->k)) return HQ_ERR_SHAPE;
+  return HQ_OK;
+}
+static void fill_fp8_native(Fp8GroupedParams& g, const hq_weight* w) {
+  g.n = (int)w->n;
+  g.k = (int)w->k;
+  g.n_experts = w->n_experts;
+  g.w = w->data;
+  g.w_scales = (const float*)w->scales;
+  g.fp8_nb = (int)((w->n + 127) / 128);
+  g.fp8_kb = (int)((w->k + 127) / 128);
+  g.bias = w->bias;
+  g.bias_dtype = w->bias_dtype;
+}
+
+int32_t hq_fp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,
+                          int64_t k, uint8_t* codes, float* scales, void* stream) {
+  if (n_rows < 0 || k < 128 || k % 128 != 0 || x_stride < k) return HQ_ERR_SHAPE;
+  if (n_rows == 0) return HQ_OK;
+  if (x == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(x_dtype)) return HQ_ERR_FORMAT;
+  return launch_fp8_quant_rows(x, x_dtype, x_stride, row_map, n_rows, k, codes, scales, (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_gated_quant_rows(const void* gate_up, int32_t dtype, int64_t n_rows, int64_t width,
+                                const hq_act_args* act, uint8_t* codes, float* scales, void* stream) {
+  if (n_rows < 0 || width < 128 || width % 128 != 0) return HQ_ERR_SHAPE;
+  if (n_rows == 0) return HQ_OK;
+  if (gate_up == nullptr || act == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(dtype) || act->act == HQ_ACT_NONE) return HQ_ERR_FORMAT;
+  return launch_fp8_gated_quant_rows(gate_up, dtype, n_rows, width, *act, codes, scales, (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_linear_forward(const hq_weight* w, const uint8_t* x_codes, const float* x_scales, int64_t m, void* y,
+                              int32_t y_dtype, int64_t y_stride, int32_t* status_dev, void* stream) {
+  int32_t rc = check_fp8_native(w);
+  if (rc != HQ_OK) return rc;
+  if (w->n_experts != 1 || m < 0 || m > (1 << 24) || y_stride < w->n) return HQ_ERR_SHAPE;
+  if (m == 0) return HQ_OK;
+  if (x_codes == nullptr || x_scales == nullptr || y == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(y_dtype)) return HQ_ERR_FORMAT;
+  if (!aligned16(x_codes) || !aligned16(x_scales)) return HQ_ERR_ALIGN;
+  Fp8GroupedParams g{};
+  fill_fp8_native(g, w);
+  g.m = (int)m;
+  g.xq = x_codes; g.xs = x_scales; g.n_rows = m;
+  g.y = y; g.y_dtype = y_dtype; g.y_stride = y_stride;
+  g.status = status_dev;
+  return launch_fp8_grouped(g, (int)((m + 127) / 128), (cudaStream_t)stream);
+}
+
+int32_t hq_moe_fp8_gather_forward(const hq_weight* w, const uint8_t* x_codes, const float* x_scales,
+                                  int64_t n_tokens, int32_t top_k, const int32_t* expert_bounds,
+                                  const int32_t* sorted_assign, const void* workspace, void* out, int32_t out_dtype,
+                                  int64_t out_stride, int32_t out_layout, int32_t* status_dev, void* stream) {
+  int32_t rc = check_fp8_native(w);
+  if (rc != HQ_OK) return rc;
+  if (n_tokens < 0 || top_k < 1 || out_stride < w->n) return HQ_ERR_SHAPE;
+  if (n_tokens == 0) return HQ_OK;
+  if (x_codes == nullptr || x_scales == nullptr || out == nullptr || expert_bounds == nullptr ||
+      sorted_assign == nullptr || workspace == nullptr)
+    return HQ_ERR_NULL;
+  if (!valid_dtype(out_dtype) || (out_layout != HQ_ROWS_PER_SLOT && out_layout != HQ_ROWS_SORTED))
+    return HQ_ERR_FORMAT;
+  if (!aligned16(x_codes) || !aligned16(x_scales)) return HQ_ERR_ALIGN;
+  const DispatchLayout l = dispatch_layout(n_tokens, top_k, w->n_experts);
+  const int32_t* ws = (const int32_t*)workspace;
+  Fp8GroupedParams g{};
+  fill_fp8_native(g, w);
+  g.xq = x_codes; g.xs = x_scales; g.n_rows = n_tokens * top_k;
+  g.y = out; g.y_dtype = out_dtype; g.y_stride = out_stride;
+  g.tiles = ws + l.off_tiles128;
+  g.tile_count = ws + 1;
+  g.expert_bounds = expert_bounds;
+  g.y_rows = out_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr;
+  g.status = status_dev;
+  return launch_fp8_grouped(g, (int)l.max_tiles128, (cudaStream_t)stream);
+}
+
 int32_t hq_moe_weighted_reduce(const void* y, int32_t y_dtype, const float* w, const int32_t* row_map,
                                const void* addend, void* out, int32_t out_dtype, int64_t n_tokens, int32_t top_k,
                                int64_t hidden, void* stream) {

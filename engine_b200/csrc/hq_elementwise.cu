@@ -173,6 +173,45 @@ int32_t launch_fp8_vector_quant(const void* x, int x_dtype, int64_t n, uint8_t* 
   fp8_vector_quant_kernel<<<(unsigned)((groups + 7) / 8), 256, 0, stream>>>(x, x_dtype, groups, codes, scales);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
+// The same 1 x 128 quantizer over rows that are looked up first (token order -> expert-sorted order): one warp per
+// (output row, group of 128 columns).  Feeds the FP8 expert GEMM, whose operand boxes need whole sorted rows.
+__global__ void __launch_bounds__(256) fp8_quant_rows_kernel(const void* __restrict__ x, int dtype, int64_t x_stride,
+                                                             const int32_t* __restrict__ row_map, int64_t n_rows,
+                                                             int kgroups, uint8_t* __restrict__ codes,
+                                                             float* __restrict__ scales) {
+  const int64_t grp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (grp >= n_rows * kgroups) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = grp / kgroups;
+  const int g = (int)(grp - row * kgroups);
+  const int64_t src_row = row_map != nullptr ? (int64_t)row_map[row] : row;
+  const int64_t src = src_row * x_stride + g * 128 + lane * 4;
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = load_as_float(x, dtype, src + i);
+  float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  const float scale = m > 0.f ? __fdiv_rn(m, 448.f) : 1e-12f;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float q = fminf(fmaxf(__fdiv_rn(v[i], scale), -448.f), 448.f);
+    packed |= (uint32_t)f32_to_e4m3(q) << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(codes + grp * 128 + lane * 4) = packed;
+  if (lane == 0) scales[grp] = scale;
+}
+
+int32_t launch_fp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,
+                              int64_t k, uint8_t* codes, float* scales, cudaStream_t stream) {
+  const int64_t groups = n_rows * (k / 128);
+  if (groups == 0) return HQ_OK;
+  fp8_quant_rows_kernel<<<(unsigned)((groups + 7) / 8), 256, 0, stream>>>(x, x_dtype, x_stride, row_map, n_rows,
+                                                                         (int)(k / 128), codes, scales);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
 int32_t launch_fp8_vector_dequant(const uint8_t* codes, const float* scales, int64_t n, void* out, int out_dtype,
                                   cudaStream_t stream) {
   if (n == 0) return HQ_OK;
@@ -242,6 +281,46 @@ int32_t launch_gated_act(const void* gate, const void* up, int dtype, int64_t n,
                          const hq_act_args& act, void* out, cudaStream_t stream) {
   if (n == 0) return HQ_OK;
   gated_act_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gate, up, dtype, n, interleaved, act, out);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+// Gated activation of a [rows, 2 * width] matrix {gate | up} followed by the 1 x 128 FP8 quantizer: the expert
+// intermediate goes to the FP8 down projection without a 16-bit round trip through memory.
+__global__ void __launch_bounds__(256) fp8_gated_quant_rows_kernel(const void* __restrict__ gu, int dtype,
+                                                                   int64_t n_rows, int width, hq_act_args act,
+                                                                   uint8_t* __restrict__ codes,
+                                                                   float* __restrict__ scales) {
+  const int kgroups = width / 128;
+  const int64_t grp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (grp >= n_rows * kgroups) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = grp / kgroups;
+  const int g = (int)(grp - row * kgroups);
+  const int64_t src = row * 2 * width + g * 128 + lane * 4;
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    v[i] = gated_act(load_as_float(gu, dtype, src + i), load_as_float(gu, dtype, src + width + i), act);
+  float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  const float scale = m > 0.f ? __fdiv_rn(m, 448.f) : 1e-12f;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float q = fminf(fmaxf(__fdiv_rn(v[i], scale), -448.f), 448.f);
+    packed |= (uint32_t)f32_to_e4m3(q) << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(codes + grp * 128 + lane * 4) = packed;
+  if (lane == 0) scales[grp] = scale;
+}
+
+int32_t launch_fp8_gated_quant_rows(const void* gu, int dtype, int64_t n_rows, int64_t width, const hq_act_args& act,
+                                    uint8_t* codes, float* scales, cudaStream_t stream) {
+  const int64_t groups = n_rows * (width / 128);
+  if (groups == 0) return HQ_OK;
+  fp8_gated_quant_rows_kernel<<<(unsigned)((groups + 7) / 8), 256, 0, stream>>>(gu, dtype, n_rows, (int)width, act,
+                                                                               codes, scales);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 

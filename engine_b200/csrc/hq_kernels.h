@@ -80,6 +80,30 @@ int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t 
 int32_t launch_fp8_scale_prepare(const float* scales, int64_t n_groups, int kb, float* tile_scale, float* rel_scale,
                                  cudaStream_t stream);
 
+// ---- block-FP8 expert GEMM with FP8 activations on tcgen05 kind::f8f6f4 (hq_fp8_grouped.cu) --------------
+struct Fp8GroupedParams {
+  int n, k, m;                  // m: dense rows (used when tiles == nullptr)
+  int n_experts;
+  const void* w;                // e4m3 codes [E, N, K]
+  const float* w_scales;        // [E, N/128, K/128]
+  int fp8_nb, fp8_kb;
+  const void* bias;
+  int bias_dtype;
+  const void* xq;               // e4m3 activation codes [n_rows, K], rows in expert-sorted order
+  const float* xs;              // [n_rows, K/128] activation scales
+  int64_t n_rows;
+  void* y;
+  int y_dtype;
+  int64_t y_stride;
+  const int32_t* tiles;         // [n_tiles][2] = (expert, first sorted row), tiles of <= 128 rows
+  const int32_t* tile_count;
+  const int32_t* expert_bounds;
+  const int32_t* y_rows;        // sorted row -> output row (nullptr = identity)
+  int32_t* status;
+};
+bool fp8_grouped_supported(int64_t n, int64_t k);
+int32_t launch_fp8_grouped(const Fp8GroupedParams& p, int max_tiles, cudaStream_t stream);
+
 // ---- dispatch tables (hq_dispatch.cu) -------------------------------------------
 constexpr int kDispatchChunk = 1024;  // flat assignments per block
 struct DispatchLayout {
@@ -118,6 +142,10 @@ int32_t launch_fp8_block_quant(const void* w, int w_dtype, int64_t rows, int64_t
                                uint8_t* codes, float* scales, cudaStream_t stream);
 int32_t launch_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t rows, int64_t cols, int by,
                                  int bx, void* out, int out_dtype, cudaStream_t stream);
+int32_t launch_fp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,
+                              int64_t k, uint8_t* codes, float* scales, cudaStream_t stream);
+int32_t launch_fp8_gated_quant_rows(const void* gu, int dtype, int64_t n_rows, int64_t width, const hq_act_args& act,
+                                    uint8_t* codes, float* scales, cudaStream_t stream);
 int32_t launch_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, cudaStream_t stream);
 int32_t launch_gated_act(const void* gate, const void* up, int dtype, int64_t n, int interleaved,
                          const hq_act_args& act, void* out, cudaStream_t stream);

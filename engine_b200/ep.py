@@ -25,12 +25,13 @@ import torch
 import torch.distributed as dist
 
 
-def _gpu_expert_fn(experts):
+def _gpu_expert_fn(experts, fp8_act: bool = False):
     def run(rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
         if rows.shape[0] == 0:
             return torch.empty((0, experts.down.n), dtype=torch.float32, device=rows.device)
         ones = torch.ones((rows.shape[0], 1), dtype=torch.float32, device=rows.device)
-        return experts.forward(rows, ones, local_ids.reshape(-1, 1).to(torch.int32), out_dtype=torch.float32)
+        fwd = experts.forward_fp8_act if fp8_act else experts.forward
+        return fwd(rows, ones, local_ids.reshape(-1, 1).to(torch.int32), out_dtype=torch.float32)
     return run
 
 
@@ -42,7 +43,7 @@ def _gpu_reduce_fn(y_rows, weights, row_map, out_dtype, addend):
 class ExpertParallelMoE:
     def __init__(self, n_experts_global: int, experts=None, group=None,
                  expert_fn: Callable | None = None, reduce_fn: Callable | None = None,
-                 wire_dtype: torch.dtype | None = None):
+                 wire_dtype: torch.dtype | None = None, fp8_act: bool = False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -50,7 +51,7 @@ class ExpertParallelMoE:
             raise ValueError(f"{n_experts_global} experts do not split over {self.world} ranks")
         self.n_experts = n_experts_global
         self.e_local = n_experts_global // self.world
-        self.expert_fn = expert_fn or _gpu_expert_fn(experts)
+        self.expert_fn = expert_fn or _gpu_expert_fn(experts, fp8_act)
         self.reduce_fn = reduce_fn or _gpu_reduce_fn
         # dtype the expert outputs travel back in (None = as computed, f32: the result then equals the single-GPU
         # layer; torch.float16 halves the return traffic at 5e-4 relative rounding per expert output)

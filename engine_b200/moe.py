@@ -10,7 +10,8 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib as L
-from .quant import (DispatchTables, QuantMethod, _ptr, _require_cuda, _stream, dt_code, moe_dispatch_build,
+from .quant import (DispatchTables, QuantMethod, _ptr, _require_cuda, _stream, dt_code, fp8_gated_quantize_rows,
+                    fp8_quantize_rows, moe_dispatch_build,
                     tensor_path_expected)
 
 
@@ -126,6 +127,44 @@ class MoEExperts:
                                               dt_code(y.dtype), L.ROWS_SORTED, _ptr(status), _stream()),
                 "hq_moe_gather_forward(down)")
         if _skip_reduce:       # measurement aid: the two projections only, output left expert-sorted
+            return y
+        out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype or xs.dtype, tables.inv_perm, shared_out)
+        return out.reshape(*lead, self.down.n)
+
+    def forward_fp8_act(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                        shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+                        tables: DispatchTables | None = None, _skip_reduce: bool = False) -> torch.Tensor:
+        """The same block with block-scaled FP8 activations (block-FP8 experts with separate gate/up banks only):
+        token rows are quantized 1x128 straight into expert-sorted order, both projections run on the FP8
+        tensor-core MMA with weights and activations unconverted, and the intermediate is quantized again by the
+        kernel that applies the gated activation."""
+        _require_cuda(xs, "xs")
+        if self.gate is None or self.gate.format != L.FMT_FP8_BLOCK:
+            raise L.HqError("forward_fp8_act needs block-FP8 experts with separate gate and up banks")
+        lead = xs.shape[:-1]
+        x = xs.reshape(-1, xs.shape[-1]).contiguous()
+        t, k = topk_ids.shape
+        tables = tables or moe_dispatch_build(topk_ids, self.n_experts)
+        lib = L.lib()
+        status = self.gate._status_buf(x.device)
+        xq, xsc = fp8_quantize_rows(x, tables.sorted_token)
+        inter = self.gate.n
+        gu = torch.empty((t * k, 2 * inter), dtype=self.inter_dtype, device=x.device)
+        for bank, col in ((self.gate, 0), (self.up, inter)):
+            w = bank._weight_struct()
+            L.check(lib.hq_moe_fp8_gather_forward(C.byref(w), _ptr(xq), _ptr(xsc), t, k, _ptr(tables.expert_bounds),
+                                                  _ptr(tables.sorted_assign), _ptr(tables.workspace),
+                                                  gu.data_ptr() + col * gu.element_size(), dt_code(gu.dtype),
+                                                  2 * inter, L.ROWS_SORTED, _ptr(status), _stream()),
+                    "hq_moe_fp8_gather_forward(gate/up)")
+        hq_, hs = fp8_gated_quantize_rows(gu, self.act)
+        y = torch.empty((t * k, self.down.n), dtype=torch.float32, device=x.device)
+        wd = self.down._weight_struct()
+        L.check(lib.hq_moe_fp8_gather_forward(C.byref(wd), _ptr(hq_), _ptr(hs), t, k, _ptr(tables.expert_bounds),
+                                              _ptr(tables.sorted_assign), _ptr(tables.workspace), _ptr(y),
+                                              dt_code(y.dtype), self.down.n, L.ROWS_SORTED, _ptr(status), _stream()),
+                "hq_moe_fp8_gather_forward(down)")
+        if _skip_reduce:
             return y
         out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype or xs.dtype, tables.inv_perm, shared_out)
         return out.reshape(*lead, self.down.n)

@@ -302,6 +302,20 @@ class BlockwiseFP8Linear(QuantMethod):
         return self if self.n_experts == 1 else BlockwiseFP8Linear(self.weight[e], self.scale[e])
 
 
+    def forward_fp8_rows(self, codes: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtype = torch.float16):
+        """Dense layer over rows that are already FP8 (codes [M, K], scales [M, K/128]): the FP8 tensor-core path
+        with block-scaled activations."""
+        if self.n_experts != 1:
+            raise L.HqError("forward_fp8_rows on an expert bank")
+        m = codes.shape[0]
+        y = torch.empty((m, self.n), dtype=out_dtype, device=codes.device)
+        w = self._weight_struct()
+        L.check(L.lib().hq_fp8_linear_forward(C.byref(w), _ptr(codes.contiguous()), _ptr(scales.contiguous()), m,
+                                              _ptr(y), dt_code(out_dtype), self.n,
+                                              _ptr(self._status_buf(codes.device)), _stream()), "hq_fp8_linear_forward")
+        return y
+
+
 class MXFP4Layer(QuantMethod):
     """MXFP4 expert bank / linear (hanzo-quant/src/mxfp4/mod.rs:29-174): blocks uint8 [E, N, K/2] (low nibble =
     even element), scales uint8 [E, N, K/32] (e8m0), optional bias [E, N].  Any 3-D input to gather_forward is
@@ -353,6 +367,32 @@ def fp8_vector_dequantize(codes: torch.Tensor, scales: torch.Tensor, out_dtype: 
     L.check(L.lib().hq_fp8_vector_dequant(_ptr(codes.contiguous()), _ptr(scales), codes.numel(), _ptr(out),
                                           dt_code(out_dtype), _stream()), "hq_fp8_vector_dequant")
     return out
+
+
+def fp8_quantize_rows(x: torch.Tensor, row_map: torch.Tensor | None = None):
+    """The 1x128 quantizer over rows x[row_map[r]] (row_map None = identity): codes uint8 [R, K] and scales f32
+    [R, K/128].  With `sorted_token` as the row map this produces the expert-sorted rows the FP8 expert GEMM reads."""
+    _require_cuda(x, "x")
+    x = x.contiguous()
+    k = x.shape[-1]
+    rows = x.shape[0] if row_map is None else row_map.numel()
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((rows, k // 128), dtype=torch.float32, device=x.device)
+    L.check(L.lib().hq_fp8_quant_rows(_ptr(x), dt_code(x.dtype), k, _ptr(row_map), rows, k, _ptr(codes), _ptr(scales),
+                                      _stream()), "hq_fp8_quant_rows")
+    return codes, scales
+
+
+def fp8_gated_quantize_rows(gate_up: torch.Tensor, act: "L.HqActArgs"):
+    """{gate | up} [R, 2W] -> act(gate) * up -> 1x128 quantizer: codes [R, W], scales [R, W/128]."""
+    _require_cuda(gate_up, "gate_up")
+    gate_up = gate_up.contiguous()
+    rows, w2 = gate_up.shape
+    codes = torch.empty((rows, w2 // 2), dtype=torch.uint8, device=gate_up.device)
+    scales = torch.empty((rows, w2 // 256), dtype=torch.float32, device=gate_up.device)
+    L.check(L.lib().hq_fp8_gated_quant_rows(_ptr(gate_up), dt_code(gate_up.dtype), rows, w2 // 2, C.byref(act),
+                                            _ptr(codes), _ptr(scales), _stream()), "hq_fp8_gated_quant_rows")
+    return codes, scales
 
 
 def fp8_blockwise_quantize(w: torch.Tensor, weight_block_size=(128, 128)):

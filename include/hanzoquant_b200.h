@@ -224,6 +224,33 @@ int32_t hq_moe_weighted_reduce(const void* y, int32_t y_dtype, const float* w, c
                                const void* addend, void* out, int32_t out_dtype, int64_t n_tokens, int32_t top_k,
                                int64_t hidden, void* stream);
 
+/* ---- block-FP8 layers with FP8 activations --------------------------------
+ * The block-scaled form of the FP8 path: activation rows are quantized 1 x 128 with the reference's vector
+ * quantizer (hanzo-quant/src/vector_fp8/ops.rs:235-287: scale = absmax / 448 or 1e-12, q = e4m3(clamp(v /
+ * scale))) and the e4m3 codes of weights and activations go into the FP8 tensor-core MMA unconverted; every
+ * 128-column block is scaled by weight_scale_inv[n/128, k/128] * activation_scale[row, k/128] as it is added.
+ * Results equal dequantize-then-matmul over the QUANTIZED activations up to f32 summation order; against
+ * unquantized activations they carry the quantizer's ~3e-2 error, which is why hq_linear_forward /
+ * hq_moe_gather_forward (16-bit activations) stay the default.  Requires N % 128 == 0, K % 512 == 0, K <= 8192.
+ *
+ * hq_fp8_quant_rows: codes [n_rows, k] / scales [n_rows, k/128] of rows x[row_map[r]] (row_map NULL = identity;
+ * pass sorted_token to produce the expert-sorted rows the expert GEMM reads).  Replaces
+ * launch_quant_fp8_vector_kernel_* (vector_fp8/ops.rs) plus the row gather.
+ * hq_fp8_gated_quant_rows: gate_up [n_rows, 2*width] = {gate | up} -> act(gate) * up -> the same quantizer.
+ * hq_fp8_linear_forward: dense layer over quantized rows.  hq_moe_fp8_gather_forward: expert bank over
+ * expert-sorted quantized rows (n_tokens * top_k of them), output rows sorted or per slot, row stride
+ * out_stride elements (so two banks can write the halves of one {gate | up} matrix). */
+int32_t hq_fp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,
+                          int64_t k, uint8_t* codes, float* scales, void* stream);
+int32_t hq_fp8_gated_quant_rows(const void* gate_up, int32_t dtype, int64_t n_rows, int64_t width,
+                                const hq_act_args* act, uint8_t* codes, float* scales, void* stream);
+int32_t hq_fp8_linear_forward(const hq_weight* w, const uint8_t* x_codes, const float* x_scales, int64_t m, void* y,
+                              int32_t y_dtype, int64_t y_stride, int32_t* status_dev, void* stream);
+int32_t hq_moe_fp8_gather_forward(const hq_weight* w, const uint8_t* x_codes, const float* x_scales,
+                                  int64_t n_tokens, int32_t top_k, const int32_t* expert_bounds,
+                                  const int32_t* sorted_assign, const void* workspace, void* out, int32_t out_dtype,
+                                  int64_t out_stride, int32_t out_layout, int32_t* status_dev, void* stream);
+
 /* ---- FP8 quantizers ---------------------------------------------------------
  * 1x128 groups along the last axis: scale = absmax/448 (1e-12 if zero),
  * code = e4m3(clamp(v/scale, +-448)).  Replaces launch_quant_fp8_vector_kernel_*

@@ -162,19 +162,23 @@ def moe_layer(x: np.ndarray, ids: np.ndarray, weights: np.ndarray,
               act: int = ACT_SWIGLU, gate_up_bank: np.ndarray | None = None,
               gate_up_bias: np.ndarray | None = None, down_bias: np.ndarray | None = None,
               alpha: float = 1.702, limit: float | None = None,
-              h_round=None) -> np.ndarray:
+              h_round=None, gu_round=None) -> np.ndarray:
     """Whole expert block in f32: gather gate/up -> gated activation -> gather
     down -> weighted sum over slots.  Separate gate/up banks (Qwen3, DeepSeek:
     hanzo-engine/src/moe/experts/backends.rs:560-605) or one interleaved bank
     with rows [gate0, up0, gate1, up1, ...] (gpt-oss:
     hanzo-engine/src/models/gpt_oss.rs:405-440).  `h_round`, if given, is applied
-    to the activated intermediate (the rounding point of a 16-bit pipeline)."""
+    to the activated intermediate (the rounding point of a 16-bit pipeline);
+    `gu_round` to the gate and up projections before the activation (a pipeline
+    that stores them in 16 bits first)."""
     if gate_up_bank is not None:
         gu = gather_forward(x, ids, gate_up_bank, gate_up_bias)
         g, u = gu[..., 0::2], gu[..., 1::2]
     else:
         g = gather_forward(x, ids, gate_bank)
         u = gather_forward(x, ids, up_bank)
+    if gu_round is not None:
+        g, u = gu_round(g), gu_round(u)
     if act == ACT_GPTOSS:
         h = gptoss_swiglu(g, u, alpha, limit if limit is not None else 7.0)
     else:
