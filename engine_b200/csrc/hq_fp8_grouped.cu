@@ -8,14 +8,14 @@
 // (cp.async.bulk.tensor, 128-byte swizzle, one 128 x 128-byte box each per stage) and from there into the
 // tensor core unchanged; the products of e4m3 values are exact and accumulate in f32 in tensor memory.
 // Because the scales change every 128 columns the accumulation is cut there: each 128-column block is
-// multiplied into a fresh tensor-memory buffer (two buffers, alternating), and the eight epilogue warps fold
+// multiplied into a fresh tensor-memory buffer (four buffers in rotation), and the eight epilogue warps fold
 // it into register accumulators with one FMA per element (factor = weight-block scale x the token's
-// scale for that block, read from a per-tile scale table that TMA brought in) while the next block is
-// already being multiplied.  With 128 tokens per expert every weight byte is used once, so the kernel is
+// scale for that block, from a per-item factor table the epilogue warps build out of the scales TMA
+// brought in) while the next block is already being multiplied.  With 128 tokens per expert every weight byte is used once, so the kernel is
 // bound by streaming the weights: five 32 KiB stages are kept in flight.
 //
-// Roles (one persistent CTA per SM, 10 warps): warp 0 issues TMA, warp 1 issues the MMAs (one elected
-// lane each), warps 2-9 are the epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31 (its 32 output
+// Roles (one persistent CTA per SM, 11 warps): warp 0 issues TMA, warps 1 and 10 issue the MMAs of alternate
+// 128-column blocks (one elected lane each), warps 2-9 are the epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31 (its 32 output
 // features) and the 64 token columns (w - 2) / 4 * 64 .. + 63.  Swapped roles as in the 16-bit kernel: lanes =
 // output features, columns = tokens.  Every wait is bounded; a wait that runs out is reported in the status
 // word and the kernel still reaches its normal exit.  No multicast, no peer memory.
@@ -26,17 +26,19 @@
 
 namespace hq {
 
-constexpr int kF8Threads = 320;
+constexpr int kF8Threads = 352;                          // TMA warp, MMA warp, 8 epilogue warps, second MMA warp
 constexpr int kF8Stages = 5;
 constexpr int kF8TileBytes = 128 * 128;                  // one operand box: 128 rows x 128 bytes
 constexpr int kF8StageBytes = 2 * kF8TileBytes;
 constexpr int kF8MaxKB = 64;                             // 128-column blocks per row (K <= 8192)
+constexpr int kF8AccBufs = 4;                            // 128-column accumulator buffers in tensor memory
 constexpr uint32_t kF8Spin = 1u << 22;
 
 struct F8Smem {
-  static constexpr int OFF_SCALES = kF8Stages * kF8StageBytes;                   // 2 x [128 tokens][KB] f32
-  static constexpr int OFF_BAR = OFF_SCALES + 2 * 128 * kF8MaxKB * 4;
-  static constexpr int TOTAL = OFF_BAR + (2 * kF8Stages + 8) * 8 + 16 + 1024;     // + alignment slack
+  static constexpr int OFF_RAW = kF8Stages * kF8StageBytes;          // activation scales as TMA brings them: [128 tokens][KB]
+  static constexpr int OFF_FAC = OFF_RAW + 128 * kF8MaxKB * 4;       // factors the epilogue reads: [KB][128 tokens]
+  static constexpr int OFF_BAR = OFF_FAC + 128 * kF8MaxKB * 4;
+  static constexpr int TOTAL = OFF_BAR + (2 * kF8Stages + 12) * 8 + 16 + 1024;    // + alignment slack
 };
 static_assert(F8Smem::TOTAL <= 227 * 1024, "shared memory budget");
 
@@ -127,13 +129,14 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_s, const Fp8GroupedParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  float* sc_tab = reinterpret_cast<float*>(smem + F8Smem::OFF_SCALES);
+  float* sc_raw = reinterpret_cast<float*>(smem + F8Smem::OFF_RAW);
+  float* sc_fac = reinterpret_cast<float*>(smem + F8Smem::OFF_FAC);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + F8Smem::OFF_BAR);
   uint64_t* empty = full + kF8Stages;
-  uint64_t* acc_full = empty + kF8Stages;   // [2] a 128-column block has been multiplied into buffer b
-  uint64_t* acc_empty = acc_full + 2;       // [2] ... and has been read out by all epilogue warps
-  uint64_t* sc_full = acc_empty + 2;        // [2] the tile's scale table has landed
-  uint64_t* sc_empty = sc_full + 2;         // [2] ... and is no longer needed
+  uint64_t* acc_full = empty + kF8Stages;            // [4] a 128-column block has been multiplied into buffer b
+  uint64_t* acc_empty = acc_full + kF8AccBufs;       // [4] ... and has been read out by all epilogue warps
+  uint64_t* sc_full = acc_empty + kF8AccBufs;        // the tile's activation scales have landed (slot [1] unused)
+  uint64_t* sc_empty = sc_full + 2;         // ... and have been turned into the factor table
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_empty + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -147,16 +150,18 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kF8AccBufs; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);
+    }
+    for (int b = 0; b < 2; ++b) {
       mbar_init(&sc_full[b], 1);
       mbar_init(&sc_empty[b], 8);
     }
     fence_barrier_init();
   }
   if (warp == 1) {
-    f8_tmem_alloc(smem_u32(tmem_slot), 256);
+    f8_tmem_alloc(smem_u32(tmem_slot), 128 * kF8AccBufs);
     f8_tmem_relinquish();
   }
   f8_fence_before();
@@ -171,15 +176,14 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       int s = 0, round = 0, item = 0;
       for (int w = blockIdx.x; w < total; w += gridDim.x, ++item) {
         const F8Item t = f8_item(p, w, n_nt);
-        const int tb = item & 1;
-        if (item >= 2) {
-          if (!mbar_wait_backoff(&sc_empty[tb], ((item >> 1) - 1) & 1, spin)) {
-            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 700 + tb);
+        if (item >= 1) {
+          if (!mbar_wait_backoff(&sc_empty[0], (item - 1) & 1, spin)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 700);
             spin = 1;
           }
         }
-        mbar_arrive_expect_tx(&sc_full[tb], (uint32_t)(128 * KB * 4));
-        f8_tma_2d(sc_tab + tb * 128 * kF8MaxKB, &tm_s, 0, t.row_start, &sc_full[tb]);
+        mbar_arrive_expect_tx(&sc_full[0], (uint32_t)(128 * KB * 4));
+        f8_tma_2d(sc_raw, &tm_s, 0, t.row_start, &sc_full[0]);
         const int wrow = t.expert * p.n + t.n0;
         for (int kb = 0; kb < KB; ++kb) {
           if (round > 0) {
@@ -200,22 +204,28 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // =========================== MMA issuer =========================================================
+  } else if (warp == 1 || warp == 10) {
+    // =========================== MMA issuers ========================================================
+    // tcgen05.commit holds its thread until the MMAs before it have gone through the pipe, and the waits that
+    // follow would leave the tensor core idle: two issuing lanes take alternate 128-column blocks, so one is
+    // always ready to issue while the other waits
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;
       const uint32_t idesc = f8_idesc();
       uint32_t spin = kF8Spin;
-      int s = 0, phase = 0, blk = 0;      // blk: 128-column blocks issued so far (buffer = blk & 1)
+      int blk = 0;      // 128-column blocks so far (buffer = blk % kF8AccBufs, stage = blk % kF8Stages)
       for (int w = blockIdx.x; w < total; w += gridDim.x) {
         for (int kb = 0; kb < KB; ++kb, ++blk) {
-          const int buf = blk & 1;
-          if (blk >= 2) {
-            if (!mbar_wait_backoff(&acc_empty[buf], ((blk >> 1) - 1) & 1, spin)) {
+          if ((blk & 1) != me) continue;
+          const int buf = blk % kF8AccBufs;
+          const int s = blk % kF8Stages;
+          if (blk >= kF8AccBufs) {
+            if (!mbar_wait(&acc_empty[buf], ((blk / kF8AccBufs) - 1) & 1, spin)) {
               report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 720 + buf);
               spin = 1;
             }
           }
-          if (!mbar_wait_backoff(&full[s], phase, spin)) {
+          if (!mbar_wait(&full[s], (blk / kF8Stages) & 1, spin)) {
             report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 730 + s);
             spin = 1;
           }
@@ -228,10 +238,6 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             f8_mma(d, adesc + 2 * kk, bdesc + 2 * kk, idesc, kk > 0 ? 1u : 0u);
           f8_commit(&empty[s]);        // the stage is free once these MMAs have read it
           f8_commit(&acc_full[buf]);   // the block's products are complete
-          if (++s == kF8Stages) {
-            s = 0;
-            phase ^= 1;
-          }
         }
       }
     }
@@ -244,20 +250,27 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     int item = 0, blk = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++item) {
       const F8Item t = f8_item(p, w, n_nt);
-      const int tb = item & 1;
-      const float* st = sc_tab + tb * 128 * kF8MaxKB + half * 64 * KB;     // this warp's 64 tokens x KB
       const float* wsc = p.w_scales + ((int64_t)t.expert * p.fp8_nb + t.n0 / 128) * p.fp8_kb;
-      if (!mbar_wait_backoff(&sc_full[tb], (item >> 1) & 1, spin)) {
-        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 740 + tb);
+      if (!mbar_wait_backoff(&sc_full[0], item & 1, spin)) {
+        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 740);
         spin = 1;
       }
+      // factor table of this item: fac[kb][token] = weight-block scale x token scale, so the inner loop reads four
+      // tokens per shared load at fixed offsets and spends one FMA per element
+      named_bar_sync(2, 256);                 // every epilogue warp is done with the previous item's factors
+      for (int idx = tid - 64; idx < 128 * KB; idx += 256) {
+        const int kb = idx >> 7, tok = idx & 127;
+        sc_fac[idx] = sc_raw[tok * KB + kb] * __ldg(wsc + kb);
+      }
+      named_bar_sync(2, 256);
+      if (lane == 0) mbar_arrive(&sc_empty[0]);   // the raw scales may be overwritten by the next item's
+      const uint32_t fac_w = smem_u32(sc_fac) + (uint32_t)(half * 64) * 4u;
       float acc[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) acc[j] = 0.f;
       for (int kb = 0; kb < KB; ++kb, ++blk) {
-        const int buf = blk & 1;
-        const float wv = __ldg(wsc + kb);
-        if (!mbar_wait_backoff(&acc_full[buf], (blk >> 1) & 1, spin)) {
+        const int buf = blk % kF8AccBufs;
+        if (!mbar_wait(&acc_full[buf], (blk / kF8AccBufs) & 1, spin)) {
           if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 750 + buf);
           spin = 1;
         }
@@ -270,14 +283,24 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         f8_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);     // the buffer may be overwritten: values are in registers
+        const uint32_t fk = fac_w + (uint32_t)kb * 512u;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          acc[j] = fmaf(__uint_as_float(c0[j]), wv * st[j * KB + kb], acc[j]);
-          acc[32 + j] = fmaf(__uint_as_float(c1[j]), wv * st[(32 + j) * KB + kb], acc[32 + j]);
+        for (int j4 = 0; j4 < 8; ++j4) {
+          float4 f0, f1;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(f0.x), "=f"(f0.y), "=f"(f0.z), "=f"(f0.w) : "r"(fk + 16u * j4));
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(f1.x), "=f"(f1.y), "=f"(f1.z), "=f"(f1.w) : "r"(fk + 128u + 16u * j4));
+          acc[4 * j4 + 0] = fmaf(__uint_as_float(c0[4 * j4 + 0]), f0.x, acc[4 * j4 + 0]);
+          acc[4 * j4 + 1] = fmaf(__uint_as_float(c0[4 * j4 + 1]), f0.y, acc[4 * j4 + 1]);
+          acc[4 * j4 + 2] = fmaf(__uint_as_float(c0[4 * j4 + 2]), f0.z, acc[4 * j4 + 2]);
+          acc[4 * j4 + 3] = fmaf(__uint_as_float(c0[4 * j4 + 3]), f0.w, acc[4 * j4 + 3]);
+          acc[32 + 4 * j4 + 0] = fmaf(__uint_as_float(c1[4 * j4 + 0]), f1.x, acc[32 + 4 * j4 + 0]);
+          acc[32 + 4 * j4 + 1] = fmaf(__uint_as_float(c1[4 * j4 + 1]), f1.y, acc[32 + 4 * j4 + 1]);
+          acc[32 + 4 * j4 + 2] = fmaf(__uint_as_float(c1[4 * j4 + 2]), f1.z, acc[32 + 4 * j4 + 2]);
+          acc[32 + 4 * j4 + 3] = fmaf(__uint_as_float(c1[4 * j4 + 3]), f1.w, acc[32 + 4 * j4 + 3]);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sc_empty[tb]);
       // ---- write this warp's 32 features x 64 tokens --------------------------------------------------
       const int n = t.n0 + 32 * q + lane;
       float bias = 0.f;
@@ -312,7 +335,7 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     f8_fence_after();
-    f8_tmem_dealloc(tmem_base, 256);
+    f8_tmem_dealloc(tmem_base, 128 * kF8AccBufs);
   }
 }
 
