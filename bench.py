@@ -667,6 +667,16 @@ def run_moe(args):
                     "peak_kind": "measured" if peaks else "fallback",
                     "kernel": "hq::grouped_gemm_kernel (gate/up + down)", "launch_ms_sum": round(gemm_ms, 4),
                     "note": "f16 operands: fraction of the measured dense 16-bit tensor peak"}
+            if cfg.get("act_fp8"):
+                # FP8 x FP8 MMA: still reported against the measured 16-bit peak (the only tensor peak the peaks
+                # file holds); this repo's tcgen05 issue-rate probe gives 4289 TFLOP/s for the kernel's
+                # 128 x 128 x 32 e4m3 instruction.  At 128 tokens per expert the layer reads every weight byte
+                # once per ~1.5 token tiles, so the HBM figure is the one that binds.
+                wbytes = 3 * (e // world) * cfg["i"] * h + (3 * cfg["i"] * h if cfg.get("shared") else 0)
+                roof.update({"kernel": "hq::fp8_grouped_kernel (gate, up, down) + row quantizers",
+                             "note": "e4m3 x e4m3 MMA (kind::f8f6f4); fraction of the measured dense 16-bit peak",
+                             "fp8_probe_peak_tflops": 4289.0,
+                             "weight_stream_gbs": round(wbytes / (gemm_ms / 1e3) / 1e9, 1)})
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
