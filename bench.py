@@ -672,7 +672,7 @@ def run_moe(args):
                 # file holds); this repo's tcgen05 issue-rate probe gives 4289 TFLOP/s for the kernel's
                 # 128 x 128 x 32 e4m3 instruction.  At 128 tokens per expert the layer reads every weight byte
                 # once per ~1.5 token tiles, so the HBM figure is the one that binds.
-                wbytes = 3 * (e // world) * cfg["i"] * h + (3 * cfg["i"] * h if cfg.get("shared") else 0)
+                wbytes = 3 * (e // world) * cfg["i"] * h      # routed experts only: what the timed calls read
                 roof.update({"kernel": "hq::fp8_grouped_kernel (gate, up, down) + row quantizers",
                              "note": "e4m3 x e4m3 MMA (kind::f8f6f4); fraction of the measured dense 16-bit peak",
                              "fp8_probe_peak_tflops": 4289.0,
