@@ -378,7 +378,7 @@ def run_gemv(args):
                          "traffic": int(NCU_TRAFFIC_RATIO * step_bytes / launches_per_step),
                          "traffic_note": "algorithmic bytes x 1.009 (ncu dram bytes / algorithmic bytes of the "
                                          "4096x128256 launch)",
-                         "peak_kind": peak_kind, "kernel": "hq::gemv_q8_kernel", "launch_ms_sum": round(kern_ms, 4),
+                         "peak_kind": peak_kind, "kernel": "hq::gemv_int8_kernel<Q8_0>", "launch_ms_sum": round(kern_ms, 4),
                          "bytes_per_step": step_bytes, "by_launch_gbs": by_shape,
                          "graph_step_gbs": round(step_bytes / (ms_total / args.steps / 1e3) / 1e9, 1)},
             "cpu_baseline": cpu,
