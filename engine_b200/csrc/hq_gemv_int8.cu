@@ -90,6 +90,13 @@ __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
 }
 
+// Programmatic dependent launch: the kernel after this one in the stream may start its CTAs as ours retire (and
+// this kernel may have been started that way): everything that does not depend on the previous kernel -- barrier
+// set-up, the first weight stages -- then overlaps its tail.  Whatever reads activations, the scratch or
+// dispatch tables, or writes outputs, first waits for the previous kernel to have completed.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // two f32 lanes per instruction (sm_100): the accumulator pairs of one weight row share every factor
 __device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
   uint64_t r;
@@ -431,6 +438,8 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
   const int NSTAGE = lay.nstage;
   extern __shared__ __align__(128) uint8_t smem[];
 
+  pdl_launch_dependents();
+  if (p.tiles != nullptr) pdl_wait();    // the item list itself comes from the previous kernel
   const int n_rt = (p.n + RT - 1) / RT;
   const int n_y = p.tiles != nullptr ? p.tile_count[0] : (p.m + 7) / 8;
   const int total = n_y * n_rt;
@@ -520,6 +529,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
 
   if (warp == WK + kQ8Producers) {
     // ================= reducing warp: adds the K-split partial sums in warp order and writes ======
+    pdl_wait();
     uint32_t spin = kQ8Spin;
     int item = 0;
     for (int w = r0; w < total; w += R) {
@@ -565,6 +575,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
   }
 
   if (warp < WK) {
+  pdl_wait();
   // ================= consumer warps ================================================================
   uint8_t* xq = smem + lay.off_x;
   float* sx = reinterpret_cast<float*>(smem + lay.off_sx);
@@ -707,6 +718,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
     // ---- split K: whichever CTA of an item stream finishes last adds the slice sums of the stream's items, in
     // slice order (so the result does not depend on who that is), and leaves the counter at zero ---------------
     __shared__ int last_flag;
+    pdl_wait();
     __syncthreads();
     if (tid == 0) {
       __threadfence();
@@ -842,8 +854,17 @@ static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cud
   if (streams > items) streams = items;
   const int64_t grid = streams * sp.kslices;
   if (grid <= 0) return HQ_OK;
-  kern<<<(unsigned)grid, kQ8Threads, lay.total, stream>>>(p, lay);
-  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kQ8Threads);
+  cfg.dynamicSmemBytes = (size_t)lay.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p, lay) == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
 int32_t launch_gemv_int8(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {

@@ -179,8 +179,17 @@ class QuantMethod {
     std::vector<int64_t> od(a.dims());
     od.back() = w.n;
     Tensor y = Tensor::empty(od, out_dtype);
-    check(hq_linear_forward(&w, x.data(), (int32_t)x.dtype(), w.k, y.data(), (int32_t)out_dtype, w.n, m, nullptr, stream),
-          "hq_linear_forward");
+    // scratch for the split-K form of the decode kernel, owned by the layer like the reference's Q8_1 buffer
+    // (hanzo-quant/src/gguf/fast_mmvq.rs:107-148): zero-filled when (re)allocated, one stream at a time
+    const int64_t need = hq_linear_workspace_bytes(&w, m);
+    if (need > scratch_bytes_) {
+      scratch_ = Tensor::empty({need}, DType::U8);
+      check_cuda(cudaMemsetAsync(scratch_.data(), 0, (size_t)need, stream), "cudaMemsetAsync");
+      scratch_bytes_ = need;
+    }
+    check(hq_linear_forward_ws(&w, x.data(), (int32_t)x.dtype(), w.k, y.data(), (int32_t)out_dtype, w.n, m,
+                               need > 0 ? scratch_.data() : nullptr, need > 0 ? scratch_bytes_ : 0, nullptr, stream),
+          "hq_linear_forward_ws");
     return y;
   }
 
@@ -214,6 +223,10 @@ class QuantMethod {
                                 (int32_t)out_dtype, HQ_ROWS_PER_SLOT, nullptr, stream), "hq_moe_gather_forward");
     return out;
   }
+
+ private:
+  mutable Tensor scratch_;
+  mutable int64_t scratch_bytes_ = 0;
 };
 
 // GGUF block-quantized linear / expert bank: `data` = raw GGUF block bytes, u8 [N, row_bytes] or [E, N, row_bytes]
