@@ -241,7 +241,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   const int n_rt = (p.n + RT - 1) / RT;
   const int n_y = p.tiles != nullptr ? p.tile_count[0] : (p.m + 7) / 8;
   const int total = n_y * n_rt;
-  if ((int)blockIdx.x >= total) return;
+  // Item walk: dense calls stride through the items; expert-indexed calls take a contiguous run each, so
+  // consecutive items of a CTA share their activation rows (one expert tile) and are staged once.
+  const bool runs = p.tiles != nullptr;
+  const int per = runs ? (total + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int w_begin = runs ? (int)blockIdx.x * per : (int)blockIdx.x;
+  const int w_end = runs ? min(total, w_begin + per) : total;
+  const int w_step = runs ? 1 : (int)gridDim.x;
+  if (w_begin >= w_end) return;
   const int kXK = lay.xk;          // activation columns staged per epoch (whole chunks)
   const int xk_sub = lay.xk_sub;   // columns one register prefetch covers
   const int n_super = (p.k + kXK - 1) / kXK;
@@ -280,7 +287,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
     int s = 0, round = 0;
-    for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    for (int w = w_begin; w < w_end; w += w_step) {
       const WorkItem wi = get_item<RT>(p, w, n_rt);
       if (wi.nrows <= 0) continue;
       const int rows_valid = min(RT, p.n - wi.n0);
@@ -321,7 +328,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     // ================= reducing warp: adds the K-split partial sums in warp order and writes ==========
     uint32_t spin = kSpinLimit;
     int item = 0;
-    for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    for (int w = w_begin; w < w_end; w += w_step) {
       const WorkItem wi = get_item<RT>(p, w, n_rt);
       if (wi.nrows <= 0) continue;
       const int rb = item & 1;
@@ -363,7 +370,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   int staged_y = -1;        // activation rows currently in shared memory (valid when n_super == 1)
   int staged_rows = 0;
   {
-    const WorkItem w0 = get_item<RT>(p, blockIdx.x, n_rt);
+    const WorkItem w0 = get_item<RT>(p, w_begin, n_rt);
     if (w0.nrows > 0) {
       x_prefetch(pf, p, w0.row0, w0.nrows, 0, min(xk_sub, p.k), tid);
       pf_valid = true;
@@ -373,7 +380,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   uint32_t spin = kSpinLimit;
   int s = 0, it = 0, item = 0;
   uint32_t phase = 0;
-  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+  for (int w = w_begin; w < w_end; w += w_step) {
     const WorkItem wi = get_item<RT>(p, w, n_rt);
     if (wi.nrows <= 0) continue;
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -399,8 +406,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
         if (sc + 1 < n_super) {
           x_prefetch(pf, p, wi.row0, wi.nrows, k_base + kXK, min(xk_sub, p.k - k_base - kXK), tid);
           pf_valid = true;
-        } else if (w + (int)gridDim.x < total) {
-          const WorkItem nx = get_item<RT>(p, w + gridDim.x, n_rt);
+        } else if (w + w_step < w_end) {
+          const WorkItem nx = get_item<RT>(p, w + w_step, n_rt);
           if (nx.nrows > 0 && (n_super > 1 || nx.y != wi.y)) {
             x_prefetch(pf, p, nx.row0, nx.nrows, 0, min(xk_sub, p.k), tid);
             pf_valid = true;

@@ -449,7 +449,15 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
   const int R = gridDim.x / S;                 // item streams
   const int r0 = blockIdx.x / S;
   const int slice = blockIdx.x - r0 * S;
-  if (r0 >= total || r0 >= R) return;
+  // Item walk: dense calls stride through the items (neighbouring CTAs read neighbouring rows); expert-indexed
+  // calls take a contiguous run each, so consecutive items of a CTA share their activation rows (one expert
+  // tile) and are staged once instead of once per item.
+  const bool runs = p.tiles != nullptr;
+  const int per = runs ? (total + R - 1) / R : 0;
+  const int w_begin = runs ? r0 * per : r0;
+  const int w_end = runs ? min(total, w_begin + per) : total;
+  const int w_step = runs ? 1 : R;
+  if (r0 >= R || w_begin >= w_end) return;
   const int nchunk = (p.k + KC - 1) / KC;
   const int ck_lo = slice * lay.chunks_per_slice;
   const int ck_hi = min(nchunk, ck_lo + lay.chunks_per_slice);
@@ -491,7 +499,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
     int s = 0, round = 0;
-    for (int w = r0; w < total; w += R) {
+    for (int w = w_begin; w < w_end; w += w_step) {
       const WorkItem wi = get_item<RT>(p, w, n_rt);
       if (wi.nrows <= 0) continue;
       const int rows_valid = min(RT, p.n - wi.n0);
@@ -532,7 +540,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
     pdl_wait();
     uint32_t spin = kQ8Spin;
     int item = 0;
-    for (int w = r0; w < total; w += R) {
+    for (int w = w_begin; w < w_end; w += w_step) {
       const WorkItem wi = get_item<RT>(p, w, n_rt);
       if (wi.nrows <= 0) continue;
       const int rb = item & 1;
@@ -593,7 +601,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
   int staged_y = -1;        // activation rows currently staged (valid when n_super == 1)
   int staged_rows = 0;
   {
-    const WorkItem w0 = get_item<RT>(p, r0, n_rt);
+    const WorkItem w0 = get_item<RT>(p, w_begin, n_rt);
     if (w0.nrows > 0) {
       q8_x_prefetch(pf, p, w0.row0, w0.nrows, k_lo, min(xk_sub, k_hi - k_lo), tid);
       pf_valid = true;
@@ -603,7 +611,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
   uint32_t spin = kQ8Spin;
   int s = 0, item = 0;
   uint32_t phase = 0;
-  for (int w = r0; w < total; w += R) {
+  for (int w = w_begin; w < w_end; w += w_step) {
     const WorkItem wi = get_item<RT>(p, w, n_rt);
     if (wi.nrows <= 0) continue;
     float acc[2][NCS][4];
@@ -644,8 +652,8 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
         if (sc + 1 < n_super) {
           q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base + kXK, min(xk_sub, k_hi - k_base - kXK), tid);
           pf_valid = true;
-        } else if (w + R < total) {
-          const WorkItem nx = get_item<RT>(p, w + R, n_rt);
+        } else if (w + w_step < w_end) {
+          const WorkItem nx = get_item<RT>(p, w + w_step, n_rt);
           if (nx.nrows > 0 && (n_super > 1 || nx.y != wi.y)) {
             q8_x_prefetch(pf, p, nx.row0, nx.nrows, k_lo, min(xk_sub, k_hi - k_lo), tid);
             pf_valid = true;
@@ -731,7 +739,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
       __threadfence();
       const int nb = p.n_banks;
       int idx = 0;
-      for (int w = r0; w < total; w += R, ++idx) {
+      for (int w = w_begin; w < w_end; w += w_step, ++idx) {
         if (idx % (kQ8Threads / 32) != warp) continue;
         const WorkItem wi = get_item<RT>(p, w, n_rt);
         if (wi.nrows <= 0) continue;
