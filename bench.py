@@ -511,6 +511,8 @@ def run_moe(args):
     cfg = dict(MOE_CFGS[args.workload])
     if args.tokens:
         cfg["t"] = args.tokens
+    if args.experts:
+        cfg["e"] = args.experts       # a smaller bank of the same expert shape (profiling cases that must stay small)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -705,6 +707,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="gemv", choices=["gemv"] + list(MOE_CFGS))
     ap.add_argument("--tokens", type=int, default=0, help="override the token count of a MoE workload")
+    ap.add_argument("--experts", type=int, default=0, help="override the expert count of a MoE workload")
     ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"],
                     help="MoE workloads on several GPUs: tokens per GPU fixed (weak) or global count split (strong)")
     ap.add_argument("--only", default=None, help="restrict the sweep to one KxN shape, e.g. 4096x128256 "
