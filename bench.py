@@ -374,7 +374,7 @@ def run_gemv(args):
                          "frac": round(achieved / peak, 4),
                          # DRAM bytes per launch (average over the step's launches): the ncu capture of the
                          # 4096 -> 128256 launch read and wrote 563.3 MB for 558.2 MB of algorithmic bytes
-                         # (profiles/gemv_q8_0_4096x128256.md); the other launches are scaled by that ratio
+                         # (profiles/gemv_int8_q8_0_4096x128256.md); the other launches are scaled by that ratio
                          "traffic": int(NCU_TRAFFIC_RATIO * step_bytes / launches_per_step),
                          "traffic_note": "algorithmic bytes x 1.009 (ncu dram bytes / algorithmic bytes of the "
                                          "4096x128256 launch)",
