@@ -531,8 +531,8 @@ def run_moe(args):
     t_local = t_global if weak else t_global // world
     t_global = t_local * world
     experts = build_moe_layer(torch, hq, cfg, gen, dev, e // world)
-    ep = (ExpertParallelMoE(e, experts, wire_dtype=torch.float16, fp8_act=bool(cfg.get("act_fp8")))
-          if world > 1 else None)
+    ep = (ExpertParallelMoE(e, experts, wire_dtype=torch.float16, fp8_act=bool(cfg.get("act_fp8")),
+                            chunks=args.ep_chunks) if world > 1 else None)
     shared = None
     if cfg.get("shared"):
         # the always-on shared expert: the same three projections as a one-expert bank over this rank's tokens
@@ -685,7 +685,7 @@ def run_moe(args):
             "scaling": "weak" if weak else "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": cfg["label"], "format": cfg["fmt"], "experts": e, "top_k": k, "hidden": h,
                        "intermediate": cfg["i"], "tokens_global": t_global, "experts_per_gpu": e // world,
-                       "parallelism": f"ep{world}", "l2": "expert banks exceed L2; activations rotate over 4 buffers"},
+                       "parallelism": f"ep{world}" + (f" x{args.ep_chunks} chunks" if world > 1 and args.ep_chunks > 1 else ""), "l2": "expert banks exceed L2; activations rotate over 4 buffers"},
             "roofline": roof,
             "parity_vs_decode_kernel_rel_l2_bf16_out": parity,
             "cpu_baseline": None,
@@ -707,6 +707,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="gemv", choices=["gemv"] + list(MOE_CFGS))
     ap.add_argument("--tokens", type=int, default=0, help="override the token count of a MoE workload")
+    ap.add_argument("--ep-chunks", type=int, default=1,
+                    help="MoE workloads on several GPUs: token chunks whose exchange overlaps the experts of other chunks")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count of a MoE workload")
     ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"],
                     help="MoE workloads on several GPUs: tokens per GPU fixed (weak) or global count split (strong)")

@@ -43,7 +43,7 @@ def _gpu_reduce_fn(y_rows, weights, row_map, out_dtype, addend):
 class ExpertParallelMoE:
     def __init__(self, n_experts_global: int, experts=None, group=None,
                  expert_fn: Callable | None = None, reduce_fn: Callable | None = None,
-                 wire_dtype: torch.dtype | None = None, fp8_act: bool = False):
+                 wire_dtype: torch.dtype | None = None, fp8_act: bool = False, chunks: int = 1):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -56,6 +56,10 @@ class ExpertParallelMoE:
         # dtype the expert outputs travel back in (None = as computed, f32: the result then equals the single-GPU
         # layer; torch.float16 halves the return traffic at 5e-4 relative rounding per expert output)
         self.wire_dtype = wire_dtype
+        # token chunks per layer call: with more than one, the exchange of a chunk runs on a second stream while
+        # the experts work on another chunk
+        self.chunks = max(1, int(chunks))
+        self._comm_stream = None
         self.last_counts = None      # (send_counts, recv_counts) of the last call, for traffic accounting
 
     def local_expert_range(self):
@@ -102,6 +106,8 @@ class ExpertParallelMoE:
     def forward(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                 shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         t, k = topk_ids.shape
+        if self.chunks > 1 and t >= 2 * self.chunks:
+            return self._forward_chunked(xs, topk_weights, topk_ids, shared_out, out_dtype)
         x = xs.reshape(t, -1)
         order, send_counts, local_ids, row_map = self.plan(topk_ids)
         recv_counts = self._exchange_counts(send_counts)
@@ -118,4 +124,82 @@ class ExpertParallelMoE:
             y = y.to(self.wire_dtype)
         back = self._all_to_all_v(y, recv_splits, send_splits)
         out = self.reduce_fn(back, topk_weights.to(torch.float32), row_map, out_dtype or xs.dtype, shared_out)
+        return out.reshape(*xs.shape[:-1], out.shape[-1])
+
+    def _forward_chunked(self, xs, topk_weights, topk_ids, shared_out, out_dtype):
+        """The same exchange in `chunks` contiguous token chunks: all plans and split sizes first (one host read),
+        then every chunk's dispatch is queued on a second stream, and each chunk's return is queued behind its
+        expert block, so the experts of one chunk overlap the exchange of its neighbours.  Every rank issues the
+        collectives in the same order."""
+        t, k = topk_ids.shape
+        x = xs.reshape(t, -1)
+        c_n = self.chunks
+        cuts = [t * c // c_n for c in range(c_n + 1)]
+        plans = [self.plan(topk_ids[cuts[c]:cuts[c + 1]]) for c in range(c_n)]
+        send_counts = torch.stack([p[1] for p in plans], dim=1).contiguous()          # [world, chunks]
+        if self.world == 1:
+            recv_counts = send_counts.clone()
+        else:
+            recv_counts = torch.empty_like(send_counts)
+            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        both = torch.stack([send_counts, recv_counts]).tolist()
+        send_splits = [[int(both[0][r][c]) for r in range(self.world)] for c in range(c_n)]
+        recv_splits = [[int(both[1][r][c]) for r in range(self.world)] for c in range(c_n)]
+        self.last_counts = ([sum(v) for v in zip(*send_splits)], [sum(v) for v in zip(*recv_splits)])
+        on_gpu = x.is_cuda
+        cur = torch.cuda.current_stream(x.device) if on_gpu else None
+        if on_gpu and self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=x.device)
+        comm = self._comm_stream if on_gpu else None
+
+        class _On:      # queue the enclosed work on the exchange stream (nothing to do for CPU ranks)
+            def __enter__(s_):
+                if on_gpu:
+                    s_.ctx = torch.cuda.stream(comm)
+                    s_.ctx.__enter__()
+            def __exit__(s_, *a):
+                if on_gpu:
+                    s_.ctx.__exit__(*a)
+
+        got, ev_disp = [], []
+        if on_gpu:
+            comm.wait_stream(cur)
+        for c in range(c_n):
+            order, _, local_ids, _ = plans[c]
+            with _On():
+                rows = x[cuts[c]:cuts[c + 1]].index_select(0, torch.div(order, k, rounding_mode="floor"))
+                g_rows = self._all_to_all_v(rows, send_splits[c], recv_splits[c])
+                g_ids = self._all_to_all_v(local_ids, send_splits[c], recv_splits[c])
+                ev = comm.record_event() if on_gpu else None
+            got.append((g_rows, g_ids, rows))
+            ev_disp.append(ev)
+        backs, ev_back, keep = [], [], []
+        for c in range(c_n):
+            g_rows, g_ids, _ = got[c]
+            if on_gpu:
+                cur.wait_event(ev_disp[c])
+                g_rows.record_stream(cur)
+                g_ids.record_stream(cur)
+            y = self.expert_fn(g_rows, g_ids)
+            if self.wire_dtype is not None and y.dtype != self.wire_dtype:
+                y = y.to(self.wire_dtype)
+            ev_y = cur.record_event() if on_gpu else None
+            with _On():
+                if on_gpu:
+                    comm.wait_event(ev_y)
+                    y.record_stream(comm)
+                back = self._all_to_all_v(y, recv_splits[c], send_splits[c])
+                ev_back.append(comm.record_event() if on_gpu else None)
+            backs.append(back)
+            keep.append(y)
+        outs = []
+        w32 = topk_weights.to(torch.float32)
+        for c in range(c_n):
+            if on_gpu:
+                cur.wait_event(ev_back[c])
+                backs[c].record_stream(cur)
+            add = None if shared_out is None else shared_out.reshape(t, -1)[cuts[c]:cuts[c + 1]]
+            outs.append(self.reduce_fn(backs[c], w32[cuts[c]:cuts[c + 1]].contiguous(), plans[c][3],
+                                       out_dtype or xs.dtype, add))
+        out = torch.cat(outs, dim=0)
         return out.reshape(*xs.shape[:-1], out.shape[-1])

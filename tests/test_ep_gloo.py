@@ -13,7 +13,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, results, chunks=1):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -32,7 +32,7 @@ def _worker(rank, world, port, results):
             logits[:, :4] += 50.0          # rank 1 routes everything to rank 0's experts: empty splits appear
         ids, w = M.router_topk(logits, k, M.SCORE_SOFTMAX, M.WEIGHT_SCORE, True)
 
-        ep = ExpertParallelMoE(e, expert_fn=None, reduce_fn=None, experts=object())
+        ep = ExpertParallelMoE(e, expert_fn=None, reduce_fn=None, experts=object(), chunks=chunks)
         lo, hi = ep.local_expert_range()
 
         def expert_fn(rows, local_ids):
@@ -58,12 +58,17 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-def test_ep_protocol_two_cpu_ranks():
+import pytest
+
+
+@pytest.mark.parametrize("chunks", [1, 3])
+def test_ep_protocol_two_cpu_ranks(chunks):
+    # chunks > 1: the same exchange in token chunks (the form that overlaps exchange and experts on the GPU)
     world = 2
-    port = 29500 + (os.getpid() % 2000)
+    port = 29500 + (os.getpid() % 2000) + 7 * chunks
     with mp.Manager() as mgr:
         results = mgr.dict()
-        mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, results, chunks), nprocs=world, join=True)
         res = dict(results)
     assert set(res) == {0, 1}
     for rank, (err, send, recv, total) in res.items():
