@@ -549,7 +549,8 @@ def run_moe(args):
     def step(j, x=None, lg=None, force_16bit=False):
         x = xs[j % n_in] if x is None else x
         lg = logits[j % n_in] if lg is None else lg
-        top = hq.moe_router_topk(lg, rcfg, sel_bias)
+        fused_call = ep is None and not cfg.get("act_fp8")      # router and experts in one library call
+        top = None if fused_call else hq.moe_router_topk(lg, rcfg, sel_bias)
         if cfg.get("act_fp8") and not force_16bit:
             # block-scaled FP8 activations (per-token 1x128 dynamic quantization, the layer's own arithmetic): the
             # codes of weights and activations go into the FP8 MMA unconverted
@@ -569,6 +570,9 @@ def run_moe(args):
             add = shared.forward(x, shared_w[:x.shape[0]], shared_ids[:x.shape[0]], out_dtype=torch.bfloat16)
         if ep is not None:
             return ep.forward(x, top.values, top.indices, shared_out=add, out_dtype=torch.bfloat16)
+        if fused_call:
+            # one library call for the whole layer (router included): no host work between the launches
+            return experts.forward_layer(x, lg, rcfg, sel_bias, shared_out=add, out_dtype=torch.bfloat16)
         return experts.forward(x, top.values, top.indices, shared_out=add, out_dtype=torch.bfloat16)
 
     for w in range(max(args.warmup, 3)):

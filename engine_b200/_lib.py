@@ -37,6 +37,11 @@ class HqActArgs(C.Structure):
     _fields_ = [("act", C.c_int32), ("has_limit", C.c_int32), ("limit", C.c_float), ("alpha", C.c_float)]
 
 
+class HqMoeLayer(C.Structure):
+    _fields_ = [("gate", C.POINTER(HqWeight)), ("up", C.POINTER(HqWeight)), ("down", C.POINTER(HqWeight)),
+                ("act", HqActArgs), ("router", HqRouterArgs)]
+
+
 _P, _I32, _I64 = C.c_void_p, C.c_int32, C.c_int64
 
 # every symbol include/hanzoquant_b200.h declares: name -> (restype, argtypes)
@@ -50,6 +55,8 @@ SIGNATURES = {
     "hq_fp8_linear_forward": (_I32, [C.POINTER(HqWeight), _P, _P, _I64, _P, _I32, _I64, _P, _P]),
     "hq_moe_fp8_gather_forward": (_I32, [C.POINTER(HqWeight), _P, _P, _I64, _I32, _P, _P, _P, _P, _I32, _I64, _I32,
                                          _P, _P]),
+    "hq_moe_layer_workspace_bytes": (_I64, [C.POINTER(HqMoeLayer), _I64, _I32]),
+    "hq_moe_layer_forward": (_I32, [C.POINTER(HqMoeLayer), _P, _I32, _P, _I32, _I64, _P, _P, _I32, _P, _I64, _P, _P]),
     "hq_linear_workspace_bytes": (_I64, [C.POINTER(HqWeight), _I64]),
     "hq_linear_forward_ws": (_I32, [C.POINTER(HqWeight), _P, _I32, _I64, _P, _I32, _I64, _I64, _P, _I64, _P, _P]),
     "hq_router_topk": (_I32, [_P, _I32, _I64, C.POINTER(HqRouterArgs), _P, _P, _P]),

@@ -449,4 +449,99 @@ int32_t hq_gated_act(const void* gate, const void* up, int32_t dtype, int64_t n_
   return launch_gated_act(gate, up, dtype, n_elems, interleaved, *act, out, (cudaStream_t)stream);
 }
 
+// ---- one MoE layer in one call -----------------------------------------------------------------------------
+namespace {
+struct MoeLayerPlan {
+  int64_t t, k, e, hidden, inter, rows;
+  bool interleaved, cast_x;
+  int64_t off_ids, off_w, off_bounds, off_sa, off_st, off_inv, off_dws, dws_bytes, off_x16, off_h, off_y, total;
+};
+int64_t up256(int64_t v) { return (v + 255) / 256 * 256; }
+int32_t plan_moe_layer(const hq_moe_layer* l, int64_t n_tokens, int32_t x_dtype, MoeLayerPlan& p) {
+  if (l == nullptr || l->gate == nullptr || l->down == nullptr) return HQ_ERR_NULL;
+  int32_t rc = check_weight(l->gate);
+  if (rc == HQ_OK) rc = check_weight(l->down);
+  if (rc == HQ_OK && l->up != nullptr) rc = check_weight(l->up);
+  if (rc != HQ_OK) return rc;
+  p.t = n_tokens;
+  p.k = l->router.top_k;
+  p.e = l->gate->n_experts;
+  if (l->router.n_experts != p.e || l->down->n_experts != p.e || p.k < 1) return HQ_ERR_SHAPE;
+  p.interleaved = l->up == nullptr;
+  p.hidden = l->gate->k;
+  p.inter = p.interleaved ? l->gate->n / 2 : l->gate->n;
+  if (l->down->k != p.inter || l->down->n != p.hidden) return HQ_ERR_SHAPE;
+  if (l->act.act == HQ_ACT_NONE) return HQ_ERR_FORMAT;
+  p.rows = p.t * p.k;
+  // the tensor-core kernel copies activations as f16: cast once per token here instead of per (token, slot) there
+  p.cast_x = x_dtype != HQ_DT_F16 && p.rows >= g_cfg[HQ_CFG_MOE_TENSOR_MIN_ROWS] * p.e &&
+             tensor_path_ok(l->gate, l->up, HQ_DT_F16, l->gate->k);
+  int64_t o = 0;
+  p.off_ids = o;    o += up256(p.rows * 4);
+  p.off_w = o;      o += up256(p.rows * 4);
+  p.off_bounds = o; o += up256((p.e + 1) * 4);
+  p.off_sa = o;     o += up256(p.rows * 4);
+  p.off_st = o;     o += up256(p.rows * 4);
+  p.off_inv = o;    o += up256(p.rows * 4);
+  p.dws_bytes = hq_moe_dispatch_workspace_bytes(p.t, (int32_t)p.k, (int32_t)p.e);
+  p.off_dws = o;    o += up256(p.dws_bytes);
+  p.off_x16 = o;    o += p.cast_x ? up256(p.t * p.hidden * 2) : 0;
+  p.off_h = o;      o += up256(p.rows * p.inter * 2);
+  p.off_y = o;      o += up256(p.rows * p.hidden * 4);
+  p.total = o;
+  return HQ_OK;
+}
+}  // namespace
+
+int64_t hq_moe_layer_workspace_bytes(const hq_moe_layer* layer, int64_t n_tokens, int32_t x_dtype) {
+  MoeLayerPlan p;
+  if (n_tokens <= 0 || plan_moe_layer(layer, n_tokens, x_dtype, p) != HQ_OK) return 0;
+  return p.total;
+}
+
+int32_t hq_moe_layer_forward(const hq_moe_layer* layer, const void* logits, int32_t logits_dtype, const void* x,
+                             int32_t x_dtype, int64_t n_tokens, const void* shared_addend, void* out,
+                             int32_t out_dtype, void* workspace, int64_t workspace_bytes, int32_t* status_dev,
+                             void* stream) {
+  if (n_tokens < 0) return HQ_ERR_SHAPE;
+  if (n_tokens == 0) return HQ_OK;
+  if (!valid_dtype(x_dtype) || !valid_dtype(out_dtype) || !valid_dtype(logits_dtype)) return HQ_ERR_FORMAT;
+  MoeLayerPlan p;
+  int32_t rc = plan_moe_layer(layer, n_tokens, x_dtype, p);
+  if (rc != HQ_OK) return rc;
+  if (logits == nullptr || x == nullptr || out == nullptr || workspace == nullptr) return HQ_ERR_NULL;
+  if (workspace_bytes < p.total) return HQ_ERR_WORKSPACE;
+  if (((uintptr_t)workspace & 255u) != 0) return HQ_ERR_ALIGN;
+  uint8_t* ws = (uint8_t*)workspace;
+  uint32_t* ids = (uint32_t*)(ws + p.off_ids);
+  float* wts = (float*)(ws + p.off_w);
+  int32_t* bounds = (int32_t*)(ws + p.off_bounds);
+  int32_t* sa = (int32_t*)(ws + p.off_sa);
+  int32_t* st = (int32_t*)(ws + p.off_st);
+  int32_t* inv = (int32_t*)(ws + p.off_inv);
+  void* dws = ws + p.off_dws;
+  rc = hq_router_topk(logits, logits_dtype, n_tokens, &layer->router, ids, wts, stream);
+  if (rc != HQ_OK) return rc;
+  rc = hq_moe_dispatch_build(ids, n_tokens, (int32_t)p.k, (int32_t)p.e, bounds, sa, st, inv, dws, p.dws_bytes, stream);
+  if (rc != HQ_OK) return rc;
+  const void* xin = x;
+  int32_t xin_dtype = x_dtype;
+  if (p.cast_x) {
+    rc = hq_convert(x, x_dtype, ws + p.off_x16, HQ_DT_F16, n_tokens * p.hidden, stream);
+    if (rc != HQ_OK) return rc;
+    xin = ws + p.off_x16;
+    xin_dtype = HQ_DT_F16;
+  }
+  void* h = ws + p.off_h;
+  rc = hq_moe_gather_forward(layer->gate, layer->up, &layer->act, xin, xin_dtype, HQ_ROWS_PER_TOKEN, n_tokens,
+                             (int32_t)p.k, bounds, sa, st, dws, h, HQ_DT_F16, HQ_ROWS_SORTED, status_dev, stream);
+  if (rc != HQ_OK) return rc;
+  void* y = ws + p.off_y;
+  rc = hq_moe_gather_forward(layer->down, nullptr, nullptr, h, HQ_DT_F16, HQ_ROWS_SORTED, n_tokens, (int32_t)p.k,
+                             bounds, sa, st, dws, y, HQ_DT_F32, HQ_ROWS_SORTED, status_dev, stream);
+  if (rc != HQ_OK) return rc;
+  return hq_moe_weighted_reduce(y, HQ_DT_F32, wts, inv, shared_addend, out, out_dtype, n_tokens, (int32_t)p.k,
+                                p.hidden, stream);
+}
+
 }  // extern "C"

@@ -33,6 +33,14 @@ class TopKOutput:
     indices: torch.Tensor   # int32 [T, k] (bit pattern of the reference's u32 ids)
 
 
+def _router_args(e: int, config: MoeRouterTopKConfig, bias, scale) -> "L.HqRouterArgs":
+    clip = config.logit_clip
+    return L.HqRouterArgs(e, config.top_k, config.score_function, config.selected_weight, int(config.renormalize),
+                          int(clip is not None), clip[0] if clip else 0.0, clip[1] if clip else 0.0,
+                          config.norm_min, config.output_scale, 0 if bias is None else bias.data_ptr(),
+                          0 if scale is None else scale.data_ptr())
+
+
 def moe_router_topk(logits: torch.Tensor, config: MoeRouterTopKConfig, selection_bias: torch.Tensor | None = None,
                     expert_scale: torch.Tensor | None = None) -> TopKOutput:
     _require_cuda(logits, "logits")
@@ -42,11 +50,7 @@ def moe_router_topk(logits: torch.Tensor, config: MoeRouterTopKConfig, selection
     w = torch.empty((t, config.top_k), dtype=torch.float32, device=logits.device)
     bias = None if selection_bias is None else selection_bias.to(torch.float32).contiguous()
     scale = None if expert_scale is None else expert_scale.to(torch.float32).contiguous()
-    clip = config.logit_clip
-    args = L.HqRouterArgs(e, config.top_k, config.score_function, config.selected_weight, int(config.renormalize),
-                          int(clip is not None), clip[0] if clip else 0.0, clip[1] if clip else 0.0,
-                          config.norm_min, config.output_scale, 0 if bias is None else bias.data_ptr(),
-                          0 if scale is None else scale.data_ptr())
+    args = _router_args(e, config, bias, scale)
     L.check(L.lib().hq_router_topk(_ptr(logits), dt_code(logits.dtype), t, C.byref(args), _ptr(ids), _ptr(w),
                                    _stream()), "hq_router_topk")
     return TopKOutput(w, ids)
@@ -167,4 +171,41 @@ class MoEExperts:
         if _skip_reduce:
             return y
         out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype or xs.dtype, tables.inv_perm, shared_out)
+        return out.reshape(*lead, self.down.n)
+
+    def forward_layer(self, xs: torch.Tensor, logits: torch.Tensor, config: MoeRouterTopKConfig,
+                      selection_bias: torch.Tensor | None = None, expert_scale: torch.Tensor | None = None,
+                      shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """Router, dispatch, both projections and the weighted sum in one library call (hq_moe_layer_forward): the
+        same kernels as moe_router_topk + forward, launched back to back without host work in between.  The
+        scratch is kept by the object and grown when a call needs more."""
+        _require_cuda(xs, "xs")
+        lead = xs.shape[:-1]
+        x = xs.reshape(-1, xs.shape[-1]).contiguous()
+        t = x.shape[0]
+        logits = logits.reshape(t, -1).contiguous()
+        out_dtype = out_dtype or xs.dtype
+        bias = None if selection_bias is None else selection_bias.to(torch.float32).contiguous()
+        scale = None if expert_scale is None else expert_scale.to(torch.float32).contiguous()
+        first = self.gate_up if self.gate_up is not None else self.gate
+        w0, wd = first._weight_struct(), self.down._weight_struct()
+        w1 = self.up._weight_struct() if self.up is not None else None
+        layer = L.HqMoeLayer(C.pointer(w0), C.pointer(w1) if w1 is not None else None, C.pointer(wd), self.act,
+                             _router_args(self.n_experts, config, bias, scale))
+        lib = L.lib()
+        need = int(lib.hq_moe_layer_workspace_bytes(C.byref(layer), t, dt_code(x.dtype)))
+        if need == 0 and t > 0:
+            raise L.HqError("hq_moe_layer_workspace_bytes: the layer description is inconsistent")
+        ws = getattr(self, "_layer_ws", None)
+        if ws is None or ws.numel() < need or ws.device != x.device:
+            ws = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+            self._layer_ws = ws
+        out = torch.empty((t, self.down.n), dtype=out_dtype, device=x.device)
+        add = None
+        if shared_out is not None:
+            add = shared_out.reshape(t, -1)
+            add = add.to(out_dtype).contiguous() if add.dtype != out_dtype else add.contiguous()
+        L.check(lib.hq_moe_layer_forward(C.byref(layer), _ptr(logits), dt_code(logits.dtype), _ptr(x), dt_code(x.dtype),
+                                         t, _ptr(add), _ptr(out), dt_code(out_dtype), _ptr(ws), ws.numel(),
+                                         _ptr(first._status_buf(x.device)), _stream()), "hq_moe_layer_forward")
         return out.reshape(*lead, self.down.n)

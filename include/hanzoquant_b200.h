@@ -211,6 +211,29 @@ int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const h
                               const int32_t* sorted_token, const void* workspace, void* out, int32_t out_dtype,
                               int32_t out_layout, int32_t* status_dev, void* stream);
 
+/* ---- one MoE layer in one call ---------------------------------------------
+ * router -> dispatch tables -> gate/up projection with the gated activation -> down projection -> weighted
+ * sum over the slots, launched back to back from one call: the fused form of the reference's per-layer
+ * sequence (hanzo-engine/src/moe/experts/backends.rs:560-605; its single-launch decode entry is
+ * indexed_moe_fused_decode, hanzo-quant/src/gguf/cuda.rs:879-1056).  What it saves over the separate calls is
+ * host time between launches, which is most of a decode step of a few tokens.
+ * `up` NULL means `gate` holds interleaved gate/up rows.  logits [n_tokens, n_experts]; x [n_tokens, hidden];
+ * shared_addend [n_tokens, hidden] in out_dtype or NULL; out [n_tokens, hidden].  All scratch (routing, tables,
+ * the expert-sorted intermediate and outputs) lives in the caller's workspace, 256-byte aligned, of
+ * hq_moe_layer_workspace_bytes(layer, n_tokens, x_dtype) bytes. */
+typedef struct hq_moe_layer {
+  const hq_weight* gate;
+  const hq_weight* up;
+  const hq_weight* down;
+  hq_act_args act;
+  hq_router_args router;
+} hq_moe_layer;
+int64_t hq_moe_layer_workspace_bytes(const hq_moe_layer* layer, int64_t n_tokens, int32_t x_dtype);
+int32_t hq_moe_layer_forward(const hq_moe_layer* layer, const void* logits, int32_t logits_dtype, const void* x,
+                             int32_t x_dtype, int64_t n_tokens, const void* shared_addend, void* out,
+                             int32_t out_dtype, void* workspace, int64_t workspace_bytes, int32_t* status_dev,
+                             void* stream);
+
 /* ---- combine: moe_weighted_reduce_flat -------------------------------------
  * out[t, :] = sum_s w[t, s] * y[t, s, :] (+ addend[t, :]), f32 accumulation in
  * slot order, no atomics.  Replaces launch_moe_weighted_reduce_flat{,_bf16}

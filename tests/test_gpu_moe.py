@@ -168,6 +168,11 @@ def _moe_case(fmt, t, e, k, h, i, interleaved, act, seed, limit=None):
         experts = hq.MoEExperts(down, gate, up, act=act, limit=limit)
         want = M.moe_layer(x_np, ids, w, g_deq, u_deq, d_deq, act, limit=limit, h_round=f16)
     got = experts.forward(x, w_d, ids_d, out_dtype=torch.float32)
+    # the one-call form of the same layer (router included) launches the same kernels: same bits
+    fused = experts.forward_layer(x, T.to_dev(logits, torch.float32, DEV),
+                                  hq.MoeRouterTopKConfig(k, L.SCORE_SOFTMAX, L.WEIGHT_SCORE, True),
+                                  out_dtype=torch.float32)
+    assert torch.equal(fused, got)
     return got.cpu().numpy(), want
 
 
