@@ -168,11 +168,14 @@ def _moe_case(fmt, t, e, k, h, i, interleaved, act, seed, limit=None):
         experts = hq.MoEExperts(down, gate, up, act=act, limit=limit)
         want = M.moe_layer(x_np, ids, w, g_deq, u_deq, d_deq, act, limit=limit, h_round=f16)
     got = experts.forward(x, w_d, ids_d, out_dtype=torch.float32)
-    # the one-call form of the same layer (router included) launches the same kernels: same bits
-    fused = experts.forward_layer(x, T.to_dev(logits, torch.float32, DEV),
-                                  hq.MoeRouterTopKConfig(k, L.SCORE_SOFTMAX, L.WEIGHT_SCORE, True),
-                                  out_dtype=torch.float32)
-    assert torch.equal(fused, got)
+    # the one-call form of the same layer (router included) launches the same kernels as the separate calls: same bits
+    rcfg = hq.MoeRouterTopKConfig(k, L.SCORE_SOFTMAX, L.WEIGHT_SCORE, True)
+    logits_d = T.to_dev(logits, torch.float32, DEV)
+    top = hq.moe_router_topk(logits_d, rcfg)
+    assert np.array_equal(top.indices.cpu().numpy().astype(np.uint32), ids)
+    split = experts.forward(x, top.values, top.indices, out_dtype=torch.float32)
+    fused = experts.forward_layer(x, logits_d, rcfg, out_dtype=torch.float32)
+    assert torch.equal(fused, split)
     return got.cpu().numpy(), want
 
 
