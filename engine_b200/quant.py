@@ -98,6 +98,8 @@ class QuantMethod:
     def __init__(self):
         self._status = None
         self._ws = {}
+        self._ws_need = {}
+        self._w_cached = None
 
     # -- plumbing -------------------------------------------------------------------
     def _weight_struct(self) -> L.HqWeight:
@@ -141,25 +143,34 @@ class QuantMethod:
         if x.dtype != torch.float16 and tensor_path_expected(self, m, dense=True):
             x = x.to(torch.float16)     # the tensor-core kernel multiplies in f16 either way
         y = torch.empty((m, self.n), dtype=out_dtype, device=a.device)
-        w = self._weight_struct()
-        ws, ws_bytes = self._linear_workspace(w, m, a.device)
-        L.check(L.lib().hq_linear_forward_ws(C.byref(w), _ptr(x), dt_code(x.dtype), x.stride(0) if m > 1 else self.k,
-                                             _ptr(y), dt_code(out_dtype), self.n, m, ws, ws_bytes,
-                                             _ptr(self._status_buf(a.device)), _stream()), "hq_linear_forward_ws")
+        # the weight descriptor never changes after construction: built once (a decode call is a few microseconds
+        # of GPU time, so host work per call matters)
+        w = self._w_cached
+        if w is None:
+            w = self._w_cached = self._weight_struct()
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        ws, ws_bytes = self._linear_workspace(w, m, a.device, stream)
+        rc = L.lib().hq_linear_forward_ws(C.byref(w), x.data_ptr(), dt_code(x.dtype), x.stride(0) if m > 1 else self.k,
+                                          y.data_ptr(), dt_code(out_dtype), self.n, m, ws, ws_bytes,
+                                          self._status_buf(a.device).data_ptr(), stream)
+        if rc != 0:
+            L.check(rc, "hq_linear_forward_ws")
         return y.reshape(*lead, self.n)
 
-    def _linear_workspace(self, w, m: int, device):
+    def _linear_workspace(self, w, m: int, device, stream: int):
         """Scratch for hq_linear_forward_ws, owned by the layer like the reference's Q8_1 activation buffer
         (fast_mmvq.rs:107-148): zero-filled once, grown when a call asks for more, one per CUDA stream."""
-        need = int(L.lib().hq_linear_workspace_bytes(C.byref(w), m))
+        need = self._ws_need.get(m)
+        if need is None:
+            need = self._ws_need[m] = int(L.lib().hq_linear_workspace_bytes(C.byref(w), m))
         if need == 0:
             return None, 0
-        key = (device.index, int(torch.cuda.current_stream(device).cuda_stream))
+        key = (device.index, stream)
         buf = self._ws.get(key)
         if buf is None or buf.numel() < need:
             buf = torch.zeros(need, dtype=torch.uint8, device=device)
             self._ws[key] = buf
-        return _ptr(buf), buf.numel()
+        return buf.data_ptr(), buf.numel()
 
     def gather_forward(self, a: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
         """Per-assignment projection out of the bank (lib.rs:1032-1040): a is [T, K], [T, 1, K] (one row per
