@@ -365,7 +365,7 @@ def run_gemv(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
             "config": {"workload": "cfg2_q8_0_decode_gemv_sweep" if len(SHAPES) == 4 else "single_shape_profile_case",
                        "shapes_k_to_n": SHAPES, "m": MS, "x_dtype": "bf16", "y_dtype": "f32", "multi_gpu": "replicas only (dense GEMV is not sharded)",
                        "l2": "every launch reads a weight copy last touched >= 700 MB of traffic earlier",

@@ -22,9 +22,11 @@ def _layer(fmt, n, k, seed):
 
 
 @pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K"])
-@pytest.mark.parametrize("m", [1, 5, 8])
+@pytest.mark.parametrize("m", [1, 5, 8, 11])
 def test_long_k_takes_the_split_and_matches(fmt, m):
     # K = 14336 does not fit beside the ring: with the layer's scratch the kernel splits K across CTAs
+    if fmt == "Q4_K" and m > 8:
+        pytest.skip("Q4_K with more than 8 rows runs on the tensor-core kernel, not the decode kernel")
     from engine_b200 import _lib as L
     n, k = 1000, 14336
     layer, deq, rng = _layer(fmt, n, k, 1)
