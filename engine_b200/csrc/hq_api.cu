@@ -315,6 +315,7 @@ int32_t hq_fp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, cons
   if (n_rows == 0) return HQ_OK;
   if (x == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
   if (!valid_dtype(x_dtype)) return HQ_ERR_FORMAT;
+  if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
   return launch_fp8_quant_rows(x, x_dtype, x_stride, row_map, n_rows, k, codes, scales, (cudaStream_t)stream);
 }
 
@@ -324,6 +325,7 @@ int32_t hq_fp8_gated_quant_rows(const void* gate_up, int32_t dtype, int64_t n_ro
   if (n_rows == 0) return HQ_OK;
   if (gate_up == nullptr || act == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
   if (!valid_dtype(dtype) || act->act == HQ_ACT_NONE) return HQ_ERR_FORMAT;
+  if (!aligned16(gate_up)) return HQ_ERR_ALIGN;
   return launch_fp8_gated_quant_rows(gate_up, dtype, n_rows, width, *act, codes, scales, (cudaStream_t)stream);
 }
 

@@ -173,6 +173,24 @@ int32_t launch_fp8_vector_quant(const void* x, int x_dtype, int64_t n, uint8_t* 
   fp8_vector_quant_kernel<<<(unsigned)((groups + 7) / 8), 256, 0, stream>>>(x, x_dtype, groups, codes, scales);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
+// four consecutive elements starting at element index i (a multiple of 4; rows are 16-byte aligned)
+__device__ __forceinline__ void load4_as_float(const void* p, int dtype, int64_t i, float (&v)[4]) {
+  if (dtype == HQ_DT_F32) {
+    const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p) + i);
+    if (dtype == HQ_DT_BF16) {
+      v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xFFFF0000u);
+      v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xFFFF0000u);
+    } else {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+      v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+  }
+}
+
 // The same 1 x 128 quantizer over rows that are looked up first (token order -> expert-sorted order): one warp per
 // (output row, group of 128 columns).  Feeds the FP8 expert GEMM, whose operand boxes need whole sorted rows.
 __global__ void __launch_bounds__(256) fp8_quant_rows_kernel(const void* __restrict__ x, int dtype, int64_t x_stride,
@@ -187,8 +205,7 @@ __global__ void __launch_bounds__(256) fp8_quant_rows_kernel(const void* __restr
   const int64_t src_row = row_map != nullptr ? (int64_t)row_map[row] : row;
   const int64_t src = src_row * x_stride + g * 128 + lane * 4;
   float v[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] = load_as_float(x, dtype, src + i);
+  load4_as_float(x, dtype, src, v);
   float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
@@ -297,10 +314,11 @@ __global__ void __launch_bounds__(256) fp8_gated_quant_rows_kernel(const void* _
   const int64_t row = grp / kgroups;
   const int g = (int)(grp - row * kgroups);
   const int64_t src = row * 2 * width + g * 128 + lane * 4;
-  float v[4];
+  float gv[4], uv[4], v[4];
+  load4_as_float(gu, dtype, src, gv);
+  load4_as_float(gu, dtype, src + width, uv);
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-    v[i] = gated_act(load_as_float(gu, dtype, src + i), load_as_float(gu, dtype, src + width + i), act);
+  for (int i = 0; i < 4; ++i) v[i] = gated_act(gv[i], uv[i], act);
   float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
