@@ -7,8 +7,7 @@
 // Two producer warps stream each item's row segments (>= 2 KiB per bulk async
 // copy -- smaller copies cannot keep HBM busy) into a shared-memory ring with
 // mbarrier completion; thirteen consumer warps split K thirteen ways, decode the
-// blocks in registers into f16 MMA fragments (e4m3 by hardware conversion, e2m1
-// codes as f16 bit patterns with the power of two folded into the block scale)
+// blocks in registers into f16 MMA fragments (e4m3 and e2m1 by hardware conversion)
 // and multiply them against the (<= 8) activation rows with m16n8k16 warp MMAs,
 // f32 accumulation, one scale FMA per 32-element block.
 // The thirteen partial sums of an item are handed through shared memory (two
@@ -196,13 +195,18 @@ __device__ __forceinline__ void fp8_compute(float (&acc)[4], const B32Regs& r, f
   for (int i = 0; i < 4; ++i) acc[i] = fmaf(scale, blk[i], acc[i]);
 }
 
-// e2m1 nibble pair (one byte: low nibble = even element) -> f16x2 holding value * 2^-14:
-// f16 bits = sign<<15 | (exp,mant)<<9.
-__device__ __forceinline__ uint32_t e2m1_byte_to_f16x2(uint32_t byte) {
-  const uint32_t lo = byte & 0xFu, hi = (byte >> 4) & 0xFu;
-  const uint32_t hl = ((lo & 7u) << 9) | ((lo & 8u) << 12);
-  const uint32_t hh = ((hi & 7u) << 9) | ((hi & 8u) << 12);
-  return hl | (hh << 16);
+// four bytes of e2m1 nibble pairs (low nibble = even element = low half) -> four f16x2 by hardware conversion
+__device__ __forceinline__ void e2m1x8_to_f16x8(uint32_t w, uint32_t (&h)[4]) {
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+      "}\n"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
 }
 // MXFP4: one 32-element block = 16 bytes; lane t owns bytes 4t..4t+3 (elements 8t..8t+7).
 __device__ __forceinline__ void mx_load(B32Regs& r, uint32_t rowA, uint32_t rowB, uint32_t xs_g, int unit, int t,
@@ -216,10 +220,11 @@ __device__ __forceinline__ void mx_load(B32Regs& r, uint32_t rowA, uint32_t rowB
 }
 __device__ __forceinline__ void mx_compute(float (&acc)[4], const B32Regs& r, float sA, float sB) {
   float blk[4];
-  mma_f16_16816_c(blk, e2m1_byte_to_f16x2(r.a0), e2m1_byte_to_f16x2(r.b0), e2m1_byte_to_f16x2(r.a0 >> 8),
-                  e2m1_byte_to_f16x2(r.b0 >> 8), r.x0.x, r.x0.y, 0.f, 0.f, 0.f, 0.f);
-  mma_f16_16816(blk, e2m1_byte_to_f16x2(r.a0 >> 16), e2m1_byte_to_f16x2(r.b0 >> 16), e2m1_byte_to_f16x2(r.a0 >> 24),
-                e2m1_byte_to_f16x2(r.b0 >> 24), r.x1.x, r.x1.y);
+  uint32_t a[4], b[4];
+  e2m1x8_to_f16x8(r.a0, a);
+  e2m1x8_to_f16x8(r.b0, b);
+  mma_f16_16816_c(blk, a[0], b[0], a[1], b[1], r.x0.x, r.x0.y, 0.f, 0.f, 0.f, 0.f);
+  mma_f16_16816(blk, a[2], b[2], a[3], b[3], r.x1.x, r.x1.y);
   acc[0] = fmaf(sA, blk[0], acc[0]);
   acc[1] = fmaf(sA, blk[1], acc[1]);
   acc[2] = fmaf(sB, blk[2], acc[2]);
@@ -464,9 +469,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
             for (int u = wrot; u < nunits; u += WK) {
               B32Regs r0;
               mx_load(r0, rowA, rowB, xs_c, u, t, xv);
-              // 2^(e-127) with the reference's bit trick (e = 0 decodes to 0), times 2^14 for the nibble encoding
-              const float sA = __uint_as_float((uint32_t)__ldg(mA + u) << 23) * 16384.f;
-              const float sB = __uint_as_float((uint32_t)__ldg(mB + u) << 23) * 16384.f;
+              // 2^(e-127) with the reference's bit trick (e = 0 decodes to 0)
+              const float sA = __uint_as_float((uint32_t)__ldg(mA + u) << 23);
+              const float sB = __uint_as_float((uint32_t)__ldg(mB + u) << 23);
               mx_compute(a, r0, sA, sB);
             }
           }
