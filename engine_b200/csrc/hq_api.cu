@@ -138,7 +138,8 @@ int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* str
 int64_t hq_linear_workspace_bytes(const hq_weight* w, int64_t m) {
   if (check_weight(w) != HQ_OK || m <= 0) return 0;
   if (w->n_experts != 1) return 0;
-  if (w->format == HQ_FMT_Q4_K && m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS]) return 0;   // tensor-core path
+  if ((w->format == HQ_FMT_Q4_K || w->format == HQ_FMT_FP8_BLOCK) && m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS])
+    return 0;   // tensor-core path
   return gemv_int8_workspace_bytes(w->format, w->n, w->k, m);
 }
 

@@ -562,7 +562,11 @@ int32_t launch_gemv(const GemvParams& p, int n_y_max, cudaStream_t stream) {
   switch (p.format) {
     case HQ_FMT_Q8_0:
     case HQ_FMT_Q4_K: return launch_gemv_int8(p, n_y_max, max_rows, stream);   // integer-MMA kernel
-    case HQ_FMT_FP8_BLOCK: return launch_cfg<HQ_FMT_FP8_BLOCK, 2048>(p, n_y_max, max_rows, stream);
+    case HQ_FMT_FP8_BLOCK:
+      // one or two activation rows: the FP8 warp-MMA kernel (weights unconverted), for shapes whose 16-row items
+      // stay inside one weight-scale block
+      if (max_rows <= 2 && p.k % 256 == 0 && p.n % 16 == 0) return launch_gemv_int8(p, n_y_max, max_rows, stream);
+      return launch_cfg<HQ_FMT_FP8_BLOCK, 2048>(p, n_y_max, max_rows, stream);
     case HQ_FMT_MXFP4: return launch_cfg<HQ_FMT_MXFP4, 4096>(p, n_y_max, max_rows, stream);
     default: return HQ_ERR_FORMAT;
   }

@@ -63,6 +63,14 @@ constexpr int kQ8SmemBudget = 227 * 1024 - 256;   // dynamic part; a few static 
 constexpr int kQ8XGroups = 8;                    // 16-byte registers a thread prefetches activations into
 constexpr uint32_t kQ8Spin = 1u << 22;
 constexpr int kQ8Magic = 0x4B400000;             // 1.5 * 2^23 as f32 bits: magic + n reads as 12582912.f + n
+template <>
+struct I8Traits<HQ_FMT_FP8_BLOCK> {
+  // e4m3 codes, one byte per weight: a 128-column group is 128 bytes and shares one weight-block scale
+  static constexpr int KC = 2048, GK = 128, GROUP_BYTES = 128;
+  static constexpr int SEG = KC, PITCH = SEG + 32, STAGE_BYTES = kQ8RT * PITCH;
+  __host__ __device__ static constexpr int64_t row_bytes(int64_t k) { return k; }
+  static constexpr bool kSubSums = false;
+};
 static_assert(I8Traits<HQ_FMT_Q8_0>::SEG >= 2048 && I8Traits<HQ_FMT_Q8_0>::SEG % 16 == 0, "bulk copy size");
 static_assert(I8Traits<HQ_FMT_Q4_K>::SEG >= 2048 && I8Traits<HQ_FMT_Q4_K>::SEG % 16 == 0, "bulk copy size");
 static_assert(I8Traits<HQ_FMT_Q8_0>::PITCH % 128 == 32 && I8Traits<HQ_FMT_Q4_K>::PITCH % 128 == 32, "row pitch");
@@ -88,6 +96,14 @@ __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t 
   asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+}
+
+// the same shape with e4m3 operands and f32 accumulation (D += A.B)
+__device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Programmatic dependent launch: the kernel after this one in the stream may start its CTAs as ours retire (and
@@ -255,6 +271,138 @@ __device__ __forceinline__ void q8_x_commit(const Q8XPrefetch& pf, const GemvPar
         }
       }
     }
+  }
+}
+
+// Staging for block-FP8 weights: the e4m3 weight codes go into the FP8 warp MMA as they are, so the activations
+// become e4m3 as well -- three terms per value, x / s ~= t1 + t2 / 16 + t3 / 256 with s a power of two at or above
+// max|x| / 448 over the 128-element group (12 significant bits: error below max|x| / 2^13 of the group).  The
+// terms occupy separate columns, `tstride` = 2 columns apart (at most two activation rows share the column set).
+__device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+__device__ __forceinline__ void e4m3x4_to_f32x4(uint32_t v, float (&f)[4]) {
+  uint32_t lo, hi;
+  asm("{\n"
+      ".reg .b16 l, h;\n"
+      "mov.b32 {l, h}, %2;\n"
+      "cvt.rn.f16x2.e4m3x2 %0, l;\n"
+      "cvt.rn.f16x2.e4m3x2 %1, h;\n"
+      "}\n"
+      : "=r"(lo), "=r"(hi)
+      : "r"(v));
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+__device__ __forceinline__ void fp8_x_commit(const Q8XPrefetch& pf, const GemvParams& p, int nrows, int k_len, int tid,
+                                             uint8_t* xq, int xpitch, float* sx, int ncols, int tstride) {
+  const bool wide = p.x_dtype == HQ_DT_F32;
+  const int ipr = k_len >> 3;
+  const int nitems = nrows * ipr;
+  const int per_thread = wide ? kQ8XGroups / 2 : kQ8XGroups;
+#pragma unroll
+  for (int i = 0; i < kQ8XGroups; ++i) {
+    const int it = i * kQ8Consumers + tid;
+    if (i < per_thread && it < nitems) {   // uniform across the warp
+      const int col = it / ipr;
+      const int kk = (it - col * ipr) << 3;
+      float f[8];
+      if (wide) {
+        const uint4 r0 = pf.v[(2 * i) % kQ8XGroups], r1 = pf.v[(2 * i + 1) % kQ8XGroups];
+        f[0] = __uint_as_float(r0.x); f[1] = __uint_as_float(r0.y);
+        f[2] = __uint_as_float(r0.z); f[3] = __uint_as_float(r0.w);
+        f[4] = __uint_as_float(r1.x); f[5] = __uint_as_float(r1.y);
+        f[6] = __uint_as_float(r1.z); f[7] = __uint_as_float(r1.w);
+      } else if (p.x_dtype == HQ_DT_BF16) {
+        const uint4 raw = pf.v[i];
+        f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+        f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+        f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xFFFF0000u);
+        f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xFFFF0000u);
+      } else {
+        const uint4 raw = pf.v[i];
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = __half22float2(h[j]);
+          f[2 * j] = t.x; f[2 * j + 1] = t.y;
+        }
+      }
+      uint32_t abits = 0u;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) abits = max(abits, __float_as_uint(f[j]) & 0x7FFFFFFFu);
+      abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 1));
+      abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 2));
+      abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 4));
+      abits = max(abits, __shfl_xor_sync(0xffffffffu, abits, 8));
+      const float amax = __uint_as_float(abits);
+      const bool finite = abits < 0x7F800000u;
+      const uint32_t tb = __float_as_uint(fmaxf(amax / 448.f, 7.888609052e-31f));
+      const float s = finite ? __uint_as_float((tb + 0x007FFFFFu) & 0x7F800000u) : __int_as_float(0x7fc00000);
+      const float inv = (finite && abits != 0u) ? 1.f / s : 0.f;
+      uint32_t t1[2], t2[2], t3[2];
+#pragma unroll
+      for (int w2 = 0; w2 < 2; ++w2) {
+        float v[4], d[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = f[4 * w2 + j] * inv;
+        t1[w2] = f32x4_to_e4m3x4(v[0], v[1], v[2], v[3]);
+        e4m3x4_to_f32x4(t1[w2], d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = (v[j] - d[j]) * 16.f;
+        t2[w2] = f32x4_to_e4m3x4(v[0], v[1], v[2], v[3]);
+        e4m3x4_to_f32x4(t2[w2], d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = (v[j] - d[j]) * 16.f;
+        t3[w2] = f32x4_to_e4m3x4(v[0], v[1], v[2], v[3]);
+      }
+      uint8_t* d1 = xq + col * xpitch + kk;
+      *reinterpret_cast<uint2*>(d1) = make_uint2(t1[0], t1[1]);
+      *reinterpret_cast<uint2*>(d1 + tstride * xpitch) = make_uint2(t2[0], t2[1]);
+      *reinterpret_cast<uint2*>(d1 + 2 * tstride * xpitch) = make_uint2(t3[0], t3[1]);
+      if ((kk & 127) == 0) {
+        float* dsx = sx + (kk >> 7) * ncols + col;
+        dsx[0] = s;
+        dsx[tstride] = s * (1.f / 16.f);
+        dsx[2 * tstride] = s * (1.f / 256.f);
+      }
+    }
+  }
+}
+
+// one 128-column group of e4m3 weights x 16 rows x NCS column sets: four MMAs accumulate in f32 (the weight-block
+// scale `ws` is the same for all 16 rows and the whole group), then one FMA per accumulator with ws x the column's
+// activation step
+template <int NCS>
+__device__ __forceinline__ void fp8_group(float (&acc)[NCS][4], uint32_t pa, uint32_t pb, uint32_t xq,
+                                          uint32_t cs_stride, uint32_t sx, float ws) {
+  const uint2 a0 = lds64<0>(pa), a1 = lds64<32>(pa), a2 = lds64<64>(pa), a3 = lds64<96>(pa);
+  const uint2 b0 = lds64<0>(pb), b1 = lds64<32>(pb), b2 = lds64<64>(pb), b3 = lds64<96>(pb);
+  uint2 xb[NCS][4];
+  uint2 sxv[NCS];
+#pragma unroll
+  for (int c = 0; c < NCS; ++c) {
+    const uint32_t xc = xq + c * cs_stride;
+    xb[c][0] = lds64<0>(xc); xb[c][1] = lds64<32>(xc); xb[c][2] = lds64<64>(xc); xb[c][3] = lds64<96>(xc);
+    sxv[c] = lds64(sx + 32u * c);
+  }
+#pragma unroll
+  for (int c = 0; c < NCS; ++c) {
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    mma_e4m3_16832(d, a0.x, b0.x, a0.y, b0.y, xb[c][0].x, xb[c][0].y);
+    mma_e4m3_16832(d, a1.x, b1.x, a1.y, b1.y, xb[c][1].x, xb[c][1].y);
+    mma_e4m3_16832(d, a2.x, b2.x, a2.y, b2.y, xb[c][2].x, xb[c][2].y);
+    mma_e4m3_16832(d, a3.x, b3.x, a3.y, b3.y, xb[c][3].x, xb[c][3].y);
+    const float s0 = ws * __uint_as_float(sxv[c].x), s1 = ws * __uint_as_float(sxv[c].y);
+    acc[c][0] = fmaf(d[0], s0, acc[c][0]);
+    acc[c][1] = fmaf(d[1], s1, acc[c][1]);
+    acc[c][2] = fmaf(d[2], s0, acc[c][2]);
+    acc[c][3] = fmaf(d[3], s1, acc[c][3]);
   }
 }
 
@@ -558,8 +706,14 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
             float sum = 0.f;
 #pragma unroll
             for (int j = 0; j < WK; ++j) sum += rbuf[((b * WK + j) * 4 + i) * 32 + lane];
-            // four-row layout: the remainder columns 4..7 sit two lanes further on
-            if (NCS == 1) sum += __shfl_down_sync(0xffffffffu, sum, 2);
+            if (NCS == 1 && FMT == HQ_FMT_FP8_BLOCK) {
+              // two-row layout of the three e4m3 terms: columns 2, 3 and 4, 5 sit one and two lanes further on
+              const float s1 = __shfl_down_sync(0xffffffffu, sum, 1), s2 = __shfl_down_sync(0xffffffffu, sum, 2);
+              sum += s1 + s2;
+            } else if (NCS == 1) {
+              // four-row layout: the remainder columns 4..7 sit two lanes further on
+              sum += __shfl_down_sync(0xffffffffu, sum, 2);
+            }
             v[b][i] = sum;
           }
         }
@@ -576,7 +730,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
             for (int i = 0; i < 4; ++i) __stcg(mine + (b * 4 + i) * 32 + lane, v[b][i]);
           }
       } else {
-        gemv_store_item(p, wi, g, 2 * t, NCS == 2 || t < 2, v);
+        gemv_store_item(p, wi, g, 2 * t, NCS > 1 || t < (FMT == HQ_FMT_FP8_BLOCK ? 1 : 2), v);
       }
       ++item;
     }
@@ -590,6 +744,10 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
   const int xpitch = lay.xpitch;
   const int ncols = lay.ncols;
   const uint32_t cs_stride = 8u * (uint32_t)xpitch;
+  // terms an activation is split into, and the column distance between them: two int8 terms half the staged
+  // columns apart, or three e4m3 terms 2 columns apart (block-FP8 runs with one column set, at most two rows)
+  constexpr int kTerms = FMT == HQ_FMT_FP8_BLOCK ? 3 : 2;
+  const int tstride = FMT == HQ_FMT_FP8_BLOCK ? 2 : (ncols >> 1);
   // this lane's staged column (column g of every set), its group within a stage, its scale-table columns
   const uint32_t xq_lane = smem_u32(xq) + (uint32_t)g * xpitch + (uint32_t)T::GK * warp + 8u * t;
   const uint32_t sx_lane = smem_u32(sx) + (uint32_t)warp * ncols * 4u + 8u * t;
@@ -632,19 +790,25 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
         if (staged_rows > wi.nrows) {
           const int per_col = xpitch / 16;
           const int stale = staged_rows - wi.nrows;
-          for (int i = tid; i < 2 * stale * per_col; i += kQ8Consumers) {
-            const int half = i / (stale * per_col);
-            const int j = i - half * (stale * per_col);
-            const int col = wi.nrows + j / per_col + half * (ncols >> 1);
+          for (int i = tid; i < kTerms * stale * per_col; i += kQ8Consumers) {
+            const int term = i / (stale * per_col);
+            const int j = i - term * (stale * per_col);
+            const int col = wi.nrows + j / per_col + term * tstride;
             reinterpret_cast<uint4*>(xq + col * xpitch)[j % per_col] = make_uint4(0, 0, 0, 0);
           }
         }
         staged_rows = wi.nrows;
-        q8_x_commit<T::GK, T::kSubSums>(pf, p, wi.nrows, min(xk_sub, k_len), tid, xq, xpitch, sx, xsub, ncols);
+        auto commit = [&](int len, int sub) {
+          if (FMT == HQ_FMT_FP8_BLOCK)
+            fp8_x_commit(pf, p, wi.nrows, len, tid, xq + sub, xpitch, sx + (sub / T::GK) * ncols, ncols, tstride);
+          else
+            q8_x_commit<T::GK, T::kSubSums>(pf, p, wi.nrows, len, tid, xq + sub, xpitch, sx + (sub / T::GK) * ncols,
+                                            xsub + (sub / T::GK) * ncols * 16, ncols);
+        };
+        commit(min(xk_sub, k_len), 0);
         for (int sub = xk_sub; sub < k_len; sub += xk_sub) {   // wide input: the rest is fetched now
           q8_x_prefetch(pf, p, wi.row0, wi.nrows, k_base + sub, min(xk_sub, k_len - sub), tid);
-          q8_x_commit<T::GK, T::kSubSums>(pf, p, wi.nrows, min(xk_sub, k_len - sub), tid, xq + sub, xpitch,
-                                          sx + (sub / T::GK) * ncols, xsub + (sub / T::GK) * ncols * 16, ncols);
+          commit(min(xk_sub, k_len - sub), sub);
         }
         staged_y = wi.y;
         pf_valid = false;
@@ -668,6 +832,18 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
 #pragma unroll
         for (int bank = 0; bank < 2; ++bank) {
           if (bank >= p.n_banks) break;
+          // block-FP8: the 128 x 128 weight-block scales of this warp's groups, fetched before the wait for the stage
+          float wsv[kQ8GroupsPerWarp];
+          if (FMT == HQ_FMT_FP8_BLOCK) {
+            const float* fsc = reinterpret_cast<const float*>(bank == 0 ? p.scales : p.scales_up) +
+                               (int64_t)wi.expert * p.scale_expert_stride +
+                               (int64_t)(wi.n0 / 128) * ((p.k + 127) / 128) + chunk * (KC / 128);
+#pragma unroll
+            for (int gi = 0; gi < kQ8GroupsPerWarp; ++gi) {
+              const int grp = warp + gi * WK;
+              wsv[gi] = grp < ngroups ? __ldg(fsc + grp) : 0.f;
+            }
+          }
           if (!mbar_wait(&full[s], phase, spin)) {
             // bounded wait ran out: flag it and carry on (every warp still reaches every barrier)
             if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 200 + s);
@@ -684,6 +860,9 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
               if (FMT == HQ_FMT_Q8_0) {
                 q8_group<NCS>(acc[bank], da + 8u * t, db + 8u * t, da, db, xq_lane + gq * T::GK, cs_stride,
                               sx_lane + gq * (uint32_t)ncols * 4u);
+              } else if (FMT == HQ_FMT_FP8_BLOCK) {
+                fp8_group<NCS>(acc[bank], da + 8u * t, db + 8u * t, xq_lane + gq * T::GK, cs_stride,
+                               sx_lane + gq * (uint32_t)ncols * 4u, wsv[gi]);
               } else {
                 q4k_group<NCS>(acc[bank], da + 8u * t, db + 8u * t, da, db, xq_lane + gq * T::GK, cs_stride,
                                sx_lane + gq * (uint32_t)ncols * 4u, xs_lane + gq * (uint32_t)ncols * 16u, 128u, t);
@@ -714,7 +893,12 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
       if (b < p.n_banks) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          rbuf[((b * WK + warp) * 4 + i) * 32 + lane] = NCS == 2 ? acc[b][0][i] + acc[b][NCS - 1][i] : acc[b][0][i];
+        {
+          float sum = acc[b][0][i];
+#pragma unroll
+          for (int c = 1; c < NCS; ++c) sum += acc[b][c][i];
+          rbuf[((b * WK + warp) * 4 + i) * 32 + lane] = sum;
+        }
       }
     __syncwarp();
     if (lane == 0) mbar_arrive(&red_full[rb]);
@@ -755,7 +939,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
               v[b][i] = sum;
             }
           }
-        gemv_store_item(p, wi, g, 2 * t, NCS == 2 || t < 2, v);
+        gemv_store_item(p, wi, g, 2 * t, NCS > 1 || t < (FMT == HQ_FMT_FP8_BLOCK ? 1 : 2), v);
       }
     }
   }
@@ -798,6 +982,8 @@ static Q8Split q8_split_plan(int64_t n, int64_t k, int64_t n_y, int n_banks, boo
 int64_t gemv_int8_workspace_bytes(int format, int64_t n, int64_t k, int64_t m) {
   if (format == HQ_FMT_Q8_0) return q8_split_plan<HQ_FMT_Q8_0>(n, k, (m + 7) / 8, 1, false, m > 4 ? 16 : 8).bytes;
   if (format == HQ_FMT_Q4_K) return q8_split_plan<HQ_FMT_Q4_K>(n, k, (m + 7) / 8, 1, false, m > 4 ? 16 : 8).bytes;
+  if (format == HQ_FMT_FP8_BLOCK && k % 256 == 0 && n % 16 == 0 && m <= 2)
+    return q8_split_plan<HQ_FMT_FP8_BLOCK>(n, k, 1, 1, false, 8).bytes;
   return 0;
 }
 
@@ -877,12 +1063,17 @@ static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cud
 
 int32_t launch_gemv_int8(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream) {
   if (p.k % 256 != 0) return HQ_ERR_SHAPE;   // row segments must stay 16-byte aligned for the bulk copies
+  if (p.format == HQ_FMT_FP8_BLOCK && p.n % 16 != 0) return HQ_ERR_SHAPE;   // a 16-row item shares one weight-block scale
   if (p.format == HQ_FMT_Q8_0)
     return max_rows > 4 ? launch_q8_cfg<HQ_FMT_Q8_0, 2>(p, n_y_max, max_rows, stream)
                         : launch_q8_cfg<HQ_FMT_Q8_0, 1>(p, n_y_max, max_rows, stream);
   if (p.format == HQ_FMT_Q4_K)
     return max_rows > 4 ? launch_q8_cfg<HQ_FMT_Q4_K, 2>(p, n_y_max, max_rows, stream)
                         : launch_q8_cfg<HQ_FMT_Q4_K, 1>(p, n_y_max, max_rows, stream);
+  // block-FP8: three e4m3 terms per activation, so one column set holds two rows.  More rows would take three
+  // MMAs per block, and the warp-level FP8 MMA is slow enough on this part that the f16 decoder then wins
+  // (measured 2.0 against 3.7 TB/s at 4 rows): the caller sends those there.
+  if (p.format == HQ_FMT_FP8_BLOCK && max_rows <= 2) return launch_q8_cfg<HQ_FMT_FP8_BLOCK, 1>(p, n_y_max, max_rows, stream);
   return HQ_ERR_FORMAT;
 }
 

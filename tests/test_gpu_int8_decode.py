@@ -99,3 +99,24 @@ def test_one_hot_rows_pass_exactly():
         x[np.arange(4), cols] = 1.0
         y = layer.forward_raw(T.to_dev(x, torch.bfloat16, DEV), torch.float32).cpu().numpy()
         assert np.array_equal(y, deq[:, cols].T.astype(np.float32)), fmt
+
+
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+def test_fp8_one_and_two_rows_on_the_fp8_warp_mma(m, x_dtype):
+    # block-FP8 with one or two activation rows: e4m3 weights unconverted, activations as three e4m3 terms;
+    # K = 7168 is too long to stay staged, so the layer's scratch brings in the K split as well
+    n, k = 512, 7168
+    layer, deq, rng = _layer("FP8", n, k, 5)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[0, 100] *= 300.0
+    xd = T.to_dev(x, x_dtype, DEV)
+    y = layer.forward_raw(xd, torch.float32)
+    torch.cuda.synchronize()
+    assert layer.device_status()[0] == 0
+    want = M.dense_forward(xd.to(torch.float32).cpu().numpy(), deq, None)
+    assert T.rel_l2(y.cpu().numpy(), want) <= 2e-3
+    assert torch.equal(y, layer.forward_raw(xd, torch.float32))
+    x[m - 1, 5] = np.nan
+    y2 = layer.forward_raw(T.to_dev(x, torch.float32, DEV), torch.float32).cpu().numpy()
+    assert np.all(~np.isfinite(y2[m - 1]))
