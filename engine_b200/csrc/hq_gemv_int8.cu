@@ -1,5 +1,7 @@
-// Decode-regime mat-vec for GGUF Q8_0 weights (1..8 activation rows per work item), dense and
-// expert-indexed.
+// Decode-regime mat-vec (1..8 activation rows per work item), dense and expert-indexed, for the formats whose
+// codes a narrow warp MMA takes as they lie in memory: GGUF Q8_0 and Q4_K on the integer MMA, block-FP8 (one or
+// two rows) on the FP8 MMA.  The description below follows Q8_0; the Q4_K and FP8 specifics are at their group
+// routines (q4k_group, fp8_group).
 //
 // HBM-bound: every weight byte is read once, straight from the 34-byte blocks {f16 d, int8 q[32]}.
 // What limits such a kernel on the SM side is the number of instructions spent per weight byte, so the
