@@ -32,7 +32,9 @@
 extern "C" {
 #endif
 
-#define HQ_ABI_VERSION 1
+/* 2: adds the caller-scratch linear call, the FP8 row quantizers and FP8-activation calls, and the one-call
+ * MoE layer; every version-1 entry point keeps its signature. */
+#define HQ_ABI_VERSION 2
 
 /* status codes */
 #define HQ_OK 0
