@@ -88,7 +88,7 @@ struct Q8Layout {
   int x_bytes;
   int off_x, off_sx, off_xs, off_red, off_bar, total;   // off_xs: Q4_K sub-block sums [group][column][16]
   int kslices;            // K slices worked by different CTAs (1 = a CTA covers the whole K)
-  int chunks_per_slice;   // stages per slice
+  int slice_k;            // activation columns per slice: a multiple of 256 (the last slice may be shorter)
   int32_t* counters;      // split K: arrivals per item stream (zero between launches)
   float* partials;        // split K: [item][slice][bank][4][32] partial sums
 };
@@ -608,10 +608,8 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
   const int w_end = runs ? min(total, w_begin + per) : total;
   const int w_step = runs ? 1 : R;
   if (r0 >= R || w_begin >= w_end) return;
-  const int nchunk = (p.k + KC - 1) / KC;
-  const int ck_lo = slice * lay.chunks_per_slice;
-  const int ck_hi = min(nchunk, ck_lo + lay.chunks_per_slice);
-  const int k_lo = ck_lo * KC, k_hi = min(p.k, ck_hi * KC);
+  const int k_lo = min(p.k, slice * lay.slice_k), k_hi = min(p.k, k_lo + lay.slice_k);
+  const int nchunk = (k_hi - k_lo + KC - 1) / KC;     // stages of this slice; the last one may be short
   const int kXK = lay.xk;
   const int xk_sub = lay.xk_sub;
   const int n_super = (k_hi - k_lo + kXK - 1) / kXK;
@@ -654,8 +652,8 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
       if (wi.nrows <= 0) continue;
       const int rows_valid = min(RT, p.n - wi.n0);
       const int my_rows = max(0, min(RPP, rows_valid - pw * RPP));
-      for (int chunk = ck_lo; chunk < ck_hi; ++chunk) {
-        const int kc_len = min(KC, p.k - chunk * KC);
+      for (int chunk = 0; chunk < nchunk; ++chunk) {
+        const int kc_len = min(KC, k_hi - (k_lo + chunk * KC));
         const uint32_t bytes = (uint32_t)T::row_bytes(kc_len);
         for (int bank = 0; bank < p.n_banks; ++bank) {
           if (round > 0) {
@@ -667,7 +665,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
           }
           const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(bank == 0 ? p.w : p.w_up) +
                                 (int64_t)wi.expert * p.w_expert_stride + (int64_t)(wi.n0 + pw * RPP) * row_bytes +
-                                (int64_t)chunk * T::SEG;
+                                T::row_bytes(k_lo + chunk * KC);
           if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * (uint32_t)my_rows);
           __syncwarp();
           uint8_t* dst = smem + s * T::STAGE_BYTES + pw * RPP * T::PITCH;
@@ -827,10 +825,12 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
         }
         named_bar_sync(1, kQ8Consumers);
       }
-      const int c0 = k_base / KC, c1 = (k_base + k_len + KC - 1) / KC;
+      // stages of this epoch, counted from the slice's first column (an epoch is a whole number of stages)
+      const int c0 = (k_base - k_lo) / KC, c1 = (k_base - k_lo + k_len + KC - 1) / KC;
       for (int chunk = c0; chunk < c1; ++chunk) {
-        const int ngroups = min(KC, p.k - chunk * KC) / T::GK;   // groups in this stage
-        const uint32_t kx = (uint32_t)(chunk * KC - k_base);  // offset of the stage inside the staged activations
+        const int k_chunk = k_lo + chunk * KC;
+        const int ngroups = min(KC, k_hi - k_chunk) / T::GK;   // groups in this stage
+        const uint32_t kx = (uint32_t)(k_chunk - k_base);      // offset of the stage inside the staged activations
 #pragma unroll
         for (int bank = 0; bank < 2; ++bank) {
           if (bank >= p.n_banks) break;
@@ -839,7 +839,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
           if (FMT == HQ_FMT_FP8_BLOCK) {
             const float* fsc = reinterpret_cast<const float*>(bank == 0 ? p.scales : p.scales_up) +
                                (int64_t)wi.expert * p.scale_expert_stride +
-                               (int64_t)(wi.n0 / 128) * ((p.k + 127) / 128) + chunk * (KC / 128);
+                               (int64_t)(wi.n0 / 128) * ((p.k + 127) / 128) + k_chunk / 128;
 #pragma unroll
             for (int gi = 0; gi < kQ8GroupsPerWarp; ++gi) {
               const int grp = warp + gi * WK;
@@ -934,10 +934,18 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
 #pragma unroll
         for (int b = 0; b < 2; ++b)
           if (b < nb) {
+            // every load of a bank is issued before the first sum needs one (at most eight slices)
+            float part[8][4];
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl)
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                part[sl][i] = sl < S ? __ldcg(all + (sl * nb + b) * 128 + i * 32 + lane) : 0.f;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               float sum = 0.f;
-              for (int sl = 0; sl < S; ++sl) sum += __ldcg(all + (sl * nb + b) * 128 + i * 32 + lane);
+#pragma unroll
+              for (int sl = 0; sl < 8; ++sl) sum += part[sl][i];   // slice order; absent slices add +0
               v[b][i] = sum;
             }
           }
@@ -948,13 +956,19 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
 }
 
 // ---- host launcher -----------------------------------------------------------------------------
-// Split K (up to eight slices of whole stages) when K is too long for a CTA to keep its activations staged
-// beside at least four ring stages: a CTA that covers the whole K would then have to stage them again for
-// every item.  Shorter K stays unsplit -- the meeting of the slice sums costs a few microseconds.
+// Split K when K is too long for a CTA to keep its activations staged beside at least four ring stages: a CTA
+// that covers the whole K would then have to stage them again for every item.  The slices are equal runs of
+// 256-column steps.  Among two to eight slices the plan takes the one with the smallest estimated time, in
+// units of one column streamed for one item: the items of the busiest stream times (columns of a slice + a
+// fixed cost per item), plus the staging of the slice's activations before the first item.  Both constants are
+// fitted to measurements of 14336-column layers with 4096 rows (four slices: 17 us, two: 18 us, seven: 21 us).
+// Shorter K stays unsplit -- the meeting of the slice sums costs a few microseconds.
 struct Q8Split {
-  int kslices, chunks_per_slice;
+  int kslices, slice_k;
   int64_t counter_bytes, bytes;
 };
+constexpr int kQ8ItemCostK = 2048;   // fixed cost of an item, in columns
+constexpr int kQ8StageCost = 2;       // staging a slice's activations, per column, against streaming it for one item
 template <int FMT>
 static int q8_fixed_bytes(int ncols, int xk, int n_banks) {
   using T = I8Traits<FMT>;
@@ -972,10 +986,25 @@ static Q8Split q8_split_plan(int64_t n, int64_t k, int64_t n_y, int n_banks, boo
   const int nchunk = (int)((k + KC - 1) / KC);
   const int64_t items = n_y * ((n + kQ8RT - 1) / kQ8RT);
   sp.kslices = 1;
-  sp.chunks_per_slice = nchunk;
+  sp.slice_k = nchunk * KC;
   if (expert_indexed || nchunk < 2 || q8_ring_stages<FMT>(ncols, nchunk * KC, n_banks) >= 4) return sp;
-  sp.chunks_per_slice = (nchunk + 7) / 8;
-  sp.kslices = (nchunk + sp.chunks_per_slice - 1) / sp.chunks_per_slice;
+  const int sms = sm_count();
+  int64_t best = -1;
+  for (int s = 2; s <= 8; ++s) {
+    const int slice_k = (int)(((k + s - 1) / s + 255) / 256 * 256);
+    const int slices = (int)((k + slice_k - 1) / slice_k);
+    if (slices != s && s != 8) continue;                 // the same plan as a smaller s
+    const bool fits = q8_ring_stages<FMT>(ncols, (slice_k + KC - 1) / KC * KC, n_banks) >= 4;
+    if (!fits && s != 8) continue;                       // eight slices are the fallback whatever they leave
+    const int64_t streams = sms / slices > 0 ? sms / slices : 1;
+    const int64_t busiest = (items + streams - 1) / streams;
+    const int64_t cost = busiest * (slice_k + kQ8ItemCostK) + kQ8StageCost * slice_k;
+    if (best < 0 || cost < best) {
+      best = cost;
+      sp.kslices = slices;
+      sp.slice_k = slice_k;
+    }
+  }
   sp.counter_bytes = 1024;     // one arrival counter per item stream (at most one stream per SM)
   sp.bytes = sp.counter_bytes + items * sp.kslices * n_banks * 512;
   return sp;
@@ -997,10 +1026,10 @@ static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cud
   Q8Split sp = q8_split_plan<FMT>(p.n, p.k, n_y_max, p.n_banks, p.tiles != nullptr, lay.ncols);
   if (sp.kslices > 1 && (p.workspace == nullptr || p.workspace_bytes < sp.bytes)) {
     sp.kslices = 1;                      // no scratch from the caller: every CTA covers the whole K
-    sp.chunks_per_slice = (p.k + T::KC - 1) / T::KC;
+    sp.slice_k = (int)((p.k + T::KC - 1) / T::KC) * T::KC;
   }
   lay.kslices = sp.kslices;
-  lay.chunks_per_slice = sp.chunks_per_slice;
+  lay.slice_k = sp.slice_k;
   if (sp.kslices > 1) {
     lay.counters = reinterpret_cast<int32_t*>(p.workspace);
     lay.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.workspace) + sp.counter_bytes);
@@ -1009,7 +1038,7 @@ static int32_t launch_q8_cfg(const GemvParams& p, int n_y_max, int max_rows, cud
   // K range when it fits -- then a persistent CTA quantizes its activations once), give every remaining byte
   // to the ring.
   const int esz = dtype_size(p.x_dtype);
-  const int k_round = sp.chunks_per_slice * T::KC;
+  const int k_round = (sp.slice_k + T::KC - 1) / T::KC * T::KC;
   const int candidates[3] = {k_round, 8192 < k_round ? 8192 : k_round, 4096 < k_round ? 4096 : k_round};
   for (int c = 0; c < 3; ++c) {
     lay.xk = candidates[c];
