@@ -584,6 +584,445 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
   }
 }
 
+// ================= weights through tensor memory ======================================================
+// Second kernel for 128-token tiles.  The kernel above is bounded by shared-memory bandwidth: per 64-k stage
+// the producers write both operand tiles and the tensor core reads both back.  Here the expanded weights never
+// touch shared memory: a producer thread owns one weight row (one TMEM lane) for a whole stage, expands its 64
+// weights in registers and writes them with tcgen05.st into a ring of A-operand stages in tensor memory; the MMA
+// takes A from tensor memory and only the activation tile B from shared memory.  With a gate and an up bank a
+// tile holds 64 features: lanes 16q..16q+15 of every 32-lane quarter q carry the gate rows, the next 16 lanes
+// the up rows of the same features, so one MMA serves both banks, one accumulator set is enough (two buffers
+// of 128 columns), and the gated activation pairs lanes 16 apart of one epilogue warp.
+//   tensor memory: columns 0..255 two accumulator buffers, 256..511 eight A stages of 32 columns (64 f16)
+//   warps 5..20: four groups of four warps (one per lane quarter); group j takes the stages it = j mod 4 of the
+//   CTA's flattened (tile, k) sequence: expands A, copies the stage's activation rows, arrives on full[s]
+constexpr int kTsACol0 = 256;                 // first tensor-memory column of the A ring
+constexpr int kTsAStageCols = kTileK / 2;
+// 128 tokens per tile.  (256-token tiles -- one accumulator buffer, six stages, an expanded stage serving twice
+// the tokens -- were built and measured slower on every layer tried: 1.17 against 0.99 ms on the Q4_K layer.)
+constexpr int kTsTokens = 128;
+struct TsSmem {
+  static constexpr int NSTAGE = 8;
+  static constexpr int NBUF = 2;
+  static constexpr int B_BYTES = kTsTokens * kTileK * 2;
+  static constexpr int OFF_BAR = NSTAGE * B_BYTES;
+  static constexpr int TOTAL = OFF_BAR + (2 * NSTAGE + 4) * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// raw bytes of one weight row for one 64-k stage
+struct TsRaw {
+  uint4 hdr;        // Q4_K: super-block header
+  uint4 v[4];       // Q4_K: 32 nibble bytes in v[0..1]; MXFP4: two 16-byte blocks in v[0..1]; FP8: 64 codes
+  uint32_t aux0;    // FP8: relative block scale (f32 bits); MXFP4: e8m0 byte of the first block
+  uint32_t aux1;    // MXFP4: e8m0 byte of the second block
+};
+template <int FMT>
+__device__ __forceinline__ void ts_fetch(TsRaw& r, const uint8_t* row_base, const uint8_t* scale_row, const float* rel,
+                                         int k0) {
+  if (FMT == HQ_FMT_Q4_K) {
+    const uint8_t* blk = row_base + 144 * (k0 >> 8);
+    const int c = (k0 & 255) >> 6;
+    r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+    r.v[0] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * c));
+    r.v[1] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * c));
+  } else if (FMT == HQ_FMT_FP8_BLOCK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.v[i] = __ldg(reinterpret_cast<const uint4*>(row_base + k0 + 16 * i));
+    r.aux0 = __float_as_uint(__ldg(rel + k0 / 128));
+  } else {
+    const int blk = k0 >> 5;
+    r.v[0] = __ldg(reinterpret_cast<const uint4*>(row_base + 16 * blk));
+    r.v[1] = __ldg(reinterpret_cast<const uint4*>(row_base + 16 * blk + 16));
+    r.aux0 = __ldg(scale_row + blk);
+    r.aux1 = __ldg(scale_row + blk + 1);
+  }
+}
+// the 32 weights k0 + 32*half .. of the stage as 16 f16 pairs, natural k order
+template <int FMT>
+__device__ __forceinline__ bool ts_expand(const TsRaw& r, int k0, int half, uint32_t (&out)[16]) {
+  bool ok = true;
+  RawA a;
+  uint32_t lo[8], hi[8];
+  if (FMT == HQ_FMT_Q4_K) {
+    a.hdr = r.hdr;
+    a.q = r.v[0];
+    emit_q4_k(a, k0, 2 * half, lo);
+    a.q = r.v[1];
+    emit_q4_k(a, k0, 2 * half + 1, hi);
+  } else if (FMT == HQ_FMT_FP8_BLOCK) {
+    a.aux = r.aux0;
+    a.q = r.v[2 * half];
+    emit_fp8(a, lo);
+    a.q = r.v[2 * half + 1];
+    emit_fp8(a, hi);
+  } else {
+    const uint4 blk = r.v[half];
+    a.aux = half == 0 ? r.aux0 : r.aux1;
+    a.q.x = blk.x; a.q.y = blk.y;
+    ok = emit_mxfp4(a, lo);
+    a.q.x = blk.z; a.q.y = blk.w;
+    ok = emit_mxfp4(a, hi) && ok;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    out[i] = lo[i];
+    out[8 + i] = hi[i];
+  }
+  return ok;
+}
+
+template <int NB>
+__device__ __forceinline__ GgTile ts_tile(const GroupedParams& p, int w, int n_nt) {
+  constexpr int FW = NB == 2 ? 64 : 128;     // features per tile
+  constexpr int TN = kTsTokens;
+  GgTile t;
+  const int tt = w / n_nt;
+  t.n0 = (w - tt * n_nt) * FW;
+  if (p.tiles != nullptr) {
+    t.expert = p.tiles[2 * tt];
+    t.row_start = p.tiles[2 * tt + 1];
+    t.count = min(TN, p.expert_bounds[t.expert + 1] - t.row_start);
+  } else {
+    t.expert = 0;
+    t.row_start = TN * tt;
+    t.count = min(TN, p.m - t.row_start);
+  }
+  return t;
+}
+
+template <int FMT, int NB>
+__global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_ts_kernel(const GroupedParams p) {
+  using L = TsSmem;
+  constexpr int TN = kTsTokens;
+  constexpr int NSTAGE = L::NSTAGE;
+  constexpr int NBUF = L::NBUF;
+  constexpr int FW = NB == 2 ? 64 : 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* empty = full + NSTAGE;
+  uint64_t* acc_full = empty + NSTAGE;     // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_nt = (p.n + FW - 1) / FW;
+  const int n_tt = p.tiles != nullptr ? p.tile_count[0] : (p.m + TN - 1) / TN;
+  const int total = n_tt * n_nt;
+  const int n_ks = p.k / kTileK;
+
+  if (tid == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&full[s], 4);       // the four warps of the group that owns the stage
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== MMA issuer ======================================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(TN);
+      uint32_t spin = kGgSpin;
+      int it = 0, tcount = 0;
+      for (int w = blockIdx.x; w < total; w += gridDim.x, ++tcount) {
+        const int buf = tcount % NBUF;
+        if (tcount >= NBUF) {
+          if (!mbar_wait_backoff(&acc_empty[buf], ((tcount / NBUF) - 1) & 1, spin)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 700 + buf);
+            spin = 1;
+          }
+        }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + (uint32_t)(buf * TN);
+        for (int ks = 0; ks < n_ks; ++ks, ++it) {
+          const int s = it % NSTAGE;
+          if (!mbar_wait_backoff(&full[s], (it / NSTAGE) & 1, spin)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 710 + s);
+            spin = 1;
+          }
+          tc_fence_after();
+          const uint64_t bdesc = make_smem_desc(smem_u32(smem + s * L::B_BYTES));
+          const uint32_t a0 = tmem_base + (uint32_t)(kTsACol0 + kTsAStageCols * s);
+#pragma unroll
+          for (int kk = 0; kk < kTileK / 16; ++kk) {
+            // 16 k per instruction: 8 columns of A in tensor memory, 32 bytes along the swizzled row of B
+            tc_mma_f16_ts(d0, a0 + 8 * kk, bdesc + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);     // A stage and B stage are free once these MMAs have read them
+        }
+        tc_commit(&acc_full[buf]);
+      }
+    }
+    __syncwarp();
+  } else if (warp <= 4) {
+    // =========================== epilogue ========================================
+    const int q = warp & 3;
+    uint32_t spin = kGgSpin;
+    int tcount = 0;
+    const bool interleaved = NB == 1 && p.act.act != HQ_ACT_NONE;
+    const int bank = NB == 2 ? (lane >> 4) : 0;
+    const int frow = NB == 2 ? 16 * q + (lane & 15) : 32 * q + lane;
+    for (int w = blockIdx.x; w < total; w += gridDim.x, ++tcount) {
+      const GgTile t = ts_tile<NB>(p, w, n_nt);
+      const int buf = tcount % NBUF;
+      if (!mbar_wait_backoff(&acc_full[buf], (tcount / NBUF) & 1, spin)) {
+        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 800 + buf);
+        spin = 1;
+      }
+      tc_fence_after();
+      const int n = t.n0 + frow;
+      const bool n_ok = n < p.n;
+      float bias = 0.f;
+      const void* bptr = bank == 0 ? p.bias : p.bias_up;
+      if (n_ok && bptr != nullptr) bias = load_as_float(bptr, p.bias_dtype, (int64_t)t.expert * p.n + n);
+      float sc = 1.f;
+      if (FMT == HQ_FMT_FP8_BLOCK) {
+        const float* ts = bank == 0 ? p.fp8_tile_scale : p.fp8_tile_scale_up;
+        sc = n_ok ? __ldg(ts + (int64_t)t.expert * p.fp8_nb + n / 128) : 0.f;
+      }
+      const int64_t out_n = interleaved ? (n >> 1) : n;
+      const bool writer = n_ok && (NB == 2 ? lane < 16 : (!interleaved || (n & 1) == 0));
+      const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * TN);
+      const int* __restrict__ yrows = p.y_rows;
+      auto row_of = [&](int cc) -> int {
+        const int col = 32 * cc + lane;
+        if (cc >= TN / 32 || col >= t.count) return -1;
+        const int sp = t.row_start + col;
+        return yrows != nullptr ? __ldg(yrows + sp) : sp;
+      };
+      const int esz = dtype_size(p.y_dtype);
+      char* const ybase = reinterpret_cast<char*>(p.y) + out_n * esz;
+      const int64_t ystride_b = (int64_t)p.y_stride * esz;
+      int myrow = row_of(0);
+#pragma unroll 1
+      for (int cc = 0; cc < TN / 32; ++cc) {
+        if (32 * cc >= t.count) break;
+        uint32_t v0[32];
+        tmem_ld32(taddr + 32 * cc, v0);
+        const int nextrow = row_of(cc + 1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float r = fmaf(__uint_as_float(v0[j]), sc, bias);
+          if (NB == 2) {
+            const float partner = __shfl_xor_sync(0xffffffffu, r, 16);   // the up row of this gate row
+            r = gg_gated(r, partner, p.act);
+          } else if (interleaved) {
+            const float partner = __shfl_xor_sync(0xffffffffu, r, 1);
+            r = gg_gated(r, partner, p.act);
+          }
+          v0[j] = __float_as_uint(r);
+        }
+        auto store_group = [&](auto cvt) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int orow = __shfl_sync(0xffffffffu, myrow, j);
+            if (writer && orow >= 0) {
+              using T = decltype(cvt(0.f));
+              *reinterpret_cast<T*>(ybase + orow * ystride_b) = cvt(__uint_as_float(v0[j]));
+            }
+          }
+        };
+        if (p.y_dtype == HQ_DT_BF16) store_group([](float f) { return __float2bfloat16_rn(f); });
+        else if (p.y_dtype == HQ_DT_F16) store_group([](float f) { return __float2half_rn(f); });
+        else store_group([](float f) { return f; });
+        myrow = nextrow;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  } else {
+    // =========================== producers ========================================
+    const int grp = (warp - 5) >> 2;              // this group's stages: it = grp (mod 4)
+    const int q = warp & 3;                       // tensor-memory lane quarter this warp may write
+    const int gt = ((warp - 5) & 3) * 32 + lane;  // thread within the group, for the activation copy
+    const int bank = NB == 2 ? (lane >> 4) : 0;
+    const int frow = NB == 2 ? 16 * q + (lane & 15) : 32 * q + lane;   // feature within the tile
+    const int bchunk = gt & 7, brow0 = gt >> 3;   // activation rows brow0 + 16 j, 16-byte chunk bchunk of each
+    constexpr int BR = TN / 16;                   // activation chunks a thread copies per stage
+    // byte offset of this thread's first chunk inside a B tile; the others lie 2048 bytes (16 rows) apart
+    const uint32_t bswz0 = swz(brow0, bchunk);
+    const uint32_t x_stride16 = (uint32_t)(p.x_stride >> 3);   // activation row pitch in 16-byte units
+    uint32_t spin = kGgSpin;
+
+    struct Cursor {
+      int w, ks, it;
+      bool n_ok;
+      const uint8_t* wrow;
+      const uint8_t* srow;
+      const float* rel;
+      uint32_t boff[BR];    // 16-byte index of each copied chunk (at k = 0) in the activations, ~0 = no row
+    };
+    auto open_tile = [&](Cursor& c) {
+      const GgTile t = ts_tile<NB>(p, c.w, n_nt);
+      const int n = t.n0 + frow;
+      c.n_ok = n < p.n;
+      const int64_t wrow = (int64_t)t.expert * p.n + (c.n_ok ? n : 0);
+      c.wrow = reinterpret_cast<const uint8_t*>(bank == 0 ? p.w : p.w_up) + wrow * p.w_row_bytes;
+      c.srow = nullptr;
+      c.rel = nullptr;
+      if (FMT == HQ_FMT_MXFP4)
+        c.srow = reinterpret_cast<const uint8_t*>(bank == 0 ? p.scales : p.scales_up) + wrow * (p.k / 32);
+      if (FMT == HQ_FMT_FP8_BLOCK)
+        c.rel = (bank == 0 ? p.fp8_rel_scale : p.fp8_rel_scale_up) +
+                ((int64_t)t.expert * p.fp8_nb + (c.n_ok ? n : 0) / 128) * p.fp8_kb;
+#pragma unroll
+      for (int j = 0; j < BR; ++j) {
+        const int row = brow0 + 16 * j;
+        c.boff[j] = 0xFFFFFFFFu;
+        if (row < t.count) {
+          const int sp = t.row_start + row;
+          c.boff[j] = (uint32_t)(p.x_rows ? p.x_rows[sp] : sp) * x_stride16 + (uint32_t)bchunk;
+        }
+      }
+    };
+    // four stages on: returns false past the CTA's last tile
+    auto advance = [&](Cursor& c) -> bool {
+      c.it += 4;
+      c.ks += 4;
+      bool moved = false;
+      while (c.ks >= n_ks && c.w < total) {
+        c.ks -= n_ks;
+        c.w += gridDim.x;
+        moved = true;
+      }
+      if (c.w >= total) return false;
+      if (moved) open_tile(c);
+      return true;
+    };
+    int waited = NSTAGE - 1;                  // stages up to this index are known to be free
+    auto ensure_empty = [&](int j) {
+      if (j > waited) {
+        if (!mbar_wait(&empty[j % NSTAGE], ((j / NSTAGE) - 1) & 1, spin)) {
+          if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 900 + j % NSTAGE);
+          spin = 1;
+        }
+        waited = j;
+      }
+    };
+    auto copy_b = [&](const Cursor& c) {
+      const uint32_t dst0 = smem_u32(smem + (c.it % NSTAGE) * L::B_BYTES) + bswz0;
+      const uint32_t kofs = (uint32_t)c.ks * (kTileK / 8);
+      const uint4* x16 = reinterpret_cast<const uint4*>(p.x);
+#pragma unroll
+      for (int j = 0; j < BR; ++j) {
+        const bool ok = c.boff[j] != 0xFFFFFFFFu;
+        const uint4* src = x16 + (ok ? c.boff[j] + kofs : 0u);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + 2048u * j), "l"(src), "r"(ok ? 16 : 0)
+                     : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto fetch = [&](const Cursor& c, TsRaw& r) {
+      if (c.n_ok) ts_fetch<FMT>(r, c.wrow, c.srow, c.rel, c.ks * kTileK);
+    };
+
+    Cursor cur;
+    cur.w = blockIdx.x;
+    cur.ks = grp - 4;
+    cur.it = grp - 4;
+    bool live = false;
+    if (cur.w < total) {
+      // the first stage of this group: ks = grp may already lie in a later tile when K is very short
+      cur.ks = grp;
+      cur.it = grp;
+      while (cur.ks >= n_ks && cur.w < total) {
+        cur.ks -= n_ks;
+        cur.w += gridDim.x;
+      }
+      live = cur.w < total;
+      if (live) open_tile(cur);
+    }
+    TsRaw ra0, ra1;
+    if (live) {
+      fetch(cur, ra0);
+      copy_b(cur);
+    }
+    // One stage: the next own stage's weight loads go out first; this stage is expanded into its tensor-memory
+    // slot (known to be free since its activation copies were issued) and handed over; only then does the group
+    // wait for the slot of its next stage and start that stage's activation copies -- by then the MMA has had a
+    // whole step to drain the slot, and the copies have the next expansion to land.
+    auto step = [&](TsRaw& use, TsRaw& ld) {
+      Cursor nxt = cur;
+      const bool next_live = advance(nxt);
+      if (next_live) fetch(nxt, ld);
+      const int s = cur.it % NSTAGE;
+      const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(kTsACol0 + kTsAStageCols * s);
+      const int k0 = cur.ks * kTileK;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[16];
+        if (cur.n_ok) {
+          if (!ts_expand<FMT>(use, k0, half, v)) report_status(p.status, HQ_DEV_BAD_INDEX, 600);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0u;
+        }
+        tmem_st16(taddr + 16 * half, v);
+      }
+      tmem_st_wait();
+      asm volatile("cp.async.wait_group 0;" ::: "memory");   // this stage's activation copies, issued a step ago
+      fence_proxy_async_smem();     // cp.async writes -> visible to the tensor core (async proxy)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[s]);
+      if (next_live) {
+        ensure_empty(nxt.it);
+        copy_b(nxt);
+      }
+      cur = nxt;
+      live = next_live;
+    };
+    while (live) {
+      step(ra0, ra1);
+      if (!live) break;
+      step(ra1, ra0);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ---- block-FP8 scale preparation (once per layer) -------------------------------------
 // scales [groups = E*NB][KB] -> tile_scale[group] = max_kb scale, rel_scale[group][kb] = scale / tile_scale.
 __global__ void __launch_bounds__(128) fp8_scale_prepare_kernel(const float* __restrict__ scales, int64_t n_groups,
@@ -632,9 +1071,36 @@ static int32_t launch_gg(const GroupedParams& p, int max_tiles, cudaStream_t str
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
+template <int FMT, int NB>
+static int32_t launch_gg_ts(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
+  using L = TsSmem;
+  constexpr int TN = kTsTokens;
+  static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
+  static_assert(kTsACol0 + kTsAStageCols * L::NSTAGE <= 512 && L::NBUF * TN <= kTsACol0, "tensor memory budget");
+  auto kern = grouped_gemm_ts_kernel<FMT, NB>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
+  if (dev < 64 && !attr_done[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return HQ_ERR_CUDA;
+    attr_done[dev] = true;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  constexpr int FW = NB == 2 ? 64 : 128;
+  const int64_t items = (int64_t)max_tiles * ((p.n + FW - 1) / FW);
+  const int64_t grid = items < sms ? items : sms;
+  if (grid <= 0) return HQ_OK;
+  kern<<<(unsigned)grid, kGgThreads, L::TOTAL, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
 template <int FMT>
 static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
   const bool two = p.w_up != nullptr;
+  if (p.tile_rows == 128 && p.weights_in_tmem)
+    return two ? launch_gg_ts<FMT, 2>(p, max_tiles, stream) : launch_gg_ts<FMT, 1>(p, max_tiles, stream);
   if (p.tile_rows == 256) {
     return two ? launch_gg<FMT, 2, 256>(p, max_tiles, stream) : launch_gg<FMT, 1, 256>(p, max_tiles, stream);
   }

@@ -69,6 +69,7 @@ struct GroupedParams {
   const int32_t* tiles;         // [n_tiles][2] = (expert, first sorted row), tiles of <= tile_rows rows
   const int32_t* tile_count;    // device word holding n_tiles
   int tile_rows;                // 128 or 256 tokens per tile
+  bool weights_in_tmem;         // 128-token tiles only: take the kernel that expands the weights into tensor memory
   const int32_t* expert_bounds;
   const int32_t* x_rows;        // sorted row -> activation row (nullptr = identity)
   const int32_t* y_rows;        // sorted row -> output row (nullptr = identity)
