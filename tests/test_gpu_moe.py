@@ -326,3 +326,26 @@ def test_tensor_path_wide_token_tiles(tensor_path):
     assert T.rel_l2(got, want) <= 2e-3
     got, want = _moe_case("FP8", 450, 8, 4, 512, 256, False, L.ACT_SWIGLU, 33)
     assert T.rel_l2(got, want) <= 2e-3
+
+
+def test_tensor_path_short_k_and_partial_feature_tiles(tensor_path):
+    # the kernel that expands the weights into tensor memory, at its edges: K of one, three and five 64-column
+    # stages (fewer stages than producer groups: a group's next stage lies in a later tile), 64-feature gate/up
+    # tiles with a partly filled last tile, a 128-lane tile with 64 valid rows, token tiles with a few rows
+    got, want = _moe_case("MXFP4", 300, 8, 4, 64, 192, True, L.ACT_GPTOSS, 41, limit=7.0)
+    assert T.rel_l2(got, want) <= 2e-3
+    got, want = _moe_case("MXFP4", 131, 4, 2, 320, 64, True, L.ACT_GPTOSS, 42, limit=7.0)
+    assert T.rel_l2(got, want) <= 2e-3
+    got, want = _moe_case("Q4_K", 260, 4, 2, 256, 256, False, L.ACT_SWIGLU, 43)
+    assert T.rel_l2(got, want) <= 1e-3
+    for fmt, n, k, m in [("MXFP4", 72, 64, 300), ("MXFP4", 200, 192, 129), ("Q4_K", 72, 256, 260)]:
+        rng = T.rng_for(5, 1000 + n + k + m)
+        arrays, deq = T.make_weight(fmt, rng, n, k)
+        layer = T.make_layer(fmt, arrays, k, DEV)
+        xd = T.to_dev(rng.standard_normal((m, k)).astype(np.float32), torch.bfloat16, DEV)
+        got = layer.forward_raw(xd, torch.float32)
+        torch.cuda.synchronize()
+        assert layer.device_status()[0] == 0, layer.device_status()
+        want = M.dense_forward(xd.to(torch.float32).cpu().numpy(), deq, None)
+        assert T.rel_l2(got.cpu().numpy(), want) <= TOL[fmt], (fmt, n, k, m)
+        assert torch.equal(got, layer.forward_raw(xd, torch.float32))
