@@ -20,6 +20,9 @@
 //
 // Tensor-core bound for large token counts; algorithmic flops per launch =
 // 2 * rows * N * K (* 2 with a gate and an up bank).
+//
+// A second kernel further down (grouped_gemm_ts_kernel) does the same product with the expanded weights written
+// to tensor memory instead of shared memory; GroupedParams::weights_in_tmem selects it for 128-token tiles.
 #include "hq_common.cuh"
 #include "hq_kernels.h"
 
