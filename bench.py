@@ -497,6 +497,14 @@ def router_config(hq, cfg):
     return hq.MoeRouterTopKConfig(cfg["k"], L.SCORE_RAW, L.WEIGHT_SOFTMAX, False)
 
 
+def gemm_kernel_name(cfg, tokens):
+    """The expert GEMM kernel the library's dispatch takes for this layer (mirrors hq_moe_gather_forward's rule:
+    MXFP4 always, Q4_K below 192 rows per expert, expand the weights into tensor memory)."""
+    rows_per_expert = tokens * cfg["k"] / cfg["e"]
+    ts = cfg["fmt"] == "MXFP4" or (cfg["fmt"] == "Q4_K" and rows_per_expert < 192)
+    return ("hq::grouped_gemm_ts_kernel" if ts else "hq::grouped_gemm_kernel") + " (gate/up + down)"
+
+
 def moe_flops(cfg, tokens, with_shared=False):
     per_expert = 2.0 * 3 * cfg["h"] * cfg["i"]
     return tokens * per_expert * (cfg["k"] + (1 if with_shared and cfg.get("shared") else 0))
@@ -671,7 +679,7 @@ def run_moe(args):
             roof = {"bound": "tensor", "achieved": round(ach, 1), "peak": peak_tf, "unit": "TFLOP/s",
                     "frac": round(ach / peak_tf, 4), "traffic": None,
                     "peak_kind": "measured" if peaks else "fallback",
-                    "kernel": "hq::grouped_gemm_kernel (gate/up + down)", "launch_ms_sum": round(gemm_ms, 4),
+                    "kernel": gemm_kernel_name(cfg, t_global), "launch_ms_sum": round(gemm_ms, 4),
                     "note": "f16 operands: fraction of the measured dense 16-bit tensor peak"}
             if cfg.get("act_fp8"):
                 # FP8 x FP8 MMA: still reported against the measured 16-bit peak (the only tensor peak the peaks
