@@ -66,3 +66,29 @@ def test_package_has_no_cpu_fallback():
         for f in files:
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 assert "oracle" not in open(os.path.join(dirpath, f)).read(), f
+
+
+def test_split_k_scratch_plan_is_host_arithmetic(lib):
+    # the scratch a dense decode call asks for: nothing while the activations of the whole K stay staged, else
+    # 1024 bytes of arrival counters + 512 bytes per (16-row item, K slice) with two to eight slices
+    from engine_b200 import _lib as L
+
+    def need(fmt, n, k, m):
+        w = L.HqWeight(fmt, 1, n, k, 16, 0, 0, 0, 0)
+        return lib.hq_linear_workspace_bytes(C.byref(w), m)
+
+    assert need(L.FMT_Q8_0, 4096, 4096, 1) == 0
+    assert need(L.FMT_Q8_0, 128256, 4096, 8) == 0
+    for n in (1000, 4096):
+        for m in (1, 4, 8):
+            b = need(L.FMT_Q8_0, n, 14336, m)
+            items = (n + 15) // 16
+            assert b > 1024 and (b - 1024) % (items * 512) == 0, (n, m, b)
+            assert 2 <= (b - 1024) // (items * 512) <= 8
+            assert b == need(L.FMT_Q8_0, n, 14336, m)
+    # more than eight rows are served as several row groups of one launch: one item per (row group, 16 rows)
+    b = need(L.FMT_Q8_0, 4096, 14336, 11)
+    assert b > 1024 and (b - 1024) % (2 * 256 * 512) == 0
+    assert need(L.FMT_Q4_K, 4096, 14336, 4) > 1024
+    bad = L.HqWeight(L.FMT_Q8_0, 1, 64, 100, 16, 0, 0, 0, 0)
+    assert lib.hq_linear_workspace_bytes(C.byref(bad), 1) == 0
