@@ -15,8 +15,9 @@ DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 SCORE_RAW, SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1, 2
 WEIGHT_SCORE, WEIGHT_SOFTMAX, WEIGHT_SIGMOID = 0, 1, 2
 ACT_NONE, ACT_SWIGLU, ACT_GPTOSS = 0, 1, 2
+DEV_OK, DEV_WAIT_TIMEOUT, DEV_BAD_INDEX, DEV_SCALE_RANGE, DEV_F16_RANGE = 0, 1, 2, 3, 4
 ROWS_PER_TOKEN, ROWS_PER_SLOT, ROWS_SORTED = 0, 1, 2
-CFG_MOE_TENSOR_MIN_ROWS, CFG_DENSE_TENSOR_MIN_ROWS = 0, 1
+CFG_MOE_TENSOR_MIN_ROWS, CFG_DENSE_TENSOR_MIN_ROWS, CFG_SPIN_LIMIT, CFG_TEST_SKIP_PRODUCER = 0, 1, 2, 3
 
 
 class HqWeight(C.Structure):
@@ -37,6 +38,12 @@ class HqActArgs(C.Structure):
     _fields_ = [("act", C.c_int32), ("has_limit", C.c_int32), ("limit", C.c_float), ("alpha", C.c_float)]
 
 
+class HqEpLayout(C.Structure):
+    _fields_ = [("world", C.c_int32), ("top_k", C.c_int32), ("experts_per_rank", C.c_int32), ("capacity", C.c_int32),
+                ("pad_rows", C.c_int32), ("rows_per_peer", C.c_int32), ("fp8", C.c_int32), ("wire_dtype", C.c_int32),
+                ("hidden", C.c_int64), ("row_bytes", C.c_int64), ("message_bytes", C.c_int64)]
+
+
 class HqMoeLayer(C.Structure):
     _fields_ = [("gate", C.POINTER(HqWeight)), ("up", C.POINTER(HqWeight)), ("down", C.POINTER(HqWeight)),
                 ("act", HqActArgs), ("router", HqRouterArgs)]
@@ -51,10 +58,17 @@ SIGNATURES = {
     "hq_status_read": (_I32, [_P, C.POINTER(_I32 * 4), _P]),
     "hq_linear_forward": (_I32, [C.POINTER(HqWeight), _P, _I32, _I64, _P, _I32, _I64, _I64, _P, _P]),
     "hq_fp8_quant_rows": (_I32, [_P, _I32, _I64, _P, _I64, _I64, _P, _P, _P]),
+    "hq_fp8_quant_rows_n": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _P, _P, _P]),
+    "hq_fp8_gather_rows": (_I32, [_P, _I64, _P, _I64, _P, _P, _I64, _I64, _P, _P, _P]),
+    "hq_ep_layout_init": (_I32, [C.POINTER(HqEpLayout), _I32, _I32, _I32, _I32, _I64, _I32, _I32]),
+    "hq_ep_pack": (_I32, [C.POINTER(HqEpLayout), _P, _I32, _P, _P, _I64, _P, _P, _P]),
+    "hq_ep_unpack_meta": (_I32, [C.POINTER(HqEpLayout), _P, _P, _P, _P]),
     "hq_fp8_gated_quant_rows": (_I32, [_P, _I32, _I64, _I64, C.POINTER(HqActArgs), _P, _P, _P]),
     "hq_fp8_linear_forward": (_I32, [C.POINTER(HqWeight), _P, _P, _I64, _P, _I32, _I64, _P, _P]),
     "hq_moe_fp8_gather_forward": (_I32, [C.POINTER(HqWeight), _P, _P, _I64, _I32, _P, _P, _P, _P, _I32, _I64, _I32,
                                          _P, _P]),
+    "hq_moe_fp8_gate_up_forward": (_I32, [C.POINTER(HqWeight), C.POINTER(HqWeight), C.POINTER(HqActArgs), _P, _P, _I64,
+                                          _I32, _P, _P, _P, _P, _P]),
     "hq_moe_layer_workspace_bytes": (_I64, [C.POINTER(HqMoeLayer), _I64, _I32]),
     "hq_moe_layer_forward": (_I32, [C.POINTER(HqMoeLayer), _P, _I32, _P, _I32, _I64, _P, _P, _I32, _P, _I64, _P, _P]),
     "hq_linear_workspace_bytes": (_I64, [C.POINTER(HqWeight), _I64]),
@@ -74,6 +88,8 @@ SIGNATURES = {
     "hq_config_set": (_I32, [_I32, _I64]),
     "hq_config_get": (_I64, [_I32]),
     "hq_convert": (_I32, [_P, _I32, _P, _I32, _I64, _P]),
+    "hq_convert_status": (_I32, [_P, _I32, _P, _I32, _I64, _P, _P]),
+    "hq_probe_tensor_peak": (_I32, [_I32, _I32, _I32, _P, C.POINTER(C.c_double), _P]),
     "hq_gated_act": (_I32, [_P, _P, _I32, _I64, _I32, C.POINTER(HqActArgs), _P, _P]),
 }
 

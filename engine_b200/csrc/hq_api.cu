@@ -46,7 +46,7 @@ int32_t check_weight(const hq_weight* w) {
   return HQ_OK;
 }
 
-int64_t g_cfg[2] = {8, 9};
+int64_t g_cfg[4] = {8, 9, 1 << 22, 0};
 
 void fill_grouped(GroupedParams& g, const hq_weight* w, const hq_weight* w_up) {
   g.format = w->format;
@@ -119,12 +119,13 @@ const char* hq_error_string(int32_t code) {
 }
 
 int32_t hq_config_set(int32_t key, int64_t value) {
-  if (key < 0 || key > 1 || value < 0) return HQ_ERR_FORMAT;
+  if (key < 0 || key > 3 || value < 0) return HQ_ERR_FORMAT;
+  if (key == HQ_CFG_SPIN_LIMIT && (value < 1 || value > (1ll << 31) - 1)) return HQ_ERR_FORMAT;
   g_cfg[key] = value;
   return HQ_OK;
 }
 
-int64_t hq_config_get(int32_t key) { return (key < 0 || key > 1) ? -1 : g_cfg[key]; }
+int64_t hq_config_get(int32_t key) { return (key < 0 || key > 3) ? -1 : g_cfg[key]; }
 
 int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* stream) {
   if (status_dev == nullptr || out_host == nullptr) return HQ_ERR_NULL;
@@ -316,6 +317,8 @@ static void fill_fp8_native(Fp8GroupedParams& g, const hq_weight* w) {
   g.fp8_kb = (int)((w->k + 127) / 128);
   g.bias = w->bias;
   g.bias_dtype = w->bias_dtype;
+  g.spin_limit = (uint32_t)g_cfg[HQ_CFG_SPIN_LIMIT];
+  g.test_skip_producer = (int)g_cfg[HQ_CFG_TEST_SKIP_PRODUCER];
 }
 
 int32_t hq_fp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,
@@ -325,7 +328,90 @@ int32_t hq_fp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, cons
   if (x == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
   if (!valid_dtype(x_dtype)) return HQ_ERR_FORMAT;
   if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
-  return launch_fp8_quant_rows(x, x_dtype, x_stride, row_map, n_rows, k, codes, scales, (cudaStream_t)stream);
+  return launch_fp8_quant_rows(x, x_dtype, x_stride, row_map, nullptr, n_rows, k, codes, scales, (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_quant_rows_n(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map,
+                            const int32_t* n_valid_dev, int64_t n_rows, int64_t k, uint8_t* codes, float* scales,
+                            void* stream) {
+  if (n_rows < 0 || k < 128 || k % 128 != 0 || x_stride < k) return HQ_ERR_SHAPE;
+  if (n_rows == 0) return HQ_OK;
+  if (x == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(x_dtype)) return HQ_ERR_FORMAT;
+  if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
+  return launch_fp8_quant_rows(x, x_dtype, x_stride, row_map, n_valid_dev, n_rows, k, codes, scales,
+                               (cudaStream_t)stream);
+}
+
+int32_t hq_fp8_gather_rows(const uint8_t* src_codes, int64_t src_code_stride, const float* src_scales,
+                           int64_t src_scale_stride_bytes, const int32_t* row_map, const int32_t* n_valid_dev,
+                           int64_t n_rows, int64_t k, uint8_t* codes, float* scales, void* stream) {
+  if (n_rows < 0 || k < 128 || k % 128 != 0 || src_code_stride < k || src_scale_stride_bytes < k / 32)
+    return HQ_ERR_SHAPE;
+  if (n_rows == 0) return HQ_OK;
+  if (src_codes == nullptr || src_scales == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
+  if (!aligned16(src_codes) || !aligned16(codes) || src_code_stride % 16 != 0 || src_scale_stride_bytes % 4 != 0 ||
+      (reinterpret_cast<uintptr_t>(src_scales) & 3u) != 0)
+    return HQ_ERR_ALIGN;
+  return launch_fp8_gather_rows(src_codes, src_code_stride, src_scales, src_scale_stride_bytes, row_map, n_valid_dev,
+                                n_rows, k, codes, scales, (cudaStream_t)stream);
+}
+
+// ---- expert-parallel exchange helpers ------------------------------------------------------------------
+int32_t hq_ep_layout_init(hq_ep_layout* l, int32_t world, int32_t top_k, int32_t experts_per_rank, int32_t capacity,
+                          int64_t hidden, int32_t wire_dtype, int32_t fp8) {
+  if (l == nullptr) return HQ_ERR_NULL;
+  if (world < 1 || world > 64 || top_k < 1 || top_k > 64 || experts_per_rank < 1 || capacity < 1 ||
+      capacity > (1 << 24) || hidden < 8)
+    return HQ_ERR_SHAPE;
+  if (fp8 ? (hidden % 512 != 0) : (hidden % 8 != 0)) return HQ_ERR_SHAPE;
+  if (!fp8 && wire_dtype != HQ_DT_F16 && wire_dtype != HQ_DT_BF16) return HQ_ERR_FORMAT;
+  l->world = world;
+  l->top_k = top_k;
+  l->experts_per_rank = experts_per_rank;
+  l->capacity = capacity;
+  l->fp8 = fp8 ? 1 : 0;
+  l->wire_dtype = wire_dtype;
+  l->hidden = hidden;
+  l->row_bytes = fp8 ? hidden + hidden / 128 * 4 : hidden * 2;
+  const int64_t meta = (int64_t)capacity * top_k * 8;
+  l->pad_rows = (int32_t)((meta + l->row_bytes - 1) / l->row_bytes);
+  l->rows_per_peer = capacity + l->pad_rows;
+  l->message_bytes = (int64_t)l->rows_per_peer * l->row_bytes;
+  return HQ_OK;
+}
+
+static int32_t check_ep_layout(const hq_ep_layout* l) {
+  if (l == nullptr) return HQ_ERR_NULL;
+  hq_ep_layout ref;
+  const int32_t rc = hq_ep_layout_init(&ref, l->world, l->top_k, l->experts_per_rank, l->capacity, l->hidden,
+                                       l->wire_dtype, l->fp8);
+  if (rc != HQ_OK) return rc;
+  if (ref.row_bytes != l->row_bytes || ref.pad_rows != l->pad_rows || ref.rows_per_peer != l->rows_per_peer ||
+      ref.message_bytes != l->message_bytes)
+    return HQ_ERR_SHAPE;
+  return HQ_OK;
+}
+
+int32_t hq_ep_pack(const hq_ep_layout* l, const void* x, int32_t x_dtype, const uint32_t* ids, const float* weights,
+                   int64_t n_tokens, void* send, int32_t* back_map, void* stream) {
+  int32_t rc = check_ep_layout(l);
+  if (rc != HQ_OK) return rc;
+  if (n_tokens < 0 || n_tokens > l->capacity) return HQ_ERR_SHAPE;
+  if (send == nullptr) return HQ_ERR_NULL;
+  if (n_tokens > 0 && (x == nullptr || ids == nullptr || weights == nullptr || back_map == nullptr)) return HQ_ERR_NULL;
+  if (!valid_dtype(x_dtype)) return HQ_ERR_FORMAT;
+  if (!aligned16(x) || !aligned16(send)) return HQ_ERR_ALIGN;
+  return launch_ep_pack(*l, x, x_dtype, ids, weights, n_tokens, send, back_map, (cudaStream_t)stream);
+}
+
+int32_t hq_ep_unpack_meta(const hq_ep_layout* l, const void* recv, uint32_t* ids_out, float* weights_out,
+                          void* stream) {
+  int32_t rc = check_ep_layout(l);
+  if (rc != HQ_OK) return rc;
+  if (recv == nullptr || ids_out == nullptr || weights_out == nullptr) return HQ_ERR_NULL;
+  if (!aligned16(recv)) return HQ_ERR_ALIGN;
+  return launch_ep_unpack_meta(*l, recv, ids_out, weights_out, (cudaStream_t)stream);
 }
 
 int32_t hq_fp8_gated_quant_rows(const void* gate_up, int32_t dtype, int64_t n_rows, int64_t width,
@@ -353,35 +439,62 @@ int32_t hq_fp8_linear_forward(const hq_weight* w, const uint8_t* x_codes, const 
   g.xq = x_codes; g.xs = x_scales; g.n_rows = m;
   g.y = y; g.y_dtype = y_dtype; g.y_stride = y_stride;
   g.status = status_dev;
-  return launch_fp8_grouped(g, (int)((m + 127) / 128), (cudaStream_t)stream);
+  return launch_fp8_grouped(g, (cudaStream_t)stream);
 }
 
 int32_t hq_moe_fp8_gather_forward(const hq_weight* w, const uint8_t* x_codes, const float* x_scales,
                                   int64_t n_tokens, int32_t top_k, const int32_t* expert_bounds,
                                   const int32_t* sorted_assign, const void* workspace, void* out, int32_t out_dtype,
                                   int64_t out_stride, int32_t out_layout, int32_t* status_dev, void* stream) {
+  (void)workspace;   // the kernel cuts its token tiles from expert_bounds; the tile lists are not read any more
   int32_t rc = check_fp8_native(w);
   if (rc != HQ_OK) return rc;
   if (n_tokens < 0 || top_k < 1 || out_stride < w->n) return HQ_ERR_SHAPE;
   if (n_tokens == 0) return HQ_OK;
-  if (x_codes == nullptr || x_scales == nullptr || out == nullptr || expert_bounds == nullptr ||
-      sorted_assign == nullptr || workspace == nullptr)
-    return HQ_ERR_NULL;
+  if (x_codes == nullptr || x_scales == nullptr || out == nullptr || expert_bounds == nullptr) return HQ_ERR_NULL;
+  if (out_layout == HQ_ROWS_PER_SLOT && sorted_assign == nullptr) return HQ_ERR_NULL;
   if (!valid_dtype(out_dtype) || (out_layout != HQ_ROWS_PER_SLOT && out_layout != HQ_ROWS_SORTED))
     return HQ_ERR_FORMAT;
   if (!aligned16(x_codes) || !aligned16(x_scales)) return HQ_ERR_ALIGN;
-  const DispatchLayout l = dispatch_layout(n_tokens, top_k, w->n_experts);
-  const int32_t* ws = (const int32_t*)workspace;
   Fp8GroupedParams g{};
   fill_fp8_native(g, w);
   g.xq = x_codes; g.xs = x_scales; g.n_rows = n_tokens * top_k;
   g.y = out; g.y_dtype = out_dtype; g.y_stride = out_stride;
-  g.tiles = ws + l.off_tiles128;
-  g.tile_count = ws + 1;
   g.expert_bounds = expert_bounds;
   g.y_rows = out_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr;
   g.status = status_dev;
-  return launch_fp8_grouped(g, (int)l.max_tiles128, (cudaStream_t)stream);
+  return launch_fp8_grouped(g, (cudaStream_t)stream);
+}
+
+int32_t hq_moe_fp8_gate_up_forward(const hq_weight* w_gate, const hq_weight* w_up, const hq_act_args* act,
+                                   const uint8_t* x_codes, const float* x_scales, int64_t n_tokens, int32_t top_k,
+                                   const int32_t* expert_bounds, uint8_t* h_codes, float* h_scales,
+                                   int32_t* status_dev, void* stream) {
+  int32_t rc = check_fp8_native(w_gate);
+  if (rc == HQ_OK) rc = check_fp8_native(w_up);
+  if (rc != HQ_OK) return rc;
+  if (w_up->n != w_gate->n || w_up->k != w_gate->k || w_up->n_experts != w_gate->n_experts) return HQ_ERR_SHAPE;
+  if (act == nullptr) return HQ_ERR_NULL;
+  if (act->act != HQ_ACT_SWIGLU && act->act != HQ_ACT_GPTOSS) return HQ_ERR_FORMAT;
+  if (n_tokens < 0 || top_k < 1) return HQ_ERR_SHAPE;
+  if (n_tokens == 0) return HQ_OK;
+  if (x_codes == nullptr || x_scales == nullptr || h_codes == nullptr || h_scales == nullptr ||
+      expert_bounds == nullptr)
+    return HQ_ERR_NULL;
+  if (!aligned16(x_codes) || !aligned16(x_scales) || !aligned16(h_codes)) return HQ_ERR_ALIGN;
+  if (w_gate->bias != nullptr && w_up->bias != nullptr && w_gate->bias_dtype != w_up->bias_dtype) return HQ_ERR_FORMAT;
+  Fp8GroupedParams g{};
+  fill_fp8_native(g, w_gate);
+  g.w_up = w_up->data;
+  g.w_up_scales = (const float*)w_up->scales;
+  g.bias_up = w_up->bias;
+  if (g.bias == nullptr) g.bias_dtype = w_up->bias_dtype;
+  g.xq = x_codes; g.xs = x_scales; g.n_rows = n_tokens * top_k;
+  g.hq = h_codes; g.hs = h_scales;
+  g.act = *act;
+  g.expert_bounds = expert_bounds;
+  g.status = status_dev;
+  return launch_fp8_grouped(g, (cudaStream_t)stream);
 }
 
 int32_t hq_moe_weighted_reduce(const void* y, int32_t y_dtype, const float* w, const int32_t* row_map,
@@ -443,12 +556,17 @@ int32_t hq_fp8_scale_prepare(const float* scales, int32_t n_experts, int64_t n, 
                                   (cudaStream_t)stream);
 }
 
-int32_t hq_convert(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int64_t n_elems, void* stream) {
+int32_t hq_convert_status(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int64_t n_elems,
+                          int32_t* status_dev, void* stream) {
   if (n_elems < 0) return HQ_ERR_SHAPE;
   if (n_elems == 0) return HQ_OK;
   if (src == nullptr || dst == nullptr) return HQ_ERR_NULL;
   if (!valid_dtype(src_dtype) || !valid_dtype(dst_dtype)) return HQ_ERR_FORMAT;
-  return launch_convert(src, src_dtype, dst, dst_dtype, n_elems, (cudaStream_t)stream);
+  return launch_convert(src, src_dtype, dst, dst_dtype, n_elems, status_dev, (cudaStream_t)stream);
+}
+
+int32_t hq_convert(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int64_t n_elems, void* stream) {
+  return hq_convert_status(src, src_dtype, dst, dst_dtype, n_elems, nullptr, stream);
 }
 
 int32_t hq_gated_act(const void* gate, const void* up, int32_t dtype, int64_t n_elems, int32_t interleaved,
@@ -458,6 +576,13 @@ int32_t hq_gated_act(const void* gate, const void* up, int32_t dtype, int64_t n_
   if (gate == nullptr || out == nullptr || act == nullptr || (!interleaved && up == nullptr)) return HQ_ERR_NULL;
   if (!valid_dtype(dtype) || (act->act != HQ_ACT_SWIGLU && act->act != HQ_ACT_GPTOSS)) return HQ_ERR_FORMAT;
   return launch_gated_act(gate, up, dtype, n_elems, interleaved, *act, out, (cudaStream_t)stream);
+}
+
+int32_t hq_probe_tensor_peak(int32_t kind, int32_t n, int32_t iters, int32_t* status_dev, double* flops_host,
+                             void* stream) {
+  if (kind != 0 && kind != 1) return HQ_ERR_FORMAT;
+  if (n < 16 || n > 256 || n % 16 != 0 || iters < 1 || iters > (1 << 20)) return HQ_ERR_SHAPE;
+  return launch_probe_mma(kind, n, iters, status_dev, flops_host, (cudaStream_t)stream);
 }
 
 // ---- one MoE layer in one call -----------------------------------------------------------------------------
@@ -538,7 +663,7 @@ int32_t hq_moe_layer_forward(const hq_moe_layer* layer, const void* logits, int3
   const void* xin = x;
   int32_t xin_dtype = x_dtype;
   if (p.cast_x) {
-    rc = hq_convert(x, x_dtype, ws + p.off_x16, HQ_DT_F16, n_tokens * p.hidden, stream);
+    rc = hq_convert_status(x, x_dtype, ws + p.off_x16, HQ_DT_F16, n_tokens * p.hidden, status_dev, stream);
     if (rc != HQ_OK) return rc;
     xin = ws + p.off_x16;
     xin_dtype = HQ_DT_F16;

@@ -12,7 +12,7 @@ namespace hq {
 
 // Device status word layout (int32[4]): [0] = first error code (0 = none),
 // [1] = blockIdx.x, [2] = blockIdx.y, [3] = phase tag of the wait that gave up.
-enum : int { HQ_DEV_OK = 0, HQ_DEV_WAIT_TIMEOUT = 1, HQ_DEV_BAD_INDEX = 2 };
+// The codes themselves (HQ_DEV_*) are part of the public header.
 
 __device__ __forceinline__ void report_status(int32_t* status, int code, int tag) {
   if (status != nullptr && atomicCAS(status, 0, code) == 0) {

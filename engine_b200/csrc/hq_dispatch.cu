@@ -11,6 +11,8 @@
 //           warp the rank among equal experts comes from a match mask + popcount
 //
 // HBM bytes: T*k*4 read twice + T*k*4*3 written; negligible next to the GEMMs.
+#include <atomic>
+
 #include "hq_common.cuh"
 #include "hq_kernels.h"
 
@@ -139,6 +141,9 @@ __global__ void __launch_bounds__(1024) dispatch_scatter_kernel(const uint32_t* 
   const bool ok = i < total;
   const uint32_t e = ok ? ids[i] : 0xFFFFFFFFu;
   const bool routed = ok && e < (uint32_t)n_experts;
+  // ids outside [0, n_experts) are skipped (padding slots such as -1): they get no sorted row and their
+  // inverse-map entry says so, which the weighted reduce reads as "contributes nothing"
+  if (ok && !routed) inv_perm[i] = -1;
   // rank inside the warp among lanes with the same expert
   const uint32_t peers = __match_any_sync(0xffffffffu, e);
   const int rank = __popc(peers & ((1u << lane) - 1u));
@@ -198,16 +203,19 @@ int32_t launch_dispatch_noalloc(const uint32_t* ids, int64_t n_tokens, int top_k
   if (l.total_words > kNoAllocWords) return HQ_ERR_TOO_LARGE;
   // The array's name is only a host-side handle; kernels need its device address, which differs per device.
   // Looked up on the first call made with a given device current (a plain runtime query, no allocation).
-  static int32_t* dev_ptr[64] = {};
+  // The cache is written by whichever host thread gets there first; every writer stores the same value.
+  static std::atomic<int32_t*> dev_ptr[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HQ_ERR_CUDA;
-  if (dev_ptr[dev] == nullptr) {
+  int32_t* scratch = dev_ptr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return HQ_ERR_CUDA;
-    dev_ptr[dev] = static_cast<int32_t*>(p);
+    scratch = static_cast<int32_t*>(p);
+    dev_ptr[dev].store(scratch, std::memory_order_release);
   }
-  return launch_dispatch(ids, n_tokens, top_k, n_experts, bounds, sorted_assign, sorted_token, inv_perm,
-                         dev_ptr[dev], stream);
+  return launch_dispatch(ids, n_tokens, top_k, n_experts, bounds, sorted_assign, sorted_token, inv_perm, scratch,
+                         stream);
 }
 
 }  // namespace hq

@@ -33,6 +33,7 @@ __global__ void __launch_bounds__(256) weighted_reduce_kernel(const TY* __restri
   for (int i = 0; i < V; ++i) acc[i] = 0.f;
   if (h0 + V <= hidden && (hidden % V) == 0) {
     for (int s = 0; s < top_k; ++s) {
+      if (srow[s] < 0) continue;      // slot without a row (skipped id): adds nothing
       const uint4 raw = *reinterpret_cast<const uint4*>(y + srow[s] * hidden + h0);
       const TY* v = reinterpret_cast<const TY*>(&raw);
       const float ws = sw[s];
@@ -50,7 +51,8 @@ __global__ void __launch_bounds__(256) weighted_reduce_kernel(const TY* __restri
   } else {
     for (int i = 0; i < V && h0 + i < hidden; ++i) {
       float r = 0.f;
-      for (int s = 0; s < top_k; ++s) r = fmaf(sw[s], to_float<TY>(y[srow[s] * hidden + h0 + i]), r);
+      for (int s = 0; s < top_k; ++s)
+        if (srow[s] >= 0) r = fmaf(sw[s], to_float<TY>(y[srow[s] * hidden + h0 + i]), r);
       if (addend) r += to_float<TO>(addend[t * hidden + h0 + i]);
       if constexpr (sizeof(TO) == 4) out[t * hidden + h0 + i] = r;
       else if constexpr (std::is_same<TO, __half>::value) out[t * hidden + h0 + i] = __float2half_rn(r);
@@ -194,11 +196,13 @@ __device__ __forceinline__ void load4_as_float(const void* p, int dtype, int64_t
 // The same 1 x 128 quantizer over rows that are looked up first (token order -> expert-sorted order): one warp per
 // (output row, group of 128 columns).  Feeds the FP8 expert GEMM, whose operand boxes need whole sorted rows.
 __global__ void __launch_bounds__(256) fp8_quant_rows_kernel(const void* __restrict__ x, int dtype, int64_t x_stride,
-                                                             const int32_t* __restrict__ row_map, int64_t n_rows,
+                                                             const int32_t* __restrict__ row_map,
+                                                             const int32_t* __restrict__ n_valid, int64_t n_rows,
                                                              int kgroups, uint8_t* __restrict__ codes,
                                                              float* __restrict__ scales) {
   const int64_t grp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (grp >= n_rows * kgroups) return;
+  const int64_t limit = n_valid != nullptr ? min((int64_t)*n_valid, n_rows) : n_rows;   // rows the map is defined for
+  if (grp >= limit * kgroups) return;
   const int lane = threadIdx.x & 31;
   const int64_t row = grp / kgroups;
   const int g = (int)(grp - row * kgroups);
@@ -220,12 +224,13 @@ __global__ void __launch_bounds__(256) fp8_quant_rows_kernel(const void* __restr
   if (lane == 0) scales[grp] = scale;
 }
 
-int32_t launch_fp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,
-                              int64_t k, uint8_t* codes, float* scales, cudaStream_t stream) {
+int32_t launch_fp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map,
+                              const int32_t* n_valid, int64_t n_rows, int64_t k, uint8_t* codes, float* scales,
+                              cudaStream_t stream) {
   const int64_t groups = n_rows * (k / 128);
   if (groups == 0) return HQ_OK;
-  fp8_quant_rows_kernel<<<(unsigned)((groups + 7) / 8), 256, 0, stream>>>(x, x_dtype, x_stride, row_map, n_rows,
-                                                                         (int)(k / 128), codes, scales);
+  fp8_quant_rows_kernel<<<(unsigned)((groups + 7) / 8), 256, 0, stream>>>(x, x_dtype, x_stride, row_map, n_valid,
+                                                                         n_rows, (int)(k / 128), codes, scales);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
@@ -252,15 +257,62 @@ int32_t launch_fp8_block_dequant(const uint8_t* codes, const float* scales, int6
 }
 
 // ---- dtype conversion (hosts holding bf16 / f32 activations cast once before a prefill-sized call) -------
+// Eight elements per thread (16-byte accesses on the 16-bit side).  A finite value beyond the f16 range is clamped
+// to +-65504 instead of becoming inf, and the call says so through the status word: the tensor-core kernels
+// multiply in f16, which the reference's bf16 / f32 activation paths do not, so the caller has to know.
 __global__ void __launch_bounds__(256) convert_kernel(const void* __restrict__ src, int src_dtype,
-                                                      void* __restrict__ dst, int dst_dtype, int64_t n) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) store_from_float(dst, dst_dtype, i, load_as_float(src, src_dtype, i));
+                                                      void* __restrict__ dst, int dst_dtype, int64_t n, int vec_ok,
+                                                      int32_t* __restrict__ status) {
+  const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i0 >= n) return;
+  float v[8];
+  const bool full = vec_ok && i0 + 8 <= n;
+  if (full) {
+    load4_as_float(src, src_dtype, i0, *reinterpret_cast<float(*)[4]>(&v[0]));
+    load4_as_float(src, src_dtype, i0 + 4, *reinterpret_cast<float(*)[4]>(&v[4]));
+  } else {
+    for (int j = 0; j < 8; ++j) v[j] = i0 + j < n ? load_as_float(src, src_dtype, i0 + j) : 0.f;
+  }
+  if (dst_dtype == HQ_DT_F16 && src_dtype != HQ_DT_F16) {
+    bool clamped = false;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = fabsf(v[j]);
+      if (a > 65504.f && a <= 3.4028235e38f) {       // finite and out of range (inf / NaN pass through)
+        v[j] = copysignf(65504.f, v[j]);
+        clamped = true;
+      }
+    }
+    if (clamped) report_status(status, HQ_DEV_F16_RANGE, 900);
+  }
+  if (full && dst_dtype != HQ_DT_F32) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (dst_dtype == HQ_DT_F16) {
+        w[j] = pack_half2(v[2 * j], v[2 * j + 1]);
+      } else {
+        __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&b);
+      }
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dst) + i0) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else if (full) {
+    float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + i0);
+    o[0] = make_float4(v[0], v[1], v[2], v[3]);
+    o[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    for (int j = 0; j < 8 && i0 + j < n; ++j) store_from_float(dst, dst_dtype, i0 + j, v[j]);
+  }
 }
 
-int32_t launch_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, cudaStream_t stream) {
+int32_t launch_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, int32_t* status,
+                       cudaStream_t stream) {
   if (n == 0) return HQ_OK;
-  convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(src, src_dtype, dst, dst_dtype, n);
+  const int64_t threads = (n + 7) / 8;
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+  convert_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(src, src_dtype, dst, dst_dtype, n, vec_ok,
+                                                                        status);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 

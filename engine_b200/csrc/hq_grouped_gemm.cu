@@ -201,7 +201,9 @@ __device__ __forceinline__ void emit_fp8(const RawA& r, uint32_t (&out)[8]) {
 
 // MXFP4: e2m1 pairs -> f16x2 (hardware conversion, low nibble = even element = low half), times 2^(e-127) as
 // an exact f16 power of two.  e = 0 decodes to a zero scale (the reference's table builds the scale from the
-// bits e << 23); scales outside the f16 exponent range are reported by the caller.
+// bits e << 23).  The f16 operand covers block scales 2^-14 .. 2^13 (e = 113 .. 140); a block outside that
+// range is expanded as zero and the caller raises HQ_DEV_SCALE_RANGE, so a bank with such blocks has to stay on
+// the decode kernel, which applies the scale in f32.
 __device__ __forceinline__ bool emit_mxfp4(const RawA& r, uint32_t (&out)[8]) {
   const uint32_t e = r.aux;
   const bool in_range = (e == 0) || (e >= 113 && e <= 140);   // 2^-14 .. 2^13: products stay finite in f16
@@ -554,7 +556,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
           } else if (FMT == HQ_FMT_FP8_BLOCK) {
             emit_fp8(use[bank], v);
           } else {
-            if (!emit_mxfp4(use[bank], v)) report_status(p.status, HQ_DEV_BAD_INDEX, 600);
+            if (!emit_mxfp4(use[bank], v)) report_status(p.status, HQ_DEV_SCALE_RANGE, 600);
           }
         } else {
 #pragma unroll
@@ -991,7 +993,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_ts_kernel(const Gr
       for (int half = 0; half < 2; ++half) {
         uint32_t v[16];
         if (cur.n_ok) {
-          if (!ts_expand<FMT>(use, k0, half, v)) report_status(p.status, HQ_DEV_BAD_INDEX, 600);
+          if (!ts_expand<FMT>(use, k0, half, v)) report_status(p.status, HQ_DEV_SCALE_RANGE, 600);
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0u;

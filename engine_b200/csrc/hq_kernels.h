@@ -83,27 +83,34 @@ int32_t launch_fp8_scale_prepare(const float* scales, int64_t n_groups, int kb, 
 
 // ---- block-FP8 expert GEMM with FP8 activations on tcgen05 kind::f8f6f4 (hq_fp8_grouped.cu) --------------
 struct Fp8GroupedParams {
-  int n, k, m;                  // m: dense rows (used when tiles == nullptr)
+  int n, k, m;                  // m: dense rows (used when expert_bounds == nullptr)
   int n_experts;
   const void* w;                // e4m3 codes [E, N, K]
   const float* w_scales;        // [E, N/128, K/128]
+  const void* w_up;             // gated mode: the up bank (w is then the gate bank), same shape
+  const float* w_up_scales;
   int fp8_nb, fp8_kb;
   const void* bias;
+  const void* bias_up;
   int bias_dtype;
   const void* xq;               // e4m3 activation codes [n_rows, K], rows in expert-sorted order
   const float* xs;              // [n_rows, K/128] activation scales
-  int64_t n_rows;
-  void* y;
+  int64_t n_rows;               // rows of xq / xs (the tensor-map bound; rows beyond expert_bounds[E] are never used)
+  void* y;                      // plain mode output
   int y_dtype;
   int64_t y_stride;
-  const int32_t* tiles;         // [n_tiles][2] = (expert, first sorted row), tiles of <= 128 rows
-  const int32_t* tile_count;
-  const int32_t* expert_bounds;
+  bool y_tile_ok;               // set by the launcher: 16-bit rows can leave as 16-byte stores
+  uint8_t* hq;                  // gated mode output: e4m3 codes [n_rows, N] ...
+  float* hs;                    // ... and scales [n_rows, N/128] of act(gate) * up, expert-sorted
+  hq_act_args act;
+  const int32_t* expert_bounds; // [E+1]; token tiles are cut from it inside the kernel
   const int32_t* y_rows;        // sorted row -> output row (nullptr = identity)
   int32_t* status;
+  uint32_t spin_limit;          // polls per bounded wait (0 = default)
+  int test_skip_producer;       // test hook: the TMA warp issues nothing, so every consumer wait runs out
 };
 bool fp8_grouped_supported(int64_t n, int64_t k);
-int32_t launch_fp8_grouped(const Fp8GroupedParams& p, int max_tiles, cudaStream_t stream);
+int32_t launch_fp8_grouped(const Fp8GroupedParams& p, cudaStream_t stream);
 
 // ---- dispatch tables (hq_dispatch.cu) -------------------------------------------
 constexpr int kDispatchChunk = 1024;  // flat assignments per block
@@ -143,12 +150,27 @@ int32_t launch_fp8_block_quant(const void* w, int w_dtype, int64_t rows, int64_t
                                uint8_t* codes, float* scales, cudaStream_t stream);
 int32_t launch_fp8_block_dequant(const uint8_t* codes, const float* scales, int64_t rows, int64_t cols, int by,
                                  int bx, void* out, int out_dtype, cudaStream_t stream);
-int32_t launch_fp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,
-                              int64_t k, uint8_t* codes, float* scales, cudaStream_t stream);
+int32_t launch_fp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map,
+                              const int32_t* n_valid, int64_t n_rows, int64_t k, uint8_t* codes, float* scales,
+                              cudaStream_t stream);
 int32_t launch_fp8_gated_quant_rows(const void* gu, int dtype, int64_t n_rows, int64_t width, const hq_act_args& act,
                                     uint8_t* codes, float* scales, cudaStream_t stream);
-int32_t launch_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, cudaStream_t stream);
+int32_t launch_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, int32_t* status,
+                       cudaStream_t stream);
 int32_t launch_gated_act(const void* gate, const void* up, int dtype, int64_t n, int interleaved,
                          const hq_act_args& act, void* out, cudaStream_t stream);
+
+
+// ---- expert-parallel exchange helpers (hq_ep.cu) -------------------------------------
+int32_t launch_ep_pack(const hq_ep_layout& l, const void* x, int x_dtype, const uint32_t* ids, const float* weights,
+                       int64_t n_tokens, void* send, int32_t* back_map, cudaStream_t stream);
+int32_t launch_ep_unpack_meta(const hq_ep_layout& l, const void* recv, uint32_t* ids, float* weights,
+                              cudaStream_t stream);
+int32_t launch_fp8_gather_rows(const void* src_codes, int64_t src_code_stride, const void* src_scales,
+                               int64_t src_scale_stride, const int32_t* row_map, const int32_t* n_valid,
+                               int64_t n_rows, int64_t k, uint8_t* codes, float* scales, cudaStream_t stream);
+
+// ---- tensor-core issue-rate probe (hq_probe.cu) ---------------------------------------
+int32_t launch_probe_mma(int kind, int n_dim, int iters, int32_t* status, double* flops_out, cudaStream_t stream);
 
 }  // namespace hq

@@ -10,9 +10,8 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib as L
-from .quant import (DispatchTables, QuantMethod, _ptr, _require_cuda, _stream, dt_code, fp8_gated_quantize_rows,
-                    fp8_quantize_rows, moe_dispatch_build,
-                    tensor_path_expected)
+from .quant import (DispatchTables, QuantMethod, _ptr, _require_cuda, _stream, convert, dt_code,
+                    moe_dispatch_build, tensor_path_expected)
 
 
 @dataclass
@@ -111,7 +110,8 @@ class MoEExperts:
         tables = tables or moe_dispatch_build(topk_ids, self.n_experts)
         first = self.gate_up if self.gate_up is not None else self.gate
         if x.dtype != torch.float16 and tensor_path_expected(first, t * k, dense=False):
-            x = x.to(torch.float16)     # one cast per token instead of one conversion per (token, slot) in the kernel
+            # one cast per token instead of one conversion per (token, slot) in the kernel
+            x = convert(x, torch.float16, first._status_buf(x.device))
         inter = first.n // 2 if self.gate_up is not None else first.n
         h = torch.empty((t * k, inter), dtype=self.inter_dtype, device=x.device)
         w0 = first._weight_struct()
@@ -137,40 +137,61 @@ class MoEExperts:
 
     def forward_fp8_act(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                         shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-                        tables: DispatchTables | None = None, _skip_reduce: bool = False) -> torch.Tensor:
+                        tables: DispatchTables | None = None, _skip_reduce: bool = False,
+                        fp8_rows: tuple | None = None) -> torch.Tensor:
         """The same block with block-scaled FP8 activations (block-FP8 experts with separate gate/up banks only):
-        token rows are quantized 1x128 straight into expert-sorted order, both projections run on the FP8
-        tensor-core MMA with weights and activations unconverted, and the intermediate is quantized again by the
-        kernel that applies the gated activation."""
-        _require_cuda(xs, "xs")
+        token rows are quantized 1x128 straight into expert-sorted order; one launch runs the gate and the up
+        projection on the FP8 tensor-core MMA (weights and activations unconverted), applies the gated activation
+        and quantizes the intermediate again; the down projection writes expert-sorted rows (16-bit when the
+        output is 16-bit, f32 otherwise) and the weighted reduce un-permutes them.
+
+        `fp8_rows` = (buffer uint8 [R, row_bytes], hidden): token rows that are FP8 already, codes followed by the
+        f32 scales in each row (the layout hq_ep_pack puts on the wire); `xs` is then ignored.
+        Slots whose id is outside [0, n_experts) are skipped."""
         if self.gate is None or self.gate.format != L.FMT_FP8_BLOCK:
             raise L.HqError("forward_fp8_act needs block-FP8 experts with separate gate and up banks")
-        lead = xs.shape[:-1]
-        x = xs.reshape(-1, xs.shape[-1]).contiguous()
         t, k = topk_ids.shape
+        if fp8_rows is None:
+            _require_cuda(xs, "xs")
+            lead = xs.shape[:-1]
+            x = xs.reshape(-1, xs.shape[-1]).contiguous()
+            dev, hidden = x.device, x.shape[-1]
+        else:
+            buf, hidden = fp8_rows
+            _require_cuda(buf, "fp8_rows")
+            lead, dev = (t,), buf.device
         tables = tables or moe_dispatch_build(topk_ids, self.n_experts)
         lib = L.lib()
-        status = self.gate._status_buf(x.device)
-        xq, xsc = fp8_quantize_rows(x, tables.sorted_token)
+        status = self.gate._status_buf(dev)
+        n_valid = tables.expert_bounds[self.n_experts:]
+        xq = torch.empty((t * k, hidden), dtype=torch.uint8, device=dev)
+        xsc = torch.empty((t * k, hidden // 128), dtype=torch.float32, device=dev)
+        if fp8_rows is None:
+            L.check(lib.hq_fp8_quant_rows_n(_ptr(x), dt_code(x.dtype), hidden, _ptr(tables.sorted_token),
+                                            _ptr(n_valid), t * k, hidden, _ptr(xq), _ptr(xsc), _stream()),
+                    "hq_fp8_quant_rows_n")
+        else:
+            L.check(lib.hq_fp8_gather_rows(buf.data_ptr(), buf.stride(0), buf.data_ptr() + hidden, buf.stride(0),
+                                           _ptr(tables.sorted_token), _ptr(n_valid), t * k, hidden, _ptr(xq),
+                                           _ptr(xsc), _stream()), "hq_fp8_gather_rows")
         inter = self.gate.n
-        gu = torch.empty((t * k, 2 * inter), dtype=self.inter_dtype, device=x.device)
-        for bank, col in ((self.gate, 0), (self.up, inter)):
-            w = bank._weight_struct()
-            L.check(lib.hq_moe_fp8_gather_forward(C.byref(w), _ptr(xq), _ptr(xsc), t, k, _ptr(tables.expert_bounds),
-                                                  _ptr(tables.sorted_assign), _ptr(tables.workspace),
-                                                  gu.data_ptr() + col * gu.element_size(), dt_code(gu.dtype),
-                                                  2 * inter, L.ROWS_SORTED, _ptr(status), _stream()),
-                    "hq_moe_fp8_gather_forward(gate/up)")
-        hq_, hs = fp8_gated_quantize_rows(gu, self.act)
-        y = torch.empty((t * k, self.down.n), dtype=torch.float32, device=x.device)
+        hq_ = torch.empty((t * k, inter), dtype=torch.uint8, device=dev)
+        hs = torch.empty((t * k, inter // 128), dtype=torch.float32, device=dev)
+        wg, wu = self.gate._weight_struct(), self.up._weight_struct()
+        L.check(lib.hq_moe_fp8_gate_up_forward(C.byref(wg), C.byref(wu), C.byref(self.act), _ptr(xq), _ptr(xsc), t, k,
+                                               _ptr(tables.expert_bounds), _ptr(hq_), _ptr(hs), _ptr(status),
+                                               _stream()), "hq_moe_fp8_gate_up_forward")
+        out_dtype = out_dtype or (xs.dtype if fp8_rows is None else torch.bfloat16)
+        y_dtype = out_dtype if out_dtype in (torch.float16, torch.bfloat16) else torch.float32
+        y = torch.empty((t * k, self.down.n), dtype=y_dtype, device=dev)
         wd = self.down._weight_struct()
         L.check(lib.hq_moe_fp8_gather_forward(C.byref(wd), _ptr(hq_), _ptr(hs), t, k, _ptr(tables.expert_bounds),
-                                              _ptr(tables.sorted_assign), _ptr(tables.workspace), _ptr(y),
+                                              _ptr(tables.sorted_assign), None, _ptr(y),
                                               dt_code(y.dtype), self.down.n, L.ROWS_SORTED, _ptr(status), _stream()),
                 "hq_moe_fp8_gather_forward(down)")
         if _skip_reduce:
             return y
-        out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype or xs.dtype, tables.inv_perm, shared_out)
+        out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype, tables.inv_perm, shared_out)
         return out.reshape(*lead, self.down.n)
 
     def forward_layer(self, xs: torch.Tensor, logits: torch.Tensor, config: MoeRouterTopKConfig,

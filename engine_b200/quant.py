@@ -73,6 +73,18 @@ def moe_dispatch_build(ids: torch.Tensor, n_experts: int) -> DispatchTables:
     return DispatchTables(t, k, n_experts, bounds, sa, st, inv, ws)
 
 
+def convert(x: torch.Tensor, dtype: torch.dtype, status: torch.Tensor | None = None) -> torch.Tensor:
+    """Elementwise cast through the library's own kernel (hq_convert_status).  Casting to f16 clamps finite values
+    beyond +-65504 and leaves HQ_DEV_F16_RANGE in `status` (the layer's device status word)."""
+    if x.dtype == dtype:
+        return x
+    x = x.contiguous()
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    L.check(L.lib().hq_convert_status(_ptr(x), dt_code(x.dtype), _ptr(out), dt_code(dtype), x.numel(), _ptr(status),
+                                      _stream()), "hq_convert_status")
+    return out
+
+
 def tensor_path_expected(layer, n_rows_total: int, dense: bool) -> bool:
     """Mirror of the C-side rule that sends a call to the tensor-core grouped GEMM (prefill-sized row counts,
     Q4_K / FP8 / MXFP4, K % 64 == 0).  Used only to decide whether to hand activations over as f16, which that
@@ -141,7 +153,8 @@ class QuantMethod:
         m = x.shape[0]
         out_dtype = out_dtype or a.dtype
         if x.dtype != torch.float16 and tensor_path_expected(self, m, dense=True):
-            x = x.to(torch.float16)     # the tensor-core kernel multiplies in f16 either way
+            # the tensor-core kernel multiplies in f16 either way (values beyond +-65504 are clamped and flagged)
+            x = convert(x if x.is_contiguous() else x.contiguous(), torch.float16, self._status_buf(a.device))
         y = torch.empty((m, self.n), dtype=out_dtype, device=a.device)
         # the weight descriptor never changes after construction: built once (a decode call is a few microseconds
         # of GPU time, so host work per call matters)
@@ -193,7 +206,7 @@ class QuantMethod:
             raise L.HqError("gather_forward: input / indices / weight shapes disagree")
         x = a.contiguous()
         if x.dtype != torch.float16 and tensor_path_expected(self, t * k, dense=False):
-            x = x.to(torch.float16)
+            x = convert(x, torch.float16, self._status_buf(a.device))
         tables = tables or moe_dispatch_build(indices, self.n_experts)
         out_dtype = out_dtype or a.dtype
         out = torch.empty((t, k, self.n), dtype=out_dtype, device=a.device)

@@ -33,8 +33,11 @@ extern "C" {
 #endif
 
 /* 2: adds the caller-scratch linear call, the FP8 row quantizers and FP8-activation calls, and the one-call
- * MoE layer; every version-1 entry point keeps its signature. */
-#define HQ_ABI_VERSION 2
+ * MoE layer; every version-1 entry point keeps its signature.
+ * 3: adds the status-reporting conversion, the fused FP8 expert block, the expert-parallel pack / unpack calls,
+ * the fused dense decode calls, more GGML types and the reference-named compatibility symbols; every version-2
+ * entry point keeps its signature. */
+#define HQ_ABI_VERSION 3
 
 /* status codes */
 #define HQ_OK 0
@@ -45,6 +48,15 @@ extern "C" {
 #define HQ_ERR_CUDA (-5)        /* CUDA runtime error at launch (no device, bad config) */
 #define HQ_ERR_WORKSPACE (-6)   /* workspace missing or too small */
 #define HQ_ERR_TOO_LARGE (-7)   /* size beyond a stated fixed maximum */
+
+/* codes a kernel may leave in word [0] of the device status buffer (int32[4]: code, blockIdx.x, blockIdx.y,
+ * tag); the first one sticks until the caller clears the buffer */
+#define HQ_DEV_OK 0
+#define HQ_DEV_WAIT_TIMEOUT 1  /* a bounded wait ran out; the kernel skipped the rest of its work */
+#define HQ_DEV_BAD_INDEX 2     /* an index read from a caller table was out of range and was skipped */
+#define HQ_DEV_SCALE_RANGE 3   /* MXFP4 on the tensor-core path: a block scale outside 2^-14 .. 2^13 (e8m0 113 .. 140,
+                                  or 0) was expanded as zero; run such banks with HQ_CFG_MOE_TENSOR_MIN_ROWS huge */
+#define HQ_DEV_F16_RANGE 4     /* an activation beyond +-65504 was clamped while being converted to f16 */
 
 /* weight formats (hanzo-quant: GgufMatMul Q8_0 / Q4_K, BlockwiseFP8Linear, MXFP4Layer) */
 #define HQ_FMT_Q8_0 0       /* GGUF block_q8_0 {half d; int8 qs[32]}, 34 B / 32 weights   */
@@ -103,6 +115,13 @@ int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* str
  * (default 9).  Shapes the grouped GEMM does not cover (Q8_0, K % 64 != 0) always take the decode kernel. */
 #define HQ_CFG_MOE_TENSOR_MIN_ROWS 0
 #define HQ_CFG_DENSE_TENSOR_MIN_ROWS 1
+/* HQ_CFG_SPIN_LIMIT: polls a kernel spends on one bounded wait before it gives up, leaves HQ_DEV_WAIT_TIMEOUT in
+ * the status word and stops storing results (default 1 << 22; read by the FP8 expert GEMM).
+ * HQ_CFG_TEST_SKIP_PRODUCER: test hook, 0 by default.  With 1 the FP8 expert GEMM's copy-issuing warp issues
+ * nothing, so every wait of the other warps runs out: the way to see the time-out path return without anything
+ * left in flight (no copy and no MMA is issued in that launch). */
+#define HQ_CFG_SPIN_LIMIT 2
+#define HQ_CFG_TEST_SKIP_PRODUCER 3
 int32_t hq_config_set(int32_t key, int64_t value);
 int64_t hq_config_get(int32_t key);
 
@@ -162,8 +181,12 @@ int32_t hq_router_topk(const void* logits, int32_t logits_dtype, int64_t n_rows,
  * order of the reference's host grouping (hanzo-quant/src/mxfp4/ops.rs:237-271).
  * Outputs: expert_bounds int32 [E+1]; sorted_assign int32 [T*k] (flat index);
  * sorted_token int32 [T*k] (token index); inv_perm int32 [T*k] (flat index ->
- * sorted position).  Also fills two tile lists for the expert GEMMs in the
- * workspace (see hq_moe_dispatch_workspace_bytes). */
+ * sorted position).  Also fills the tile lists for the expert GEMMs in the
+ * workspace (see hq_moe_dispatch_workspace_bytes).
+ * An id outside [0, n_experts) -- a padding slot such as 0xFFFFFFFF -- is skipped:
+ * it gets no sorted row, expert_bounds[E] counts only the routed assignments (the
+ * tail of sorted_assign / sorted_token beyond it is left unwritten), and its
+ * inv_perm entry is -1, which hq_moe_weighted_reduce reads as "adds nothing". */
 int64_t hq_moe_dispatch_workspace_bytes(int64_t n_tokens, int32_t top_k, int32_t n_experts);
 int32_t hq_moe_dispatch_build(const uint32_t* ids, int64_t n_tokens, int32_t top_k, int32_t n_experts,
                               int32_t* expert_bounds, int32_t* sorted_assign, int32_t* sorted_token,
@@ -174,8 +197,11 @@ int32_t hq_moe_dispatch_build(const uint32_t* ids, int64_t n_tokens, int32_t top
  * asked for memory.  This entry point has no counterpart in the reference.  The scratch it needs sits in a
  * fixed array inside the library (about 220 KB per GPU, held until the process exits), so it only accepts
  * n_tokens*top_k <= 65536 and n_experts <= 512 and answers HQ_ERR_TOO_LARGE beyond that.  It calls no
- * allocator of any kind.  The first call on a device looks up the array's device address; make that
- * first call outside any stream capture.  All calls share the one array: calls that run at the same time
+ * allocator of any kind.  The first call on a device looks up the array's device address (with lazy module
+ * loading that is also when the driver backs the array with memory, so it can fail with HQ_ERR_CUDA on a GPU
+ * that is already full): make that first call at start-up, before the host's own pool claims the rest of the
+ * memory, and outside any stream capture.  `stream` must belong to the device that is current when the call is
+ * made (the address is looked up for the current device).  All calls share the one array: calls that run at the same time
  * on one GPU corrupt each other, so keep them on one stream or order them yourself.  (The tile lists the
  * expert projections consume stay inside that array; this variant is for callers that only need the
  * four tables.) */
@@ -244,7 +270,7 @@ int32_t hq_moe_layer_forward(const hq_moe_layer* layer, const void* logits, int3
  * y [T*k, H] in y_dtype, w f32 [T, k], addend [T, H] in out_dtype or NULL.
  * row_map int32 [T*k] gives the row of y that holds assignment (t, s) -- pass
  * inv_perm from hq_moe_dispatch_build when y is expert-sorted, NULL when y is
- * already in (token, slot) order. */
+ * already in (token, slot) order.  A negative row_map entry skips that slot. */
 int32_t hq_moe_weighted_reduce(const void* y, int32_t y_dtype, const float* w, const int32_t* row_map,
                                const void* addend, void* out, int32_t out_dtype, int64_t n_tokens, int32_t top_k,
                                int64_t hidden, void* stream);
@@ -264,7 +290,13 @@ int32_t hq_moe_weighted_reduce(const void* y, int32_t y_dtype, const float* w, c
  * hq_fp8_gated_quant_rows: gate_up [n_rows, 2*width] = {gate | up} -> act(gate) * up -> the same quantizer.
  * hq_fp8_linear_forward: dense layer over quantized rows.  hq_moe_fp8_gather_forward: expert bank over
  * expert-sorted quantized rows (n_tokens * top_k of them), output rows sorted or per slot, row stride
- * out_stride elements (so two banks can write the halves of one {gate | up} matrix). */
+ * out_stride elements (so two banks can write the halves of one {gate | up} matrix); `workspace` is not read
+ * (the kernel cuts its token tiles from expert_bounds) and may be NULL.
+ * hq_moe_fp8_gate_up_forward: gate and up projection, gated activation and the 1 x 128 quantizer of the result in
+ * one launch -- the fused form of the reference's gate/up GEMMs + fused_glu + quantizer sequence
+ * (hanzo-engine/src/moe/experts/backends.rs:560-605, hanzo-quant/kernels/ops/ops.cu:845-858): gate and up are
+ * rounded to f16, act(gate) * up is computed in f32 and rounded to f16, then quantized; h_codes [n_tokens * top_k,
+ * N] and h_scales [n_tokens * top_k, N / 128] come out expert-sorted, ready for the down projection. */
 int32_t hq_fp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,
                           int64_t k, uint8_t* codes, float* scales, void* stream);
 int32_t hq_fp8_gated_quant_rows(const void* gate_up, int32_t dtype, int64_t n_rows, int64_t width,
@@ -275,6 +307,57 @@ int32_t hq_moe_fp8_gather_forward(const hq_weight* w, const uint8_t* x_codes, co
                                   int64_t n_tokens, int32_t top_k, const int32_t* expert_bounds,
                                   const int32_t* sorted_assign, const void* workspace, void* out, int32_t out_dtype,
                                   int64_t out_stride, int32_t out_layout, int32_t* status_dev, void* stream);
+int32_t hq_moe_fp8_gate_up_forward(const hq_weight* w_gate, const hq_weight* w_up, const hq_act_args* act,
+                                   const uint8_t* x_codes, const float* x_scales, int64_t n_tokens, int32_t top_k,
+                                   const int32_t* expert_bounds, uint8_t* h_codes, float* h_scales,
+                                   int32_t* status_dev, void* stream);
+
+/* hq_fp8_quant_rows with a row count that lives on the device: only rows r < min(*n_valid_dev, n_rows) are
+ * produced.  For row maps whose tail is undefined -- sorted_token after a dispatch build that skipped padding
+ * ids has expert_bounds[E] valid entries, so pass expert_bounds + E. */
+int32_t hq_fp8_quant_rows_n(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map,
+                            const int32_t* n_valid_dev, int64_t n_rows, int64_t k, uint8_t* codes, float* scales,
+                            void* stream);
+/* Row gather of rows that are FP8 already (received over the wire): codes [r] = src_codes + row_map[r] *
+ * src_code_stride (k bytes), scales [r] = src_scales + row_map[r] * src_scale_stride_bytes (k / 128 floats), for
+ * r < min(*n_valid_dev, n_rows) (n_valid_dev NULL = all).  No counterpart in the reference. */
+int32_t hq_fp8_gather_rows(const uint8_t* src_codes, int64_t src_code_stride, const float* src_scales,
+                           int64_t src_scale_stride_bytes, const int32_t* row_map, const int32_t* n_valid_dev,
+                           int64_t n_rows, int64_t k, uint8_t* codes, float* scales, void* stream);
+
+/* ---- expert parallelism: what a rank does either side of the two all-to-all exchanges --------------------
+ * The reference shards quantized experts over GPUs nowhere (its MoE collective is the tensor-parallel all-reduce
+ * behind hanzo-engine/src/moe/experts/mod.rs:260-263, NCCL wrapper hanzo-quant/src/distributed/mod.rs:213-274,
+ * :494-617); these calls are the device side of an expert-parallel layer built on the same local kernels, so that
+ * a host only adds two equal-split all-to-all calls (ncclSend / ncclRecv of message_bytes per peer).
+ *
+ * Experts are sharded in contiguous ranges of experts_per_rank.  A token travels ONCE to every rank that hosts at
+ * least one of its top_k experts, and that rank returns ONE row for it: the router-weighted sum over the experts
+ * it hosts.  Every per-peer message has the same size (capacity token rows + the meta rows), so no counts go
+ * through the host.  capacity = the largest number of tokens a rank brings to one call; it must be the same on
+ * every rank.
+ *   message to peer d: rows [0, capacity) = token payloads (written only for tokens that go to d): hidden values
+ *   in wire_dtype, or with fp8 = 1 hidden e4m3 codes + hidden / 128 f32 scales (1 x 128 quantizer, so the expert
+ *   rank feeds the FP8 MMA unchanged); rows [capacity, rows_per_peer) = per token and slot (int32 local expert id
+ *   or -1, f32 router weight).
+ * hq_ep_pack fills `send` [world, rows_per_peer, row_bytes] and back_map int32 [n_tokens, world] (row of the
+ * returned buffer that holds rank d's partial sum for token t, or -1).  After the dispatch all-to-all,
+ * hq_ep_unpack_meta turns the meta rows of `recv` (same shape) into ids uint32 / weights f32 [world *
+ * rows_per_peer, top_k] for the local expert block (hq_moe_dispatch_build skips the -1 slots).  The local block's
+ * weighted reduce over those rows gives [world * rows_per_peer, hidden] partial sums; after the return all-to-all
+ * the source rank calls hq_moe_weighted_reduce(y = returned rows, w = ones [n_tokens, world], row_map = back_map,
+ * top_k = world) to add the partial sums (and the shared expert, as the addend). */
+typedef struct hq_ep_layout {
+  int32_t world, top_k, experts_per_rank, capacity;
+  int32_t pad_rows, rows_per_peer, fp8, wire_dtype;
+  int64_t hidden, row_bytes, message_bytes;
+} hq_ep_layout;
+int32_t hq_ep_layout_init(hq_ep_layout* layout, int32_t world, int32_t top_k, int32_t experts_per_rank,
+                          int32_t capacity, int64_t hidden, int32_t wire_dtype, int32_t fp8);
+int32_t hq_ep_pack(const hq_ep_layout* layout, const void* x, int32_t x_dtype, const uint32_t* ids,
+                   const float* weights, int64_t n_tokens, void* send, int32_t* back_map, void* stream);
+int32_t hq_ep_unpack_meta(const hq_ep_layout* layout, const void* recv, uint32_t* ids_out, float* weights_out,
+                          void* stream);
 
 /* ---- FP8 quantizers ---------------------------------------------------------
  * 1x128 groups along the last axis: scale = absmax/448 (1e-12 if zero),
@@ -304,6 +387,20 @@ int32_t hq_fp8_scale_prepare(const float* scales, int32_t n_experts, int64_t n, 
  * bf16 or f32 activations converts once with this call -- the reference's Tensor::to_dtype
  * (e.g. hanzo-quant/src/gguf/mod.rs:196-209). */
 int32_t hq_convert(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int64_t n_elems, void* stream);
+/* The same conversion with a device status word.  The tensor-core kernels multiply f16 by f16, so their inputs are
+ * limited to +-65504 -- a limit the reference's bf16 / f32 activation paths do not have (it quantizes from f32,
+ * hanzo-quant/kernels/mmvq_gguf/mmvq_gguf.cu:1263-1295, or multiplies bf16, blockwise_fp8_gemm.cu:131-258).  A finite
+ * value beyond the range is clamped to +-65504 and HQ_DEV_F16_RANGE is left in status_dev; hq_moe_layer_forward
+ * converts through this call. */
+int32_t hq_convert_status(const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, int64_t n_elems,
+                          int32_t* status_dev, void* stream);
+
+/* Measurement aid, no counterpart in the reference: every SM issues iters x 4 tcgen05.mma instructions back to back
+ * (M = 128, N = n, operands resident in shared memory; kind 0 = f16 x f16, K = 16 per instruction; kind 1 = e4m3 x
+ * e4m3 on kind::f8f6f4, K = 32).  *flops_host receives the floating-point operations of the launch; the caller
+ * times the launch with events.  Gives the FP8 tensor peak the expert GEMM's fraction is quoted against. */
+int32_t hq_probe_tensor_peak(int32_t kind, int32_t n, int32_t iters, int32_t* status_dev, double* flops_host,
+                             void* stream);
 
 /* ---- gated activations as stand-alone ops -----------------------------------
  * out = act(gate, up) elementwise over n_elems; interleaved = 1 reads pairs

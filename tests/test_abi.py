@@ -30,7 +30,7 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
     for n in names:
         assert hasattr(lib, n), n
         assert n in L.SIGNATURES, f"{n} has no ctypes signature"
-    assert lib.hq_abi_version() == 2
+    assert lib.hq_abi_version() == 3
     assert lib.hq_error_string(-2).decode() == "unsupported size"
 
 
