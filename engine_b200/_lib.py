@@ -18,6 +18,7 @@ ACT_NONE, ACT_SWIGLU, ACT_GPTOSS = 0, 1, 2
 DEV_OK, DEV_WAIT_TIMEOUT, DEV_BAD_INDEX, DEV_SCALE_RANGE, DEV_F16_RANGE = 0, 1, 2, 3, 4
 ROWS_PER_TOKEN, ROWS_PER_SLOT, ROWS_SORTED = 0, 1, 2
 CFG_MOE_TENSOR_MIN_ROWS, CFG_DENSE_TENSOR_MIN_ROWS, CFG_SPIN_LIMIT, CFG_TEST_SKIP_PRODUCER = 0, 1, 2, 3
+CFG_FP8_LOAD_BURST, CFG_FP8_L2_PREFETCH = 4, 5
 
 
 class HqWeight(C.Structure):

@@ -46,7 +46,7 @@ int32_t check_weight(const hq_weight* w) {
   return HQ_OK;
 }
 
-int64_t g_cfg[4] = {8, 9, 1 << 22, 0};
+int64_t g_cfg[6] = {8, 9, 1 << 22, 0, 2, 0};
 
 void fill_grouped(GroupedParams& g, const hq_weight* w, const hq_weight* w_up) {
   g.format = w->format;
@@ -119,13 +119,14 @@ const char* hq_error_string(int32_t code) {
 }
 
 int32_t hq_config_set(int32_t key, int64_t value) {
-  if (key < 0 || key > 3 || value < 0) return HQ_ERR_FORMAT;
+  if (key < 0 || key > 5 || value < 0) return HQ_ERR_FORMAT;
+  if (key == HQ_CFG_FP8_LOAD_BURST && value != 1 && value != 2 && value != 4) return HQ_ERR_FORMAT;
   if (key == HQ_CFG_SPIN_LIMIT && (value < 1 || value > (1ll << 31) - 1)) return HQ_ERR_FORMAT;
   g_cfg[key] = value;
   return HQ_OK;
 }
 
-int64_t hq_config_get(int32_t key) { return (key < 0 || key > 3) ? -1 : g_cfg[key]; }
+int64_t hq_config_get(int32_t key) { return (key < 0 || key > 5) ? -1 : g_cfg[key]; }
 
 int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* stream) {
   if (status_dev == nullptr || out_host == nullptr) return HQ_ERR_NULL;
@@ -319,6 +320,8 @@ static void fill_fp8_native(Fp8GroupedParams& g, const hq_weight* w) {
   g.bias_dtype = w->bias_dtype;
   g.spin_limit = (uint32_t)g_cfg[HQ_CFG_SPIN_LIMIT];
   g.test_skip_producer = (int)g_cfg[HQ_CFG_TEST_SKIP_PRODUCER];
+  g.load_burst = (int)g_cfg[HQ_CFG_FP8_LOAD_BURST];
+  g.load_burst_prefetch_off = g_cfg[HQ_CFG_FP8_L2_PREFETCH] == 0;
 }
 
 int32_t hq_fp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map, int64_t n_rows,

@@ -99,7 +99,7 @@ struct Fp8GroupedParams {
   void* y;                      // plain mode output
   int y_dtype;
   int64_t y_stride;
-  bool y_tile_ok;               // set by the launcher: 16-bit rows can leave as 16-byte stores
+  bool y_vec_ok;                // set by the launcher: output row segments can be written with 16-byte stores
   uint8_t* hq;                  // gated mode output: e4m3 codes [n_rows, N] ...
   float* hs;                    // ... and scales [n_rows, N/128] of act(gate) * up, expert-sorted
   hq_act_args act;
@@ -108,6 +108,9 @@ struct Fp8GroupedParams {
   int32_t* status;
   uint32_t spin_limit;          // polls per bounded wait (0 = default)
   int test_skip_producer;       // test hook: the TMA warp issues nothing, so every consumer wait runs out
+  int load_burst;               // 128-column blocks the TMA warp requests together: 1, 2 or 4 (0 = default)
+  int load_burst_prefetch_off;  // 1 = do not pull weight rows into L2 ahead of the operand copies
+  int l2_prefetch;              // set by the launcher
 };
 bool fp8_grouped_supported(int64_t n, int64_t k);
 int32_t launch_fp8_grouped(const Fp8GroupedParams& p, cudaStream_t stream);

@@ -117,6 +117,8 @@ class MoEExperts:
         w0 = first._weight_struct()
         w1 = self.up._weight_struct() if self.up is not None else None
         status = first._status_buf(x.device)
+        self._last_tables = tables
+        ev0 = self._mark()
         L.check(L.lib().hq_moe_gather_forward(C.byref(w0), None if w1 is None else C.byref(w1), C.byref(self.act),
                                               _ptr(x), dt_code(x.dtype), L.ROWS_PER_TOKEN, t, k,
                                               _ptr(tables.expert_bounds), _ptr(tables.sorted_assign),
@@ -130,6 +132,7 @@ class MoEExperts:
                                               _ptr(tables.sorted_token), _ptr(tables.workspace), _ptr(y),
                                               dt_code(y.dtype), L.ROWS_SORTED, _ptr(status), _stream()),
                 "hq_moe_gather_forward(down)")
+        self._mark(ev0)
         if _skip_reduce:       # measurement aid: the two projections only, output left expert-sorted
             return y
         out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype or xs.dtype, tables.inv_perm, shared_out)
@@ -178,6 +181,8 @@ class MoEExperts:
         hq_ = torch.empty((t * k, inter), dtype=torch.uint8, device=dev)
         hs = torch.empty((t * k, inter // 128), dtype=torch.float32, device=dev)
         wg, wu = self.gate._weight_struct(), self.up._weight_struct()
+        self._last_tables = tables
+        ev0 = self._mark()
         L.check(lib.hq_moe_fp8_gate_up_forward(C.byref(wg), C.byref(wu), C.byref(self.act), _ptr(xq), _ptr(xsc), t, k,
                                                _ptr(tables.expert_bounds), _ptr(hq_), _ptr(hs), _ptr(status),
                                                _stream()), "hq_moe_fp8_gate_up_forward")
@@ -189,10 +194,57 @@ class MoEExperts:
                                               _ptr(tables.sorted_assign), None, _ptr(y),
                                               dt_code(y.dtype), self.down.n, L.ROWS_SORTED, _ptr(status), _stream()),
                 "hq_moe_fp8_gather_forward(down)")
+        self._mark(ev0)
         if _skip_reduce:
             return y
         out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype, tables.inv_perm, shared_out)
         return out.reshape(*lead, self.down.n)
+
+    def forward_fp8_dense(self, xs: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """A one-expert block applied to every token (DeepSeek's shared expert,
+        hanzo-engine/src/models/deepseek3.rs:783-786) on the FP8 path: 1x128 row quantizer, the fused gate/up
+        launch over one expert holding all rows, and the dense FP8 down projection.  No routing tables."""
+        _require_cuda(xs, "xs")
+        if self.gate is None or self.gate.format != L.FMT_FP8_BLOCK or self.n_experts != 1:
+            raise L.HqError("forward_fp8_dense needs a one-expert block-FP8 bank with separate gate and up")
+        lead = xs.shape[:-1]
+        x = xs.reshape(-1, xs.shape[-1]).contiguous()
+        t, hidden = x.shape
+        dev = x.device
+        lib = L.lib()
+        status = self.gate._status_buf(dev)
+        bounds = getattr(self, "_dense_bounds", None)
+        if bounds is None or bounds[1] != t or bounds[0].device != dev:
+            bounds = (torch.tensor([0, t], dtype=torch.int32, device=dev), t)
+            self._dense_bounds = bounds
+        xq = torch.empty((t, hidden), dtype=torch.uint8, device=dev)
+        xsc = torch.empty((t, hidden // 128), dtype=torch.float32, device=dev)
+        L.check(lib.hq_fp8_quant_rows(_ptr(x), dt_code(x.dtype), hidden, None, t, hidden, _ptr(xq), _ptr(xsc),
+                                      _stream()), "hq_fp8_quant_rows")
+        inter = self.gate.n
+        hq_ = torch.empty((t, inter), dtype=torch.uint8, device=dev)
+        hs = torch.empty((t, inter // 128), dtype=torch.float32, device=dev)
+        wg, wu, wd = self.gate._weight_struct(), self.up._weight_struct(), self.down._weight_struct()
+        L.check(lib.hq_moe_fp8_gate_up_forward(C.byref(wg), C.byref(wu), C.byref(self.act), _ptr(xq), _ptr(xsc), t, 1,
+                                               _ptr(bounds[0]), _ptr(hq_), _ptr(hs), _ptr(status), _stream()),
+                "hq_moe_fp8_gate_up_forward(shared)")
+        out_dtype = out_dtype or xs.dtype
+        y = torch.empty((t, self.down.n), dtype=out_dtype, device=dev)
+        L.check(lib.hq_fp8_linear_forward(C.byref(wd), _ptr(hq_), _ptr(hs), t, _ptr(y), dt_code(out_dtype), self.down.n,
+                                          _ptr(status), _stream()), "hq_fp8_linear_forward(shared)")
+        return y.reshape(*lead, self.down.n)
+
+    def _mark(self, start=None):
+        """Measurement hook: with `gemm_events` set to a list, every forward appends a (start, end) CUDA event
+        pair around its two expert-GEMM launches."""
+        evs = getattr(self, "gemm_events", None)
+        if evs is None:
+            return None
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        if start is not None:
+            evs.append((start, ev))
+        return ev
 
     def forward_layer(self, xs: torch.Tensor, logits: torch.Tensor, config: MoeRouterTopKConfig,
                       selection_bias: torch.Tensor | None = None, expert_scale: torch.Tensor | None = None,

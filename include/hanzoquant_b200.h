@@ -122,6 +122,12 @@ int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* str
  * left in flight (no copy and no MMA is issued in that launch). */
 #define HQ_CFG_SPIN_LIMIT 2
 #define HQ_CFG_TEST_SKIP_PRODUCER 3
+/* HQ_CFG_FP8_LOAD_BURST: 128-column blocks the FP8 expert GEMM requests from memory together (1, 2 or 4; default
+ * 2): more of each weight row is read in one go, at the cost of pipeline depth. */
+#define HQ_CFG_FP8_LOAD_BURST 4
+/* HQ_CFG_FP8_L2_PREFETCH: 1 = the FP8 expert GEMM pulls 1 KiB of every weight row into L2 sixteen blocks ahead of
+ * the operand copies; 0 (default) = off (it measured slower on the DeepSeek-V3-shaped layer). */
+#define HQ_CFG_FP8_L2_PREFETCH 5
 int32_t hq_config_set(int32_t key, int64_t value);
 int64_t hq_config_get(int32_t key);
 

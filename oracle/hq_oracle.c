@@ -35,7 +35,7 @@ static float half_to_float(uint16_t h) {
   float f; memcpy(&f, &b, 4); return f;
 }
 
-static float e4m3_to_float(uint8_t c) {
+static float e4m3_decode(uint8_t c) {
   int e = (c >> 3) & 15, m = c & 7;
   float v;
   if (e == 15 && m == 7) v = NAN;
@@ -43,6 +43,16 @@ static float e4m3_to_float(uint8_t c) {
   else v = ldexpf(1.0f + (float)m / 8.0f, e - 7);
   return (c & 0x80) ? -v : v;
 }
+/* the 256 values of the format, decoded once (every entry point fills it before its parallel region) */
+static float E4M3[256];
+static int e4m3_ready = 0;
+static void e4m3_init(void) {
+  if (!e4m3_ready) {
+    for (int c = 0; c < 256; ++c) E4M3[c] = e4m3_decode((uint8_t)c);
+    e4m3_ready = 1;
+  }
+}
+static inline float e4m3_to_float(uint8_t c) { return E4M3[c]; }
 
 static const float FP4[16] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
                               -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
@@ -112,6 +122,7 @@ static const void* row_scales(int fmt, const void* scales, int64_t n_row, int64_
 void oracle_linear(int fmt, const uint8_t* w, const void* scales, const float* bias, const float* x, float* y,
                    int64_t n, int64_t k, int64_t m, int threads) {
   const int64_t rb = oracle_row_bytes(fmt, k);
+  e4m3_init();
 #ifdef _OPENMP
   if (threads > 0) omp_set_num_threads(threads);
 #endif
@@ -138,6 +149,7 @@ void oracle_gather(int fmt, const uint8_t* w, const void* scales, const float* b
                    int64_t n, int64_t k, int n_experts, const int32_t* bounds, const int32_t* xrows,
                    const int32_t* orows, int threads) {
   const int64_t rb = oracle_row_bytes(fmt, k);
+  e4m3_init();
 #ifdef _OPENMP
   if (threads > 0) omp_set_num_threads(threads);
 #endif

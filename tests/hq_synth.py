@@ -148,60 +148,69 @@ def _bank_slices(layer, experts):
     return fmt, layer.blocks.index_select(0, idx).cpu().numpy(), layer.scales.index_select(0, idx).cpu().numpy(), bias
 
 
-def oracle_moe_subset(experts, x_sub: np.ndarray, ids_sub: np.ndarray, w_sub: np.ndarray, *, fp8_act=False,
-                      threads=0, timer=None):
-    """The expert block of `experts` (an engine_b200.MoEExperts living on the GPU) for the token rows x_sub
-    [S, H] with routing ids_sub / w_sub [S, k], computed by the C oracle (dequantize each expert row to f32, f32
-    dot) from host copies of the experts those tokens touch.  Rounding points mirror the CUDA path: the 16-bit
-    path rounds the activated intermediate to f16; the FP8-activation path quantizes x 1x128, rounds gate and up to
-    f16, rounds the activated product to f16 and quantizes it 1x128.  Returns f32 [S, H].
-    `timer`, if given, is called with the seconds spent in the oracle's arithmetic (bank copies excluded)."""
-    import time
+def oracle_moe_host(first_banks, down_bank, n_used, act, x_sub, ids_c, w_sub, *, fp8_act=False, threads=0):
+    """Expert block on host copies of `n_used` experts.  first_banks: [(fmt, bytes [n_used, N, row_bytes], scales,
+    bias)] -- one interleaved gate/up bank, or the gate and the up bank; ids_c [S, k] index into the copies (-1 =
+    skipped slot); act = (code, has_limit, limit, alpha).  Rounding points mirror the CUDA path: the 16-bit path
+    rounds the activated intermediate to f16; the FP8-activation path quantizes x 1x128, rounds gate and up to f16,
+    rounds the activated product to f16 and quantizes it 1x128.  Returns f32 [S, H]."""
     from oracle import cbuild, formats as F, moe as M
-    s, k = ids_sub.shape
-    used = sorted(set(int(v) for v in ids_sub.reshape(-1) if 0 <= int(v) < experts.n_experts))
-    remap = {e: j for j, e in enumerate(used)}
-    ids_c = np.array([[remap.get(int(v), -1) for v in row] for row in ids_sub], dtype=np.int64)
+    s, k = ids_c.shape
     f16 = lambda a: a.astype(np.float16).astype(np.float32)
     qdq = lambda a: F.fp8_vector_dequant(*F.fp8_vector_quant(np.ascontiguousarray(a).reshape(-1), 128), 128) \
         .reshape(a.shape).astype(np.float32)
     # stable (token, slot) order grouped by expert
     flat = [(int(ids_c[t, sl]), t * k + sl) for t in range(s) for sl in range(k) if ids_c[t, sl] >= 0]
     flat.sort(key=lambda p: p[0])
-    bounds = np.zeros(len(used) + 1, np.int32)
+    bounds = np.zeros(n_used + 1, np.int32)
     for e_c, _ in flat:
         bounds[e_c + 1] += 1
     bounds = np.cumsum(bounds).astype(np.int32)
     assign = np.array([a for _, a in flat], np.int32)
     tok = assign // k
     rows = np.arange(assign.size, dtype=np.int32)
-    interleaved = experts.gate_up is not None
-    first = experts.gate_up if interleaved else experts.gate
-    banks = [_bank_slices(first, used)] + ([] if interleaved else [_bank_slices(experts.up, used)]) + \
-            [_bank_slices(experts.down, used)]
-    t0 = time.perf_counter()
     x_in = qdq(x_sub) if fp8_act else x_sub.astype(np.float32)
-    outs = []
-    for fmt, data, scales, bias in banks[:-1]:
-        outs.append(cbuild.gather(fmt, data, scales, bias, x_in, len(used), bounds, tok, rows, assign.size, threads))
-    if interleaved:
+    outs = [cbuild.gather(fmt, data, scales, bias, x_in, n_used, bounds, tok, rows, assign.size, threads)
+            for fmt, data, scales, bias in first_banks]
+    if len(first_banks) == 1:
         g, u = outs[0][:, 0::2], outs[0][:, 1::2]
     else:
         g, u = outs
     if fp8_act:
         g, u = f16(g), f16(u)
-    if experts.act.act == M.ACT_GPTOSS:
-        hmid = M.gptoss_swiglu(g, u, experts.act.alpha, experts.act.limit)
+    code, has_limit, limit, alpha = act
+    if code == M.ACT_GPTOSS:
+        hmid = M.gptoss_swiglu(g, u, alpha, limit)
     else:
-        hmid = M.swiglu(g, u, experts.act.limit if experts.act.has_limit else None)
+        hmid = M.swiglu(g, u, limit if has_limit else None)
     hmid = qdq(f16(hmid)) if fp8_act else f16(hmid)
-    fmt, data, scales, bias = banks[-1]
-    y = cbuild.gather(fmt, data, scales, bias, hmid, len(used), bounds, rows, rows, assign.size, threads)
+    fmt, data, scales, bias = down_bank
+    y = cbuild.gather(fmt, data, scales, bias, hmid, n_used, bounds, rows, rows, assign.size, threads)
     out = np.zeros((s, y.shape[1]), np.float32)
     order = np.argsort(assign, kind="stable")            # add a token's slots in slot order, as the reduce does
     for pos in order:
         a = int(assign[pos])
         out[a // k] += np.float32(w_sub[a // k, a % k]) * y[pos]
+    return out
+
+
+def oracle_moe_subset(experts, x_sub: np.ndarray, ids_sub: np.ndarray, w_sub: np.ndarray, *, fp8_act=False,
+                      threads=0, timer=None):
+    """The expert block of `experts` (an engine_b200.MoEExperts living on the GPU) for the token rows x_sub
+    [S, H] with routing ids_sub / w_sub [S, k], computed by the C oracle (dequantize each expert row to f32, f32
+    dot) from host copies of the experts those tokens touch.  `timer`, if given, is called with the seconds spent
+    in the oracle's arithmetic (bank copies excluded)."""
+    import time
+    used = sorted(set(int(v) for v in ids_sub.reshape(-1) if 0 <= int(v) < experts.n_experts))
+    remap = {e: j for j, e in enumerate(used)}
+    ids_c = np.array([[remap.get(int(v), -1) for v in row] for row in ids_sub], dtype=np.int64)
+    interleaved = experts.gate_up is not None
+    first = [_bank_slices(experts.gate_up, used)] if interleaved else \
+        [_bank_slices(experts.gate, used), _bank_slices(experts.up, used)]
+    down = _bank_slices(experts.down, used)
+    act = (experts.act.act, experts.act.has_limit, experts.act.limit, experts.act.alpha)
+    t0 = time.perf_counter()
+    out = oracle_moe_host(first, down, len(used), act, x_sub, ids_c, w_sub, fp8_act=fp8_act, threads=threads)
     if timer is not None:
         timer(time.perf_counter() - t0)
     return out
