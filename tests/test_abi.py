@@ -34,6 +34,17 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
     assert lib.hq_error_string(-2).decode() == "unsupported size"
 
 
+def test_every_reference_named_symbol_is_exported(lib):
+    text = open(os.path.join(ROOT, "include", "hanzoquant_compat.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"#define[^\n]*(\\\n[^\n]*)*", "", text)          # macro bodies declare nothing by themselves
+    names = set(re.findall(r"\b((?:launch_|moe_router_topk_|gptoss_swiglu_|fused_glu_|mxfp4_get_)[a-z0-9_]+)\s*\(", text))
+    names |= set(re.findall(r"HQ_COMPAT_[A-Z0-9_]+\((\w+)\);", text))
+    assert len(names) >= 50, sorted(names)
+    for n in sorted(names):
+        assert hasattr(lib, n), n
+
+
 def test_host_side_argument_errors(lib):
     from engine_b200 import _lib as L
     w = L.HqWeight(L.FMT_Q8_0, 1, 64, 100, 16, 0, 0, 0, 0)           # K % 256 != 0
