@@ -74,7 +74,13 @@ SIGNATURES = {
     "hq_moe_layer_forward": (_I32, [C.POINTER(HqMoeLayer), _P, _I32, _P, _I32, _I64, _P, _P, _I32, _P, _I64, _P, _P]),
     "hq_linear_workspace_bytes": (_I64, [C.POINTER(HqWeight), _I64]),
     "hq_linear_forward_ws": (_I32, [C.POINTER(HqWeight), _P, _I32, _I64, _P, _I32, _I64, _I64, _P, _I64, _P, _P]),
+    "hq_linear_glu_forward": (_I32, [C.POINTER(HqWeight), C.POINTER(HqWeight), C.POINTER(HqActArgs), _P, _I32, _I64, _P,
+                                     _I32, _I64, _I64, _P, _P]),
+    "hq_linear_qkv_forward": (_I32, [C.POINTER(HqWeight), C.POINTER(HqWeight), C.POINTER(HqWeight), _P, _I32, _I64, _P,
+                                     _P, _P, _I32, _I64, _P, _P]),
+    "hq_dense_gemv": (_I32, [_P, _I32, _I64, _I64, _P, _I32, _P, _I32, _I64, _P, _I32, _I64, _I64, _P]),
     "hq_router_topk": (_I32, [_P, _I32, _I64, C.POINTER(HqRouterArgs), _P, _P, _P]),
+    "hq_router_topk_grouped": (_I32, [_P, _I32, _I64, C.POINTER(HqRouterArgs), _I32, _I32, _I32, _P, _P, _P]),
     "hq_moe_dispatch_workspace_bytes": (_I64, [_I64, _I32, _I32]),
     "hq_moe_dispatch_build": (_I32, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P, _I64, _P]),
     "hq_moe_dispatch_build_noalloc": (_I32, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P]),

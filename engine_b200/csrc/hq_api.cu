@@ -186,6 +186,75 @@ int32_t hq_linear_forward(const hq_weight* w, const void* x, int32_t x_dtype, in
   return hq_linear_forward_ws(w, x, x_dtype, x_stride, y, y_dtype, y_stride, m, nullptr, 0, status_dev, stream);
 }
 
+// ---- fused dense decode set ----------------------------------------------------------------------------
+int32_t hq_linear_glu_forward(const hq_weight* w_gate, const hq_weight* w_up, const hq_act_args* act, const void* x,
+                              int32_t x_dtype, int64_t x_stride, void* y, int32_t y_dtype, int64_t y_stride, int64_t m,
+                              int32_t* status_dev, void* stream) {
+  int32_t rc = check_weight(w_gate);
+  if (rc != HQ_OK) return rc;
+  if (w_up != nullptr) {
+    rc = check_weight(w_up);
+    if (rc != HQ_OK) return rc;
+    if (w_up->format != w_gate->format || w_up->n != w_gate->n || w_up->k != w_gate->k) return HQ_ERR_SHAPE;
+  } else if (w_gate->n % 2 != 0) {
+    return HQ_ERR_SHAPE;
+  }
+  if (w_gate->n_experts != 1 || (w_up != nullptr && w_up->n_experts != 1)) return HQ_ERR_SHAPE;
+  if (act == nullptr) return HQ_ERR_NULL;
+  if (act->act != HQ_ACT_SWIGLU && act->act != HQ_ACT_GPTOSS) return HQ_ERR_FORMAT;
+  if (m < 0 || m > (1 << 24)) return HQ_ERR_SHAPE;
+  if (m == 0) return HQ_OK;
+  if (x == nullptr || y == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return HQ_ERR_FORMAT;
+  if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
+  const int64_t n_out = w_up != nullptr ? w_gate->n : w_gate->n / 2;
+  if (x_stride < w_gate->k || y_stride < n_out) return HQ_ERR_SHAPE;
+  if (m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS] && tensor_path_ok(w_gate, w_up, x_dtype, x_stride)) {
+    GroupedParams g{};
+    fill_grouped(g, w_gate, w_up);
+    g.m = (int)m;
+    g.x = x; g.x_dtype = x_dtype; g.x_stride = x_stride;
+    g.y = y; g.y_dtype = y_dtype; g.y_stride = y_stride;
+    g.act = *act;
+    g.status = status_dev;
+    g.tile_rows = 128;
+    g.weights_in_tmem = w_gate->format != HQ_FMT_FP8_BLOCK;
+    return launch_grouped_gemm(g, (int)((m + 127) / 128), (cudaStream_t)stream);
+  }
+  GemvParams p{};
+  fill_weight(p, w_gate, w_up);
+  p.m = (int)m;
+  p.x = x; p.x_dtype = x_dtype; p.x_stride = x_stride;
+  p.y = y; p.y_dtype = y_dtype; p.y_stride = y_stride;
+  p.act = *act;
+  p.status = status_dev;
+  return launch_gemv(p, (int)((m + 7) / 8), (cudaStream_t)stream);
+}
+
+int32_t hq_linear_qkv_forward(const hq_weight* w_q, const hq_weight* w_k, const hq_weight* w_v, const void* x,
+                              int32_t x_dtype, int64_t x_stride, void* q, void* k, void* v, int32_t y_dtype,
+                              int64_t m, int32_t* status_dev, void* stream) {
+  if (w_q == nullptr || w_k == nullptr || w_v == nullptr) return HQ_ERR_NULL;
+  if (w_q->k != w_k->k || w_q->k != w_v->k) return HQ_ERR_SHAPE;
+  int32_t rc = hq_linear_forward(w_q, x, x_dtype, x_stride, q, y_dtype, w_q->n, m, status_dev, stream);
+  if (rc == HQ_OK) rc = hq_linear_forward(w_k, x, x_dtype, x_stride, k, y_dtype, w_k->n, m, status_dev, stream);
+  if (rc == HQ_OK) rc = hq_linear_forward(w_v, x, x_dtype, x_stride, v, y_dtype, w_v->n, m, status_dev, stream);
+  return rc;
+}
+
+int32_t hq_dense_gemv(const void* w, int32_t w_dtype, int64_t n, int64_t k, const void* bias, int32_t bias_dtype,
+                      const void* x, int32_t x_dtype, int64_t x_stride, void* y, int32_t y_dtype, int64_t y_stride,
+                      int64_t m, void* stream) {
+  if (n < 1 || k < 8 || k % 8 != 0 || m < 0 || m > 8 || x_stride < k || y_stride < n) return HQ_ERR_SHAPE;
+  if (m == 0) return HQ_OK;
+  if (w == nullptr || x == nullptr || y == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(w_dtype) || !valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return HQ_ERR_FORMAT;
+  if (bias != nullptr && !valid_dtype(bias_dtype)) return HQ_ERR_FORMAT;
+  if (!aligned16(w) || (k * dtype_size(w_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
+  return launch_dense_gemv(w, w_dtype, n, k, bias, bias_dtype, x, x_dtype, x_stride, y, y_dtype, y_stride, (int)m,
+                           (cudaStream_t)stream);
+}
+
 int32_t hq_router_topk(const void* logits, int32_t logits_dtype, int64_t n_rows, const hq_router_args* args,
                        uint32_t* ids_out, float* weights_out, void* stream) {
   if (args == nullptr) return HQ_ERR_NULL;
@@ -197,7 +266,30 @@ int32_t hq_router_topk(const void* logits, int32_t logits_dtype, int64_t n_rows,
   if (args->top_k < 1 || args->top_k > 32 || args->top_k > args->n_experts) return HQ_ERR_SHAPE;
   if (args->score_mode < 0 || args->score_mode > 2 || args->weight_mode < 0 || args->weight_mode > 2)
     return HQ_ERR_FORMAT;
-  return launch_router(logits, logits_dtype, n_rows, *args, ids_out, weights_out, (cudaStream_t)stream);
+  return launch_router(logits, logits_dtype, n_rows, *args, 1, 1, 0, ids_out, weights_out, (cudaStream_t)stream);
+}
+
+int32_t hq_router_topk_grouped(const void* logits, int32_t logits_dtype, int64_t n_rows, const hq_router_args* args,
+                               int32_t n_group, int32_t topk_group, int32_t group_score_mode, uint32_t* ids_out,
+                               float* weights_out, void* stream) {
+  if (args == nullptr) return HQ_ERR_NULL;
+  if (n_group < 1 || n_group > 32 || topk_group < 1 || topk_group > n_group) return HQ_ERR_SHAPE;
+  if (args->n_experts % n_group != 0) return HQ_ERR_SHAPE;
+  if (group_score_mode != 0 && group_score_mode != 1) return HQ_ERR_FORMAT;
+  if (group_score_mode == 0 && n_group > 1 && args->n_experts / n_group < 2) return HQ_ERR_SHAPE;
+  if ((int64_t)topk_group * (args->n_experts / n_group) < args->top_k) return HQ_ERR_SHAPE;
+  const int32_t rc = hq_router_topk(nullptr, logits_dtype, 0, args, ids_out, weights_out, stream);   // argument checks
+  if (rc != HQ_OK) return rc;
+  if (n_rows < 0) return HQ_ERR_SHAPE;
+  if (n_rows == 0) return HQ_OK;
+  if (logits == nullptr || ids_out == nullptr || weights_out == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(logits_dtype)) return HQ_ERR_FORMAT;
+  if (args->n_experts < 1 || args->n_experts > 1024) return HQ_ERR_SHAPE;
+  if (args->top_k < 1 || args->top_k > 32 || args->top_k > args->n_experts) return HQ_ERR_SHAPE;
+  if (args->score_mode < 0 || args->score_mode > 2 || args->weight_mode < 0 || args->weight_mode > 2)
+    return HQ_ERR_FORMAT;
+  return launch_router(logits, logits_dtype, n_rows, *args, n_group, topk_group, group_score_mode, ids_out, weights_out,
+                       (cudaStream_t)stream);
 }
 
 int64_t hq_moe_dispatch_workspace_bytes(int64_t n_tokens, int32_t top_k, int32_t n_experts) {

@@ -138,8 +138,8 @@ int32_t launch_dispatch_noalloc(const uint32_t* ids, int64_t n_tokens, int top_k
                                 cudaStream_t stream);
 
 // ---- router (hq_router.cu) --------------------------------------------------------
-int32_t launch_router(const void* logits, int dtype, int64_t n_rows, const hq_router_args& a, uint32_t* ids,
-                      float* weights, cudaStream_t stream);
+int32_t launch_router(const void* logits, int dtype, int64_t n_rows, const hq_router_args& a, int n_group,
+                      int topk_group, int group_mode, uint32_t* ids, float* weights, cudaStream_t stream);
 
 // ---- elementwise / reduce (hq_elementwise.cu) --------------------------------------
 int32_t launch_weighted_reduce(const void* y, int y_dtype, const float* w, const int32_t* row_map,
@@ -172,6 +172,11 @@ int32_t launch_ep_unpack_meta(const hq_ep_layout& l, const void* recv, uint32_t*
 int32_t launch_fp8_gather_rows(const void* src_codes, int64_t src_code_stride, const void* src_scales,
                                int64_t src_scale_stride, const int32_t* row_map, const int32_t* n_valid,
                                int64_t n_rows, int64_t k, uint8_t* codes, float* scales, cudaStream_t stream);
+
+// ---- unquantized decode mat-vec (hq_gemv_dense.cu) -----------------------------------
+int32_t launch_dense_gemv(const void* w, int w_dtype, int64_t n, int64_t k, const void* bias, int bias_dtype,
+                          const void* x, int x_dtype, int64_t x_stride, void* y, int y_dtype, int64_t y_stride, int m,
+                          cudaStream_t stream);
 
 // ---- tensor-core issue-rate probe (hq_probe.cu) ---------------------------------------
 int32_t launch_probe_mma(int kind, int n_dim, int iters, int32_t* status, double* flops_out, cudaStream_t stream);

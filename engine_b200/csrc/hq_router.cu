@@ -27,7 +27,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 __global__ void __launch_bounds__(kRouterWarps * 32) router_kernel(const void* __restrict__ logits, int dtype,
-                                                                   int64_t n_rows, hq_router_args a,
+                                                                   int64_t n_rows, hq_router_args a, int n_group,
+                                                                   int topk_group, int group_mode,
                                                                    uint32_t* __restrict__ ids,
                                                                    float* __restrict__ weights) {
   extern __shared__ float rsm[];
@@ -70,6 +71,44 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_kernel(const void* _
     sel[e] = v;
   }
   __syncwarp();
+
+  // Group-limited selection (DeepSeek): experts form n_group contiguous groups; a group's score is the sum of its
+  // two best selection scores (group_mode 0, "noaux_tc") or its best one (1, "group_limited_greedy"); only the
+  // topk_group best groups stay selectable, the selection score of every other expert becomes 0
+  // (hanzo-engine/src/models/deepseek3.rs:623-690).  Lane g scores group g; ties go to the lower group.
+  if (n_group > 1) {
+    const int gs = E / n_group;
+    float gscore = -CUDART_INF_F;
+    if (lane < n_group) {
+      float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
+      for (int e = lane * gs; e < (lane + 1) * gs; ++e) {
+        const float v = sel[e];
+        if (v > t1) { t2 = t1; t1 = v; }
+        else if (v > t2) t2 = v;
+      }
+      gscore = group_mode == 0 ? t1 + t2 : t1;
+    }
+    uint32_t keep = 0;
+    bool consumed = lane >= n_group;
+    for (int r = 0; r < topk_group; ++r) {
+      float best = consumed ? -CUDART_INF_F : gscore;
+      int best_g = consumed ? 0x7fffffff : lane;
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, m);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, m);
+        if (og != 0x7fffffff && (best_g == 0x7fffffff || ov > best || (ov == best && og < best_g))) {
+          best = ov;
+          best_g = og;
+        }
+      }
+      if (best_g != 0x7fffffff) keep |= 1u << best_g;
+      if (lane == best_g) consumed = true;
+    }
+    for (int e = lane; e < E; e += 32)
+      if (((keep >> (e / gs)) & 1u) == 0u) sel[e] = 0.f;
+    __syncwarp();
+  }
 
   // k rounds of arg-max; ties go to the lower expert id.  Lane j keeps the j-th result.
   float my_w = 0.f;
@@ -118,12 +157,13 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_kernel(const void* _
   }
 }
 
-int32_t launch_router(const void* logits, int dtype, int64_t n_rows, const hq_router_args& a, uint32_t* ids,
-                      float* weights, cudaStream_t stream) {
+int32_t launch_router(const void* logits, int dtype, int64_t n_rows, const hq_router_args& a, int n_group,
+                      int topk_group, int group_mode, uint32_t* ids, float* weights, cudaStream_t stream) {
   if (n_rows == 0) return HQ_OK;
   const size_t smem = (size_t)kRouterWarps * 3 * a.n_experts * sizeof(float);
   const unsigned grid = (unsigned)((n_rows + kRouterWarps - 1) / kRouterWarps);
-  router_kernel<<<grid, kRouterWarps * 32, smem, stream>>>(logits, dtype, n_rows, a, ids, weights);
+  router_kernel<<<grid, kRouterWarps * 32, smem, stream>>>(logits, dtype, n_rows, a, n_group, topk_group, group_mode,
+                                                          ids, weights);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 

@@ -41,7 +41,10 @@ def _router_args(e: int, config: MoeRouterTopKConfig, bias, scale) -> "L.HqRoute
 
 
 def moe_router_topk(logits: torch.Tensor, config: MoeRouterTopKConfig, selection_bias: torch.Tensor | None = None,
-                    expert_scale: torch.Tensor | None = None) -> TopKOutput:
+                    expert_scale: torch.Tensor | None = None, n_group: int = 1, topk_group: int = 1,
+                    group_score: str = "top2_sum") -> TopKOutput:
+    """`n_group` > 1 adds the DeepSeek group-limited selection (hanzo-engine/src/models/deepseek3.rs:623-690):
+    group_score "top2_sum" = noaux_tc, "max" = group_limited_greedy."""
     _require_cuda(logits, "logits")
     t, e = logits.shape
     logits = logits.contiguous()
@@ -50,9 +53,29 @@ def moe_router_topk(logits: torch.Tensor, config: MoeRouterTopKConfig, selection
     bias = None if selection_bias is None else selection_bias.to(torch.float32).contiguous()
     scale = None if expert_scale is None else expert_scale.to(torch.float32).contiguous()
     args = _router_args(e, config, bias, scale)
-    L.check(L.lib().hq_router_topk(_ptr(logits), dt_code(logits.dtype), t, C.byref(args), _ptr(ids), _ptr(w),
-                                   _stream()), "hq_router_topk")
+    if n_group > 1:
+        mode = {"top2_sum": 0, "max": 1}[group_score]
+        L.check(L.lib().hq_router_topk_grouped(_ptr(logits), dt_code(logits.dtype), t, C.byref(args), n_group,
+                                               topk_group, mode, _ptr(ids), _ptr(w), _stream()),
+                "hq_router_topk_grouped")
+    else:
+        L.check(L.lib().hq_router_topk(_ptr(logits), dt_code(logits.dtype), t, C.byref(args), _ptr(ids), _ptr(w),
+                                       _stream()), "hq_router_topk")
     return TopKOutput(w, ids)
+
+
+def moe_router_forward(xs: torch.Tensor, router_weight: torch.Tensor, config: MoeRouterTopKConfig,
+                       selection_bias: torch.Tensor | None = None, **group) -> TopKOutput:
+    """Router logits + selection for hidden states: logits = xs . Wr^T in f32 (hanzo-engine/src/models/
+    qwen3_moe.rs:397-410, deepseek3.rs:588-595), by this library's mat-vec for decode-sized calls (<= 8 rows) and a
+    plain library GEMM beyond that, followed by moe_router_topk."""
+    from .quant import gemv, should_use_gemv
+    x = xs.reshape(-1, xs.shape[-1])
+    if should_use_gemv(x, router_weight):
+        logits = gemv(x, router_weight, None, out_dtype=torch.float32)
+    else:
+        logits = x.to(torch.float32) @ router_weight.to(torch.float32).t()
+    return moe_router_topk(logits, config, selection_bias, None, **group)
 
 
 def moe_weighted_reduce(y: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, row_map: torch.Tensor | None = None,

@@ -372,6 +372,96 @@ class MXFP4Layer(QuantMethod):
         return self if self.n_experts == 1 else MXFP4Layer(self.blocks[e], self.scales[e])
 
 
+# ---- fused dense decode set (hanzo-quant/src/lib.rs:1116-1204, gemv/mod.rs) --------------------------
+
+def try_fused_quantized_gate_up(xs: torch.Tensor, gate: QuantMethod, up: QuantMethod, act: int = L.ACT_SWIGLU,
+                                limit: float | None = None, alpha: float = 1.702,
+                                out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """act(xs . Wgate^T) * (xs . Wup^T) in one launch (hanzo-quant/src/lib.rs:1116-1160).  Returns None where the
+    reference's function would (biases, mismatched layers, expert banks), so callers keep their unfused route."""
+    if getattr(gate, "bias", None) is not None or getattr(up, "bias", None) is not None:
+        return None
+    if gate.format != up.format or (gate.n, gate.k) != (up.n, up.k) or gate.n_experts != 1 or up.n_experts != 1:
+        return None
+    if xs.shape[-1] != gate.k or xs.dtype not in _DT:
+        return None
+    _require_cuda(xs, "xs")
+    lead = xs.shape[:-1]
+    x = xs.reshape(-1, gate.k)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    m = x.shape[0]
+    if m == 0:
+        return None
+    if x.dtype != torch.float16 and tensor_path_expected(gate, m, dense=True):
+        x = convert(x.contiguous(), torch.float16, gate._status_buf(xs.device))
+    out_dtype = out_dtype or xs.dtype
+    y = torch.empty((m, gate.n), dtype=out_dtype, device=xs.device)
+    a = L.HqActArgs(act, int(limit is not None), 0.0 if limit is None else limit, alpha)
+    wg, wu = gate._weight_struct(), up._weight_struct()
+    L.check(L.lib().hq_linear_glu_forward(C.byref(wg), C.byref(wu), C.byref(a), _ptr(x), dt_code(x.dtype),
+                                          x.stride(0) if m > 1 else gate.k, _ptr(y), dt_code(out_dtype), gate.n, m,
+                                          _ptr(gate._status_buf(xs.device)), _stream()), "hq_linear_glu_forward")
+    return y.reshape(*lead, gate.n)
+
+
+def try_fused_quantized_qkv(xs: torch.Tensor, q: QuantMethod, k: QuantMethod, v: QuantMethod,
+                            out_dtype: torch.dtype | None = None):
+    """The three attention projections of one activation in one call (hanzo-quant/src/lib.rs:1162-1204)."""
+    layers = (q, k, v)
+    if any(getattr(l, "bias", None) is not None for l in layers) or any(l.n_experts != 1 for l in layers):
+        return None
+    if len({l.format for l in layers}) != 1 or any(l.k != xs.shape[-1] for l in layers) or xs.dtype not in _DT:
+        return None
+    _require_cuda(xs, "xs")
+    lead = xs.shape[:-1]
+    x = xs.reshape(-1, q.k).contiguous()
+    m = x.shape[0]
+    if m == 0:
+        return None
+    if x.dtype != torch.float16 and tensor_path_expected(q, m, dense=True):
+        x = convert(x, torch.float16, q._status_buf(xs.device))
+    out_dtype = out_dtype or xs.dtype
+    outs = [torch.empty((m, l.n), dtype=out_dtype, device=xs.device) for l in layers]
+    ws = [l._weight_struct() for l in layers]
+    L.check(L.lib().hq_linear_qkv_forward(C.byref(ws[0]), C.byref(ws[1]), C.byref(ws[2]), _ptr(x), dt_code(x.dtype),
+                                          q.k, _ptr(outs[0]), _ptr(outs[1]), _ptr(outs[2]), dt_code(out_dtype), m,
+                                          _ptr(q._status_buf(xs.device)), _stream()), "hq_linear_qkv_forward")
+    return tuple(o.reshape(*lead, o.shape[-1]) for o in outs)
+
+
+MAX_GEMV_BATCH_SIZE = 8
+
+
+def should_use_gemv(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """hanzo-quant/src/gemv/mod.rs:65-110: CUDA tensors, 1..8 rows, K a multiple of 8."""
+    if not (x.is_cuda and w.is_cuda) or w.dim() != 2 or x.shape[-1] != w.shape[1] or w.shape[1] % 8:
+        return False
+    rows = 1
+    for d in x.shape[:-1]:
+        rows *= d
+    return 1 <= rows <= MAX_GEMV_BATCH_SIZE
+
+
+def gemv(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+         out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Unquantized decode mat-vec y = x . w^T (+ bias), w [N, K] f16 / bf16 / f32 (hanzo-quant/src/gemv/mod.rs:120-185)."""
+    _require_cuda(x, "x")
+    if not should_use_gemv(x, w):
+        raise L.HqError(f"GEMV batch size exceeds maximum {MAX_GEMV_BATCH_SIZE} or shapes disagree")
+    lead = x.shape[:-1]
+    k = w.shape[1]
+    xr = x.reshape(-1, k).contiguous()
+    m = xr.shape[0]
+    w = w.contiguous()
+    out_dtype = out_dtype or x.dtype
+    y = torch.empty((m, w.shape[0]), dtype=out_dtype, device=x.device)
+    L.check(L.lib().hq_dense_gemv(_ptr(w), dt_code(w.dtype), w.shape[0], k, _ptr(bias),
+                                  0 if bias is None else dt_code(bias.dtype), _ptr(xr), dt_code(xr.dtype), k, _ptr(y),
+                                  dt_code(out_dtype), w.shape[0], m, _stream()), "hq_dense_gemv")
+    return y.reshape(*lead, w.shape[0])
+
+
 # ---- FP8 quantizers (hanzo-quant/src/vector_fp8/ops.rs, blockwise_fp8/ops.rs) --------------------
 
 def fp8_vector_quantize(x: torch.Tensor):

@@ -102,6 +102,14 @@ typedef struct hq_weight {
   const void* fp8_rel_scale;   /* f32 [E, ceil(N/128), ceil(K/128)] */
 } hq_weight;
 
+/* parameters of a gated activation (HQ_ACT_*) */
+typedef struct hq_act_args {
+  int32_t act;          /* HQ_ACT_* */
+  int32_t has_limit;    /* SWIGLU: clamp gate<=limit, |up|<=limit first */
+  float limit;          /* GPTOSS: L */
+  float alpha;          /* GPTOSS: alpha */
+} hq_act_args;
+
 /* ---- library ------------------------------------------------------------ */
 int32_t hq_abi_version(void);
 const char* hq_error_string(int32_t code);
@@ -161,6 +169,27 @@ int32_t hq_linear_forward_ws(const hq_weight* w, const void* x, int32_t x_dtype,
                              int32_t y_dtype, int64_t y_stride, int64_t m, void* workspace, int64_t workspace_bytes,
                              int32_t* status_dev, void* stream);
 
+/* ---- fused dense decode set ---------------------------------------------------
+ * hq_linear_glu_forward: y[m, n] = act(x . Wgate^T) * (x . Wup^T) in one launch, the two mat-vecs sharing the staged
+ * activations.  Replaces launch_mmvq_gguf_{q4_k,q8_0}_*_fused_glu (QuantMethod-level try_fused_quantized_gate_up,
+ * hanzo-quant/src/lib.rs:1116-1160; gguf/fast_mmvq.rs:463-700; kernel mmvq_gguf.cu:788-900).  w_up NULL = the rows
+ * of w_gate interleave gate / up and y has n / 2 columns.  Any format; m >= 9 takes the tensor-core kernel when the
+ * activations are f16.
+ * hq_linear_qkv_forward: the three attention projections of one activation in one call (three back-to-back
+ * launches; the reference's fused_qkv kernel, gguf/fast_mmvq.rs:702-925, saves the same host work).  q / k / v are
+ * [m, n_q] / [m, n_k] / [m, n_v], dense.
+ * hq_dense_gemv: unquantized weights W [n, k] in f16 / bf16 / f32, 1..8 activation rows: launch_gemv_{bf16,f16,f32}
+ * (hanzo-quant/src/gemv/mod.rs:120-185, kernels/gemv/gemv.cu:51-282).  k % 8 == 0, W rows 16-byte aligned. */
+int32_t hq_linear_glu_forward(const hq_weight* w_gate, const hq_weight* w_up, const hq_act_args* act, const void* x,
+                              int32_t x_dtype, int64_t x_stride, void* y, int32_t y_dtype, int64_t y_stride, int64_t m,
+                              int32_t* status_dev, void* stream);
+int32_t hq_linear_qkv_forward(const hq_weight* w_q, const hq_weight* w_k, const hq_weight* w_v, const void* x,
+                              int32_t x_dtype, int64_t x_stride, void* q, void* k, void* v, int32_t y_dtype,
+                              int64_t m, int32_t* status_dev, void* stream);
+int32_t hq_dense_gemv(const void* w, int32_t w_dtype, int64_t n, int64_t k, const void* bias, int32_t bias_dtype,
+                      const void* x, int32_t x_dtype, int64_t x_stride, void* y, int32_t y_dtype, int64_t y_stride,
+                      int64_t m, void* stream);
+
 /* ---- router: moe_router_topk ---------------------------------------------
  * Replaces moe_router_topk_{f32,bf16,f16} (hanzo-engine/src/cuda/ffi.rs:466-520,
  * kernel hanzo-engine/src/cuda/sort.cu:1048-1201) with the canonical tie-break
@@ -179,6 +208,14 @@ typedef struct hq_router_args {
 } hq_router_args;
 int32_t hq_router_topk(const void* logits, int32_t logits_dtype, int64_t n_rows, const hq_router_args* args,
                        uint32_t* ids_out, float* weights_out, void* stream);
+/* Group-limited selection of the DeepSeek routers (hanzo-engine/src/models/deepseek3.rs:623-690): the experts form
+ * n_group contiguous groups; a group's score is the sum of its two best selection scores (group_score_mode 0,
+ * "noaux_tc") or its best one (1, "group_limited_greedy"); only the topk_group best groups stay selectable (the
+ * selection score of every other expert becomes 0, as the reference's mask multiply does), then the usual top-k.
+ * Ties between groups go to the lower group.  n_group <= 32, n_experts % n_group == 0. */
+int32_t hq_router_topk_grouped(const void* logits, int32_t logits_dtype, int64_t n_rows, const hq_router_args* args,
+                               int32_t n_group, int32_t topk_group, int32_t group_score_mode, uint32_t* ids_out,
+                               float* weights_out, void* stream);
 
 /* ---- dispatch tables: moe_dispatch_build ----------------------------------
  * Replaces launch_moe_dispatch (hanzo-quant/src/gguf/ffi.rs:251-262; kernels
@@ -230,12 +267,6 @@ int32_t hq_moe_dispatch_build_noalloc(const uint32_t* ids, int64_t n_tokens, int
  * act != HQ_ACT_NONE fuses the gated activation: with `w_up` given, W is the
  * gate bank and w_up the up bank (out [T,k,N]); with w_up NULL the bank rows
  * interleave gate/up (row 2i = gate_i, 2i+1 = up_i) and out is [T,k,N/2]. */
-typedef struct hq_act_args {
-  int32_t act;          /* HQ_ACT_* */
-  int32_t has_limit;    /* SWIGLU: clamp gate<=limit, |up|<=limit first */
-  float limit;          /* GPTOSS: L */
-  float alpha;          /* GPTOSS: alpha */
-} hq_act_args;
 #define HQ_ROWS_PER_TOKEN 0
 #define HQ_ROWS_PER_SLOT 1
 #define HQ_ROWS_SORTED 2

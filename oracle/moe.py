@@ -74,6 +74,40 @@ def router_topk(logits: np.ndarray, top_k: int, score_mode: int, weight_mode: in
     return ids, vals
 
 
+def router_topk_grouped(logits: np.ndarray, top_k: int, score_mode: int, n_group: int, topk_group: int,
+                        group_score: str = "top2_sum", selection_bias: np.ndarray | None = None,
+                        renormalize: bool = True, norm_min: float = 1e-20, output_scale: float = 1.0):
+    """DeepSeek group-limited routing (hanzo-engine/src/models/deepseek3.rs:623-690): scores -> + bias -> group
+    score (sum of the two best of a group for "top2_sum" / noaux_tc, the best one for "max" /
+    group_limited_greedy) -> keep the topk_group best groups, zero the selection score elsewhere -> top-k ->
+    weights = unbiased scores of the selected experts, renormalised, scaled.  Ties by (score DESC, index ASC)."""
+    lg = np.asarray(logits, dtype=np.float32)
+    t, e = lg.shape
+    sc = _softmax_rows(lg) if score_mode == SCORE_SOFTMAX else (_sigmoid(lg) if score_mode == SCORE_SIGMOID else lg.copy())
+    sel = sc + selection_bias.astype(np.float32)[None, :] if selection_bias is not None else sc.copy()
+    gs = e // n_group
+    grouped = sel.reshape(t, n_group, gs)
+    if group_score == "top2_sum":
+        srt = -np.sort(-grouped, axis=-1)
+        gsc = (srt[..., 0] + srt[..., 1]).astype(np.float32)
+    else:
+        gsc = grouped.max(axis=-1)
+    gidx = deterministic_topk_indices(gsc, topk_group).astype(np.int64)
+    mask = np.zeros((t, n_group), dtype=bool)
+    np.put_along_axis(mask, gidx, True, axis=1)
+    tmp = np.where(np.repeat(mask, gs, axis=1), sel, np.float32(0.0)).astype(np.float32)
+    ids = deterministic_topk_indices(tmp, top_k)
+    vals = np.take_along_axis(sc, ids.astype(np.int64), axis=1).astype(np.float32)
+    if renormalize:
+        den = vals.sum(axis=1, keepdims=True, dtype=np.float32)
+        if norm_min > 0.0:
+            den = np.maximum(den, np.float32(norm_min))
+        vals = (vals / den).astype(np.float32)
+    if output_scale != 1.0:
+        vals = (vals * np.float32(output_scale)).astype(np.float32)
+    return ids, vals
+
+
 def stable_permutation(ids: np.ndarray, n_experts: int):
     """Stable counting sort of the flat assignment index t*k+s by expert id: the
     reference's only deterministic grouping (hanzo-quant/src/mxfp4/ops.rs:237-271,

@@ -349,3 +349,26 @@ def test_tensor_path_short_k_and_partial_feature_tiles(tensor_path):
         want = M.dense_forward(xd.to(torch.float32).cpu().numpy(), deq, None)
         assert T.rel_l2(got.cpu().numpy(), want) <= TOL[fmt], (fmt, n, k, m)
         assert torch.equal(got, layer.forward_raw(xd, torch.float32))
+
+
+@pytest.mark.parametrize("group_score", ["top2_sum", "max"])
+def test_group_limited_router_matches_oracle(group_score):
+    """DeepSeek-V3 routing: 256 experts in 8 groups, 4 groups kept, top-8, sigmoid scores + selection bias,
+    renormalised and scaled by 2.5 (hanzo-engine/src/models/deepseek3.rs:623-702)."""
+    import engine_b200 as hq
+    from engine_b200 import _lib as L
+    rng = T.rng_for(4, 77)
+    t, e, k = 500, 256, 8
+    logits = rng.standard_normal((t, e)).astype(np.float32)
+    logits[7] = logits[7, 0]                 # a row of exact ties: decided by index order alone
+    bias = (rng.standard_normal(e) * 0.01).astype(np.float32)
+    cfg = hq.MoeRouterTopKConfig(k, L.SCORE_SIGMOID, L.WEIGHT_SCORE, True, 1e-20, 2.5)
+    top = hq.moe_router_topk(T.to_dev(logits, torch.float32, DEV), cfg, T.to_dev(bias, torch.float32, DEV),
+                             n_group=8, topk_group=4, group_score=group_score)
+    ids, w = M.router_topk_grouped(logits, k, M.SCORE_SIGMOID, 8, 4, group_score, bias, True, 1e-20, 2.5)
+    got = top.indices.cpu().numpy().astype(np.uint32)
+    same = (got == ids).all(axis=1)
+    assert same.mean() >= 0.995 and same[7]
+    assert np.allclose(top.values.cpu().numpy()[same], w[same], rtol=2e-6, atol=1e-9)
+    # the selected experts come from at most 4 groups
+    assert all(len(set(int(v) // 32 for v in row)) <= 4 for row in got)

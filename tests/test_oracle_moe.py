@@ -96,3 +96,17 @@ def test_moe_layer_matches_dense_loop():
     gu[:, 0::2], gu[:, 1::2] = gb, ub
     got2 = M.moe_layer(x, ids, w, None, None, db, gate_up_bank=gu)
     assert np.allclose(got, got2, rtol=1e-5, atol=1e-5)
+
+
+def test_group_limited_routing_hand_case():
+    """hanzo-engine/src/models/deepseek3.rs:623-660 on a case small enough to do by hand: 8 experts in 4 groups of
+    2, keep the 2 best groups by the sum of their two scores, then top-3 among what is left."""
+    from oracle import moe as M
+    scores = np.array([[0.9, 0.1, 0.5, 0.6, 0.2, 0.95, 0.3, 0.3]], np.float32)    # raw scores, no bias
+    # group sums: 1.0, 1.1, 1.15, 0.6 -> groups 2 and 1 stay -> candidates 2, 3, 4, 5 (the rest score 0)
+    ids, w = M.router_topk_grouped(scores, 3, M.SCORE_RAW, 4, 2, "top2_sum", renormalize=True, norm_min=0.0)
+    assert ids.tolist() == [[5, 3, 2]]
+    np.testing.assert_allclose(w[0], np.array([0.95, 0.6, 0.5], np.float32) / np.float32(2.05), rtol=1e-6)
+    # group_limited_greedy: group score = its best expert: 0.9, 0.6, 0.95, 0.3 -> groups 2 and 0
+    ids, _ = M.router_topk_grouped(scores, 3, M.SCORE_RAW, 4, 2, "max", renormalize=False)
+    assert ids.tolist() == [[5, 0, 4]]
