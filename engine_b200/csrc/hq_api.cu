@@ -452,6 +452,100 @@ int32_t hq_fp8_gather_rows(const uint8_t* src_codes, int64_t src_code_stride, co
                                 n_rows, k, codes, scales, (cudaStream_t)stream);
 }
 
+// ---- MXFP4 layers with MXFP8 activations (block-scaled MMA) ---------------------------------------------
+int32_t hq_mxfp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map,
+                            const int32_t* n_valid_dev, int64_t n_rows, int64_t k, uint8_t* codes, uint8_t* scales,
+                            void* stream) {
+  if (n_rows < 0 || k < 32 || k % 32 != 0 || x_stride < k) return HQ_ERR_SHAPE;
+  if (n_rows == 0) return HQ_OK;
+  if (x == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(x_dtype)) return HQ_ERR_FORMAT;
+  if ((reinterpret_cast<uintptr_t>(codes) & 3u) != 0 || k % 4 != 0) return HQ_ERR_ALIGN;
+  return launch_mxfp8_quant_rows(x, x_dtype, x_stride, row_map, n_valid_dev, n_rows, k, codes, scales,
+                                 (cudaStream_t)stream);
+}
+
+static int32_t fill_mx(MxGroupedParams& g, const hq_weight* w, const hq_act_args* act, const uint8_t* x_codes,
+                       const uint8_t* x_scales) {
+  int32_t rc = check_weight(w);
+  if (rc != HQ_OK) return rc;
+  if (w->format != HQ_FMT_MXFP4) return HQ_ERR_FORMAT;
+  if (!mx_grouped_supported(w->n, w->k)) return HQ_ERR_SHAPE;
+  if (x_codes == nullptr || x_scales == nullptr) return HQ_ERR_NULL;
+  if (!aligned16(x_codes) || (reinterpret_cast<uintptr_t>(x_scales) & 1u) != 0 ||
+      (reinterpret_cast<uintptr_t>(w->scales) & 1u) != 0 || (reinterpret_cast<uintptr_t>(w->data) & 31u) != 0)
+    return HQ_ERR_ALIGN;
+  g.n = (int)w->n;
+  g.k = (int)w->k;
+  g.n_experts = w->n_experts;
+  g.w = w->data;
+  g.w_scales = (const uint8_t*)w->scales;
+  g.bias = w->bias;
+  g.bias_dtype = w->bias_dtype;
+  g.xq = x_codes;
+  g.xs = x_scales;
+  g.act.act = HQ_ACT_NONE;
+  if (act != nullptr && act->act != HQ_ACT_NONE) {
+    if (act->act != HQ_ACT_SWIGLU && act->act != HQ_ACT_GPTOSS) return HQ_ERR_FORMAT;
+    if (w->n % 2 != 0) return HQ_ERR_SHAPE;
+    g.act = *act;
+    g.h_width = (int)(w->n / 2);
+  }
+  g.spin_limit = (uint32_t)g_cfg[HQ_CFG_SPIN_LIMIT];
+  g.test_skip_producer = (int)g_cfg[HQ_CFG_TEST_SKIP_PRODUCER];
+  return HQ_OK;
+}
+
+int32_t hq_mx_linear_forward(const hq_weight* w, const uint8_t* x_codes, const uint8_t* x_scales, int64_t m, void* y,
+                             int32_t y_dtype, int64_t y_stride, int32_t* status_dev, void* stream) {
+  MxGroupedParams g{};
+  int32_t rc = fill_mx(g, w, nullptr, x_codes, x_scales);
+  if (rc != HQ_OK) return rc;
+  if (w->n_experts != 1 || m < 0 || m > (1 << 24) || y_stride < w->n) return HQ_ERR_SHAPE;
+  if (m == 0) return HQ_OK;
+  if (y == nullptr) return HQ_ERR_NULL;
+  if (!valid_dtype(y_dtype)) return HQ_ERR_FORMAT;
+  g.m = (int)m;
+  g.n_rows = m;
+  g.y = y; g.y_dtype = y_dtype; g.y_stride = y_stride;
+  g.status = status_dev;
+  return launch_mx_grouped(g, (cudaStream_t)stream);
+}
+
+int32_t hq_moe_mx_gather_forward(const hq_weight* w, const hq_act_args* act, const uint8_t* x_codes,
+                                 const uint8_t* x_scales, int64_t n_tokens, int32_t top_k, const int32_t* expert_bounds,
+                                 const int32_t* sorted_assign, void* out, int32_t out_dtype, int64_t out_stride,
+                                 int32_t out_layout, uint8_t* h_codes, uint8_t* h_scales, int32_t* status_dev,
+                                 void* stream) {
+  MxGroupedParams g{};
+  int32_t rc = fill_mx(g, w, act, x_codes, x_scales);
+  if (rc != HQ_OK) return rc;
+  if (n_tokens < 0 || top_k < 1) return HQ_ERR_SHAPE;
+  if (n_tokens == 0) return HQ_OK;
+  if (expert_bounds == nullptr) return HQ_ERR_NULL;
+  const bool gated = g.act.act != HQ_ACT_NONE;
+  const bool quantized_out = gated && h_codes != nullptr;
+  if (quantized_out) {
+    if (h_scales == nullptr) return HQ_ERR_NULL;
+    if (g.h_width % 32 != 0 || !aligned16(h_codes)) return HQ_ERR_ALIGN;
+    g.hq = h_codes;
+    g.hs = h_scales;
+  } else {
+    if (out == nullptr) return HQ_ERR_NULL;
+    if (!valid_dtype(out_dtype)) return HQ_ERR_FORMAT;
+    if (out_stride < (gated ? w->n / 2 : w->n)) return HQ_ERR_SHAPE;
+    if (out_layout != HQ_ROWS_PER_SLOT && out_layout != HQ_ROWS_SORTED) return HQ_ERR_FORMAT;
+    if (gated && out_layout != HQ_ROWS_SORTED) return HQ_ERR_FORMAT;
+    if (out_layout == HQ_ROWS_PER_SLOT && sorted_assign == nullptr) return HQ_ERR_NULL;
+    g.y = out; g.y_dtype = out_dtype; g.y_stride = out_stride;
+    g.y_rows = out_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr;
+  }
+  g.n_rows = n_tokens * top_k;
+  g.expert_bounds = expert_bounds;
+  g.status = status_dev;
+  return launch_mx_grouped(g, (cudaStream_t)stream);
+}
+
 // ---- expert-parallel exchange helpers ------------------------------------------------------------------
 int32_t hq_ep_layout_init(hq_ep_layout* l, int32_t world, int32_t top_k, int32_t experts_per_rank, int32_t capacity,
                           int64_t hidden, int32_t wire_dtype, int32_t fp8) {

@@ -734,7 +734,7 @@ static F8EncodeTiledFn f8_encode_fn() {
   }
   return fn;
 }
-static bool f8_encode_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t rows,
+bool f8_encode_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t rows,
                          uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz) {
   const F8EncodeTiledFn encode = f8_encode_fn();
   if (encode == nullptr) return false;

@@ -115,6 +115,36 @@ struct Fp8GroupedParams {
 bool fp8_grouped_supported(int64_t n, int64_t k);
 int32_t launch_fp8_grouped(const Fp8GroupedParams& p, cudaStream_t stream);
 
+// ---- MXFP4 expert GEMM with MXFP8 activations on tcgen05 kind::mxf8f6f4.block_scale (hq_mx_grouped.cu) ------
+struct MxGroupedParams {
+  int n, k, m;                  // m: dense rows (used when expert_bounds == nullptr)
+  int n_experts;
+  const void* w;                // packed e2m1 nibbles [E, N, K/2]
+  const uint8_t* w_scales;      // e8m0 [E, N, K/32]
+  const void* bias;             // [E, N] or nullptr
+  int bias_dtype;
+  const void* xq;               // e4m3 activation codes [n_rows, K], rows in expert-sorted order
+  const uint8_t* xs;            // e8m0 [n_rows, K/32]
+  int64_t n_rows;
+  void* y;                      // plain mode: [rows, N]; gated mode without quantizer: [rows, N/2]
+  int y_dtype;
+  int64_t y_stride;
+  uint8_t* hq;                  // gated mode with quantizer: e4m3 codes [n_rows, h_width] ...
+  uint8_t* hs;                  // ... and e8m0 scales [n_rows, h_width/32] of the activated values
+  int h_width;                  // N / 2 in gated mode
+  hq_act_args act;              // HQ_ACT_NONE = plain; else rows interleave gate / up
+  const int32_t* expert_bounds;
+  const int32_t* y_rows;        // plain mode: sorted row -> output row (nullptr = identity)
+  int32_t* status;
+  uint32_t spin_limit;
+  int test_skip_producer;
+};
+bool mx_grouped_supported(int64_t n, int64_t k);
+int32_t launch_mx_grouped(const MxGroupedParams& p, cudaStream_t stream);
+int32_t launch_mxfp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map,
+                                const int32_t* n_valid, int64_t n_rows, int64_t k, uint8_t* codes, uint8_t* scales,
+                                cudaStream_t stream);
+
 // ---- dispatch tables (hq_dispatch.cu) -------------------------------------------
 constexpr int kDispatchChunk = 1024;  // flat assignments per block
 struct DispatchLayout {

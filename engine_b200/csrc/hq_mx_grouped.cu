@@ -1,0 +1,580 @@
+// MXFP4 expert GEMM on the block-scaled tensor-core path: tcgen05.mma kind::mxf8f6f4 with .block_scale.
+//
+// y[row, n] = sum over 32-element blocks b of  2^(sx[row, b] - 127) * 2^(sw[expert, n, b] - 127) *
+//             sum_{k in b} e4m3(X[row, k]) * e2m1(W[expert, n, k])
+// W: MXFP4Layer's bytes as they are (hanzo-quant/src/mxfp4/mod.rs:29-41: blocks [E, N, K/2], low nibble = even k;
+// scales [E, N, K/32] e8m0) -- the nibbles are never expanded: TMA copies them with the 16-packed-4-bit tensor-map
+// type, which spreads every 8 bytes of nibbles over a 16-byte slot of shared memory, the form the MMA reads for a
+// 4-bit operand.  X: activation rows quantized to MXFP8 (e4m3 codes + one e8m0 scale per 32 elements), already in
+// expert-sorted order.  The e8m0 scale factors of both operands sit in tensor memory and are applied by the MMA
+// per 32-element block, so the f32 accumulator in tensor memory runs over the whole K and is drained once per tile.
+//
+// Orientation: tensor-memory lanes = tokens (MMA M = 128, A = the token tile), columns = output features (MMA
+// N = 128, B = the weight tile).  Where the scale factors have to be (found by a probe on this part, one MMA with
+// distinct values in every cell): for row r of A, lane r, column sfa + r / 32, byte a_sf_id; for column n of B,
+// column sfb + n / 32, lane n % 32 of EVERY lane quarter (each quarter reads its own copy), byte b_sf_id.  The four
+// "scale" warps (one per lane quarter) write them from registers with tcgen05.st: one word per token (its four
+// blocks of the 128-wide K stage) and four words per lane for the 128 features.
+//
+// Work item = (token tile of <= 128 rows of one expert, 128 weight rows); token tiles are cut inside the kernel
+// from expert_bounds.  Epilogues: plain (bias, rows out in f32 / f16 / bf16) or gated for interleaved gate/up rows
+// (gpt-oss: row 2i = gate_i, 2i + 1 = up_i): bias, activation, then the MXFP8 quantizer of the 64 results per
+// thread (two 32-element blocks), written as codes + scales for the down projection.
+//
+// Roles (one persistent CTA per SM, 12 warps): warp 0 issues TMA, warp 1 issues the MMAs (one lane; the stages of a
+// tile accumulate into one buffer, so they must be issued in order), warps 4-7 write scale factors, warps 8-11
+// drain finished tiles (two accumulator buffers, so a drain overlaps the next tile's MMAs).  Every wait is
+// bounded; after a time-out the remaining waits poll once, nothing more is multiplied or stored and the kernel
+// reaches its normal exit.  No multicast, no peer memory.
+#include <cuda.h>
+#include <cuda_fp8.h>
+
+#include "hq_common.cuh"
+#include "hq_kernels.h"
+
+namespace hq {
+
+bool f8_encode_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t rows,
+                  uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz);
+
+constexpr int kMxThreads = 384;
+constexpr int kMxStages = 6;
+constexpr int kMxTile = 128 * 128;                       // one operand box in shared memory: 128 rows x 128 bytes
+constexpr int kMxStageBytes = 2 * kMxTile;
+constexpr int kMxSfSlots = 4;                            // scale-factor slots in tensor memory (8 columns each)
+constexpr int kMxAccBufs = 2;
+constexpr int kMxSfBase = 256;                           // tensor-memory column of the first slot
+constexpr int kMxTmemCols = 512;
+constexpr int kMxMaxExperts = 1024;
+
+struct MxSmem {
+  static constexpr int OFF_PREF = kMxStages * kMxStageBytes;
+  static constexpr int OFF_BAR = OFF_PREF + (kMxMaxExperts + 1) * 4 + 12;
+  static constexpr int N_BAR = 2 * kMxStages + 2 * kMxSfSlots + 2 * kMxAccBufs;
+  static constexpr int TOTAL = OFF_BAR + N_BAR * 8 + 16 + 1024;
+};
+static_assert(MxSmem::OFF_BAR % 8 == 0, "barriers are 8-byte aligned");
+static_assert(MxSmem::TOTAL <= 227 * 1024, "shared memory budget");
+
+__device__ __forceinline__ void mx_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mx_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mx_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mx_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa,
+                                       uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mx_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// K-major operand tile of 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart, descriptor version 1
+__device__ __forceinline__ uint64_t mx_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Block-scaled instruction descriptor: b_sf_id [4,6), a format [7,10) = e4m3 (0), b format [10,13) = e2m1 (5),
+// N >> 3 [17,23), scale format ue8m0 [23], M >> 4 [24,29), a_sf_id [29,31); both operands K-major, f32 accumulate.
+__device__ __forceinline__ uint32_t mx_idesc(int sf_id) {
+  return ((uint32_t)sf_id << 4) | (0u << 7) | (5u << 10) | ((uint32_t)(128 >> 3) << 17) | (1u << 23) |
+         ((uint32_t)(128 >> 4) << 24) | ((uint32_t)sf_id << 29);
+}
+
+__device__ __forceinline__ void mx_tma_2d(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+          "r"(smem_u32(dst_smem)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// four consecutive scale bytes of a row whose start is only 2-byte aligned; `have` of them exist (2 or 4), the
+// rest read as 127 (2^0) -- they belong to K blocks whose products are never issued
+__device__ __forceinline__ uint32_t mx_scale_word(const uint8_t* p, int have) {
+  const uint16_t lo = __ldg(reinterpret_cast<const uint16_t*>(p));
+  uint32_t hi = 0x7F7Fu;
+  if (have > 2) hi = __ldg(reinterpret_cast<const uint16_t*>(p + 2));
+  return (uint32_t)lo | (hi << 16);
+}
+
+__device__ __forceinline__ float mx_gated(float g, float u, const hq_act_args& a) {
+  if (a.act == HQ_ACT_GPTOSS) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return (u + 1.f) * (g / (1.f + expf(-a.alpha * g)));
+  }
+  if (a.has_limit) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+  }
+  return (g / (1.f + expf(-g))) * u;
+}
+
+// MXFP8 (OCP microscaling, e4m3 elements): shared exponent = floor(log2(amax)) - 8 (e4m3's largest power of two is
+// 2^8), stored biased by 127 and kept inside 0..254; an all-zero block gets 127.  Elements are scaled by 2^-e and
+// converted with saturation at +-448.
+__device__ __forceinline__ int mx_shared_exp(float amax) {
+  if (!(amax > 0.f)) return 127;
+  const int e = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127;      // floor(log2) of a normal number
+  return min(max(e - 8 + 127, 0), 254);
+}
+__device__ __forceinline__ float mx_exp_to_inv_scale(int e) {              // 2^-(e - 127), e in 0..254
+  return __uint_as_float((uint32_t)(254 - e) << 23);
+}
+
+struct MxItem {
+  int expert, row_start, count, n0;
+};
+__device__ __forceinline__ MxItem mx_item(const MxGroupedParams& p, const int32_t* pref, int n_exp, int w, int n_nt) {
+  MxItem t;
+  const int tt = w / n_nt;
+  t.n0 = (w - tt * n_nt) * 128;
+  int lo = 0, hi = n_exp - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (pref[mid] <= tt) lo = mid; else hi = mid - 1;
+  }
+  t.expert = lo;
+  int base = 0, cnt = p.m;
+  if (p.expert_bounds != nullptr) {
+    base = __ldg(p.expert_bounds + lo);
+    cnt = __ldg(p.expert_bounds + lo + 1) - base;
+  }
+  const int j = tt - pref[lo];
+  t.row_start = base + j * 128;
+  t.count = min(128, cnt - j * 128);
+  return t;
+}
+
+__global__ void __launch_bounds__(kMxThreads, 1)
+mx_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wtail,
+                  const __grid_constant__ CUtensorMap tm_x, const MxGroupedParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  int32_t* pref = reinterpret_cast<int32_t*>(smem + MxSmem::OFF_PREF);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + MxSmem::OFF_BAR);
+  uint64_t* empty = full + kMxStages;
+  uint64_t* sf_full = empty + kMxStages;            // [4] the slot's scale factors are in tensor memory
+  uint64_t* sf_empty = sf_full + kMxSfSlots;        // [4] ... and the MMAs that read them are done
+  uint64_t* acc_full = sf_empty + kMxSfSlots;       // [2] a tile's accumulation is complete
+  uint64_t* acc_empty = acc_full + kMxAccBufs;      // [2] ... and has been drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kMxAccBufs);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_nt = (p.n + 127) / 128;
+  const int KS = (p.k + 127) / 128;                 // K stages; the last one may hold 32, 64 or 96 elements
+  const int k_tail = p.k - (KS - 1) * 128;          // elements of the last stage (32 .. 128)
+  const int n_exp = p.expert_bounds != nullptr ? p.n_experts : 1;
+  const int sb = p.k / 32;                          // scale bytes per row
+
+  for (int e = tid; e < n_exp; e += kMxThreads) {
+    const int cnt = p.expert_bounds != nullptr ? __ldg(p.expert_bounds + e + 1) - __ldg(p.expert_bounds + e) : p.m;
+    pref[e + 1] = (cnt + 127) / 128;
+  }
+  if (tid == 0) {
+    pref[0] = 0;
+    for (int s = 0; s < kMxStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < kMxSfSlots; ++s) {
+      mbar_init(&sf_full[s], 4);
+      mbar_init(&sf_empty[s], 1);
+    }
+    for (int b = 0; b < kMxAccBufs; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < n_exp; base += 32) {
+      const int e = base + lane;
+      int v = e < n_exp ? pref[e + 1] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += o;
+      }
+      if (e < n_exp) pref[e + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kMxTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  mx_fence_before();
+  __syncthreads();
+  mx_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total = pref[n_exp] * n_nt;
+  const uint32_t spin_limit = p.spin_limit;
+
+  if (warp == 0) {
+    // =========================== TMA issuer =========================================================
+    if (lane == 0 && p.test_skip_producer != 1) {
+      uint32_t spin = spin_limit;
+      int s = 0, round = 0;
+      for (int w = blockIdx.x; w < total; w += gridDim.x) {
+        const MxItem t = mx_item(p, pref, n_exp, w, n_nt);
+        const int wrow = t.expert * p.n + t.n0;
+        for (int ks = 0; ks < KS; ++ks) {
+          if (round > 0) {
+            if (!mbar_wait(&empty[s], (round - 1) & 1, spin)) {
+              report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 810 + s);
+              spin = 1;
+            }
+          }
+          uint8_t* stage = smem + s * kMxStageBytes;
+          mbar_arrive_expect_tx(&full[s], (uint32_t)kMxStageBytes);
+          mx_tma_2d(stage, &tm_x, ks * 128, t.row_start, &full[s]);
+          // a K that is not a multiple of 128 ends in a stage of its own tensor map (the packed 4-bit map type
+          // needs a row length that is a multiple of 128 elements)
+          if (ks == KS - 1 && k_tail != 128) mx_tma_2d(stage + kMxTile, &tm_wtail, 0, wrow, &full[s]);
+          else mx_tma_2d(stage + kMxTile, &tm_w, ks * 128, wrow, &full[s]);
+          if (++s == kMxStages) {
+            s = 0;
+            ++round;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // =========================== MMA issuer =========================================================
+    if (lane == 0) {
+      uint32_t spin = spin_limit;
+      bool failed = false;
+      int st = 0;          // stages so far: shared-memory stage st % kMxStages, scale slot st % kMxSfSlots
+      int tile = 0;
+      for (int w = blockIdx.x; w < total; w += gridDim.x, ++tile) {
+        const int buf = tile & 1;
+        if (tile >= kMxAccBufs) {
+          if (!mbar_wait(&acc_empty[buf], ((tile >> 1) - 1) & 1, spin)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 820 + buf);
+            spin = 1;
+            failed = true;
+          }
+        }
+        const uint32_t d = tmem_base + (uint32_t)(buf * 128);
+        for (int ks = 0; ks < KS; ++ks, ++st) {
+          const int s = st % kMxStages, slot = st % kMxSfSlots;
+          if (!mbar_wait(&full[s], (st / kMxStages) & 1, spin)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 830 + s);
+            spin = 1;
+            failed = true;
+          }
+          if (!mbar_wait(&sf_full[slot], (st / kMxSfSlots) & 1, spin)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 840 + slot);
+            spin = 1;
+            failed = true;
+          }
+          if (failed) continue;
+          mx_fence_after();
+          const uint32_t stage = smem_u32(smem + s * kMxStageBytes);
+          const uint64_t adesc = mx_smem_desc(stage), bdesc = mx_smem_desc(stage + kMxTile);
+          const uint32_t sfa = tmem_base + (uint32_t)(kMxSfBase + 8 * slot), sfb = sfa + 4;
+          const int n_mma = (ks == KS - 1) ? k_tail / 32 : 4;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            if (kk < n_mma) mx_mma(d, adesc + 2 * kk, bdesc + 2 * kk, mx_idesc(kk), sfa, sfb, (ks | kk) != 0 ? 1u : 0u);
+          mx_commit(&empty[s]);
+          mx_commit(&sf_empty[slot]);
+          if (ks == KS - 1) mx_commit(&acc_full[buf]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4 && warp < 8) {
+    // =========================== scale factors ======================================================
+    // Per K stage and lane quarter q: one word for this thread's token (its four e8m0 bytes of the stage) into
+    // column sfa + q, four words for the features 32 j + lane into columns sfb + j.  The loads run four stages
+    // ahead of the stores.
+    const int q = warp - 4;
+    uint32_t spin = spin_limit;
+    constexpr int D = 4;
+    uint32_t wa[D], wb[D][4];
+    // cursors: (item, stage) being loaded / being stored
+    int lw = blockIdx.x, lks = 0;
+    int cw = blockIdx.x, cks = 0;
+    MxItem lt;
+    if (lw < total) lt = mx_item(p, pref, n_exp, lw, n_nt);
+    auto load = [&](uint32_t& a, uint32_t (&b)[4]) {
+      a = 0x7F7F7F7Fu;
+      b[0] = b[1] = b[2] = b[3] = 0x7F7F7F7Fu;
+      if (lw >= total) return;
+      const int have = (lks == KS - 1) ? k_tail / 32 : 4;
+      const int tok = 32 * q + lane;
+      if (tok < lt.count) a = mx_scale_word(p.xs + (int64_t)(lt.row_start + tok) * sb + 4 * lks, have);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = lt.n0 + 32 * j + lane;
+        if (n < p.n) b[j] = mx_scale_word(p.w_scales + ((int64_t)lt.expert * p.n + n) * sb + 4 * lks, have);
+      }
+      if (++lks == KS) {
+        lks = 0;
+        lw += gridDim.x;
+        if (lw < total) lt = mx_item(p, pref, n_exp, lw, n_nt);
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < D; ++d) load(wa[d], wb[d]);
+    int st = 0;
+    while (cw < total) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        if (cw < total) {
+          const int slot = st % kMxSfSlots;
+          if (st >= kMxSfSlots) {
+            if (!mbar_wait(&sf_empty[slot], ((st / kMxSfSlots) - 1) & 1, spin)) {
+              if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 850 + slot);
+              spin = 1;
+            }
+          }
+          mx_fence_after();
+          const uint32_t base = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(kMxSfBase + 8 * slot);
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(base + q), "r"(wa[d]) : "memory");
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + 4), "r"(wb[d][0]),
+                       "r"(wb[d][1]), "r"(wb[d][2]), "r"(wb[d][3])
+                       : "memory");
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          mx_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sf_full[slot]);
+          ++st;
+          if (++cks == KS) {
+            cks = 0;
+            cw += gridDim.x;
+          }
+          load(wa[d], wb[d]);
+        }
+      }
+    }
+  } else if (warp >= 8) {
+    // =========================== epilogue ===========================================================
+    const int q = warp - 8;                  // lane quarter: tokens 32q .. 32q + 31
+    const int tok = 32 * q + lane;
+    uint32_t spin = spin_limit;
+    bool failed = false;
+    const bool gated = p.act.act != HQ_ACT_NONE;
+    int tile = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x, ++tile) {
+      const MxItem t = mx_item(p, pref, n_exp, w, n_nt);
+      const int buf = tile & 1;
+      if (!mbar_wait(&acc_full[buf], (tile >> 1) & 1, spin)) {
+        if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 860 + buf);
+        spin = 1;
+        failed = true;
+      }
+      mx_fence_after();
+      const bool live = tok < t.count && !failed;
+      const int64_t srow = t.row_start + tok;
+      const bool quarter_live = 32 * q < t.count && !failed;
+      if (gated) {
+        // interleaved rows: columns 2i / 2i + 1 are gate_i / up_i, so 64 columns give 32 results = one MXFP8 block
+#pragma unroll 1
+        for (int c2 = 0; c2 < 2; ++c2) {
+          const int n_first = t.n0 + 64 * c2;
+          if (n_first >= p.n || !quarter_live) continue;
+          uint32_t c[64];
+          const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * 128 + 64 * c2);
+          mx_tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&c[0]));
+          mx_tmem_ld32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&c[32]));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (!live) continue;
+          float a[32];
+          float m = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float g = __uint_as_float(c[2 * j]), u = __uint_as_float(c[2 * j + 1]);
+            if (p.bias != nullptr) {
+              const int64_t bi = (int64_t)t.expert * p.n + n_first + 2 * j;
+              if (n_first + 2 * j + 1 < p.n) {
+                g += load_as_float(p.bias, p.bias_dtype, bi);
+                u += load_as_float(p.bias, p.bias_dtype, bi + 1);
+              }
+            }
+            a[j] = mx_gated(g, u, p.act);
+            m = fmaxf(m, fabsf(a[j]));
+          }
+          const int i_first = n_first / 2;               // first intermediate feature of these 32 results
+          if (p.hq == nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (i_first + j < p.h_width) store_from_float(p.y, p.y_dtype, srow * p.y_stride + i_first + j, a[j]);
+          } else {
+            const int e = mx_shared_exp(m);
+            const float inv = mx_exp_to_inv_scale(e);
+            uint32_t wds[8];
+#pragma unroll
+            for (int g4 = 0; g4 < 8; ++g4) {
+              uint32_t pk = 0;
+#pragma unroll
+              for (int b = 0; b < 4; ++b)
+                pk |= (uint32_t)__nv_cvt_float_to_fp8(fminf(fmaxf(a[4 * g4 + b] * inv, -448.f), 448.f), __NV_SATFINITE,
+                                                      __NV_E4M3)
+                      << (8 * b);
+              wds[g4] = pk;
+            }
+            uint4* dst = reinterpret_cast<uint4*>(p.hq + srow * p.h_width + i_first);
+            dst[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+            dst[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
+            p.hs[srow * (p.h_width / 32) + i_first / 32] = (uint8_t)e;
+          }
+        }
+      } else {
+        const int64_t orow = live ? (p.y_rows != nullptr ? (int64_t)__ldg(p.y_rows + srow) : srow) : 0;
+#pragma unroll 1
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int n_first = t.n0 + 32 * c4;
+          if (n_first >= p.n || !quarter_live) continue;
+          uint32_t c[32];
+          mx_tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * 128 + 32 * c4), c);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (!live) continue;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (n_first + j < p.n) {
+              float v = __uint_as_float(c[j]);
+              if (p.bias != nullptr) v += load_as_float(p.bias, p.bias_dtype, (int64_t)t.expert * p.n + n_first + j);
+              store_from_float(p.y, p.y_dtype, orow * p.y_stride + n_first + j, v);
+            }
+          }
+        }
+      }
+      mx_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  mx_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    mx_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kMxTmemCols) : "memory");
+  }
+}
+
+// ---- MXFP8 row quantizer: rows looked up through row_map (token order -> expert-sorted order) ---------------
+// One warp per (row, 128-element span): lane owns 4 consecutive elements, a 32-element block is 8 lanes.
+__global__ void __launch_bounds__(256) mxfp8_quant_rows_kernel(const void* __restrict__ x, int dtype, int64_t x_stride,
+                                                               const int32_t* __restrict__ row_map,
+                                                               const int32_t* __restrict__ n_valid, int64_t n_rows,
+                                                               int k, uint8_t* __restrict__ codes,
+                                                               uint8_t* __restrict__ scales) {
+  const int spans = (k + 127) / 128;
+  const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int64_t limit = n_valid != nullptr ? min((int64_t)*n_valid, n_rows) : n_rows;
+  if (item >= limit * spans) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = item / spans;
+  const int c0 = (int)(item - row * spans) * 128 + lane * 4;
+  const int64_t src_row = row_map != nullptr ? (int64_t)row_map[row] : row;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool in = c0 < k;
+  if (in) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = load_as_float(x, dtype, src_row * x_stride + c0 + i);
+  }
+  float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int d = 1; d < 8; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  const int e = mx_shared_exp(m);
+  const float inv = mx_exp_to_inv_scale(e);
+  if (!in) return;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    packed |= (uint32_t)__nv_cvt_float_to_fp8(fminf(fmaxf(v[i] * inv, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3)
+              << (8 * i);
+  *reinterpret_cast<uint32_t*>(codes + row * k + c0) = packed;
+  if ((lane & 7) == 0) scales[row * (k / 32) + c0 / 32] = (uint8_t)e;
+}
+
+int32_t launch_mxfp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map,
+                                const int32_t* n_valid, int64_t n_rows, int64_t k, uint8_t* codes, uint8_t* scales,
+                                cudaStream_t stream) {
+  const int64_t items = n_rows * ((k + 127) / 128);
+  if (items == 0) return HQ_OK;
+  mxfp8_quant_rows_kernel<<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(x, x_dtype, x_stride, row_map, n_valid,
+                                                                           n_rows, (int)k, codes, scales);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+// K % 64 == 0: whole 32-element blocks, 32-byte row stride of the packed nibbles, 2-byte aligned scale rows
+bool mx_grouped_supported(int64_t n, int64_t k) { return k % 64 == 0 && k >= 128 && n >= 1; }
+
+int32_t launch_mx_grouped(const MxGroupedParams& p_in, cudaStream_t stream) {
+  MxGroupedParams p = p_in;
+  if (!mx_grouped_supported(p.n, p.k)) return HQ_ERR_SHAPE;
+  if (p.expert_bounds != nullptr && p.n_experts > kMxMaxExperts) return HQ_ERR_SHAPE;
+  if (p.n_rows <= 0) return HQ_OK;
+  // the packed 4-bit tensor-map type wants a 32-byte aligned base and row stride
+  if ((reinterpret_cast<uintptr_t>(p.w) & 31u) != 0) return HQ_ERR_ALIGN;
+  CUtensorMap tm_w, tm_wtail, tm_x;
+  const uint64_t wrows = (uint64_t)(p.expert_bounds != nullptr ? p.n_experts : 1) * p.n;
+  const uint64_t k_main = (uint64_t)(p.k / 128) * 128;
+  const uint64_t wstride = (uint64_t)p.k / 2;
+  if (k_main > 0 && !f8_encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, p.w, k_main, wrows, wstride, 128, 128,
+                                  CU_TENSOR_MAP_SWIZZLE_128B))
+    return HQ_ERR_CUDA;
+  tm_wtail = tm_w;
+  if (k_main != (uint64_t)p.k) {
+    // the last 32 / 64 / 96 elements of every row: a map of its own whose rows are 128 elements long; what it
+    // reads past the row's end meets zero activations (the bank needs 64 readable bytes after its last row)
+    const uint8_t* tail = reinterpret_cast<const uint8_t*>(p.w) + k_main / 2;
+    if (!f8_encode_2d(&tm_wtail, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, tail, 128, wrows, wstride, 128, 128,
+                      CU_TENSOR_MAP_SWIZZLE_128B))
+      return HQ_ERR_CUDA;
+  }
+  if (!f8_encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.xq, (uint64_t)p.k, (uint64_t)p.n_rows, (uint64_t)p.k, 128,
+                    128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return HQ_ERR_CUDA;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
+  if (dev < 64 && !attr_done[dev]) {
+    if (cudaFuncSetAttribute(mx_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem::TOTAL) !=
+        cudaSuccess)
+      return HQ_ERR_CUDA;
+    attr_done[dev] = true;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  const int64_t n_exp = p.expert_bounds != nullptr ? p.n_experts : 1;
+  const int64_t items = (p.n_rows / 128 + n_exp) * ((p.n + 127) / 128);
+  const int64_t grid = items < sms ? items : sms;
+  if (p.spin_limit == 0) p.spin_limit = 1u << 22;
+  mx_grouped_kernel<<<(unsigned)grid, kMxThreads, MxSmem::TOTAL, stream>>>(tm_w, tm_wtail, tm_x, p);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+}  // namespace hq

@@ -11,7 +11,7 @@ import torch
 
 from . import _lib as L
 from .quant import (DispatchTables, QuantMethod, _ptr, _require_cuda, _stream, convert, dt_code,
-                    moe_dispatch_build, tensor_path_expected)
+                    moe_dispatch_build, mxfp8_quantize_rows, tensor_path_expected)
 
 
 @dataclass
@@ -217,6 +217,68 @@ class MoEExperts:
                                               _ptr(tables.sorted_assign), None, _ptr(y),
                                               dt_code(y.dtype), self.down.n, L.ROWS_SORTED, _ptr(status), _stream()),
                 "hq_moe_fp8_gather_forward(down)")
+        self._mark(ev0)
+        if _skip_reduce:
+            return y
+        out = moe_weighted_reduce(y, topk_weights.to(torch.float32), out_dtype, tables.inv_perm, shared_out)
+        return out.reshape(*lead, self.down.n)
+
+    def forward_mx_act(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                       shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+                       tables: DispatchTables | None = None, _skip_reduce: bool = False) -> torch.Tensor:
+        """The block with MXFP8 activations for MXFP4 experts on the block-scaled tensor-core MMA: token rows are
+        quantized (e4m3 + one e8m0 scale per 32 elements) straight into expert-sorted order; the gate/up launch
+        multiplies them with the e2m1 nibbles as stored, adds the bias, applies the gated activation and quantizes
+        the intermediate the same way; the down projection writes expert-sorted rows for the weighted reduce.
+        An interleaved gate_up bank (gpt-oss) takes one launch; separate gate and up banks take two plain
+        launches, the gated activation and the row quantizer.  Slots with ids outside [0, n_experts) are skipped."""
+        first = self.gate_up if self.gate_up is not None else self.gate
+        banks = [first, self.down] + ([self.up] if self.up is not None else [])
+        if any(b.format != L.FMT_MXFP4 or not b.mx_supported() for b in banks):
+            raise L.HqError("forward_mx_act needs MXFP4 experts with K % 64 == 0")
+        _require_cuda(xs, "xs")
+        lead = xs.shape[:-1]
+        x = xs.reshape(-1, xs.shape[-1]).contiguous()
+        dev, hidden = x.device, x.shape[-1]
+        t, k = topk_ids.shape
+        tables = tables or moe_dispatch_build(topk_ids, self.n_experts)
+        lib = L.lib()
+        status = first._status_buf(dev)
+        n_valid = tables.expert_bounds[self.n_experts:]
+        xq, xsc = mxfp8_quantize_rows(x, tables.sorted_token, n_valid)
+        self._last_tables = tables
+        ev0 = self._mark()
+        inter = first.n // 2 if self.gate_up is not None else first.n
+        if inter % 32 != 0:
+            raise L.HqError("forward_mx_act: the intermediate width must be a multiple of 32")
+        if self.gate_up is not None:
+            hq_ = torch.empty((t * k, inter), dtype=torch.uint8, device=dev)
+            hs = torch.empty((t * k, inter // 32), dtype=torch.uint8, device=dev)
+            w0 = first._weight_struct()
+            L.check(lib.hq_moe_mx_gather_forward(C.byref(w0), C.byref(self.act), _ptr(xq), _ptr(xsc), t, k,
+                                                 _ptr(tables.expert_bounds), None, None, 0, 0, L.ROWS_SORTED,
+                                                 _ptr(hq_), _ptr(hs), _ptr(status), _stream()),
+                    "hq_moe_mx_gather_forward(gate_up)")
+        else:
+            gu = []
+            for bank in (self.gate, self.up):
+                o = torch.empty((t * k, inter), dtype=torch.float32, device=dev)
+                wb = bank._weight_struct()
+                L.check(lib.hq_moe_mx_gather_forward(C.byref(wb), None, _ptr(xq), _ptr(xsc), t, k,
+                                                     _ptr(tables.expert_bounds), None, _ptr(o), dt_code(o.dtype), inter,
+                                                     L.ROWS_SORTED, None, None, _ptr(status), _stream()),
+                        "hq_moe_mx_gather_forward(gate/up)")
+                gu.append(o)
+            hmid = gated_act(gu[0], gu[1], self.act.act, self.act.limit if self.act.has_limit else None,
+                             self.act.alpha)
+            hq_, hs = mxfp8_quantize_rows(hmid, None, n_valid)
+        out_dtype = out_dtype or xs.dtype
+        y_dtype = out_dtype if out_dtype in (torch.float16, torch.bfloat16) else torch.float32
+        y = torch.empty((t * k, self.down.n), dtype=y_dtype, device=dev)
+        wd = self.down._weight_struct()
+        L.check(lib.hq_moe_mx_gather_forward(C.byref(wd), None, _ptr(hq_), _ptr(hs), t, k, _ptr(tables.expert_bounds),
+                                             None, _ptr(y), dt_code(y.dtype), self.down.n, L.ROWS_SORTED, None, None,
+                                             _ptr(status), _stream()), "hq_moe_mx_gather_forward(down)")
         self._mark(ev0)
         if _skip_reduce:
             return y

@@ -349,7 +349,13 @@ class MXFP4Layer(QuantMethod):
         super().__init__()
         _require_cuda(blocks, "blocks")
         self.format = L.FMT_MXFP4
-        self.blocks = blocks.contiguous()
+        # the bytes live in a buffer with 64 spare bytes behind them: the packed 4-bit tensor map of the
+        # block-scaled path reads whole 128-element groups and may run past the last row's end
+        store = torch.empty(blocks.numel() + 64, dtype=torch.uint8, device=blocks.device)
+        store[:blocks.numel()].copy_(blocks.reshape(-1))
+        store[blocks.numel():].zero_()
+        self._store = store
+        self.blocks = store[:blocks.numel()].view(blocks.shape)
         self.scales = scales.contiguous()
         self.n_experts = blocks.shape[0] if blocks.dim() == 3 else 1
         self.n, self.k = blocks.shape[-2], blocks.shape[-1] * 2
@@ -370,6 +376,23 @@ class MXFP4Layer(QuantMethod):
 
     def _expert_view(self, e):
         return self if self.n_experts == 1 else MXFP4Layer(self.blocks[e], self.scales[e])
+
+    def mx_supported(self) -> bool:
+        """Shapes the block-scaled tensor-core path takes (K a multiple of 64, at least 128)."""
+        return self.k % 64 == 0 and self.k >= 128
+
+    def forward_mx_rows(self, codes: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16):
+        """Dense layer over rows that are MXFP8 already (mxfp8_quantize_rows): block-scaled MMA, nibbles and
+        activation codes unconverted."""
+        if self.n_experts != 1:
+            raise L.HqError("forward_mx_rows is the dense call; expert banks go through MoEExperts.forward_mx_act")
+        m = codes.shape[0]
+        y = torch.empty((m, self.n), dtype=out_dtype, device=codes.device)
+        w = self._weight_struct()
+        L.check(L.lib().hq_mx_linear_forward(C.byref(w), _ptr(codes), _ptr(scales), m, _ptr(y), dt_code(out_dtype),
+                                             self.n, _ptr(self._status_buf(codes.device)), _stream()),
+                "hq_mx_linear_forward")
+        return y
 
 
 # ---- fused dense decode set (hanzo-quant/src/lib.rs:1116-1204, gemv/mod.rs) --------------------------
@@ -494,6 +517,20 @@ def fp8_quantize_rows(x: torch.Tensor, row_map: torch.Tensor | None = None):
     scales = torch.empty((rows, k // 128), dtype=torch.float32, device=x.device)
     L.check(L.lib().hq_fp8_quant_rows(_ptr(x), dt_code(x.dtype), k, _ptr(row_map), rows, k, _ptr(codes), _ptr(scales),
                                       _stream()), "hq_fp8_quant_rows")
+    return codes, scales
+
+
+def mxfp8_quantize_rows(x: torch.Tensor, row_map: torch.Tensor | None = None, n_valid: torch.Tensor | None = None):
+    """MXFP8 quantizer over rows x[row_map[r]]: e4m3 codes uint8 [R, K] and e8m0 scales uint8 [R, K/32] (shared
+    exponent floor(log2 amax) - 8 per 32 elements).  Rows at or past *n_valid (a device int32) are left unwritten."""
+    _require_cuda(x, "x")
+    x = x.contiguous()
+    k = x.shape[-1]
+    rows = x.shape[0] if row_map is None else row_map.numel()
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((rows, k // 32), dtype=torch.uint8, device=x.device)
+    L.check(L.lib().hq_mxfp8_quant_rows(_ptr(x), dt_code(x.dtype), k, _ptr(row_map), _ptr(n_valid), rows, k,
+                                        _ptr(codes), _ptr(scales), _stream()), "hq_mxfp8_quant_rows")
     return codes, scales
 
 

@@ -362,6 +362,36 @@ int32_t hq_fp8_gather_rows(const uint8_t* src_codes, int64_t src_code_stride, co
                            int64_t src_scale_stride_bytes, const int32_t* row_map, const int32_t* n_valid_dev,
                            int64_t n_rows, int64_t k, uint8_t* codes, float* scales, void* stream);
 
+/* ---- MXFP4 layers with MXFP8 activations: the block-scaled tensor-core path --------------------------------
+ * The counterpart of the FP8-activation calls above for MXFP4Layer banks (hanzo-quant/src/mxfp4/mod.rs:29-174): the
+ * e2m1 nibbles are never expanded, the activations are MXFP8 (e4m3 codes + one e8m0 scale per 32 elements) and
+ * tcgen05.mma kind::mxf8f6f4 with block scaling applies both operands' e8m0 scales per 32-element block.  The
+ * reference has no activation quantizer for this format (its MXFP4 kernels multiply bf16 / f16 activations,
+ * kernels/mxfp4/mxfp4_gemm_wmma.cu:310-492); the one used here is the OCP microscaling rule for e4m3 elements:
+ * shared exponent = floor(log2(amax)) - 8, biased by 127 and kept in 0..254 (127 for an all-zero block), elements
+ * scaled by 2^-e and converted with saturation at +-448 (the structure of MXFP4Layer::quantize, mxfp4/mod.rs:216-300).
+ * Results equal dequantize-then-matmul over the QUANTIZED activations up to f32 summation order.
+ * Requires K % 64 == 0, K >= 128; w->data 32-byte aligned with at least 64 readable bytes after the last row (the
+ * packed 4-bit tensor map reads whole 128-element groups; what lies past a row's end meets zero activations).
+ *
+ * hq_mxfp8_quant_rows: codes [n_rows, k] / scales u8 [n_rows, k/32] of rows x[row_map[r]], r < min(*n_valid_dev,
+ * n_rows) (row_map / n_valid_dev may be NULL).
+ * hq_mx_linear_forward: dense layer over quantized rows.
+ * hq_moe_mx_gather_forward: expert bank over expert-sorted quantized rows.  act NULL / HQ_ACT_NONE: plain
+ * projection, out [rows, N] sorted or per slot.  Otherwise the bank's rows interleave gate / up (gpt-oss): bias,
+ * gated activation, and either h_codes / h_scales (MXFP8 of the N/2 activated values per row, for the down
+ * projection) when h_codes is given, or out [rows, N/2] sorted. */
+int32_t hq_mxfp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, const int32_t* row_map,
+                            const int32_t* n_valid_dev, int64_t n_rows, int64_t k, uint8_t* codes, uint8_t* scales,
+                            void* stream);
+int32_t hq_mx_linear_forward(const hq_weight* w, const uint8_t* x_codes, const uint8_t* x_scales, int64_t m, void* y,
+                             int32_t y_dtype, int64_t y_stride, int32_t* status_dev, void* stream);
+int32_t hq_moe_mx_gather_forward(const hq_weight* w, const hq_act_args* act, const uint8_t* x_codes,
+                                 const uint8_t* x_scales, int64_t n_tokens, int32_t top_k, const int32_t* expert_bounds,
+                                 const int32_t* sorted_assign, void* out, int32_t out_dtype, int64_t out_stride,
+                                 int32_t out_layout, uint8_t* h_codes, uint8_t* h_scales, int32_t* status_dev,
+                                 void* stream);
+
 /* ---- expert parallelism: what a rank does either side of the two all-to-all exchanges --------------------
  * The reference shards quantized experts over GPUs nowhere (its MoE collective is the tensor-parallel all-reduce
  * behind hanzo-engine/src/moe/experts/mod.rs:260-263, NCCL wrapper hanzo-quant/src/distributed/mod.rs:213-274,

@@ -345,6 +345,34 @@ def mxfp4_dequant(blocks: np.ndarray, scales: np.ndarray) -> np.ndarray:
 
 
 # ----------------------------------------------------------------------------
+# MXFP8 activations (e4m3 elements, 32-element blocks, e8m0 shared exponent)
+# ----------------------------------------------------------------------------
+
+def mxfp8_quant(x: np.ndarray):
+    """f32 [..., K] -> (codes uint8 [..., K], scales uint8 [..., K/32]).  The reference has no MXFP8 quantizer; this
+    is the OCP microscaling rule for e4m3 elements with the structure of MXFP4Layer::quantize
+    (hanzo-quant/src/mxfp4/mod.rs:216-300): e = clamp(floor(log2(absmax)) - 8 + 127, 0, 254) (8 = exponent of
+    e4m3's largest binade), 127 for an all-zero block; elements times 2^-(e-127), clamped to +-448, rounded to
+    nearest even."""
+    x = np.asarray(x, dtype=np.float32)
+    shp = x.shape
+    g = x.reshape(-1, MXFP4_BLOCK)
+    amax = np.abs(g).max(1)
+    ex = ((amax.view(np.uint32) >> np.uint32(23)) & np.uint32(0xFF)).astype(np.int64) - 127   # floor(log2), normals
+    e = np.where(amax > 0, np.clip(ex - 8 + 127, 0, 254), 127).astype(np.uint8)
+    inv = ((np.uint32(254) - e.astype(np.uint32)) << np.uint32(23)).view(np.float32)
+    with np.errstate(over="ignore", invalid="ignore"):
+        scaled = np.clip(g * inv[:, None], -FP8_MAX, FP8_MAX).astype(np.float32)
+    codes = e4m3_encode(scaled).reshape(shp)
+    return codes, e.reshape(shp[:-1] + (shp[-1] // MXFP4_BLOCK,))
+
+
+def mxfp8_dequant(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """inverse of mxfp8_quant: e4m3 value times 2^(scale - 127) per 32-element block."""
+    return e4m3_decode(codes) * np.repeat(e8m0_to_f32(scales), MXFP4_BLOCK, axis=-1)
+
+
+# ----------------------------------------------------------------------------
 # 16-bit rounding helpers
 # ----------------------------------------------------------------------------
 

@@ -153,12 +153,18 @@ def oracle_moe_host(first_banks, down_bank, n_used, act, x_sub, ids_c, w_sub, *,
     bias)] -- one interleaved gate/up bank, or the gate and the up bank; ids_c [S, k] index into the copies (-1 =
     skipped slot); act = (code, has_limit, limit, alpha).  Rounding points mirror the CUDA path: the 16-bit path
     rounds the activated intermediate to f16; the FP8-activation path quantizes x 1x128, rounds gate and up to f16,
-    rounds the activated product to f16 and quantizes it 1x128.  Returns f32 [S, H]."""
+    rounds the activated product to f16 and quantizes it 1x128; fp8_act="mx" is the MXFP8 path: x quantized per 32
+    elements with a power-of-two scale, gate / up / product kept in f32, product quantized the same way.
+    Returns f32 [S, H]."""
     from oracle import cbuild, formats as F, moe as M
     s, k = ids_c.shape
     f16 = lambda a: a.astype(np.float16).astype(np.float32)
     qdq = lambda a: F.fp8_vector_dequant(*F.fp8_vector_quant(np.ascontiguousarray(a).reshape(-1), 128), 128) \
         .reshape(a.shape).astype(np.float32)
+    mx = fp8_act == "mx"
+    if mx:
+        f16 = lambda a: a
+        qdq = lambda a: F.mxfp8_dequant(*F.mxfp8_quant(np.ascontiguousarray(a, dtype=np.float32))).astype(np.float32)
     # stable (token, slot) order grouped by expert
     flat = [(int(ids_c[t, sl]), t * k + sl) for t in range(s) for sl in range(k) if ids_c[t, sl] >= 0]
     flat.sort(key=lambda p: p[0])
@@ -183,7 +189,7 @@ def oracle_moe_host(first_banks, down_bank, n_used, act, x_sub, ids_c, w_sub, *,
         hmid = M.gptoss_swiglu(g, u, alpha, limit)
     else:
         hmid = M.swiglu(g, u, limit if has_limit else None)
-    hmid = qdq(f16(hmid)) if fp8_act else f16(hmid)
+    hmid = qdq(f16(hmid.astype(np.float32))) if fp8_act else f16(hmid)
     fmt, data, scales, bias = down_bank
     y = cbuild.gather(fmt, data, scales, bias, hmid, n_used, bounds, rows, rows, assign.size, threads)
     out = np.zeros((s, y.shape[1]), np.float32)
