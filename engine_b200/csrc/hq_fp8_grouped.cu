@@ -341,10 +341,12 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   if (warp == 0) {
     // =========================== TMA issuer =========================================================
     if (lane == 0 && p.test_skip_producer != 1) {
-      uint32_t spin = spin_limit;
+      const uint32_t spin = spin_limit;
       int s = 0, round = 0;
+      int issued = 0;              // stages handed to the copy engine so far
+      bool stop = false;           // a wait ran out: nothing more is issued (the stage may still be in use)
       const int burst = p.load_burst;
-      for (int w = blockIdx.x; w < total; w += gridDim.x) {
+      for (int w = blockIdx.x; w < total && !stop; w += gridDim.x) {
         const F8Item t = f8_item(p, pref, n_exp, w, n_nt);
         // the smallest token box that covers the tile (rows past it keep whatever the stage held: they only feed
         // tensor-memory lanes nobody reads)
@@ -352,26 +354,28 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const CUtensorMap* mx = bsel == 1 ? &tm_x0 : (bsel == 2 ? &tm_x1 : (bsel == 3 ? &tm_x2 : &tm_x3));
         const uint32_t box_bytes = (uint32_t)bsel * 32u * 128u;
         const int wrow = t.expert * p.n + t.n0;
-        for (int pass = 0; pass < npass; ++pass) {
+        for (int pass = 0; pass < npass && !stop; ++pass) {
           const CUtensorMap* mw = pass == 0 ? &tm_w : &tm_wu;
           // `burst` consecutive blocks are requested together, so that every weight row is read burst x 128
           // contiguous bytes at a time (a 128-row box on its own touches 128 DRAM pages for 128 bytes each)
-          for (int kb0 = 0; kb0 < KB; kb0 += burst) {
+          for (int kb0 = 0; kb0 < KB && !stop; kb0 += burst) {
             int s2 = s, round2 = round;
             for (int b = 0; b < burst; ++b) {
               if (round2 > 0) {
                 F8_PROF_BEGIN();
                 if (!mbar_wait(&empty[s2], (round2 - 1) & 1, spin)) {
                   report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 710 + s2);
-                  spin = 1;
+                  stop = true;
                 }
                 F8_PROF_END(0, true);
               }
+              if (stop) break;
               if (++s2 == kF8Stages) {
                 s2 = 0;
                 ++round2;
               }
             }
+            if (stop) break;
             s2 = s;
 #ifdef HQ_F8_STREAM_ONLY
             // experiment: test_skip_producer 2 = weights only, 3 = tokens only
@@ -397,8 +401,15 @@ fp8_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 ++round;
               }
             }
+            issued += burst;
           }
         }
+      }
+      // no copy may still be writing this CTA's shared memory when it exits: wait (bounded) for the last copies of
+      // every stage.  On the normal path the MMA warps consumed them long ago and these waits return at once.
+      for (int j = 0; j < kF8Stages && j < issued; ++j) {
+        const int idx = issued - 1 - j;
+        if (!mbar_wait(&full[idx % kF8Stages], (idx / kF8Stages) & 1, spin)) break;
       }
     }
     __syncwarp();

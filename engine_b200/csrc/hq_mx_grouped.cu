@@ -240,30 +240,39 @@ mx_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   if (warp == 0) {
     // =========================== TMA issuer =========================================================
     if (lane == 0 && p.test_skip_producer != 1) {
-      uint32_t spin = spin_limit;
       int s = 0, round = 0;
-      for (int w = blockIdx.x; w < total; w += gridDim.x) {
+      int issued = 0;              // stages handed to the copy engine so far
+      bool stop = false;           // a wait ran out: nothing more is issued (the stage may still be in use)
+      for (int w = blockIdx.x; w < total && !stop; w += gridDim.x) {
         const MxItem t = mx_item(p, pref, n_exp, w, n_nt);
         const int wrow = t.expert * p.n + t.n0;
         for (int ks = 0; ks < KS; ++ks) {
-          if (round > 0) {
-            if (!mbar_wait(&empty[s], (round - 1) & 1, spin)) {
-              report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 810 + s);
-              spin = 1;
-            }
+          if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, spin_limit)) {
+            report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 810 + s);
+            stop = true;
+            break;
           }
           uint8_t* stage = smem + s * kMxStageBytes;
-          mbar_arrive_expect_tx(&full[s], (uint32_t)kMxStageBytes);
+          // the copy engine reports the bytes it read: the packed nibbles (half a byte per element), not the
+          // 16-byte slots they are spread over in shared memory
+          mbar_arrive_expect_tx(&full[s], (uint32_t)(kMxTile + kMxTile / 2));
           mx_tma_2d(stage, &tm_x, ks * 128, t.row_start, &full[s]);
           // a K that is not a multiple of 128 ends in a stage of its own tensor map (the packed 4-bit map type
           // needs a row length that is a multiple of 128 elements)
           if (ks == KS - 1 && k_tail != 128) mx_tma_2d(stage + kMxTile, &tm_wtail, 0, wrow, &full[s]);
           else mx_tma_2d(stage + kMxTile, &tm_w, ks * 128, wrow, &full[s]);
+          ++issued;
           if (++s == kMxStages) {
             s = 0;
             ++round;
           }
         }
+      }
+      // no copy may still be writing this CTA's shared memory when it exits: wait (bounded) for the last copies of
+      // every stage.  On the normal path the MMA warp consumed them long ago and these waits return at once.
+      for (int j = 0; j < kMxStages && j < issued; ++j) {
+        const int idx = issued - 1 - j;
+        if (!mbar_wait(&full[idx % kMxStages], (idx / kMxStages) & 1, spin_limit)) break;
       }
     }
     __syncwarp();
