@@ -390,7 +390,15 @@ def moe_cfg(args):
         cfg["t"] = args.tokens
     if args.experts:
         cfg["e"] = args.experts       # a smaller bank of the same expert shape (profiling cases that must stay small)
+    if getattr(args, "act16", False):
+        cfg["act_fp8"] = cfg["act_mx"] = False
     return cfg
+
+
+def act_mode(cfg):
+    """False (16-bit activations), True (1x128 FP8 activations) or "mx" (MXFP8 activations): the value the subset
+    oracle takes for the same rounding points."""
+    return True if cfg.get("act_fp8") else ("mx" if cfg.get("act_mx") else False)
 
 
 def moe_config(cfg, world, scaling):
@@ -400,7 +408,8 @@ def moe_config(cfg, world, scaling):
             "tokens_global": cfg["t"], "experts_per_gpu": cfg["e"] // world, "parallelism": f"ep{world}",
             "scaling": scaling,
             "activation_mode": ("B: per-token 1x128 FP8 activations, e4m3 x e4m3 MMA" if cfg.get("act_fp8") else
-                                "A: 16-bit activations, weights expanded to f16"),
+                                "B: MXFP8 activations (e4m3 + e8m0 per 32), block-scaled e4m3 x e2m1 MMA"
+                                if cfg.get("act_mx") else "A: 16-bit activations, weights expanded to f16"),
             "l2": "expert banks exceed L2; activations rotate over 4 buffers"}
 
 
@@ -455,9 +464,10 @@ def run_moe(args):
     t_local = cfg["t"] // world if strong else cfg["t"]
     t_global = t_local * world
     fp8 = bool(cfg.get("act_fp8"))
+    mx = bool(cfg.get("act_mx"))
     experts = S.build_moe_layer(torch, hq, cfg, gen, dev, e // world)
-    ep = (ExpertParallelMoE(e, experts, top_k=k, hidden=h, capacity=t_local, wire_dtype=torch.bfloat16, fp8_act=fp8)
-          if world > 1 else None)
+    ep = (ExpertParallelMoE(e, experts, top_k=k, hidden=h, capacity=t_local, wire_dtype=torch.bfloat16, fp8_act=fp8,
+                            mx_act=mx) if world > 1 else None)
     shared = S.build_moe_layer(torch, hq, cfg, gen, dev, 1) if cfg.get("shared") else None
     if shared is not None and not fp8:
         shared_ids = torch.zeros((t_local, 1), dtype=torch.int32, device=dev)
@@ -486,14 +496,21 @@ def run_moe(args):
             top = hq.moe_router_topk(lg, rcfg, sel_bias)
             return experts.forward_fp8_act(x, top.values, top.indices, shared_out=shared_fwd(x, out_dtype),
                                            out_dtype=out_dtype)
+        if mx:
+            top = hq.moe_router_topk(lg, rcfg, sel_bias)
+            return experts.forward_mx_act(x, top.values, top.indices, shared_out=shared_fwd(x, out_dtype),
+                                          out_dtype=out_dtype)
         # one library call for the whole layer (router included): no host work between the launches
         return experts.forward_layer(x, lg, rcfg, sel_bias, shared_out=shared_fwd(x, out_dtype), out_dtype=out_dtype)
 
     # launches of this library's kernels per step (the collectives' own kernels are not counted)
     if ep is not None:
-        launches_per_step = 1 + 1 + 1 + 3 + (3 if fp8 else 2) + 1 + 1 + (4 if (shared is not None and fp8) else 0)
+        launches_per_step = 1 + 1 + 1 + 3 + (3 if (fp8 or mx) else 2) + 1 + 1 + \
+            (4 if (shared is not None and fp8) else 0)
     elif fp8:
         launches_per_step = 1 + 3 + 3 + 1 + (4 if shared is not None else 0)
+    elif mx:
+        launches_per_step = 1 + 3 + 1 + 2 + 1          # router, dispatch build, row quantizer, two GEMMs, reduce
     else:
         launches_per_step = 1 + 3 + 1 + 2 + 1
 
@@ -574,7 +591,8 @@ def run_moe(args):
             ids_o, w_o = S.oracle_router(cfg, l0.cpu().numpy(), None if sel_bias is None else sel_bias.cpu().numpy())
             t_r = time.perf_counter() - t_r
             x_np = x0.to(torch.float32).cpu().numpy()
-            want = S.oracle_moe_subset(experts, x_np, ids_o, w_o, fp8_act=fp8, threads=threads, timer=secs.append)
+            want = S.oracle_moe_subset(experts, x_np, ids_o, w_o, fp8_act=act_mode(cfg), threads=threads,
+                                       timer=secs.append)
             if shared is not None:
                 want = want + S.oracle_moe_subset(shared, x_np, np.zeros((n_chk, 1), np.int64),
                                                   np.ones((n_chk, 1), np.float32), fp8_act=fp8, threads=threads,
@@ -632,6 +650,15 @@ def run_moe(args):
                 if NCU_TRAFFIC_RATIO_FP8 is not None:
                     roof["traffic"] = int(NCU_TRAFFIC_RATIO_FP8 * abytes / 2)
                     roof["traffic_note"] = "per launch: algorithmic bytes x the ncu dram/algorithmic ratio"
+            elif mx:
+                wbytes = 3 * e_l * i_ * h // 2 + 3 * e_l * i_ * h // 32
+                abytes = wbytes + rows_here * (h + 2 * i_ + 2 * h) + rows_here * (h // 32 + 2 * (i_ // 32))
+                roof.update({"kernel": "hq::mx_grouped_kernel x2 (gate/up fused with bias + clamped SwiGLU + MXFP8 "
+                                       "quantizer; down)",
+                             "frac_of_fp8_nominal_4500": round(ach / 4500.0, 4),
+                             "algorithmic_bytes": abytes,
+                             "hbm_gbs": round(abytes / (gemm_ms / 1e3) / 1e9, 1),
+                             "hbm_frac_of_measured": round(abytes / (gemm_ms / 1e3) / 1e9 / peaks["hbm_gbs"], 4)})
             else:
                 rows_per_expert = rows_here / max(1, e_l)
                 ts_k = cfg["fmt"] == "MXFP4" or (cfg["fmt"] == "Q4_K" and rows_per_expert < 192)
@@ -641,7 +668,7 @@ def run_moe(args):
             "metric": MOE_METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "strong" if strong else "weak", "vs_baseline": None,
-            "dtype": "e4m3" if fp8 else "f16", "data": "synthetic",
+            "dtype": "e4m3" if fp8 else ("e4m3 x e2m1, e8m0 block scales" if mx else "f16"), "data": "synthetic",
             "config": moe_config(cfg, world, "strong" if strong else "weak"),
             "roofline": roof,
             "parity_vs_cpu_oracle_rel_l2": parity,
@@ -694,7 +721,7 @@ def run_reference(args):
     from tests import hq_synth as S
     from oracle import moe as M
     cfg = moe_cfg(args)
-    fp8 = bool(cfg.get("act_fp8"))
+    fp8 = act_mode(cfg)
     e, k, h, i_ = cfg["e"], cfg["k"], cfg["h"], cfg["i"]
     n_tok = args.cpu_tokens or (2 if cfg["fmt"] == "FP8" else 16)     # tokens per step: a bounded sample of the step
     e_c = min(e, 16)                                                   # experts kept on the host
@@ -766,6 +793,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="moe_fp8", choices=["gemv", "moe_q4k", "moe_fp8", "moe_mxfp4"])
     ap.add_argument("--tokens", type=int, default=0, help="override the global token count of a MoE workload")
+    ap.add_argument("--act16", action="store_true",
+                    help="MoE workloads: 16-bit activations (mode A) instead of the quantized-activation path")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count of a MoE workload")
     ap.add_argument("--ep-scaling", default="strong", choices=["weak", "strong"],
                     help="MoE workloads on several GPUs: global token count split (strong) or tokens per GPU fixed")

@@ -62,13 +62,15 @@ def _gpu_unpack(lay, recv):
     return ids, w
 
 
-def _gpu_expert_fn(experts, wire_dtype):
+def _gpu_expert_fn(experts, wire_dtype, mx_act=False):
     def run(lay, recv, ids, weights):
         rows = lay.world * lay.rows_per_peer
         if lay.fp8:
             buf = recv.view(rows, lay.row_bytes)
             return experts.forward_fp8_act(None, weights, ids, out_dtype=wire_dtype, fp8_rows=(buf, lay.hidden))
         x = recv.view(wire_dtype).view(rows, lay.hidden)
+        if mx_act:
+            return experts.forward_mx_act(x, weights, ids, out_dtype=wire_dtype)
         return experts.forward(x, weights, ids, out_dtype=wire_dtype)
     return run
 
@@ -80,11 +82,13 @@ def _gpu_reduce_fn(y_rows, weights, row_map, out_dtype, addend):
 
 class ExpertParallelMoE:
     def __init__(self, n_experts_global: int, experts=None, *, top_k: int, hidden: int, capacity: int, group=None,
-                 wire_dtype: torch.dtype = torch.bfloat16, fp8_act: bool = False,
+                 wire_dtype: torch.dtype = torch.bfloat16, fp8_act: bool = False, mx_act: bool = False,
                  pack_fn: Callable | None = None, unpack_fn: Callable | None = None,
                  expert_fn: Callable | None = None, reduce_fn: Callable | None = None):
         """capacity: the largest number of tokens a rank brings to one call; the same value on every rank (it fixes
-        the slab size, so ranks may bring different token counts without telling each other)."""
+        the slab size, so ranks may bring different token counts without telling each other).
+        fp8_act: block-FP8 experts, rows cross the wire as e4m3 + 1x128 scales; mx_act: MXFP4 experts on the
+        block-scaled MMA (rows cross as `wire_dtype` and are quantized to MXFP8 on the expert rank)."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -96,7 +100,7 @@ class ExpertParallelMoE:
         self.layout = make_layout(self.world, top_k, self.e_local, capacity, hidden, wire_dtype, fp8_act)
         self.pack_fn = pack_fn or _gpu_pack
         self.unpack_fn = unpack_fn or _gpu_unpack
-        self.expert_fn = expert_fn or _gpu_expert_fn(experts, wire_dtype)
+        self.expert_fn = expert_fn or _gpu_expert_fn(experts, wire_dtype, mx_act)
         self.reduce_fn = reduce_fn or _gpu_reduce_fn
         self._bufs = None
         self._side = None

@@ -13,7 +13,7 @@ MOE_CFGS = {
     "moe_fp8": dict(fmt="FP8", e=256, k=8, h=7168, i=2048, t=4096, router="sigmoid_bias", inter=False,
                     shared=True, act_fp8=True, label="cfg4_deepseek_v3_block_fp8_moe"),
     "moe_mxfp4": dict(fmt="MXFP4", e=128, k=4, h=2880, i=2880, t=8192, router="topk_softmax", inter=True,
-                      label="cfg5_gpt_oss_120b_mxfp4_moe"),
+                      act_mx=True, label="cfg5_gpt_oss_120b_mxfp4_moe"),
 }
 
 
