@@ -545,7 +545,9 @@ def run_moe(args):
     gemm_ts = [a.elapsed_time(b) for a, b in experts.gemm_events]
     experts.gemm_events = None
     gemm_ms = statistics.median(gemm_ts) if gemm_ts else None
-    rows_here = int(experts._last_tables.expert_bounds[-1])      # routed assignments this rank's experts received
+    # routed assignments this rank's experts received
+    tables = getattr(experts, "_last_tables", None)
+    rows_here = int(tables.expert_bounds[-1]) if tables is not None else t_local * k
 
     # end to end with pinned host buffers: activations + logits in, layer output back
     hx = [x.cpu().pin_memory() for x in xs]

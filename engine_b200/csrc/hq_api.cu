@@ -472,8 +472,8 @@ static int32_t fill_mx(MxGroupedParams& g, const hq_weight* w, const hq_act_args
   if (w->format != HQ_FMT_MXFP4) return HQ_ERR_FORMAT;
   if (!mx_grouped_supported(w->n, w->k)) return HQ_ERR_SHAPE;
   if (x_codes == nullptr || x_scales == nullptr) return HQ_ERR_NULL;
-  if (!aligned16(x_codes) || (reinterpret_cast<uintptr_t>(x_scales) & 1u) != 0 ||
-      (reinterpret_cast<uintptr_t>(w->scales) & 1u) != 0 || (reinterpret_cast<uintptr_t>(w->data) & 31u) != 0)
+  if (!aligned16(x_codes) || !aligned16(x_scales) || !aligned16(w->scales) ||
+      (reinterpret_cast<uintptr_t>(w->data) & 31u) != 0)
     return HQ_ERR_ALIGN;
   g.n = (int)w->n;
   g.k = (int)w->k;

@@ -129,6 +129,7 @@ struct MxGroupedParams {
   void* y;                      // plain mode: [rows, N]; gated mode without quantizer: [rows, N/2]
   int y_dtype;
   int64_t y_stride;
+  int y_vec_ok;                 // y base and row pitch allow 16-byte stores (set by the launcher)
   uint8_t* hq;                  // gated mode with quantizer: e4m3 codes [n_rows, h_width] ...
   uint8_t* hs;                  // ... and e8m0 scales [n_rows, h_width/32] of the activated values
   int h_width;                  // N / 2 in gated mode

@@ -371,8 +371,10 @@ int32_t hq_fp8_gather_rows(const uint8_t* src_codes, int64_t src_code_stride, co
  * shared exponent = floor(log2(amax)) - 8, biased by 127 and kept in 0..254 (127 for an all-zero block), elements
  * scaled by 2^-e and converted with saturation at +-448 (the structure of MXFP4Layer::quantize, mxfp4/mod.rs:216-300).
  * Results equal dequantize-then-matmul over the QUANTIZED activations up to f32 summation order.
- * Requires K % 64 == 0, K >= 128; w->data 32-byte aligned with at least 64 readable bytes after the last row (the
- * packed 4-bit tensor map reads whole 128-element groups; what lies past a row's end meets zero activations).
+ * Requires K % 64 == 0, 128 <= K <= 9728 (the scale bytes of a work item are staged in shared memory); w->data
+ * 32-byte aligned with at least 64 readable bytes after the last row (the packed 4-bit tensor map reads whole
+ * 128-element groups; what lies past a row's end meets zero activations); x_codes, x_scales and w->scales 16-byte
+ * aligned.
  *
  * hq_mxfp8_quant_rows: codes [n_rows, k] / scales u8 [n_rows, k/32] of rows x[row_map[r]], r < min(*n_valid_dev,
  * n_rows) (row_map / n_valid_dev may be NULL).
