@@ -43,7 +43,8 @@ UNIT = "tokens/s"
 
 # DRAM bytes over algorithmic bytes from the ncu captures under profiles/
 NCU_TRAFFIC_RATIO_GEMV = 563.3 / 558.2      # hq::gemv_int8_kernel, 4096 -> 128256
-NCU_TRAFFIC_RATIO_FP8 = None                # hq::fp8_grouped_kernel (set once captured)
+NCU_TRAFFIC_RATIO_FP8 = 1573.4 / 1515.6     # hq::fp8_grouped_kernel, routed gate/up + down, 32 experts x 128 rows
+NCU_TRAFFIC_RATIO_MX = 527.3 / 543.2        # hq::mx_grouped_kernel, gate/up + down, 32 experts x 256 rows
 
 
 def algorithmic_bytes(k, n, m, x_size=2, y_size=4):
@@ -149,6 +150,49 @@ def gemv_cpu_step(threads, shapes, ws, xs):
         for m in MS:
             cbuild.linear("Q8_0", ws[(k, n)], None, None, xs[(k, m)], threads)
     return time.perf_counter() - t0
+
+
+def decode_other_formats(torch, dev, peak_gbs):
+    """Decode mat-vec of the other weight formats on one 4096 -> 65536 projection (142 - 268 MB of weights: larger
+    than L2, so every launch streams them from HBM), M = 1 and 4: median isolated launch duration by CUDA events,
+    algorithmic GB/s and the fraction of the measured HBM peak."""
+    import engine_b200 as hq
+    from tests import hq_synth as S
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2100)
+    n, k = 65536, 4096
+    out = {}
+    for fmt in ("Q4_K", "MXFP4", "FP8"):
+        if fmt == "Q4_K":
+            layer = hq.GgufMatMul(S.q4k_bank(torch, 1, n, k, gen, dev)[0], "Q4_K", k)
+            wbytes = n * (k // 256) * 144
+        elif fmt == "MXFP4":
+            b, sc = S.mxfp4_bank(torch, 1, n, k, gen, dev)
+            layer = hq.MXFP4Layer(b[0], sc[0])
+            wbytes = n * k // 2 + n * k // 32
+        else:
+            c, sc = S.fp8_bank(torch, 1, n, k, gen, dev)
+            layer = hq.BlockwiseFP8Linear(c[0], sc[0])
+            wbytes = n * k + (n // 128) * (k // 128) * 4
+        for m in (1, 4):
+            x = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
+            ts = []
+            for r in range(8):
+                a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                layer.forward_raw(x, torch.float32)
+                b_.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b_))
+            assert layer.device_status()[0] == 0
+            ms = statistics.median(ts[2:])
+            nbytes = wbytes + m * k * 2 + m * n * 4
+            out[f"{fmt}_4096x65536_m{m}"] = {"us": round(ms * 1e3, 1), "gbs": round(nbytes / ms / 1e6, 1),
+                                              "frac": round(nbytes / ms / 1e6 / peak_gbs, 4)}
+        del layer
+        torch.cuda.empty_cache()
+    return out
 
 
 def gemv_measure(args, torch, dev, rank, world, dist, with_cpu=True):
@@ -312,6 +356,11 @@ def gemv_measure(args, torch, dev, rank, world, dist, with_cpu=True):
         return None
     tokens_per_step = sum(MS)
     peaks = load_peaks()
+    other = None
+    if world == 1 and len(SHAPES) == 4:
+        layers.clear()
+        torch.cuda.empty_cache()
+        other = decode_other_formats(torch, dev, peaks["hbm_gbs"])
     step_bytes = sum(algorithmic_bytes(k, n, m) for (k, n) in SHAPES for m in MS)
     kern_ms = sum(per.values())
     achieved = step_bytes / (kern_ms / 1e3) / 1e9
@@ -347,6 +396,9 @@ def gemv_measure(args, torch, dev, rank, world, dist, with_cpu=True):
                      "by_launch_gbs": by_shape,
                      "by_launch_note": "throughput of back-to-back launches under programmatic dependent launch",
                      "isolated_launch_us": iso,
+                     "other_formats_decode": other,
+                     "other_formats_note": "isolated launches through QuantMethod.forward (event pair around one "
+                                           "call, weights larger than L2)",
                      "graph_step_gbs": round(step_bytes / (ms_total / args.steps / 1e3) / 1e9, 1)},
         "cpu_baseline": cpu,
         "e2e": {"value": world * tokens_per_step * args.steps / (e2e_ms / 1e3), "unit": UNIT,
@@ -532,17 +584,31 @@ def run_moe(args):
         time.sleep(0.3)
     experts.gemm_events = []
     barrier()
+    if args.profiler_range:
+        torch.cuda.profiler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for s_ in range(args.steps):
         step(s_)
     e1.record()
     barrier()
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
     # dominant kernels: the expert GEMM pair of the routed experts, by the CUDA events recorded around those two
     # launches inside the timed steps (on the stream they are launched on)
     gemm_ts = [a.elapsed_time(b) for a, b in experts.gemm_events]
+    gemm_timing = "median over the timed steps of CUDA events around the two launches"
+    if not gemm_ts and ep is None:
+        # the one-call layer path gives no place for events between its launches: the same two launches are timed
+        # through the two-call route after the timed steps
+        for j in range(5):
+            top = hq.moe_router_topk(logits[j % n_in], rcfg, sel_bias)
+            experts.forward(xs[j % n_in], top.values, top.indices, out_dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        gemm_ts = [a.elapsed_time(b) for a, b in experts.gemm_events][2:]
+        gemm_timing = "median of three separate runs of the same two launches after the timed steps"
     experts.gemm_events = None
     gemm_ms = statistics.median(gemm_ts) if gemm_ts else None
     # routed assignments this rank's experts received
@@ -633,7 +699,7 @@ def run_moe(args):
                     "frac": round(ach / peaks["bf16_tflops"], 4), "traffic": None, "peak_kind": peaks["kind"],
                     "peak_note": "measured dense bf16 peak (cuBLAS burst)",
                     "launch_ms_sum": round(gemm_ms, 4), "rows": rows_here,
-                    "timing": "median over the timed steps of CUDA events around the two launches"}
+                    "timing": gemm_timing}
             if fp8:
                 wbytes = 3 * e_l * i_ * h
                 # algorithmic bytes of the pair: every weight once, activation codes in, intermediate codes out and
@@ -660,7 +726,9 @@ def run_moe(args):
                              "frac_of_fp8_nominal_4500": round(ach / 4500.0, 4),
                              "algorithmic_bytes": abytes,
                              "hbm_gbs": round(abytes / (gemm_ms / 1e3) / 1e9, 1),
-                             "hbm_frac_of_measured": round(abytes / (gemm_ms / 1e3) / 1e9 / peaks["hbm_gbs"], 4)})
+                             "hbm_frac_of_measured": round(abytes / (gemm_ms / 1e3) / 1e9 / peaks["hbm_gbs"], 4),
+                             "traffic": int(NCU_TRAFFIC_RATIO_MX * abytes / 2),
+                             "traffic_note": "per launch: algorithmic bytes x the ncu dram/algorithmic ratio"})
             else:
                 rows_per_expert = rows_here / max(1, e_l)
                 ts_k = cfg["fmt"] == "MXFP4" or (cfg["fmt"] == "Q4_K" and rows_per_expert < 192)
@@ -795,6 +863,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="moe_fp8", choices=["gemv", "moe_q4k", "moe_fp8", "moe_mxfp4"])
     ap.add_argument("--tokens", type=int, default=0, help="override the global token count of a MoE workload")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="MoE workloads: bracket the timed steps with cudaProfilerStart/Stop, so that a profiler "
+                         "started with --profile-from-start off sees the timed steps only")
     ap.add_argument("--act16", action="store_true",
                     help="MoE workloads: 16-bit activations (mode A) instead of the quantized-activation path")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count of a MoE workload")

@@ -68,6 +68,16 @@ void fill_grouped(GroupedParams& g, const hq_weight* w, const hq_weight* w_up) {
   g.fp8_kb = (int)((w->k + 127) / 128);
 }
 
+// Row counts from which a call goes to the tensor-core grouped GEMM.  Q8_0's decode kernel streams at HBM speed,
+// so re-reading the weights once per 8 rows stays cheaper than expanding them for longer: four times the
+// configured thresholds.
+int64_t dense_tensor_min_rows(int format) {
+  return g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS] * (format == HQ_FMT_Q8_0 ? 4 : 1);
+}
+int64_t moe_tensor_min_rows(int format) {
+  return g_cfg[HQ_CFG_MOE_TENSOR_MIN_ROWS] * (format == HQ_FMT_Q8_0 ? 4 : 1);
+}
+
 // the tensor-core kernel takes f16 activation rows (it copies them into its operand tiles); hosts holding bf16 or
 // f32 activations cast once per call (cheaper than converting every gathered copy of a row)
 bool tensor_path_ok(const hq_weight* w, const hq_weight* w_up, int x_dtype, int64_t x_stride) {
@@ -140,7 +150,8 @@ int32_t hq_status_read(const int32_t* status_dev, int32_t out_host[4], void* str
 int64_t hq_linear_workspace_bytes(const hq_weight* w, int64_t m) {
   if (check_weight(w) != HQ_OK || m <= 0) return 0;
   if (w->n_experts != 1) return 0;
-  if ((w->format == HQ_FMT_Q4_K || w->format == HQ_FMT_FP8_BLOCK) && m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS])
+  if ((w->format == HQ_FMT_Q4_K || w->format == HQ_FMT_FP8_BLOCK || w->format == HQ_FMT_Q8_0) &&
+      m >= dense_tensor_min_rows(w->format))
     return 0;   // tensor-core path
   return gemv_int8_workspace_bytes(w->format, w->n, w->k, m);
 }
@@ -157,7 +168,7 @@ int32_t hq_linear_forward_ws(const hq_weight* w, const void* x, int32_t x_dtype,
   if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
   if (x_stride < w->k || y_stride < w->n) return HQ_ERR_SHAPE;
   if (workspace != nullptr && (workspace_bytes < 0 || ((uintptr_t)workspace & 255u) != 0)) return HQ_ERR_ALIGN;
-  if (m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS] && w->n_experts == 1 && tensor_path_ok(w, nullptr, x_dtype, x_stride)) {
+  if (m >= dense_tensor_min_rows(w->format) && w->n_experts == 1 && tensor_path_ok(w, nullptr, x_dtype, x_stride)) {
     GroupedParams g{};
     fill_grouped(g, w, nullptr);
     g.m = (int)m;
@@ -166,7 +177,7 @@ int32_t hq_linear_forward_ws(const hq_weight* w, const void* x, int32_t x_dtype,
     g.act.act = HQ_ACT_NONE;
     g.status = status_dev;
     g.tile_rows = m >= 512 ? 256 : 128;
-    g.weights_in_tmem = w->format != HQ_FMT_FP8_BLOCK;
+    g.weights_in_tmem = w->format != HQ_FMT_FP8_BLOCK && w->format != HQ_FMT_Q8_0;
     return launch_grouped_gemm(g, (int)((m + g.tile_rows - 1) / g.tile_rows), (cudaStream_t)stream);
   }
   GemvParams p{};
@@ -209,7 +220,7 @@ int32_t hq_linear_glu_forward(const hq_weight* w_gate, const hq_weight* w_up, co
   if (!aligned16(x) || (x_stride * dtype_size(x_dtype)) % 16 != 0) return HQ_ERR_ALIGN;
   const int64_t n_out = w_up != nullptr ? w_gate->n : w_gate->n / 2;
   if (x_stride < w_gate->k || y_stride < n_out) return HQ_ERR_SHAPE;
-  if (m >= g_cfg[HQ_CFG_DENSE_TENSOR_MIN_ROWS] && tensor_path_ok(w_gate, w_up, x_dtype, x_stride)) {
+  if (m >= dense_tensor_min_rows(w_gate->format) && tensor_path_ok(w_gate, w_up, x_dtype, x_stride)) {
     GroupedParams g{};
     fill_grouped(g, w_gate, w_up);
     g.m = (int)m;
@@ -351,7 +362,7 @@ int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const h
   const int32_t* x_rows =
       x_layout == HQ_ROWS_PER_TOKEN ? sorted_token : (x_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr);
   const int32_t* y_rows = out_layout == HQ_ROWS_PER_SLOT ? sorted_assign : nullptr;
-  if (n_tokens * top_k >= g_cfg[HQ_CFG_MOE_TENSOR_MIN_ROWS] * (int64_t)w->n_experts && tensor_path_ok(w, w_up, x_dtype, w->k)) {
+  if (n_tokens * top_k >= moe_tensor_min_rows(w->format) * (int64_t)w->n_experts && tensor_path_ok(w, w_up, x_dtype, w->k)) {
     GroupedParams g{};
     fill_grouped(g, w, w_up);
     g.x = x; g.x_dtype = x_dtype; g.x_stride = w->k;
@@ -799,7 +810,7 @@ int32_t plan_moe_layer(const hq_moe_layer* l, int64_t n_tokens, int32_t x_dtype,
   if (l->act.act == HQ_ACT_NONE) return HQ_ERR_FORMAT;
   p.rows = p.t * p.k;
   // the tensor-core kernel copies activations as f16: cast once per token here instead of per (token, slot) there
-  p.cast_x = x_dtype != HQ_DT_F16 && p.rows >= g_cfg[HQ_CFG_MOE_TENSOR_MIN_ROWS] * p.e &&
+  p.cast_x = x_dtype != HQ_DT_F16 && p.rows >= moe_tensor_min_rows(l->gate->format) * p.e &&
              tensor_path_ok(l->gate, l->up, HQ_DT_F16, l->gate->k);
   int64_t o = 0;
   p.off_ids = o;    o += up256(p.rows * 4);

@@ -60,12 +60,19 @@ __global__ void __launch_bounds__(1024) dispatch_scan_kernel(int32_t* __restrict
   int32_t* t8 = sm + n_experts;         // [E] tile8 offsets
   int32_t* t128 = sm + 2 * n_experts;   // [E] tile128 offsets
   int32_t* t256 = sm + 3 * n_experts;   // [E] tile256 offsets
+  __shared__ int32_t s_total;
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
     int32_t run = 0;
-    for (int b = 0; b < n_blocks; ++b) {
-      const int32_t c = counts[(int64_t)b * n_experts + e];
-      counts[(int64_t)b * n_experts + e] = run;
-      run += c;
+    // eight chunk counts are loaded before the first running sum is written back, so the loads overlap
+    for (int b0 = 0; b0 < n_blocks; b0 += 8) {
+      int32_t c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = b0 + j < n_blocks ? counts[(int64_t)(b0 + j) * n_experts + e] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (b0 + j < n_blocks) counts[(int64_t)(b0 + j) * n_experts + e] = run;
+        run += c[j];
+      }
     }
     tot[e] = run;
   }
@@ -99,6 +106,7 @@ __global__ void __launch_bounds__(1024) dispatch_scan_kernel(int32_t* __restrict
     }
     if (threadIdx.x == 0) {
       bounds[n_experts] = carry;
+      s_total = carry;
       header[0] = c8;
       header[1] = c128;
       header[2] = carry;
@@ -108,19 +116,20 @@ __global__ void __launch_bounds__(1024) dispatch_scan_kernel(int32_t* __restrict
   __syncthreads();
   // add the expert base to every chunk offset
   for (int64_t i = threadIdx.x; i < (int64_t)n_blocks * n_experts; i += blockDim.x) counts[i] += tot[i % n_experts];
-  // tile lists
-  for (int e = 0; e < n_experts; ++e) {
+  // tile lists: one warp per expert, lanes over the expert's tiles
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  for (int e = warp; e < n_experts; e += n_warps) {
     const int32_t start = tot[e];
-    const int32_t cnt = (e + 1 < n_experts ? tot[e + 1] : bounds[n_experts]) - start;
-    for (int i = threadIdx.x; i < (cnt + 7) / 8; i += blockDim.x) {
+    const int32_t cnt = (e + 1 < n_experts ? tot[e + 1] : s_total) - start;
+    for (int i = lane; i < (cnt + 7) / 8; i += 32) {
       tiles8[2 * (t8[e] + i)] = e;
       tiles8[2 * (t8[e] + i) + 1] = start + 8 * i;
     }
-    for (int i = threadIdx.x; i < (cnt + 127) / 128; i += blockDim.x) {
+    for (int i = lane; i < (cnt + 127) / 128; i += 32) {
       tiles128[2 * (t128[e] + i)] = e;
       tiles128[2 * (t128[e] + i) + 1] = start + 128 * i;
     }
-    for (int i = threadIdx.x; i < (cnt + 255) / 256; i += blockDim.x) {
+    for (int i = lane; i < (cnt + 255) / 256; i += 32) {
       tiles256[2 * (t256[e] + i)] = e;
       tiles256[2 * (t256[e] + i) + 1] = start + 256 * i;
     }
@@ -170,11 +179,13 @@ int32_t launch_dispatch(const uint32_t* ids, int64_t n_tokens, int top_k, int n_
   const int total = (int)(n_tokens * top_k);
   int32_t* counts = ws + l.off_counts;
   const size_t sm1 = (size_t)n_experts * 4;
-  dispatch_count_kernel<<<(unsigned)l.n_blocks, 1024, sm1, stream>>>(ids, total, n_experts, counts);
+  // no tokens: only the scan runs and writes all-zero bounds (a grid of zero blocks is not a valid launch)
+  if (l.n_blocks > 0) dispatch_count_kernel<<<(unsigned)l.n_blocks, 1024, sm1, stream>>>(ids, total, n_experts, counts);
   dispatch_scan_kernel<<<1, 1024, 4 * sm1, stream>>>(counts, (int)l.n_blocks, n_experts, bounds, ws,
                                                     ws + l.off_tiles8, ws + l.off_tiles128, ws + l.off_tiles256);
-  dispatch_scatter_kernel<<<(unsigned)l.n_blocks, 1024, sm1, stream>>>(ids, total, top_k, n_experts, counts,
-                                                                      sorted_assign, sorted_token, inv_perm);
+  if (l.n_blocks > 0)
+    dispatch_scatter_kernel<<<(unsigned)l.n_blocks, 1024, sm1, stream>>>(ids, total, top_k, n_experts, counts,
+                                                                        sorted_assign, sorted_token, inv_perm);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 

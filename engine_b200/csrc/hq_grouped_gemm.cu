@@ -113,9 +113,9 @@ struct GgSmem {
 // this stage is converted: fetch_a issues the loads into registers, emit_* converts to f16.  A thread owns 16
 // consecutive k (quarter `q` of the stage's 64) of one weight row: two 16-byte chunks, natural k order.
 struct RawA {
-  uint4 hdr;          // Q4_K: super-block header {d, dmin, 12 scale bytes}
-  uint4 q;            // Q4_K: 16 nibble bytes; FP8: 16 codes; MXFP4: .x/.y = 8 nibble bytes
-  uint32_t aux;       // FP8: relative block scale (f32 bits); MXFP4: e8m0 byte
+  uint4 hdr;          // Q4_K: super-block header {d, dmin, 12 scale bytes}; Q8_0: .x = fifth payload word
+  uint4 q;            // Q4_K: 16 nibble bytes; FP8: 16 codes; MXFP4: .x/.y = 8 nibble bytes; Q8_0: payload words
+  uint32_t aux;       // FP8: relative block scale (f32 bits); MXFP4: e8m0 byte; Q8_0: d (f16 bits) | shift << 16
 };
 
 template <int FMT>
@@ -130,6 +130,17 @@ __device__ __forceinline__ void fetch_a(RawA& r, const uint8_t* row_base, const 
   } else if (FMT == HQ_FMT_FP8_BLOCK) {
     r.q = __ldg(reinterpret_cast<const uint4*>(row_base + k0 + 16 * q));
     r.aux = __float_as_uint(__ldg(rel + k0 / 128));
+  } else if (FMT == HQ_FMT_Q8_0) {
+    // half a 34-byte block: 16 int8 behind the block's f16 d.  Blocks start on 2-byte boundaries (rows on 4-byte
+    // ones), so the payload is fetched as aligned words -- five when it starts in the middle of a word, in which
+    // case the fifth still lies inside the block -- and shifted into place by emit_q8_0
+    const uint8_t* blk = row_base + 34 * ((k0 >> 5) + (q >> 1));
+    const uint8_t* pay = blk + 2 + 16 * (q & 1);
+    const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(pay) & 2u);
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(pay - mis);
+    r.q = make_uint4(__ldg(wp), __ldg(wp + 1), __ldg(wp + 2), __ldg(wp + 3));
+    r.hdr.x = mis ? __ldg(wp + 4) : 0u;
+    r.aux = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk)) | (mis << 19);
   } else {
     const int blk = (k0 >> 5) + (q >> 1);
     const uint2 v = __ldg(reinterpret_cast<const uint2*>(row_base + 16 * blk + 8 * (q & 1)));
@@ -171,6 +182,28 @@ __device__ __forceinline__ void emit_q4_k(const RawA& r, int k0, int q, uint32_t
     const __half2 h01 = *reinterpret_cast<__half2*>(&p01), h23 = *reinterpret_cast<__half2*>(&p23);
     __half2 w01 = __hadd2(__hfma2(h01, dh2, ch2), __hfma2(h01, dl2, cl2));
     __half2 w23 = __hadd2(__hfma2(h23, dh2, ch2), __hfma2(h23, dl2, cl2));
+    out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
+    out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
+  }
+}
+
+// Q8_0: w = d * q.  Bytes q + 128 become the f16 pair (1024 + u0, 1024 + u1) with one permute, 1152 is subtracted
+// exactly, and the product with the block's f16 d is rounded once to f16 (relative error <= 2^-11 per weight).
+__device__ __forceinline__ void emit_q8_0(const RawA& r, uint32_t (&out)[8]) {
+  const uint32_t sh = (r.aux >> 16) & 31u;          // 0 or 16
+  const uint32_t raw[5] = {r.q.x, r.q.y, r.q.z, r.q.w, r.hdr.x};
+  const uint32_t d16 = r.aux & 0xFFFFu;
+  const uint32_t dd = d16 | (d16 << 16);
+  const __half2 d2 = *reinterpret_cast<const __half2*>(&dd);
+  const uint32_t off = 0x64806480u;                  // f16 1152 twice
+  const __half2 o2 = *reinterpret_cast<const __half2*>(&off);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t w = __funnelshift_r(raw[i], raw[i + 1], sh) ^ 0x80808080u;
+    uint32_t p01 = __byte_perm(w, 0x64646464u, 0x4140);
+    uint32_t p23 = __byte_perm(w, 0x64646464u, 0x4342);
+    __half2 w01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), o2), d2);
+    __half2 w23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), o2), d2);
     out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
     out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
   }
@@ -555,6 +588,8 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
             emit_q4_k(use[bank], k0, q, v);
           } else if (FMT == HQ_FMT_FP8_BLOCK) {
             emit_fp8(use[bank], v);
+          } else if (FMT == HQ_FMT_Q8_0) {
+            emit_q8_0(use[bank], v);
           } else {
             if (!emit_mxfp4(use[bank], v)) report_status(p.status, HQ_DEV_SCALE_RANGE, 600);
           }
@@ -1104,8 +1139,10 @@ static int32_t launch_gg_ts(const GroupedParams& p, int max_tiles, cudaStream_t 
 template <int FMT>
 static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
   const bool two = p.w_up != nullptr;
-  if (p.tile_rows == 128 && p.weights_in_tmem)
-    return two ? launch_gg_ts<FMT, 2>(p, max_tiles, stream) : launch_gg_ts<FMT, 1>(p, max_tiles, stream);
+  if constexpr (FMT != HQ_FMT_Q8_0) {       // Q8_0 has no tensor-memory variant
+    if (p.tile_rows == 128 && p.weights_in_tmem)
+      return two ? launch_gg_ts<FMT, 2>(p, max_tiles, stream) : launch_gg_ts<FMT, 1>(p, max_tiles, stream);
+  }
   if (p.tile_rows == 256) {
     return two ? launch_gg<FMT, 2, 256>(p, max_tiles, stream) : launch_gg<FMT, 1, 256>(p, max_tiles, stream);
   }
@@ -1113,7 +1150,8 @@ static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t
 }
 
 bool grouped_gemm_supported(int format, int64_t n, int64_t k) {
-  if (format != HQ_FMT_Q4_K && format != HQ_FMT_FP8_BLOCK && format != HQ_FMT_MXFP4) return false;
+  if (format != HQ_FMT_Q4_K && format != HQ_FMT_FP8_BLOCK && format != HQ_FMT_MXFP4 && format != HQ_FMT_Q8_0)
+    return false;
   if (k % kTileK != 0) return false;
   if (format == HQ_FMT_FP8_BLOCK && (n % 128 != 0 || k % 128 != 0)) return false;
   return true;
@@ -1126,6 +1164,10 @@ int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t 
     case HQ_FMT_Q4_K: return launch_gg_fmt<HQ_FMT_Q4_K>(p, max_tiles, stream);
     case HQ_FMT_FP8_BLOCK: return launch_gg_fmt<HQ_FMT_FP8_BLOCK>(p, max_tiles, stream);
     case HQ_FMT_MXFP4: return launch_gg_fmt<HQ_FMT_MXFP4>(p, max_tiles, stream);
+    case HQ_FMT_Q8_0:
+      if ((reinterpret_cast<uintptr_t>(p.w) & 3u) != 0 || (p.w_up != nullptr && (reinterpret_cast<uintptr_t>(p.w_up) & 3u) != 0))
+        return HQ_ERR_ALIGN;
+      return launch_gg_fmt<HQ_FMT_Q8_0>(p, max_tiles, stream);
     default: return HQ_ERR_FORMAT;
   }
 }

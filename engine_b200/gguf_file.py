@@ -124,7 +124,7 @@ class GgufFile:
             raise GgufError(f"{name}: GGML type {t.type_name} is not on this path (Q8_0, Q4_K and Q6_K are)")
         if len(t.shape) not in (2, 3):
             raise GgufError(f"{name}: expected a matrix or an expert bank, got shape {t.shape}")
-        data = torch.from_numpy(np.ascontiguousarray(self.raw(name))).to(device)
+        data = torch.from_numpy(np.array(self.raw(name), copy=True)).to(device)
         bias = None
         if bias_name is not None and bias_name in self.tensors:
             b = self.tensors[bias_name]

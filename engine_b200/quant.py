@@ -87,16 +87,18 @@ def convert(x: torch.Tensor, dtype: torch.dtype, status: torch.Tensor | None = N
 
 def tensor_path_expected(layer, n_rows_total: int, dense: bool) -> bool:
     """Mirror of the C-side rule that sends a call to the tensor-core grouped GEMM (prefill-sized row counts,
-    Q4_K / FP8 / MXFP4, K % 64 == 0).  Used only to decide whether to hand activations over as f16, which that
-    kernel copies into its operand tiles without a conversion pass."""
-    if layer.format == L.FMT_Q8_0 or layer.k % 64:
+    K % 64 == 0; Q8_0 from four times the configured row thresholds, because its decode kernel streams at HBM
+    speed).  Used only to decide whether to hand activations over as f16, which that kernel copies into its
+    operand tiles without a conversion pass."""
+    if layer.k % 64:
         return False
     if layer.format == L.FMT_FP8_BLOCK and (layer.n % 128 or layer.k % 128):
         return False
     lib = L.lib()
+    mult = 4 if layer.format == L.FMT_Q8_0 else 1
     if dense:
-        return n_rows_total >= lib.hq_config_get(L.CFG_DENSE_TENSOR_MIN_ROWS)
-    return n_rows_total >= lib.hq_config_get(L.CFG_MOE_TENSOR_MIN_ROWS) * layer.n_experts
+        return n_rows_total >= mult * lib.hq_config_get(L.CFG_DENSE_TENSOR_MIN_ROWS)
+    return n_rows_total >= mult * lib.hq_config_get(L.CFG_MOE_TENSOR_MIN_ROWS) * layer.n_experts
 
 
 class QuantMethod:

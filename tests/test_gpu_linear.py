@@ -54,6 +54,15 @@ def test_q4_k_config_f32_activations(m):
     assert T.rel_l2(got, want) <= 1e-3
 
 
+@pytest.mark.parametrize("m", [36, 128, 300, 700])
+@pytest.mark.parametrize("dt", ["float16", "bfloat16"])
+def test_q8_0_prefill_rows_on_the_tensor_cores(m, dt):
+    # more than 32 rows: the 34-byte blocks are expanded to f16 (q x d rounded once) and multiplied by tcgen05,
+    # instead of streaming the weights once per 8 rows; N = 1000 ends in a partial 128-row tile
+    got, want = run_case("Q8_0", 1000, 2048, m, getattr(torch, dt), torch.float32, 60 + m)
+    assert T.rel_l2(got, want) <= 1e-3
+
+
 @pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "FP8", "MXFP4"])
 def test_ragged_rows_and_tile_heights(fmt):
     # N not a multiple of the row tile, M not a multiple of 8, and an N large enough for the tall tiles

@@ -53,6 +53,39 @@ def test_noalloc_dispatch_matches_regular_entry_point_twice():
             assert torch.equal(a, b)       # integer tables: exact
 
 
+def test_noalloc_dispatch_at_exact_capacity_and_with_no_tokens():
+    """8192 x 8 ids over 512 experts fill the fixed array to its last word; an off-by-one in its size would write
+    into neighbouring device globals, so the tables are compared and the regular entry point is run again
+    afterwards (it shares no state with the array).  Zero tokens: both entry points return at once and touch
+    nothing."""
+    from engine_b200 import _lib as L
+    lib = L.lib()
+    rng = np.random.Generator(np.random.PCG64(4343))
+    t, k, e = 8192, 8, 512
+    ids_np = np.stack([rng.choice(e, size=k, replace=False) for _ in range(t)]).astype(np.int32)
+    ids = torch.from_numpy(ids_np).to(DEV)
+    want = _tables(lib, ids, e, noalloc=False)
+    got = _tables(lib, ids, e, noalloc=True)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    again = _tables(lib, ids, e, noalloc=False)
+    for a, b in zip(again, want):
+        assert torch.equal(a, b)
+    sentinel = torch.full((8,), -5, dtype=torch.int32, device=DEV)
+    p = sentinel.data_ptr()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.hq_moe_dispatch_build_noalloc(p, 0, 8, 4, p, p, p, p, stream) == 0
+    torch.cuda.synchronize()
+    # the bounds of an empty call are all zero (n_experts + 1 words); nothing else is written
+    assert sentinel.tolist() == [0, 0, 0, 0, 0, -5, -5, -5]
+    sentinel.fill_(-5)
+    nbytes = lib.hq_moe_dispatch_workspace_bytes(0, 8, 4)
+    ws = torch.empty(max(nbytes // 4, 4), dtype=torch.int32, device=DEV)
+    assert lib.hq_moe_dispatch_build(p, 0, 8, 4, p, p, p, p, ws.data_ptr(), nbytes, stream) == 0
+    torch.cuda.synchronize()
+    assert sentinel.tolist() == [0, 0, 0, 0, 0, -5, -5, -5]
+
+
 def test_noalloc_dispatch_rejects_sizes_beyond_its_array():
     from engine_b200 import _lib as L
     lib = L.lib()
