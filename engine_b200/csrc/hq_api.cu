@@ -16,6 +16,7 @@ int64_t weight_row_bytes(int format, int64_t k) {
     case HQ_FMT_Q4_K: return k / 256 * 144;
     case HQ_FMT_FP8_BLOCK: return k;
     case HQ_FMT_MXFP4: return k / 2;
+    case HQ_FMT_Q6_K: return k / 256 * 210;
     default: return -1;
   }
 }
@@ -27,6 +28,7 @@ int32_t check_weight(const hq_weight* w) {
   switch (w->format) {
     case HQ_FMT_Q8_0:
     case HQ_FMT_Q4_K:
+    case HQ_FMT_Q6_K:
       if (w->k % 256 != 0) return HQ_ERR_SHAPE;
       break;
     case HQ_FMT_FP8_BLOCK:
@@ -41,7 +43,8 @@ int32_t check_weight(const hq_weight* w) {
       return HQ_ERR_FORMAT;
   }
   if (!aligned16(w->data)) return HQ_ERR_ALIGN;
-  if (weight_row_bytes(w->format, w->k) % 16 != 0) return HQ_ERR_ALIGN;
+  // Q6_K rows (210 bytes per super-block) are only 2-byte aligned; its kernels read bytes and aligned words
+  if (w->format != HQ_FMT_Q6_K && weight_row_bytes(w->format, w->k) % 16 != 0) return HQ_ERR_ALIGN;
   if (w->bias != nullptr && !valid_dtype(w->bias_dtype)) return HQ_ERR_FORMAT;
   return HQ_OK;
 }
@@ -372,10 +375,8 @@ int32_t hq_moe_gather_forward(const hq_weight* w, const hq_weight* w_up, const h
     // memory for two accumulator buffers
     const bool many_rows = n_tokens * top_k >= 192 * (int64_t)w->n_experts;
     g.tile_rows = (w_up == nullptr && many_rows) ? 256 : 128;
-    // The kernel that expands the weights into tensor memory (128-token tiles) against the one that writes them
-    // to shared memory, measured on whole layers: MXFP4 at 8192 tokens 3.23 against 3.68 ms; Q4_K at 1024 tokens
-    // 0.39 against 0.45 ms, but at 4096 tokens (experts fill their tiles) 0.99 against 0.91 ms; the 16-bit
-    // block-FP8 path was not measured on it and stays where it was.
+    // the variant that expands the weights into tensor memory (128-token tiles): MXFP4 always, Q4_K while the
+    // experts do not fill 256-token tiles; block-FP8 and Q8_0 expand into shared memory
     g.weights_in_tmem = w->format == HQ_FMT_MXFP4 || (w->format == HQ_FMT_Q4_K && !many_rows);
     if (w->format == HQ_FMT_MXFP4) g.tile_rows = 128;
     g.tiles = ws + (g.tile_rows == 256 ? l.off_tiles256 : l.off_tiles128);

@@ -103,6 +103,9 @@ inline int sm_count() {
   return cached[dev];
 }
 
+// the Q6_K decode kernel (hq_gemv_q6k.cu)
+int32_t launch_gemv_q6k(const GemvParams& p, int n_y_max, cudaStream_t stream);
+
 // the Q8_0 / Q4_K decode kernel (hq_gemv_int8.cu)
 int32_t launch_gemv_int8(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream);
 

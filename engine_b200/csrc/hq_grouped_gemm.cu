@@ -116,6 +116,8 @@ struct RawA {
   uint4 hdr;          // Q4_K: super-block header {d, dmin, 12 scale bytes}; Q8_0: .x = fifth payload word
   uint4 q;            // Q4_K: 16 nibble bytes; FP8: 16 codes; MXFP4: .x/.y = 8 nibble bytes; Q8_0: payload words
   uint32_t aux;       // FP8: relative block scale (f32 bits); MXFP4: e8m0 byte; Q8_0: d (f16 bits) | shift << 16
+  uint4 ext;          // Q6_K only: .x / .y = fifth word of the low-nibble / high-bit bytes, .z = d (f16 bits) |
+                      // scale byte << 16, .w = shifts (low-nibble bytes | high-bit bytes << 8)
 };
 
 template <int FMT>
@@ -130,6 +132,27 @@ __device__ __forceinline__ void fetch_a(RawA& r, const uint8_t* row_base, const 
   } else if (FMT == HQ_FMT_FP8_BLOCK) {
     r.q = __ldg(reinterpret_cast<const uint4*>(row_base + k0 + 16 * q));
     r.aux = __float_as_uint(__ldg(rel + k0 / 128));
+  } else if (FMT == HQ_FMT_Q6_K) {
+    // 16 consecutive k inside a 210-byte super-block: position 128 h + 32 j + 16 s + t (t = 0..15) takes the low
+    // (j < 2) or high nibbles of ql[64 h + 32 (j & 1) + 16 s + t] and bits 2j, 2j + 1 of qh[32 h + 16 s + t], with
+    // scale 8 h + 2 j + s.  Blocks start on 2-byte boundaries: aligned words, five when the run starts in the
+    // middle of a word (the extra bytes are inside the block or, in front of it, inside the tensor)
+    const int pos = (k0 & 255) + 16 * q;
+    const int h = pos >> 7, j = (pos >> 5) & 3, sx = (pos >> 4) & 1;
+    const uint8_t* blk = row_base + 210 * (k0 >> 8);
+    const uint8_t* pl = blk + 64 * h + 32 * (j & 1) + 16 * sx;
+    const uint8_t* ph = blk + 128 + 32 * h + 16 * sx;
+    const uint32_t ml = (uint32_t)(reinterpret_cast<uintptr_t>(pl) & 2u), mh = (uint32_t)(reinterpret_cast<uintptr_t>(ph) & 2u);
+    const uint32_t* wl = reinterpret_cast<const uint32_t*>(pl - ml);
+    const uint32_t* wh = reinterpret_cast<const uint32_t*>(ph - mh);
+    r.q = make_uint4(__ldg(wl), __ldg(wl + 1), __ldg(wl + 2), __ldg(wl + 3));
+    r.hdr = make_uint4(__ldg(wh), __ldg(wh + 1), __ldg(wh + 2), __ldg(wh + 3));
+    r.ext.x = ml ? __ldg(wl + 4) : 0u;
+    r.ext.y = mh ? __ldg(wh + 4) : 0u;
+    r.ext.z = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk + 208)) |
+              ((uint32_t)__ldg(blk + 192 + 8 * h + 2 * j + sx) << 16);
+    r.ext.w = (ml << 3) | (mh << 11);
+    r.aux = (uint32_t)j;
   } else if (FMT == HQ_FMT_Q8_0) {
     // half a 34-byte block: 16 int8 behind the block's f16 d.  Blocks start on 2-byte boundaries (rows on 4-byte
     // ones), so the payload is fetched as aligned words -- five when it starts in the middle of a word, in which
@@ -204,6 +227,33 @@ __device__ __forceinline__ void emit_q8_0(const RawA& r, uint32_t (&out)[8]) {
     uint32_t p23 = __byte_perm(w, 0x64646464u, 0x4342);
     __half2 w01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), o2), d2);
     __half2 w23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), o2), d2);
+    out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
+    out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
+  }
+}
+
+// Q6_K: w = d * scale * (q - 32).  The 6-bit codes are assembled bytewise (nibble | two high bits << 4), become the
+// f16 pair (1024 + q0, 1024 + q1) with one permute, 1056 is subtracted exactly, and the product with d * scale
+// (computed in f32, rounded to f16) is rounded once more: two roundings of 2^-11 per weight.
+__device__ __forceinline__ void emit_q6_k(const RawA& r, uint32_t (&out)[8]) {
+  const uint32_t shl = r.ext.w & 31u, shh = (r.ext.w >> 8) & 31u;   // 0 or 16
+  const uint32_t j = r.aux;
+  const uint32_t lo[5] = {r.q.x, r.q.y, r.q.z, r.q.w, r.ext.x};
+  const uint32_t hi[5] = {r.hdr.x, r.hdr.y, r.hdr.z, r.hdr.w, r.ext.y};
+  const float ds = half_bits_to_float(r.ext.z & 0xFFFFu) * (float)(int)(int8_t)((r.ext.z >> 16) & 0xFFu);
+  const __half2 ds2 = __float2half2_rn(ds);
+  const uint32_t off = 0x64206420u;                  // f16 1056 twice
+  const __half2 o2 = *reinterpret_cast<const __half2*>(&off);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lw = __funnelshift_r(lo[i], lo[i + 1], shl);
+    const uint32_t hw = __funnelshift_r(hi[i], hi[i + 1], shh);
+    const uint32_t nib = (j < 2 ? lw : (lw >> 4)) & 0x0F0F0F0Fu;
+    const uint32_t w6 = nib | (((hw >> (2 * j)) & 0x03030303u) << 4);
+    uint32_t p01 = __byte_perm(w6, 0x64646464u, 0x4140);
+    uint32_t p23 = __byte_perm(w6, 0x64646464u, 0x4342);
+    __half2 w01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), o2), ds2);
+    __half2 w23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), o2), ds2);
     out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
     out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
   }
@@ -590,6 +640,8 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
             emit_fp8(use[bank], v);
           } else if (FMT == HQ_FMT_Q8_0) {
             emit_q8_0(use[bank], v);
+          } else if (FMT == HQ_FMT_Q6_K) {
+            emit_q6_k(use[bank], v);
           } else {
             if (!emit_mxfp4(use[bank], v)) report_status(p.status, HQ_DEV_SCALE_RANGE, 600);
           }
@@ -1139,7 +1191,7 @@ static int32_t launch_gg_ts(const GroupedParams& p, int max_tiles, cudaStream_t 
 template <int FMT>
 static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
   const bool two = p.w_up != nullptr;
-  if constexpr (FMT != HQ_FMT_Q8_0) {       // Q8_0 has no tensor-memory variant
+  if constexpr (FMT != HQ_FMT_Q8_0 && FMT != HQ_FMT_Q6_K) {       // Q8_0 and Q6_K have no tensor-memory variant
     if (p.tile_rows == 128 && p.weights_in_tmem)
       return two ? launch_gg_ts<FMT, 2>(p, max_tiles, stream) : launch_gg_ts<FMT, 1>(p, max_tiles, stream);
   }
@@ -1150,7 +1202,8 @@ static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t
 }
 
 bool grouped_gemm_supported(int format, int64_t n, int64_t k) {
-  if (format != HQ_FMT_Q4_K && format != HQ_FMT_FP8_BLOCK && format != HQ_FMT_MXFP4 && format != HQ_FMT_Q8_0)
+  if (format != HQ_FMT_Q4_K && format != HQ_FMT_FP8_BLOCK && format != HQ_FMT_MXFP4 && format != HQ_FMT_Q8_0 &&
+      format != HQ_FMT_Q6_K)
     return false;
   if (k % kTileK != 0) return false;
   if (format == HQ_FMT_FP8_BLOCK && (n % 128 != 0 || k % 128 != 0)) return false;
@@ -1168,6 +1221,10 @@ int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t 
       if ((reinterpret_cast<uintptr_t>(p.w) & 3u) != 0 || (p.w_up != nullptr && (reinterpret_cast<uintptr_t>(p.w_up) & 3u) != 0))
         return HQ_ERR_ALIGN;
       return launch_gg_fmt<HQ_FMT_Q8_0>(p, max_tiles, stream);
+    case HQ_FMT_Q6_K:
+      if ((reinterpret_cast<uintptr_t>(p.w) & 3u) != 0 || (p.w_up != nullptr && (reinterpret_cast<uintptr_t>(p.w_up) & 3u) != 0))
+        return HQ_ERR_ALIGN;
+      return launch_gg_fmt<HQ_FMT_Q6_K>(p, max_tiles, stream);
     default: return HQ_ERR_FORMAT;
   }
 }

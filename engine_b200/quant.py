@@ -248,8 +248,8 @@ class QuantMethod:
         raise NotImplementedError
 
 
-GGML_Q8_0, GGML_Q4_K = "Q8_0", "Q4_K"
-_GGML = {GGML_Q8_0: (L.FMT_Q8_0, 32, 34), GGML_Q4_K: (L.FMT_Q4_K, 256, 144)}
+GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = "Q8_0", "Q4_K", "Q6_K"
+_GGML = {GGML_Q8_0: (L.FMT_Q8_0, 32, 34), GGML_Q4_K: (L.FMT_Q4_K, 256, 144), GGML_Q6_K: (L.FMT_Q6_K, 256, 210)}
 
 
 class GgufMatMul(QuantMethod):
@@ -259,7 +259,7 @@ class GgufMatMul(QuantMethod):
     def __init__(self, data: torch.Tensor, qtype: str, k: int, bias: torch.Tensor | None = None):
         super().__init__()
         if qtype not in _GGML:
-            raise L.HqError(f"GGML type {qtype} is not on this path (Q8_0 and Q4_K are)")
+            raise L.HqError(f"GGML type {qtype} is not on this path (Q8_0, Q4_K and Q6_K are)")
         _require_cuda(data, "data")
         self.format, blk, nbytes = _GGML[qtype]
         self.qtype = qtype

@@ -23,6 +23,7 @@ QK8_0 = 32          # elements per Q8_0 block
 Q8_0_BYTES = 34     # half d + 32 int8
 QK_K = 256          # elements per k-quant super-block
 Q4_K_BYTES = 144    # half d, half dmin, 12 scale bytes, 128 nibble bytes
+Q6_K_BYTES = 210    # 128 low-nibble bytes, 64 high-bit bytes, 16 int8 scales, half d
 MXFP4_BLOCK = 32
 FP8_MAX = 448.0
 
@@ -103,6 +104,67 @@ def q4_k_dequant(raw: np.ndarray, k: int) -> np.ndarray:
     d1 = (d * sc.astype(np.float32))[..., None]                            # [rows, nsb, 8, 1]
     m1 = (dmin * mn.astype(np.float32))[..., None]
     return (d1 * q - m1).reshape(rows, k)
+
+
+# ----------------------------------------------------------------------------
+# Q6_K  (block_q6_K {uint8 ql[128]; uint8 qh[64]; int8 scales[16]; half d}; 16 sub-blocks of 16 elements,
+#        value = d * scale * (q - 32), q = 4 low bits from ql + 2 high bits from qh.  The type carries
+#        attn_v / ffn_down in Q4_K_M files; it is in the reference's decode list,
+#        hanzo-quant/src/gguf/fast_mmvq.rs:36-50.  Element order per 128-element half: for l in 0..31 the bytes
+#        ql[l], ql[l+32], qh[l] give elements l, l+32, l+64, l+96 -- ggml's dequantize_row_q6_K.)
+# ----------------------------------------------------------------------------
+
+def q6_k_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/256*210] -> f32 [rows, K]."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    nsb = k // QK_K
+    blk = raw.reshape(rows, nsb, Q6_K_BYTES)
+    ql = blk[:, :, 0:128].reshape(rows, nsb, 2, 2, 32)        # [half][first/second 32 bytes][l]
+    qh = blk[:, :, 128:192].reshape(rows, nsb, 2, 32)         # [half][l]
+    sc = blk[:, :, 192:208].copy().view(np.int8).astype(np.float32).reshape(rows, nsb, 2, 8)
+    d = blk[:, :, 208:210].copy().view(np.float16).astype(np.float32)          # [rows, nsb, 1]
+    q = np.empty((rows, nsb, 2, 4, 32), np.int32)             # [half][j][l] -> element 128 half + 32 j + l
+    for j in range(4):
+        nib = (ql[:, :, :, j & 1, :] & 0x0F) if j < 2 else (ql[:, :, :, j & 1, :] >> 4)
+        q[:, :, :, j, :] = (nib.astype(np.int32) | (((qh >> (2 * j)) & 3).astype(np.int32) << 4)) - 32
+    # scale index inside a half: 2 j + l // 16
+    s = sc.reshape(rows, nsb, 2, 4, 2)
+    s = np.repeat(s, 16, axis=-1)                              # [half][j][l]
+    out = d[:, :, :, None, None] * s * q.astype(np.float32)
+    return out.reshape(rows, k).astype(np.float32)
+
+
+def q6_k_quantize(w: np.ndarray) -> np.ndarray:
+    """f32 [rows, K] -> uint8 [rows, K/256*210].  A plain quantizer for building test and benchmark weights (ggml's
+    own make_qx_quants search is not restated; any valid block exercises the kernels): per 16-element sub-block
+    scale = absmax / 31 signed by the element of largest magnitude, d = max|scale| / 127, integer scales and
+    6-bit codes by round-to-nearest."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    rows, k = w.shape
+    nsb = k // QK_K
+    x = w.reshape(rows, nsb, 16, 16)
+    amax = np.abs(x).max(-1)
+    scale = amax / np.float32(31.0)
+    dmax = scale.max(-1, keepdims=True)
+    d = (dmax / np.float32(127.0)).astype(np.float16)
+    df = d.astype(np.float32)
+    isc = np.where(df > 0, np.rint(scale / np.where(df > 0, df, 1)), 0).clip(-128, 127).astype(np.int8)
+    step = df * isc.astype(np.float32)
+    q = np.where(step[..., None] != 0, np.rint(x / np.where(step[..., None] != 0, step[..., None], 1)), 0)
+    q = (q.clip(-32, 31) + 32).astype(np.uint8).reshape(rows, nsb, 2, 4, 32)   # [half][j][l]
+    blk = np.zeros((rows, nsb, Q6_K_BYTES), np.uint8)
+    ql = np.zeros((rows, nsb, 2, 2, 32), np.uint8)
+    qh = np.zeros((rows, nsb, 2, 32), np.uint8)
+    for j in range(4):
+        nib = q[:, :, :, j, :] & 0x0F
+        ql[:, :, :, j & 1, :] |= nib if j < 2 else (nib << 4)
+        qh |= ((q[:, :, :, j, :] >> 4) & 3) << (2 * j)
+    blk[:, :, 0:128] = ql.reshape(rows, nsb, 128)
+    blk[:, :, 128:192] = qh.reshape(rows, nsb, 64)
+    blk[:, :, 192:208] = isc.reshape(rows, nsb, 16).view(np.uint8)
+    blk[:, :, 208:210] = d.reshape(rows, nsb, 1).view(np.uint8)
+    return blk.reshape(rows, nsb * Q6_K_BYTES)
 
 
 def _nearest_int(f: np.ndarray) -> np.ndarray:

@@ -30,7 +30,7 @@ def _sigmoid(x: np.ndarray) -> np.ndarray:
 def deterministic_topk_indices(scores: np.ndarray, k: int) -> np.ndarray:
     """Canonical selection: order each row by (score DESC, expert id ASC), take k
     (hanzo-engine/src/ops.rs:241-251).  NaN scores are treated as -inf, as the
-    reference's CUDA kernel does (hanzo-engine/src/cuda/sort.cu:1088-1090); its CPU
+    reference's CUDA kernel does (hanzo-engine/src/cuda/sort.cu:1084-1086); its CPU
     fallback sorts with f32::total_cmp, which would put a positive NaN first -- the
     two reference paths disagree there and this restatement follows the GPU one."""
     s = np.where(np.isnan(scores), -np.inf, scores).astype(np.float32)

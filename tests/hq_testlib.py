@@ -28,6 +28,10 @@ def make_weight(fmt: str, rng, n: int, k: int, experts: int = 0, sigma: float = 
         raw = F.q4_k_quantize(w)
         deq = F.q4_k_dequant(raw, k)
         arrays = {"data": raw.reshape(e, n, -1)}
+    elif fmt == "Q6_K":
+        raw = F.q6_k_quantize(w)
+        deq = F.q6_k_dequant(raw, k)
+        arrays = {"data": raw.reshape(e, n, -1)}
     elif fmt == "FP8":
         codes, scales, deqs = [], [], []
         for i in range(e):
@@ -52,7 +56,7 @@ def make_layer(fmt: str, arrays: dict, k: int, device, bias=None):
     import torch
     import engine_b200 as hq
     t = {k_: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k_, v in arrays.items()}
-    if fmt in ("Q8_0", "Q4_K"):
+    if fmt in ("Q8_0", "Q4_K", "Q6_K"):
         return hq.GgufMatMul(t["data"], fmt, k, bias)
     if fmt == "FP8":
         return hq.BlockwiseFP8Linear(t["weight"], t["scale"], bias)

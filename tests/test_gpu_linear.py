@@ -10,7 +10,7 @@ from oracle import formats as F
 from oracle import moe as M
 from tests import hq_testlib as T
 
-TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
+TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "Q6_K": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
 DEV = "cuda:0"
 
 
@@ -33,7 +33,7 @@ def run_case(fmt, n, k, m, x_dtype, out_dtype, seed, bias=False):
     return y.to(torch.float32).cpu().numpy(), want
 
 
-@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "FP8", "MXFP4"])
+@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "Q6_K", "FP8", "MXFP4"])
 @pytest.mark.parametrize("m", [1, 2, 4, 8])
 def test_decode_rows_f32_out(fmt, m):
     got, want = run_case(fmt, 512, 1024, m, torch.bfloat16, torch.float32, 10 + m)
@@ -41,7 +41,8 @@ def test_decode_rows_f32_out(fmt, m):
 
 
 @pytest.mark.parametrize("fmt,n,k", [("Q8_0", 4096, 4096), ("Q4_K", 4096, 4096), ("Q8_0", 1000, 14336),
-                                     ("FP8", 2048, 7168), ("MXFP4", 5760, 2880), ("Q4_K", 2048, 768)])
+                                     ("FP8", 2048, 7168), ("MXFP4", 5760, 2880), ("Q4_K", 2048, 768),
+                                     ("Q6_K", 2048, 768), ("Q6_K", 1000, 4096)])
 def test_model_shapes(fmt, n, k):
     got, want = run_case(fmt, n, k, 3, torch.bfloat16, torch.float32, 20, bias=(fmt == "MXFP4"))
     assert T.rel_l2(got, want) <= TOL[fmt]
@@ -63,7 +64,16 @@ def test_q8_0_prefill_rows_on_the_tensor_cores(m, dt):
     assert T.rel_l2(got, want) <= 1e-3
 
 
-@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "FP8", "MXFP4"])
+@pytest.mark.parametrize("m", [9, 130, 600])
+@pytest.mark.parametrize("k", [768, 2048])
+def test_q6_k_prefill_rows_on_the_tensor_cores(m, k):
+    # K = 768 has three super-blocks per row, so rows alternate between 4-byte aligned and 2 bytes off: both forms
+    # of the producers' word loads are exercised
+    got, want = run_case("Q6_K", 1000, k, m, torch.bfloat16, torch.float32, 70 + m)
+    assert T.rel_l2(got, want) <= 1e-3
+
+
+@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "Q6_K", "FP8", "MXFP4"])
 def test_ragged_rows_and_tile_heights(fmt):
     # N not a multiple of the row tile, M not a multiple of 8, and an N large enough for the tall tiles
     for n, m in [(40, 11), (9472 + 24, 1), (19000, 2)]:
@@ -96,7 +106,7 @@ def test_run_twice_is_bit_identical():
 
 def test_dequantize_w_is_exact():
     rng = T.rng_for(1, 70)
-    for fmt in ["Q8_0", "Q4_K", "FP8", "MXFP4"]:
+    for fmt in ["Q8_0", "Q4_K", "Q6_K", "FP8", "MXFP4"]:
         arrays, deq = T.make_weight(fmt, rng, 128, 256)
         layer = T.make_layer(fmt, arrays, 256, DEV)
         got = layer.dequantize_w().cpu().numpy()

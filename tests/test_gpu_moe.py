@@ -140,8 +140,9 @@ def test_gather_forward_matches_oracle(fmt, k, n, per_slot):
     assert layer.device_status()[0] == 0
 
 
-def _moe_case(fmt, t, e, k, h, i, interleaved, act, seed, limit=None):
+def _moe_case(fmt, t, e, k, h, i, interleaved, act, seed, limit=None, down_fmt=None):
     rng = T.rng_for(4, seed)
+    down_fmt = down_fmt or fmt
     if interleaved:
         gu_a, gu_deq = T.make_weight(fmt, rng, 2 * i, h, experts=e)
         gub = T.to_dev(rng.normal(0, 0.02, (e, 2 * i)).astype(np.float32), torch.bfloat16, DEV)
@@ -150,9 +151,9 @@ def _moe_case(fmt, t, e, k, h, i, interleaved, act, seed, limit=None):
         g_a, g_deq = T.make_weight(fmt, rng, i, h, experts=e)
         u_a, u_deq = T.make_weight(fmt, rng, i, h, experts=e)
         gate, up = T.make_layer(fmt, g_a, h, DEV), T.make_layer(fmt, u_a, h, DEV)
-    d_a, d_deq = T.make_weight(fmt, rng, h, i, experts=e)
+    d_a, d_deq = T.make_weight(down_fmt, rng, h, i, experts=e)
     db = T.to_dev(rng.normal(0, 0.02, (e, h)).astype(np.float32), torch.bfloat16, DEV) if interleaved else None
-    down = T.make_layer(fmt, d_a, i, DEV, db)
+    down = T.make_layer(down_fmt, d_a, i, DEV, db)
     x = T.to_dev(rng.standard_normal((t, h)).astype(np.float32), torch.bfloat16, DEV)
     logits = rng.standard_normal((t, e)).astype(np.float32)
     ids, w = M.router_topk(logits, k, L.SCORE_SOFTMAX, L.WEIGHT_SCORE, True)
@@ -183,6 +184,19 @@ def _moe_case(fmt, t, e, k, h, i, interleaved, act, seed, limit=None):
 def test_moe_block_q4_k_swiglu(t):
     # Qwen3-30B-A3B-shaped layer at reduced width: separate gate/up banks, plain SwiGLU
     got, want = _moe_case("Q4_K", t, 16, 4, 512, 256, False, L.ACT_SWIGLU, t)
+    assert T.rel_l2(got, want) <= 1e-3
+
+
+@pytest.mark.parametrize("t", [5, 300])
+def test_moe_block_q4_k_m_mix(t):
+    # a Q4_K_M file's layer: gate / up experts in Q4_K, down experts in Q6_K; decode rows and prefill rows
+    got, want = _moe_case("Q4_K", t, 8, 2, 512, 256, False, L.ACT_SWIGLU, 20 + t, down_fmt="Q6_K")
+    assert T.rel_l2(got, want) <= 1e-3
+
+
+@pytest.mark.parametrize("t", [3, 200])
+def test_moe_block_q6_k_gate_and_up(t):
+    got, want = _moe_case("Q6_K", t, 4, 2, 256, 256, False, L.ACT_SWIGLU, 30 + t)
     assert T.rel_l2(got, want) <= 1e-3
 
 

@@ -131,3 +131,27 @@ def test_bf16_rounding_helpers():
     want = torch.from_numpy(x).to(torch.bfloat16).to(torch.float32).numpy()
     assert np.array_equal(F.round_bf16(x), want)
     assert np.array_equal(F.from_bf16_bits(F.to_bf16_bits(x)), want)
+
+
+def test_q6_k_dequant_matches_gguf_py_bit_for_bit():
+    """Q6_K blocks (random valid bytes and blocks built by the oracle's quantizer) against gguf-py's dequantize;
+    vectors from tests/golden/make_golden_q6k.py."""
+    import os
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "q6k_vectors.npz"))
+    got = F.q6_k_dequant(z["raw"], 512)
+    assert np.array_equal(got, z["deq"])
+
+
+def test_q6_k_quantizer_round_trip():
+    rng = np.random.Generator(np.random.PCG64(606))
+    w = rng.normal(0.0, 0.02, (5, 768)).astype(np.float32)
+    w[2, :32] = 0.0
+    raw = F.q6_k_quantize(w)
+    assert raw.shape == (5, 3 * 210) and raw.dtype == np.uint8
+    back = F.q6_k_dequant(raw, 768)
+    # 6-bit codes: half a step of absmax / 31 per 16-element sub-block, plus the 8-bit scale's own rounding
+    blk = np.abs(w.reshape(5, 48, 16)).max(2, keepdims=True)
+    assert (np.abs(back - w).reshape(5, 48, 16) <= blk / 31 * 0.55 + 1e-9).all()
+    assert not back[2, :32].any()
+    # quantizing the dequantized weights again reproduces the same values
+    assert np.array_equal(F.q6_k_dequant(F.q6_k_quantize(back), 768), back)
