@@ -193,44 +193,66 @@ __device__ __forceinline__ void load4_as_float(const void* p, int dtype, int64_t
   }
 }
 
-// The same 1 x 128 quantizer over rows that are looked up first (token order -> expert-sorted order): one warp per
-// (output row, group of 128 columns).  Feeds the FP8 expert GEMM, whose operand boxes need whole sorted rows.
+// The same 1 x 128 quantizer over rows that are looked up first (token order -> expert-sorted order).  Feeds the
+// FP8 expert GEMM, whose operand boxes need whole sorted rows.  One warp per (output row, 512 columns): a lane owns
+// 8 consecutive values in each half of the chunk (16-byte loads on 16-bit inputs, both issued before anything is
+// used), a 128-column group is 16 lanes.
 __global__ void __launch_bounds__(256) fp8_quant_rows_kernel(const void* __restrict__ x, int dtype, int64_t x_stride,
                                                              const int32_t* __restrict__ row_map,
                                                              const int32_t* __restrict__ n_valid, int64_t n_rows,
                                                              int kgroups, uint8_t* __restrict__ codes,
                                                              float* __restrict__ scales) {
-  const int64_t grp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int chunks = (kgroups + 3) / 4;
+  const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int64_t limit = n_valid != nullptr ? min((int64_t)*n_valid, n_rows) : n_rows;   // rows the map is defined for
-  if (grp >= limit * kgroups) return;
+  if (item >= limit * chunks) return;
   const int lane = threadIdx.x & 31;
-  const int64_t row = grp / kgroups;
-  const int g = (int)(grp - row * kgroups);
+  const int64_t row = item / chunks;
+  const int chunk = (int)(item - row * chunks);
   const int64_t src_row = row_map != nullptr ? (int64_t)row_map[row] : row;
-  const int64_t src = src_row * x_stride + g * 128 + lane * 4;
-  float v[4];
-  load4_as_float(x, dtype, src, v);
-  float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  const int k = kgroups * 128;
+  float v[2][8];
+  bool in[2];
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-  const float scale = m > 0.f ? __fdiv_rn(m, 448.f) : 1e-12f;
-  uint32_t packed = 0;
+  for (int j = 0; j < 2; ++j) {
+    const int c0 = chunk * 512 + j * 256 + lane * 8;
+    in[j] = c0 < k;
+    if (in[j]) {
+      load4_as_float(x, dtype, src_row * x_stride + c0, *reinterpret_cast<float(*)[4]>(&v[j][0]));
+      load4_as_float(x, dtype, src_row * x_stride + c0 + 4, *reinterpret_cast<float(*)[4]>(&v[j][4]));
+    } else {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float q = fminf(fmaxf(__fdiv_rn(v[i], scale), -448.f), 448.f);
-    packed |= (uint32_t)f32_to_e4m3(q) << (8 * i);
+      for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+    }
   }
-  *reinterpret_cast<uint32_t*>(codes + grp * 128 + lane * 4) = packed;
-  if (lane == 0) scales[grp] = scale;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[j][i]));
+#pragma unroll
+    for (int d = 8; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    if (!in[j]) continue;
+    const float scale = m > 0.f ? __fdiv_rn(m, 448.f) : 1e-12f;
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float q = fminf(fmaxf(__fdiv_rn(v[j][i], scale), -448.f), 448.f);
+      packed[i >> 2] |= (uint32_t)f32_to_e4m3(q) << (8 * (i & 3));
+    }
+    const int c0 = chunk * 512 + j * 256 + lane * 8;
+    *reinterpret_cast<uint2*>(codes + row * k + c0) = make_uint2(packed[0], packed[1]);
+    if ((lane & 15) == 0) scales[row * kgroups + c0 / 128] = scale;
+  }
 }
 
 int32_t launch_fp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map,
                               const int32_t* n_valid, int64_t n_rows, int64_t k, uint8_t* codes, float* scales,
                               cudaStream_t stream) {
-  const int64_t groups = n_rows * (k / 128);
-  if (groups == 0) return HQ_OK;
-  fp8_quant_rows_kernel<<<(unsigned)((groups + 7) / 8), 256, 0, stream>>>(x, x_dtype, x_stride, row_map, n_valid,
-                                                                         n_rows, (int)(k / 128), codes, scales);
+  const int64_t items = n_rows * ((k / 128 + 3) / 4);
+  if (items == 0) return HQ_OK;
+  fp8_quant_rows_kernel<<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(x, x_dtype, x_stride, row_map, n_valid,
+                                                                        n_rows, (int)(k / 128), codes, scales);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 

@@ -9,6 +9,7 @@ pub const HQ_FMT_Q8_0: i32 = 0;
 pub const HQ_FMT_Q4_K: i32 = 1;
 pub const HQ_FMT_FP8_BLOCK: i32 = 2;
 pub const HQ_FMT_MXFP4: i32 = 3;
+pub const HQ_FMT_Q6_K: i32 = 4;
 pub const HQ_DT_F32: i32 = 0;
 pub const HQ_DT_F16: i32 = 1;
 pub const HQ_DT_BF16: i32 = 2;
