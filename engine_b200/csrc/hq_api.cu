@@ -472,7 +472,7 @@ int32_t hq_mxfp8_quant_rows(const void* x, int32_t x_dtype, int64_t x_stride, co
   if (n_rows == 0) return HQ_OK;
   if (x == nullptr || codes == nullptr || scales == nullptr) return HQ_ERR_NULL;
   if (!valid_dtype(x_dtype)) return HQ_ERR_FORMAT;
-  if ((reinterpret_cast<uintptr_t>(codes) & 3u) != 0 || k % 4 != 0) return HQ_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(codes) & 7u) != 0) return HQ_ERR_ALIGN;
   return launch_mxfp8_quant_rows(x, x_dtype, x_stride, row_map, n_valid_dev, n_rows, k, codes, scales,
                                  (cudaStream_t)stream);
 }

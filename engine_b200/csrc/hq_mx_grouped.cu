@@ -621,48 +621,91 @@ extern "C" int32_t hq_debug_mx_prof(unsigned long long* out_host, int32_t reset)
 #endif
 
 // ---- MXFP8 row quantizer: rows looked up through row_map (token order -> expert-sorted order) ---------------
-// One warp per (row, 128-element span): lane owns 4 consecutive elements, a 32-element block is 8 lanes.
+// One warp per (row, 512-element span): a lane owns 8 consecutive elements in each half of the span (both loads
+// issued before anything is used), a 32-element block is 4 lanes.
+__device__ __forceinline__ void mx_load8(const void* x, int dtype, int64_t i, float (&v)[8]) {
+  if (dtype == HQ_DT_F32) {
+    const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + i);
+    const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + i + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 t = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + i);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (dtype == HQ_DT_BF16) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        v[2 * j] = f.x;
+        v[2 * j + 1] = f.y;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) mxfp8_quant_rows_kernel(const void* __restrict__ x, int dtype, int64_t x_stride,
                                                                const int32_t* __restrict__ row_map,
                                                                const int32_t* __restrict__ n_valid, int64_t n_rows,
-                                                               int k, uint8_t* __restrict__ codes,
+                                                               int k, int vec_ok, uint8_t* __restrict__ codes,
                                                                uint8_t* __restrict__ scales) {
-  const int spans = (k + 127) / 128;
+  const int spans = (k + 511) / 512;
   const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int64_t limit = n_valid != nullptr ? min((int64_t)*n_valid, n_rows) : n_rows;
   if (item >= limit * spans) return;
   const int lane = threadIdx.x & 31;
   const int64_t row = item / spans;
-  const int c0 = (int)(item - row * spans) * 128 + lane * 4;
+  const int span = (int)(item - row * spans);
   const int64_t src_row = row_map != nullptr ? (int64_t)row_map[row] : row;
-  float v[4] = {0.f, 0.f, 0.f, 0.f};
-  const bool in = c0 < k;
-  if (in) {
+  float v[2][8];
+  bool in[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = load_as_float(x, dtype, src_row * x_stride + c0 + i);
+  for (int j = 0; j < 2; ++j) {
+    const int c0 = span * 512 + j * 256 + lane * 8;
+    in[j] = c0 < k;                                   // k is a multiple of 32, so a lane's 8 elements are all in or out
+    if (in[j] && vec_ok) {
+      mx_load8(x, dtype, src_row * x_stride + c0, v[j]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[j][i] = in[j] ? load_as_float(x, dtype, src_row * x_stride + c0 + i) : 0.f;
+    }
   }
-  float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-  for (int d = 1; d < 8; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-  const int e = mx_shared_exp(m);
-  const float inv = mx_exp_to_inv_scale(e);
-  if (!in) return;
-  uint32_t packed = 0;
+  for (int j = 0; j < 2; ++j) {
+    float m = 0.f;
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-    packed |= (uint32_t)__nv_cvt_float_to_fp8(fminf(fmaxf(v[i] * inv, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3)
-              << (8 * i);
-  *reinterpret_cast<uint32_t*>(codes + row * k + c0) = packed;
-  if ((lane & 7) == 0) scales[row * (k / 32) + c0 / 32] = (uint8_t)e;
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[j][i]));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    if (!in[j]) continue;
+    const int e = mx_shared_exp(m);
+    const float inv = mx_exp_to_inv_scale(e);
+    uint32_t packed[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[j][4 * h] * inv, v[j][4 * h + 1] * inv), __NV_SATFINITE,
+                                                   __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[j][4 * h + 2] * inv, v[j][4 * h + 3] * inv),
+                                                   __NV_SATFINITE, __NV_E4M3);
+      packed[h] = lo | (hi << 16);
+    }
+    const int c0 = span * 512 + j * 256 + lane * 8;
+    *reinterpret_cast<uint2*>(codes + row * k + c0) = make_uint2(packed[0], packed[1]);
+    if ((lane & 3) == 0) scales[row * (k / 32) + c0 / 32] = (uint8_t)e;
+  }
 }
 
 int32_t launch_mxfp8_quant_rows(const void* x, int x_dtype, int64_t x_stride, const int32_t* row_map,
                                 const int32_t* n_valid, int64_t n_rows, int64_t k, uint8_t* codes, uint8_t* scales,
                                 cudaStream_t stream) {
-  const int64_t items = n_rows * ((k + 127) / 128);
+  const int64_t items = n_rows * ((k + 511) / 512);
   if (items == 0) return HQ_OK;
+  // 16-byte loads need an aligned base and row pitch; otherwise elements are loaded one at a time
+  const int esz = dtype_size(x_dtype);
+  const int vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (x_stride * esz) % 16 == 0 ? 1 : 0;
   mxfp8_quant_rows_kernel<<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(x, x_dtype, x_stride, row_map, n_valid,
-                                                                           n_rows, (int)k, codes, scales);
+                                                                           n_rows, (int)k, vec_ok, codes, scales);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
