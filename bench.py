@@ -578,37 +578,72 @@ def run_moe(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # The step as a CUDA graph per input set (launches, the two all-to-alls and the side-stream shared expert
+    # included): with the experts sharded over several GPUs the step is short enough for the host-side launch
+    # work to bound it otherwise.  Every rank captures the same sequence.
+    graphs, graph_note = None, "off (--no-graph)"
+    if not args.no_graph:
+        try:
+            cap = torch.cuda.Stream(device=dev)
+            glist, gouts = [], []
+            with torch.cuda.stream(cap):
+                for j in range(n_in):
+                    g = torch.cuda.CUDAGraph()
+                    # thread-local error mode: the process group's watchdog thread polls its events meanwhile
+                    with torch.cuda.graph(g, stream=cap, capture_error_mode="thread_local"):
+                        gouts.append(step(j))
+                    glist.append(g)
+            torch.cuda.synchronize()
+            for g in glist:
+                g.replay()
+            torch.cuda.synchronize()
+            graphs, graph_note = glist, f"one CUDA graph per input set ({n_in}), replayed"
+        except Exception as exc:
+            if world > 1:
+                raise       # a capture that broke off half-way has left collectives queued on this rank only
+            # no graph: the eager loop below measures the same step
+            graphs, graph_note = None, f"capture failed ({type(exc).__name__}), eager launches"
+            torch.cuda.synchronize()
+    assert experts.down.device_status()[0] == 0
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    experts.gemm_events = []
+    experts.gemm_events = [] if graphs is None else None
     barrier()
     if args.profiler_range:
         torch.cuda.profiler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for s_ in range(args.steps):
-        step(s_)
+        if graphs is not None:
+            graphs[s_ % n_in].replay()
+        else:
+            step(s_)
     e1.record()
     barrier()
     if args.profiler_range:
         torch.cuda.profiler.stop()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
-    # dominant kernels: the expert GEMM pair of the routed experts, by the CUDA events recorded around those two
-    # launches inside the timed steps (on the stream they are launched on)
-    gemm_ts = [a.elapsed_time(b) for a, b in experts.gemm_events]
+    # dominant kernels: the expert GEMM pair of the routed experts, by CUDA events recorded around those two
+    # launches on the stream they are launched on -- inside the timed steps when these are launched eagerly, in
+    # separate eager steps after them when the timed steps are graph replays (events cannot be read back from a graph)
+    gemm_ts = [a.elapsed_time(b) for a, b in (experts.gemm_events or [])]
     gemm_timing = "median over the timed steps of CUDA events around the two launches"
-    if not gemm_ts and ep is None:
-        # the one-call layer path gives no place for events between its launches: the same two launches are timed
-        # through the two-call route after the timed steps
-        for j in range(5):
-            top = hq.moe_router_topk(logits[j % n_in], rcfg, sel_bias)
-            experts.forward(xs[j % n_in], top.values, top.indices, out_dtype=torch.bfloat16)
+    if not gemm_ts:
+        experts.gemm_events = []
+        for j in range(6):
+            if ep is None and not (fp8 or mx):
+                # the one-call layer path gives no place for events between its launches: the two-call route
+                top = hq.moe_router_topk(logits[j % n_in], rcfg, sel_bias)
+                experts.forward(xs[j % n_in], top.values, top.indices, out_dtype=torch.bfloat16)
+            else:
+                step(j)
         torch.cuda.synchronize()
         gemm_ts = [a.elapsed_time(b) for a, b in experts.gemm_events][2:]
-        gemm_timing = "median of three separate runs of the same two launches after the timed steps"
+        gemm_timing = "median of four separate eager runs of the same two launches after the timed steps"
     experts.gemm_events = None
     gemm_ms = statistics.median(gemm_ts) if gemm_ts else None
     # routed assignments this rank's experts received
@@ -629,6 +664,25 @@ def run_moe(args):
     hys = [hy, torch.empty_like(hy).pin_memory()]
     main = torch.cuda.current_stream()
 
+    e2e_graphs = None
+    if graphs is not None:
+        try:
+            cap2 = torch.cuda.Stream(device=dev)
+            eg = []
+            with torch.cuda.stream(cap2):
+                for b_ in range(2):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=cap2, capture_error_mode="thread_local"):
+                        dout[b_].copy_(step(0, dx[b_], dl[b_]))
+                    eg.append(g)
+            torch.cuda.synchronize()
+            e2e_graphs = eg
+        except Exception:
+            if world > 1:
+                raise
+            e2e_graphs = None
+            torch.cuda.synchronize()
+
     def e2e_run(n_steps):
         ev_in = [None, None]          # inputs of slot b are on the device
         ev_done = [None, None]        # the layer has consumed slot b's inputs and produced slot b's output
@@ -645,7 +699,10 @@ def run_moe(args):
             main.wait_event(ev_in[b_])
             if ev_out[b_] is not None:
                 main.wait_event(ev_out[b_])
-            dout[b_].copy_(step(j, dx[b_], dl[b_]))
+            if e2e_graphs is not None:
+                e2e_graphs[b_].replay()
+            else:
+                dout[b_].copy_(step(j, dx[b_], dl[b_]))
             ev_done[b_] = torch.cuda.Event()
             ev_done[b_].record(main)
             with torch.cuda.stream(s_out):
@@ -775,6 +832,7 @@ def run_moe(args):
                     "note": "host-to-device copies, layer and device-to-host copy of neighbouring steps overlap "
                             "(three streams, two buffer sets)"},
             "gpu_launches": args.steps * launches_per_step,
+            "launch_mode": graph_note,
             "clocks": clocks,
         }
         if ep is not None:
@@ -787,6 +845,16 @@ def run_moe(args):
             line["gemv"] = gemv
         print(json.dumps(line), flush=True)
     if dist is not None:
+        if graphs is not None:
+            # Graphs that hold captured collectives keep the communicator's teardown waiting (it did not return
+            # within minutes): every rank finishes its work, meets the others once more and leaves the process
+            # without destroying the group.
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 
@@ -895,6 +963,8 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="MoE workloads: bracket the timed steps with cudaProfilerStart/Stop, so that a profiler "
                          "started with --profile-from-start off sees the timed steps only")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="MoE workloads: launch every step eagerly instead of replaying a CUDA graph of it")
     ap.add_argument("--act16", action="store_true",
                     help="MoE workloads: 16-bit activations (mode A) instead of the quantized-activation path")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count of a MoE workload")
