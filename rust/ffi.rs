@@ -178,4 +178,74 @@ extern "C" {
         gate: *const c_void, up: *const c_void, dtype: i32, n_elems: i64, interleaved: i32,
         act: *const hq_act_args, out: *mut c_void, stream: *mut c_void,
     ) -> i32;
+
+    // ---- the remaining entry points of the header ----
+    pub fn hq_linear_forward(
+        w: *const hq_weight, x: *const c_void, x_dtype: i32, x_stride: i64, y: *mut c_void, y_dtype: i32,
+        y_stride: i64, m: i64, status_dev: *mut i32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_linear_qkv_forward(
+        w_q: *const hq_weight, w_k: *const hq_weight, w_v: *const hq_weight, x: *const c_void, x_dtype: i32,
+        x_stride: i64, q: *mut c_void, k: *mut c_void, v: *mut c_void, y_dtype: i32, m: i64,
+        status_dev: *mut i32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_dense_gemv(
+        w: *const c_void, w_dtype: i32, n: i64, k: i64, bias: *const c_void, bias_dtype: i32, x: *const c_void,
+        x_dtype: i32, x_stride: i64, y: *mut c_void, y_dtype: i32, y_stride: i64, m: i64, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_router_topk_grouped(
+        logits: *const c_void, logits_dtype: i32, n_rows: i64, args: *const hq_router_args, n_group: i32,
+        topk_group: i32, group_score_mode: i32, ids_out: *mut u32, weights_out: *mut f32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_moe_dispatch_build_noalloc(
+        ids: *const u32, n_tokens: i64, top_k: i32, n_experts: i32, expert_bounds: *mut i32,
+        sorted_assign: *mut i32, sorted_token: *mut i32, inv_perm: *mut i32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_fp8_quant_rows(
+        x: *const c_void, x_dtype: i32, x_stride: i64, row_map: *const i32, n_rows: i64, k: i64, codes: *mut u8,
+        scales: *mut f32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_fp8_gated_quant_rows(
+        gate_up: *const c_void, dtype: i32, n_rows: i64, width: i64, act: *const hq_act_args, codes: *mut u8,
+        scales: *mut f32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_fp8_linear_forward(
+        w: *const hq_weight, x_codes: *const u8, x_scales: *const f32, m: i64, y: *mut c_void, y_dtype: i32,
+        y_stride: i64, status_dev: *mut i32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_fp8_vector_quant(
+        x: *const c_void, x_dtype: i32, n_elems: i64, codes: *mut u8, scales: *mut f32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_fp8_vector_dequant(
+        codes: *const u8, scales: *const f32, n_elems: i64, out: *mut c_void, out_dtype: i32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_fp8_block_quant(
+        w: *const c_void, w_dtype: i32, rows: i64, cols: i64, by: i32, bx: i32, codes: *mut u8, scales: *mut f32,
+        stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_fp8_block_dequant(
+        codes: *const u8, scales: *const f32, rows: i64, cols: i64, by: i32, bx: i32, out: *mut c_void,
+        out_dtype: i32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_convert(
+        src: *const c_void, src_dtype: i32, dst: *mut c_void, dst_dtype: i32, n_elems: i64, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_probe_tensor_peak(
+        kind: i32, n: i32, iters: i32, status_dev: *mut i32, flops_host: *mut f64, stream: *mut c_void,
+    ) -> i32;
+    // MXFP4 layers with MXFP8 activations (block-scaled tensor-core MMA)
+    pub fn hq_mxfp8_quant_rows(
+        x: *const c_void, x_dtype: i32, x_stride: i64, row_map: *const i32, n_valid_dev: *const i32, n_rows: i64,
+        k: i64, codes: *mut u8, scales: *mut u8, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_mx_linear_forward(
+        w: *const hq_weight, x_codes: *const u8, x_scales: *const u8, m: i64, y: *mut c_void, y_dtype: i32,
+        y_stride: i64, status_dev: *mut i32, stream: *mut c_void,
+    ) -> i32;
+    pub fn hq_moe_mx_gather_forward(
+        w: *const hq_weight, act: *const hq_act_args, x_codes: *const u8, x_scales: *const u8, n_tokens: i64,
+        top_k: i32, expert_bounds: *const i32, sorted_assign: *const i32, out: *mut c_void, out_dtype: i32,
+        out_stride: i64, out_layout: i32, h_codes: *mut u8, h_scales: *mut u8, status_dev: *mut i32,
+        stream: *mut c_void,
+    ) -> i32;
 }
