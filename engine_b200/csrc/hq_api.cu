@@ -615,6 +615,23 @@ int32_t hq_ep_unpack_meta(const hq_ep_layout* l, const void* recv, uint32_t* ids
   return launch_ep_unpack_meta(*l, recv, ids_out, weights_out, (cudaStream_t)stream);
 }
 
+int32_t hq_ep_push(const void* send, void* const* peer_slabs_dev, int32_t world, int32_t rank, int64_t slab_bytes,
+                   void* stream) {
+  if (world < 1 || world > 64 || rank < 0 || rank >= world || slab_bytes < 0 || slab_bytes % 16 != 0) return HQ_ERR_SHAPE;
+  if (slab_bytes == 0) return HQ_OK;
+  if (send == nullptr || peer_slabs_dev == nullptr) return HQ_ERR_NULL;
+  if (!aligned16(send)) return HQ_ERR_ALIGN;
+  return launch_ep_push(send, peer_slabs_dev, world, rank, slab_bytes, (cudaStream_t)stream);
+}
+
+int32_t hq_ep_barrier(int32_t* const* peer_flags_dev, int32_t world, int32_t rank, int32_t* seq_counter_dev,
+                      int32_t* status_dev, void* stream) {
+  if (world < 1 || world > 64 || rank < 0 || rank >= world) return HQ_ERR_SHAPE;
+  if (peer_flags_dev == nullptr || seq_counter_dev == nullptr) return HQ_ERR_NULL;
+  return launch_ep_barrier(peer_flags_dev, world, rank, seq_counter_dev, (uint32_t)g_cfg[HQ_CFG_SPIN_LIMIT],
+                           status_dev, (cudaStream_t)stream);
+}
+
 int32_t hq_fp8_gated_quant_rows(const void* gate_up, int32_t dtype, int64_t n_rows, int64_t width,
                                 const hq_act_args* act, uint8_t* codes, float* scales, void* stream) {
   if (n_rows < 0 || width < 128 || width % 128 != 0) return HQ_ERR_SHAPE;

@@ -162,6 +162,63 @@ __global__ void __launch_bounds__(256) fp8_gather_rows_kernel(const uint8_t* __r
   for (int i = lane; i < k / 128; i += 32) scales[row * (k / 128) + i] = ss[i];
 }
 
+
+// ---- the exchange itself over peer memory --------------------------------------------------------------
+// Slab d of the local send buffer goes to slot `rank` of peer d's receive buffer with plain stores over NVLink
+// (16 bytes per store, a grid-stride loop per slab; peer pointers come from a symmetric allocation the host set
+// up).  No TMA, no multicast.  Each thread ends with a system-scope fence; the barrier kernel below tells the
+// peers that the data is there.
+__global__ void __launch_bounds__(256) ep_push_kernel(const uint4* __restrict__ send, uint4* const* __restrict__ peers,
+                                                      int world, int rank, int64_t slab_vec, int ctas_per_slab) {
+  const int d = blockIdx.x / ctas_per_slab;
+  const int c = blockIdx.x - d * ctas_per_slab;
+  if (d >= world) return;
+  const uint4* src = send + (int64_t)d * slab_vec;
+  uint4* dst = peers[d] + (int64_t)rank * slab_vec;
+  const int64_t stride = (int64_t)ctas_per_slab * 256;
+  int64_t i = (int64_t)c * 256 + threadIdx.x;
+  for (; i + 3 * stride < slab_vec; i += 4 * stride) {
+    const uint4 a = __ldg(src + i), b = __ldg(src + i + stride), e = __ldg(src + i + 2 * stride),
+                f = __ldg(src + i + 3 * stride);
+    dst[i] = a;
+    dst[i + stride] = b;
+    dst[i + 2 * stride] = e;
+    dst[i + 3 * stride] = f;
+  }
+  for (; i < slab_vec; i += stride) dst[i] = __ldg(src + i);
+  __threadfence_system();
+}
+
+// Barrier over the ranks of the exchange: thread p tells peer p "rank `rank` has finished its step `seq`" by
+// storing seq into slot `rank` of peer p's flag array, then waits until slot p of the local flag array has
+// reached seq.  Flags only grow, one per barrier, so a peer that is already one barrier ahead satisfies the
+// wait as well; it cannot get further ahead without this rank's next signal.  The wait is bounded: after
+// `spin_limit` polls the kernel reports HQ_DEV_WAIT_TIMEOUT (tag 950 + p) and returns.
+__global__ void __launch_bounds__(64) ep_barrier_kernel(int32_t* const* __restrict__ flags, int world, int rank,
+                                                        int32_t* __restrict__ seq_counter, uint32_t spin_limit,
+                                                        int32_t* __restrict__ status) {
+  const int p = threadIdx.x;
+  const int32_t seq = *seq_counter + 1;
+  if (p < world) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags[p] + rank), "r"(seq) : "memory");
+    const int32_t* mine = flags[rank] + p;
+    bool ok = false;
+    for (uint32_t it = 0; it < spin_limit; ++it) {
+      int32_t v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (v - seq >= 0) {
+        ok = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (!ok) report_status(status, HQ_DEV_WAIT_TIMEOUT, 950 + p);
+  }
+  __syncthreads();
+  if (p == 0) *seq_counter = seq;
+}
+
 }  // namespace
 
 int32_t launch_ep_pack(const hq_ep_layout& l, const void* x, int x_dtype, const uint32_t* ids, const float* weights,
@@ -185,6 +242,26 @@ int32_t launch_fp8_gather_rows(const void* src_codes, int64_t src_code_stride, c
   fp8_gather_rows_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, stream>>>(
       (const uint8_t*)src_codes, src_code_stride, (const uint8_t*)src_scales, src_scale_stride, row_map, n_valid,
       n_rows, (int)k, codes, scales);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+int32_t launch_ep_push(const void* send, void* const* peers, int world, int rank, int64_t slab_bytes,
+                       cudaStream_t stream) {
+  if (world <= 0 || slab_bytes <= 0) return HQ_OK;
+  const int64_t slab_vec = slab_bytes / 16;
+  int per = (int)((slab_vec + 256 * 16 - 1) / (256 * 16));       // about 16 stores per thread
+  const int cap = 8 * 148 / world > 0 ? 8 * 148 / world : 1;
+  if (per > cap) per = cap;
+  if (per < 1) per = 1;
+  ep_push_kernel<<<(unsigned)(world * per), 256, 0, stream>>>(reinterpret_cast<const uint4*>(send),
+                                                             reinterpret_cast<uint4* const*>(peers), world, rank,
+                                                             slab_vec, per);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+int32_t launch_ep_barrier(int32_t* const* flags, int world, int rank, int32_t* seq_counter, uint32_t spin_limit,
+                          int32_t* status, cudaStream_t stream) {
+  ep_barrier_kernel<<<1, 64, 0, stream>>>(flags, world, rank, seq_counter, spin_limit, status);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 

@@ -198,6 +198,10 @@ int32_t launch_gated_act(const void* gate, const void* up, int dtype, int64_t n,
 // ---- expert-parallel exchange helpers (hq_ep.cu) -------------------------------------
 int32_t launch_ep_pack(const hq_ep_layout& l, const void* x, int x_dtype, const uint32_t* ids, const float* weights,
                        int64_t n_tokens, void* send, int32_t* back_map, cudaStream_t stream);
+int32_t launch_ep_push(const void* send, void* const* peers, int world, int rank, int64_t slab_bytes,
+                       cudaStream_t stream);
+int32_t launch_ep_barrier(int32_t* const* flags, int world, int rank, int32_t* seq_counter, uint32_t spin_limit,
+                          int32_t* status, cudaStream_t stream);
 int32_t launch_ep_unpack_meta(const hq_ep_layout& l, const void* recv, uint32_t* ids, float* weights,
                               cudaStream_t stream);
 int32_t launch_fp8_gather_rows(const void* src_codes, int64_t src_code_stride, const void* src_scales,

@@ -84,11 +84,18 @@ class ExpertParallelMoE:
     def __init__(self, n_experts_global: int, experts=None, *, top_k: int, hidden: int, capacity: int, group=None,
                  wire_dtype: torch.dtype = torch.bfloat16, fp8_act: bool = False, mx_act: bool = False,
                  pack_fn: Callable | None = None, unpack_fn: Callable | None = None,
-                 expert_fn: Callable | None = None, reduce_fn: Callable | None = None):
+                 expert_fn: Callable | None = None, reduce_fn: Callable | None = None, exchange: str = "nccl"):
         """capacity: the largest number of tokens a rank brings to one call; the same value on every rank (it fixes
         the slab size, so ranks may bring different token counts without telling each other).
         fp8_act: block-FP8 experts, rows cross the wire as e4m3 + 1x128 scales; mx_act: MXFP4 experts on the
-        block-scaled MMA (rows cross as `wire_dtype` and are quantized to MXFP8 on the expert rank)."""
+        block-scaled MMA (rows cross as `wire_dtype` and are quantized to MXFP8 on the expert rank).
+        exchange: "nccl" = two all_to_all_single calls; "p2p" = the receive buffers live in symmetric memory
+        (torch.distributed._symmetric_memory) and every rank stores its slabs straight into its peers' buffers
+        (hq_ep_push) followed by a flag barrier (hq_ep_barrier); GPU ranks of one NVLink domain only."""
+        if exchange not in ("nccl", "p2p"):
+            raise ValueError("exchange must be 'nccl' or 'p2p'")
+        self.exchange = exchange
+        self._symm = None
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -124,6 +131,45 @@ class ExpertParallelMoE:
             self._bufs = (send, recv, back, ones)
         return self._bufs
 
+    def _symm_buffers(self, device):
+        """Receive buffers, flag array and their peer-pointer tables for the "p2p" exchange (collective: every rank
+        of the group calls this at the same point, the first time it runs a layer)."""
+        if self._symm is None:
+            import torch.distributed._symmetric_memory as symm
+            lay = self.layout
+            grp = self.group if self.group is not None else dist.group.WORLD
+            recv = symm.empty((lay.world, lay.rows_per_peer, lay.row_bytes), dtype=torch.uint8, device=device)
+            back = symm.empty((lay.world * lay.rows_per_peer, lay.hidden), dtype=self.wire_dtype, device=device)
+            flags = symm.empty((64,), dtype=torch.int32, device=device)
+            recv.zero_()
+            back.zero_()
+            flags.zero_()
+            handles = [symm.rendezvous(t, grp) for t in (recv, back, flags)]
+            torch.cuda.synchronize(device)
+            dist.barrier(grp)          # every rank's flags are zero before anyone signals
+            self._symm = {
+                "recv": recv, "back": back, "flags": flags, "handles": handles,
+                "p_recv": C.c_void_p(handles[0].buffer_ptrs_dev), "p_back": C.c_void_p(handles[1].buffer_ptrs_dev),
+                "p_flags": C.c_void_p(handles[2].buffer_ptrs_dev),
+                "seq": torch.zeros(1, dtype=torch.int32, device=device),
+                "status": torch.zeros(4, dtype=torch.int32, device=device),
+            }
+        return self._symm
+
+    def exchange_status(self) -> list[int]:
+        """Device status word of the "p2p" exchange ({code, block, thread, tag}; all zero = no wait ran out)."""
+        if self._symm is None:
+            return [0, 0, 0, 0]
+        return [int(v) for v in self._symm["status"].cpu()]
+
+    def _push(self, src: torch.Tensor, peers, slab_bytes: int):
+        sm = self._symm
+        stream = C.c_void_p(torch.cuda.current_stream(src.device).cuda_stream)
+        lib = L.lib()
+        L.check(lib.hq_ep_push(src.data_ptr(), peers, self.world, self.rank, slab_bytes, stream), "hq_ep_push")
+        L.check(lib.hq_ep_barrier(sm["p_flags"], self.world, self.rank, sm["seq"].data_ptr(),
+                                  sm["status"].data_ptr(), stream), "hq_ep_barrier")
+
     def forward(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                 shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
                 shared_fn: Callable | None = None) -> torch.Tensor:
@@ -149,13 +195,20 @@ class ExpertParallelMoE:
                     ev_shared = self._side.record_event()
             else:
                 shared_out = shared_fn()
-        if self.world > 1:
+        p2p = self.exchange == "p2p" and self.world > 1 and x.is_cuda
+        if p2p:
+            sm = self._symm_buffers(x.device)
+            recv, back = sm["recv"], sm["back"]
+            self._push(send, sm["p_recv"], lay.message_bytes)
+        elif self.world > 1:
             dist.all_to_all_single(recv, send, group=self.group)
         else:
             recv = send
         ids_l, w_l = self.unpack_fn(lay, recv)
         y = self.expert_fn(lay, recv, ids_l, w_l)
-        if self.world > 1:
+        if p2p:
+            self._push(y.contiguous(), sm["p_back"], lay.rows_per_peer * lay.hidden * y.element_size())
+        elif self.world > 1:
             dist.all_to_all_single(back, y.contiguous(), group=self.group)
         else:
             back = y

@@ -429,6 +429,24 @@ int32_t hq_ep_pack(const hq_ep_layout* layout, const void* x, int32_t x_dtype, c
 int32_t hq_ep_unpack_meta(const hq_ep_layout* layout, const void* recv, uint32_t* ids_out, float* weights_out,
                           void* stream);
 
+/* The exchange itself over peer memory, for hosts that hold their receive buffers in a symmetric allocation (every
+ * rank's buffer mapped into every other rank's address space, e.g. cuMemMap of exported handles or
+ * torch.distributed._symmetric_memory): an alternative to the two all-to-all calls.
+ * hq_ep_push copies slab d (slab_bytes, a multiple of 16) of the local `send` buffer into slot `rank` of peer d's
+ * buffer with plain stores over NVLink (peer_slabs_dev: device array of `world` base pointers, 16-byte aligned;
+ * entry `rank` is this rank's own buffer).  hq_ep_barrier then tells every peer that this rank's data has arrived
+ * and waits for theirs: peer_flags_dev is a device array of `world` pointers to int32[world] flag arrays in
+ * symmetric memory, zero before the first call; seq_counter_dev a local device int32, zero before the first call,
+ * that counts the barriers (kept on the device so that the calls can sit in a replayed CUDA graph).  The wait is
+ * bounded by HQ_CFG_SPIN_LIMIT; when it runs out HQ_DEV_WAIT_TIMEOUT (tag 950 + peer) is left in status_dev and the
+ * call returns.  With two barriers per layer (after the dispatch push and after the return push) single buffers
+ * are safe to reuse in the next layer: a peer can only pass a barrier after this rank has finished everything it
+ * queued before its own signal. */
+int32_t hq_ep_push(const void* send, void* const* peer_slabs_dev, int32_t world, int32_t rank, int64_t slab_bytes,
+                   void* stream);
+int32_t hq_ep_barrier(int32_t* const* peer_flags_dev, int32_t world, int32_t rank, int32_t* seq_counter_dev,
+                      int32_t* status_dev, void* stream);
+
 /* ---- FP8 quantizers ---------------------------------------------------------
  * 1x128 groups along the last axis: scale = absmax/448 (1e-12 if zero),
  * code = e4m3(clamp(v/scale, +-448)).  Replaces launch_quant_fp8_vector_kernel_*

@@ -95,7 +95,36 @@ def test_single_rank_exchange_matches_the_oracle(fmt, fp8):
     assert T.rel_l2(out.cpu().numpy(), want) <= (2e-3 if fp8 else 1e-3)
 
 
-def _worker(rank, world, port, results):
+def test_push_moves_slab_d_to_slot_rank_of_peer_d():
+    """hq_ep_push with the peers of a three-rank exchange emulated by three local buffers: after every rank has
+    pushed, buffer d holds in slot r the slab d of rank r's send buffer (the all-to-all's result); the barrier
+    entry point is exercised as a one-rank exchange (it signals and waits for itself)."""
+    import ctypes as C
+    from engine_b200 import _lib as L
+    lib = L.lib()
+    world, slab = 3, 4096 + 48                      # a slab size that is not a multiple of the CTA's stride
+    rng = np.random.Generator(np.random.PCG64(11))
+    sends = [torch.from_numpy(rng.integers(0, 256, (world, slab), dtype=np.uint8)).to(DEV) for _ in range(world)]
+    recvs = [torch.zeros((world, slab), dtype=torch.uint8, device=DEV) for _ in range(world)]
+    table = torch.tensor([r.data_ptr() for r in recvs], dtype=torch.int64, device=DEV)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for rank in range(world):
+        assert lib.hq_ep_push(sends[rank].data_ptr(), table.data_ptr(), world, rank, slab, stream) == 0
+    torch.cuda.synchronize()
+    for d in range(world):
+        for r in range(world):
+            assert torch.equal(recvs[d][r], sends[r][d]), (d, r)
+    flags = torch.zeros(64, dtype=torch.int32, device=DEV)
+    ftable = torch.tensor([flags.data_ptr()], dtype=torch.int64, device=DEV)
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    for n in range(1, 4):
+        assert lib.hq_ep_barrier(ftable.data_ptr(), 1, 0, seq.data_ptr(), status.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        assert int(seq[0]) == n and int(flags[0]) == n and int(status[0]) == 0
+
+
+def _worker(rank, world, port, results, exchange="nccl"):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -119,7 +148,8 @@ def _worker(rank, world, port, results):
         cut = lambda a: {key: v[sl] for key, v in a.items()}
         experts = hq.MoEExperts(T.make_layer("Q4_K", cut(da), i, dev), T.make_layer("Q4_K", cut(ga), h, dev),
                                 T.make_layer("Q4_K", cut(ua), h, dev))
-        ep = ExpertParallelMoE(e, experts, top_k=k, hidden=h, capacity=128, wire_dtype=torch.float16)
+        ep = ExpertParallelMoE(e, experts, top_k=k, hidden=h, capacity=128, wire_dtype=torch.float16,
+                               exchange=exchange)
         rr = T.rng_for(8, 10 + rank)
         x = T.to_dev(rr.standard_normal((t_local, h)).astype(np.float32), torch.bfloat16, dev)
         logits = rr.standard_normal((t_local, e)).astype(np.float32)
@@ -127,7 +157,9 @@ def _worker(rank, world, port, results):
                                  hq.MoeRouterTopKConfig(k, L.SCORE_SOFTMAX, L.WEIGHT_SCORE, True))
         ids, w = M.router_topk(logits, k, L.SCORE_SOFTMAX, L.WEIGHT_SCORE, True)
         out = ep.forward(x, top.values, top.indices, out_dtype=torch.float32)
+        out = ep.forward(x, top.values, top.indices, out_dtype=torch.float32)     # twice: the buffers are reused
         torch.cuda.synchronize()
+        assert ep.exchange_status()[0] == 0
         f16 = lambda a: a.astype(np.float16).astype(np.float32)
         want = M.moe_layer(f16(x.to(torch.float32).cpu().numpy()), ids, w, gd, ud, dd, h_round=f16)
         results[rank] = (T.rel_l2(out.cpu().numpy(), want),
@@ -137,13 +169,14 @@ def _worker(rank, world, port, results):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_two_gpus():
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
+def test_expert_parallel_two_gpus(exchange):
     import torch.multiprocessing as mp
     world = 2
-    port = 29600 + (os.getpid() % 1000)
+    port = 29600 + (os.getpid() % 1000) + (7 if exchange == "p2p" else 0)
     with mp.Manager() as mgr:
         results = mgr.dict()
-        mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, results, exchange), nprocs=world, join=True)
         res = dict(results)
     assert set(res) == {0, 1}
     for rank, (err, ids_ok) in res.items():
