@@ -520,6 +520,20 @@ def run_moe(args):
     experts = S.build_moe_layer(torch, hq, cfg, gen, dev, e // world)
     ep = (ExpertParallelMoE(e, experts, top_k=k, hidden=h, capacity=t_local, wire_dtype=torch.bfloat16, fp8_act=fp8,
                             mx_act=mx, exchange=args.exchange) if (world > 1 or args.force_ep) else None)
+    exchange_note = None
+    if ep is not None and world > 1 and args.exchange == "p2p":
+        # the symmetric buffers are set up collectively; if any rank cannot have them, every rank takes NCCL
+        try:
+            ep._symm_buffers(dev)
+            ok = 1
+        except Exception as exc:
+            ok = 0
+            exchange_note = f"symmetric memory unavailable ({type(exc).__name__}): all_to_all_single instead"
+        agreed = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed[0]) == 0:
+            ep.exchange = "nccl"
+            exchange_note = exchange_note or "symmetric memory unavailable on another rank: all_to_all_single instead"
     shared = S.build_moe_layer(torch, hq, cfg, gen, dev, 1) if cfg.get("shared") else None
     if shared is not None and not fp8:
         shared_ids = torch.zeros((t_local, 1), dtype=torch.int32, device=dev)
@@ -839,8 +853,9 @@ def run_moe(args):
         }
         if ep is not None:
             d_b, r_b = ep.wire_bytes_per_direction()
-            line["exchange"] = {"transport": "all_to_all_single (NCCL)" if args.exchange == "nccl" or world == 1 else
+            line["exchange"] = {"transport": "all_to_all_single (NCCL)" if ep.exchange == "nccl" or world == 1 else
                                 "hq_ep_push into symmetric memory + hq_ep_barrier",
+                                "note": exchange_note,
                                 "dispatch_bytes_per_rank": d_b, "return_bytes_per_rank": r_b,
                                 "rows": "one per (token, destination rank); equal-sized slabs, no host read",
                                 "wire": "e4m3 + f32 1x128 scales out, bf16 partial sums back" if fp8 else
@@ -967,7 +982,7 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="MoE workloads: bracket the timed steps with cudaProfilerStart/Stop, so that a profiler "
                          "started with --profile-from-start off sees the timed steps only")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--exchange", default="p2p", choices=["nccl", "p2p"],
                     help="expert-parallel exchange: two NCCL all-to-alls, or stores into the peers' symmetric-memory "
                          "buffers by this library's own kernels followed by a flag barrier")
     ap.add_argument("--force-ep", action="store_true",
