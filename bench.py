@@ -45,6 +45,8 @@ UNIT = "tokens/s"
 NCU_TRAFFIC_RATIO_GEMV = 563.3 / 558.2      # hq::gemv_int8_kernel, 4096 -> 128256
 NCU_TRAFFIC_RATIO_FP8 = 1573.4 / 1515.6     # hq::fp8_grouped_kernel, routed gate/up + down, 32 experts x 128 rows
 NCU_TRAFFIC_RATIO_MX = 527.3 / 543.2        # hq::mx_grouped_kernel, gate/up + down, 32 experts x 256 rows
+NCU_TRAFFIC_RATIO_Q4K = 118.8 / 181.3       # hq::grouped_gemm_kernel<Q4_K>, gate/up + down, 32 experts x 256 rows
+                                            # (below 1: most of the f32 output rows are still in L2 at the end)
 
 
 def algorithmic_bytes(k, n, m, x_size=2, y_size=4):
@@ -834,6 +836,14 @@ def run_moe(args):
                 ts_k = cfg["fmt"] == "MXFP4" or (cfg["fmt"] == "Q4_K" and rows_per_expert < 192)
                 roof["kernel"] = ("hq::grouped_gemm_ts_kernel" if ts_k else "hq::grouped_gemm_kernel") + \
                                  " (gate/up + down)"
+                bits = 4.5 if cfg["fmt"] == "Q4_K" else 4.25
+                # every weight once, f16 token rows in, f16 intermediate out and in again, f32 rows out
+                abytes = int(3 * e_l * i_ * h * bits / 8) + t_local * h * 2 + rows_here * (4 * i_ + 4 * h)
+                roof["algorithmic_bytes"] = abytes
+                roof["hbm_gbs"] = round(abytes / (gemm_ms / 1e3) / 1e9, 1)
+                if cfg["fmt"] == "Q4_K":
+                    roof["traffic"] = int(NCU_TRAFFIC_RATIO_Q4K * abytes / 2)
+                    roof["traffic_note"] = "per launch: algorithmic bytes x the ncu dram/algorithmic ratio"
         line = {
             "metric": MOE_METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
