@@ -80,6 +80,11 @@ def _gpu_reduce_fn(y_rows, weights, row_map, out_dtype, addend):
     return moe_weighted_reduce(y_rows, weights, out_dtype, row_map, addend)
 
 
+# symmetric exchange buffers, shared by every layer with the same slab geometry (layers run one after the other and
+# the barrier protocol makes the buffers safe to reuse from one call to the next)
+_SYMM_CACHE: dict = {}
+
+
 class ExpertParallelMoE:
     def __init__(self, n_experts_global: int, experts=None, *, top_k: int, hidden: int, capacity: int, group=None,
                  wire_dtype: torch.dtype = torch.bfloat16, fp8_act: bool = False, mx_act: bool = False,
@@ -138,6 +143,10 @@ class ExpertParallelMoE:
             import torch.distributed._symmetric_memory as symm
             lay = self.layout
             grp = self.group if self.group is not None else dist.group.WORLD
+            key = (id(grp), lay.world, lay.rows_per_peer, lay.row_bytes, lay.hidden, self.wire_dtype, str(device))
+            if key in _SYMM_CACHE:
+                self._symm = _SYMM_CACHE[key]
+                return self._symm
             recv = symm.empty((lay.world, lay.rows_per_peer, lay.row_bytes), dtype=torch.uint8, device=device)
             back = symm.empty((lay.world * lay.rows_per_peer, lay.hidden), dtype=self.wire_dtype, device=device)
             flags = symm.empty((64,), dtype=torch.int32, device=device)
@@ -154,6 +163,7 @@ class ExpertParallelMoE:
                 "seq": torch.zeros(1, dtype=torch.int32, device=device),
                 "status": torch.zeros(4, dtype=torch.int32, device=device),
             }
+            _SYMM_CACHE[key] = self._symm
         return self._symm
 
     def exchange_status(self) -> list[int]:

@@ -321,11 +321,15 @@ class MoEExperts:
 
     def _mark(self, start=None):
         """Measurement hook: with `gemm_events` set to a list, every forward appends a (start, end) CUDA event
-        pair around its two expert-GEMM launches."""
+        pair around its two expert-GEMM launches.  While the stream is being captured into a CUDA graph the
+        events are created as external event nodes, so they can be read after every replay of the graph."""
         evs = getattr(self, "gemm_events", None)
         if evs is None:
             return None
-        ev = torch.cuda.Event(enable_timing=True)
+        if torch.cuda.is_current_stream_capturing():
+            ev = torch.cuda.Event(enable_timing=True, external=True)
+        else:
+            ev = torch.cuda.Event(enable_timing=True)
         ev.record()
         if start is not None:
             evs.append((start, ev))
