@@ -117,7 +117,7 @@ def dist_env():
 
 
 # ======================================================================================================
-# Q8_0 decode mat-vec sweep (BASELINE config 2)
+# Q8_0 decode mat-vec sweep (benchmark configuration 2: Llama-3-8B shapes)
 # ======================================================================================================
 GEMV_METRIC = "quant_linear_decode_tokens_per_s"
 
@@ -164,10 +164,17 @@ def decode_other_formats(torch, dev, peak_gbs):
     gen.manual_seed(2100)
     n, k = 65536, 4096
     out = {}
-    for fmt in ("Q4_K", "MXFP4", "FP8"):
+    for fmt in ("Q4_K", "Q6_K", "MXFP4", "FP8"):
         if fmt == "Q4_K":
             layer = hq.GgufMatMul(S.q4k_bank(torch, 1, n, k, gen, dev)[0], "Q4_K", k)
             wbytes = n * (k // 256) * 144
+        elif fmt == "Q6_K":
+            # any byte pattern is a valid Q6_K block; d (the last two bytes of a block) is set to a small f16
+            raw = torch.randint(0, 256, (n, k // 256, 210), generator=gen, device=dev, dtype=torch.uint8)
+            raw[:, :, 208] = 0x00
+            raw[:, :, 209] = 0x10            # f16 0x1000 = 2^-11
+            layer = hq.GgufMatMul(raw.reshape(n, -1), "Q6_K", k)
+            wbytes = n * (k // 256) * 210
         elif fmt == "MXFP4":
             b, sc = S.mxfp4_bank(torch, 1, n, k, gen, dev)
             layer = hq.MXFP4Layer(b[0], sc[0])
@@ -432,7 +439,7 @@ def run_gemv(args):
 
 
 # ======================================================================================================
-# MoE layer workloads (BASELINE configs 3-5)
+# MoE layer workloads (benchmark configurations 3-5)
 # ======================================================================================================
 MOE_METRIC = "moe_layer_tokens_per_s"
 

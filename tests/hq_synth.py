@@ -7,7 +7,7 @@ from __future__ import annotations
 import numpy as np
 
 MOE_CFGS = {
-    # BASELINE configs 3-5
+    # benchmark configurations 3-5: Qwen3-30B-A3B Q4_K, DeepSeek-V3 block-FP8, gpt-oss-120b MXFP4 layer shapes
     "moe_q4k": dict(fmt="Q4_K", e=128, k=8, h=2048, i=768, t=4096, router="softmax", inter=False,
                     label="cfg3_qwen3_30b_a3b_q4k_moe"),
     "moe_fp8": dict(fmt="FP8", e=256, k=8, h=7168, i=2048, t=4096, router="sigmoid_bias", inter=False,
