@@ -553,6 +553,8 @@ def run_moe(args):
     xs = [torch.randn((t_local, h), generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_in)]
     logits = [torch.randn((t_local, e), generator=gen, device=dev) for _ in range(n_in)]
 
+    side_stream = torch.cuda.Stream(device=dev)
+
     def shared_fwd(x, out_dtype):
         if shared is None:
             return None
@@ -564,9 +566,16 @@ def run_moe(args):
         x = xs[j % n_in] if x is None else x
         lg = logits[j % n_in] if lg is None else lg
         if ep is not None:
+            sh, ev = None, None
+            if shared is not None:
+                # the shared expert depends on the activations only: it starts on its own stream before the router
+                cur = torch.cuda.current_stream(dev)
+                side_stream.wait_stream(cur)
+                with torch.cuda.stream(side_stream):
+                    sh = shared_fwd(x, out_dtype)
+                    ev = side_stream.record_event()
             top = hq.moe_router_topk(lg, rcfg, sel_bias)
-            return ep.forward(x, top.values, top.indices, out_dtype=out_dtype,
-                              shared_fn=(lambda: shared_fwd(x, out_dtype)) if shared is not None else None)
+            return ep.forward(x, top.values, top.indices, out_dtype=out_dtype, shared_out=sh, shared_event=ev)
         if fp8:
             top = hq.moe_router_topk(lg, rcfg, sel_bias)
             return experts.forward_fp8_act(x, top.values, top.indices, shared_out=shared_fwd(x, out_dtype),

@@ -62,6 +62,7 @@ SIGNATURES = {
     "hq_fp8_quant_rows_n": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _P, _P, _P]),
     "hq_fp8_gather_rows": (_I32, [_P, _I64, _P, _I64, _P, _P, _I64, _I64, _P, _P, _P]),
     "hq_ep_push": (_I32, [_P, _P, _I32, _I32, _I64, _P]),
+    "hq_ep_push_rows": (_I32, [_P, _P, _I32, _I32, _I32, _I64, _I32, _P, _I32, _P, _I32, _P]),
     "hq_ep_barrier": (_I32, [_P, _I32, _I32, _P, _P, _P]),
     "hq_mxfp8_quant_rows": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _P, _P, _P]),
     "hq_mx_linear_forward": (_I32, [C.POINTER(HqWeight), _P, _P, _I64, _P, _I32, _I64, _P, _P]),

@@ -624,6 +624,21 @@ int32_t hq_ep_push(const void* send, void* const* peer_slabs_dev, int32_t world,
   return launch_ep_push(send, peer_slabs_dev, world, rank, slab_bytes, (cudaStream_t)stream);
 }
 
+int32_t hq_ep_push_rows(const void* send, void* const* peer_slabs_dev, int32_t world, int32_t rank,
+                        int32_t rows_per_slab, int64_t row_bytes, int32_t always_from, const int32_t* back_map,
+                        int32_t n_tokens, const uint32_t* ids, int32_t top_k, void* stream) {
+  if (world < 1 || world > 64 || rank < 0 || rank >= world || rows_per_slab < 0 || row_bytes < 0 || row_bytes % 16 != 0)
+    return HQ_ERR_SHAPE;
+  if (always_from < 0 || always_from > rows_per_slab) return HQ_ERR_SHAPE;
+  if (rows_per_slab == 0 || row_bytes == 0) return HQ_OK;
+  if (send == nullptr || peer_slabs_dev == nullptr) return HQ_ERR_NULL;
+  if ((back_map == nullptr) == (ids == nullptr) && always_from > 0) return HQ_ERR_NULL;   // exactly one row filter
+  if (ids != nullptr && (top_k < 1 || top_k > 64)) return HQ_ERR_SHAPE;
+  if (!aligned16(send)) return HQ_ERR_ALIGN;
+  return launch_ep_push_rows(send, peer_slabs_dev, world, rank, rows_per_slab, row_bytes, always_from, back_map,
+                             n_tokens, ids, top_k, (cudaStream_t)stream);
+}
+
 int32_t hq_ep_barrier(int32_t* const* peer_flags_dev, int32_t world, int32_t rank, int32_t* seq_counter_dev,
                       int32_t* status_dev, void* stream) {
   if (world < 1 || world > 64 || rank < 0 || rank >= world) return HQ_ERR_SHAPE;

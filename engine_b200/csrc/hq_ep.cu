@@ -189,6 +189,36 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const uint4* __restrict__ 
   __threadfence_system();
 }
 
+// The same push row by row, leaving out the rows nobody will read: a token travels to 5 of 8 ranks on average, so
+// a third of the rows of a slab carry nothing.  One CTA per slab row.  A row is sent when
+//   - it lies at or behind `always_from` (the meta rows of the dispatch slabs), or
+//   - dispatch: back_map[t * world + d] >= 0 (token t goes to rank d), or
+//   - return: any of the row's top_k slot ids is a real expert (ids != 0xFFFFFFFF).
+__global__ void __launch_bounds__(256) ep_push_rows_kernel(const uint4* __restrict__ send,
+                                                           uint4* const* __restrict__ peers, int world, int rank,
+                                                           int rows_per_slab, int row_vec, int always_from,
+                                                           const int32_t* __restrict__ back_map, int n_tokens,
+                                                           const uint32_t* __restrict__ ids, int top_k) {
+  const int64_t gr = blockIdx.x;                      // row over all slabs
+  const int d = (int)(gr / rows_per_slab);
+  const int r = (int)(gr - (int64_t)d * rows_per_slab);
+  if (d >= world) return;
+  if (r < always_from) {
+    bool live;
+    if (back_map != nullptr) {
+      live = r < n_tokens && back_map[(int64_t)r * world + d] >= 0;
+    } else {
+      live = false;
+      for (int s = 0; s < top_k; ++s) live = live || ids[gr * top_k + s] != 0xFFFFFFFFu;
+    }
+    if (!live) return;                                // block-uniform
+  }
+  const uint4* src = send + gr * row_vec;
+  uint4* dst = peers[d] + ((int64_t)rank * rows_per_slab + r) * row_vec;
+  for (int i = threadIdx.x; i < row_vec; i += 256) dst[i] = __ldg(src + i);
+  __threadfence_system();
+}
+
 // Barrier over the ranks of the exchange: thread p tells peer p "rank `rank` has finished its step `seq`" by
 // storing seq into slot `rank` of peer p's flag array, then waits until slot p of the local flag array has
 // reached seq.  Flags only grow, one per barrier, so a peer that is already one barrier ahead satisfies the
@@ -256,6 +286,18 @@ int32_t launch_ep_push(const void* send, void* const* peers, int world, int rank
   ep_push_kernel<<<(unsigned)(world * per), 256, 0, stream>>>(reinterpret_cast<const uint4*>(send),
                                                              reinterpret_cast<uint4* const*>(peers), world, rank,
                                                              slab_vec, per);
+  return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
+}
+
+int32_t launch_ep_push_rows(const void* send, void* const* peers, int world, int rank, int rows_per_slab,
+                            int64_t row_bytes, int always_from, const int32_t* back_map, int n_tokens,
+                            const uint32_t* ids, int top_k, cudaStream_t stream) {
+  const int64_t rows = (int64_t)world * rows_per_slab;
+  if (rows <= 0 || row_bytes <= 0) return HQ_OK;
+  ep_push_rows_kernel<<<(unsigned)rows, 256, 0, stream>>>(reinterpret_cast<const uint4*>(send),
+                                                          reinterpret_cast<uint4* const*>(peers), world, rank,
+                                                          rows_per_slab, (int)(row_bytes / 16), always_from, back_map,
+                                                          n_tokens, ids, top_k);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 

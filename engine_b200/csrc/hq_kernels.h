@@ -200,6 +200,9 @@ int32_t launch_ep_pack(const hq_ep_layout& l, const void* x, int x_dtype, const 
                        int64_t n_tokens, void* send, int32_t* back_map, cudaStream_t stream);
 int32_t launch_ep_push(const void* send, void* const* peers, int world, int rank, int64_t slab_bytes,
                        cudaStream_t stream);
+int32_t launch_ep_push_rows(const void* send, void* const* peers, int world, int rank, int rows_per_slab,
+                            int64_t row_bytes, int always_from, const int32_t* back_map, int n_tokens,
+                            const uint32_t* ids, int top_k, cudaStream_t stream);
 int32_t launch_ep_barrier(int32_t* const* flags, int world, int rank, int32_t* seq_counter, uint32_t spin_limit,
                           int32_t* status, cudaStream_t stream);
 int32_t launch_ep_unpack_meta(const hq_ep_layout& l, const void* recv, uint32_t* ids, float* weights,

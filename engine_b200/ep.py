@@ -172,19 +172,26 @@ class ExpertParallelMoE:
             return [0, 0, 0, 0]
         return [int(v) for v in self._symm["status"].cpu()]
 
-    def _push(self, src: torch.Tensor, peers, slab_bytes: int):
+    def _push(self, src: torch.Tensor, peers, row_bytes: int, always_from: int, back_map=None, n_tokens: int = 0,
+              ids=None):
+        """Rows of the local slabs -> the peers' buffers (only the rows somebody reads), then the flag barrier."""
         sm = self._symm
+        lay = self.layout
         stream = C.c_void_p(torch.cuda.current_stream(src.device).cuda_stream)
         lib = L.lib()
-        L.check(lib.hq_ep_push(src.data_ptr(), peers, self.world, self.rank, slab_bytes, stream), "hq_ep_push")
+        L.check(lib.hq_ep_push_rows(src.data_ptr(), peers, self.world, self.rank, lay.rows_per_peer, row_bytes,
+                                    always_from, None if back_map is None else back_map.data_ptr(), n_tokens,
+                                    None if ids is None else ids.data_ptr(), lay.top_k, stream), "hq_ep_push_rows")
         L.check(lib.hq_ep_barrier(sm["p_flags"], self.world, self.rank, sm["seq"].data_ptr(),
                                   sm["status"].data_ptr(), stream), "hq_ep_barrier")
 
     def forward(self, xs: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                 shared_out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-                shared_fn: Callable | None = None) -> torch.Tensor:
+                shared_fn: Callable | None = None, shared_event=None) -> torch.Tensor:
         """`shared_fn`, if given, computes the shared expert's output; on a GPU it is queued on a second stream
-        behind the pack so that it runs beside the dispatch exchange."""
+        behind the pack so that it runs beside the dispatch exchange.  A caller that has started the shared expert
+        earlier on a stream of its own passes its result as `shared_out` with the CUDA event recorded behind it
+        as `shared_event`; the final reduce waits for that event."""
         t, k = topk_ids.shape
         lay = self.layout
         if t > lay.capacity:
@@ -209,7 +216,7 @@ class ExpertParallelMoE:
         if p2p:
             sm = self._symm_buffers(x.device)
             recv, back = sm["recv"], sm["back"]
-            self._push(send, sm["p_recv"], lay.message_bytes)
+            self._push(send, sm["p_recv"], lay.row_bytes, lay.capacity, back_map=back_map, n_tokens=t)
         elif self.world > 1:
             dist.all_to_all_single(recv, send, group=self.group)
         else:
@@ -217,11 +224,13 @@ class ExpertParallelMoE:
         ids_l, w_l = self.unpack_fn(lay, recv)
         y = self.expert_fn(lay, recv, ids_l, w_l)
         if p2p:
-            self._push(y.contiguous(), sm["p_back"], lay.rows_per_peer * lay.hidden * y.element_size())
+            self._push(y.contiguous(), sm["p_back"], lay.hidden * y.element_size(), lay.rows_per_peer, ids=ids_l)
         elif self.world > 1:
             dist.all_to_all_single(back, y.contiguous(), group=self.group)
         else:
             back = y
+        if ev_shared is None and shared_event is not None and shared_out is not None:
+            ev_shared = shared_event
         if ev_shared is not None:
             torch.cuda.current_stream(x.device).wait_event(ev_shared)
             shared_out.record_stream(torch.cuda.current_stream(x.device))

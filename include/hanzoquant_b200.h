@@ -446,6 +446,15 @@ int32_t hq_ep_push(const void* send, void* const* peer_slabs_dev, int32_t world,
                    void* stream);
 int32_t hq_ep_barrier(int32_t* const* peer_flags_dev, int32_t world, int32_t rank, int32_t* seq_counter_dev,
                       int32_t* status_dev, void* stream);
+/* hq_ep_push row by row, without the rows nobody reads (a token goes to about 5 of 8 ranks).  Slab d has
+ * rows_per_slab rows of row_bytes (a multiple of 16) bytes.  Rows at or behind always_from are always sent (the meta
+ * rows of a dispatch slab); an earlier row r of slab d is sent when back_map[r * world + d] >= 0 and r < n_tokens
+ * (dispatch: back_map as written by hq_ep_pack, ids NULL), or when one of its top_k ids is not 0xFFFFFFFF (return:
+ * ids [world * rows_per_slab, top_k] as written by hq_ep_unpack_meta, back_map NULL).  What is left out keeps
+ * whatever the peer's buffer held; the receiver never reads those rows. */
+int32_t hq_ep_push_rows(const void* send, void* const* peer_slabs_dev, int32_t world, int32_t rank,
+                        int32_t rows_per_slab, int64_t row_bytes, int32_t always_from, const int32_t* back_map,
+                        int32_t n_tokens, const uint32_t* ids, int32_t top_k, void* stream);
 
 /* ---- FP8 quantizers ---------------------------------------------------------
  * 1x128 groups along the last axis: scale = absmax/448 (1e-12 if zero),

@@ -124,6 +124,46 @@ def test_push_moves_slab_d_to_slot_rank_of_peer_d():
         assert int(seq[0]) == n and int(flags[0]) == n and int(status[0]) == 0
 
 
+def test_push_rows_sends_only_the_rows_somebody_reads():
+    """hq_ep_push_rows on emulated peers: dispatch filter (back_map, meta rows always) and return filter (slot ids)."""
+    import ctypes as C
+    from engine_b200 import _lib as L
+    lib = L.lib()
+    world, rows, row_bytes, cap, k, n_tok = 2, 6, 64, 4, 2, 3
+    rng = np.random.Generator(np.random.PCG64(12))
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    send = torch.from_numpy(rng.integers(1, 256, (world, rows, row_bytes), dtype=np.uint8)).to(DEV)
+    recvs = [torch.zeros((world, rows, row_bytes), dtype=torch.uint8, device=DEV) for _ in range(world)]
+    table = torch.tensor([r.data_ptr() for r in recvs], dtype=torch.int64, device=DEV)
+    back_map = torch.tensor([[0, -1], [-1, 7], [2, 8], [3, 9]], dtype=torch.int32, device=DEV)   # row 3 >= n_tok
+    rank = 1
+    assert lib.hq_ep_push_rows(send.data_ptr(), table.data_ptr(), world, rank, rows, row_bytes, cap,
+                               back_map.data_ptr(), n_tok, None, k, stream) == 0
+    torch.cuda.synchronize()
+    for d in range(world):
+        for r in range(rows):
+            sent = r >= cap or (r < n_tok and int(back_map[r, d]) >= 0)
+            got = recvs[d][rank, r]
+            assert torch.equal(got, send[d, r]) if sent else not bool(got.any()), (d, r)
+        assert not bool(recvs[d][0].any())                 # slot of the other rank untouched
+    # return direction: a row travels when one of its slots names an expert
+    for r_ in recvs:
+        r_.zero_()
+    ids = torch.full((world * rows, k), 0xFFFFFFFF, dtype=torch.int64, device=DEV).to(torch.uint32)
+    ids_np = np.full((world * rows, k), 0xFFFFFFFF, np.uint32)
+    ids_np[1, 0] = 3
+    ids_np[8, 1] = 0
+    ids = torch.from_numpy(ids_np.view(np.int32)).to(DEV)
+    assert lib.hq_ep_push_rows(send.data_ptr(), table.data_ptr(), world, rank, rows, row_bytes, rows, None, 0,
+                               ids.data_ptr(), k, stream) == 0
+    torch.cuda.synchronize()
+    for d in range(world):
+        for r in range(rows):
+            sent = (d * rows + r) in (1, 8)
+            got = recvs[d][rank, r]
+            assert torch.equal(got, send[d, r]) if sent else not bool(got.any()), (d, r)
+
+
 def _worker(rank, world, port, results, exchange="nccl"):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
