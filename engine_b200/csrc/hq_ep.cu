@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const uint4* __restrict__ 
 }
 
 // The same push row by row, leaving out the rows nobody will read: a token travels to 5 of 8 ranks on average, so
-// a third of the rows of a slab carry nothing.  One CTA per slab row.  A row is sent when
+// a third of the rows of a slab carry nothing.  CTAs stride over the slab rows.  A row is sent when
 //   - it lies at or behind `always_from` (the meta rows of the dispatch slabs), or
 //   - dispatch: back_map[t * world + d] >= 0 (token t goes to rank d), or
 //   - return: any of the row's top_k slot ids is a real expert (ids != 0xFFFFFFFF).
@@ -199,23 +199,24 @@ __global__ void __launch_bounds__(256) ep_push_rows_kernel(const uint4* __restri
                                                            int rows_per_slab, int row_vec, int always_from,
                                                            const int32_t* __restrict__ back_map, int n_tokens,
                                                            const uint32_t* __restrict__ ids, int top_k) {
-  const int64_t gr = blockIdx.x;                      // row over all slabs
-  const int d = (int)(gr / rows_per_slab);
-  const int r = (int)(gr - (int64_t)d * rows_per_slab);
-  if (d >= world) return;
-  if (r < always_from) {
-    bool live;
-    if (back_map != nullptr) {
-      live = r < n_tokens && back_map[(int64_t)r * world + d] >= 0;
-    } else {
-      live = false;
-      for (int s = 0; s < top_k; ++s) live = live || ids[gr * top_k + s] != 0xFFFFFFFFu;
+  const int64_t total = (int64_t)world * rows_per_slab;
+  for (int64_t gr = blockIdx.x; gr < total; gr += gridDim.x) {      // row over all slabs
+    const int d = (int)(gr / rows_per_slab);
+    const int r = (int)(gr - (int64_t)d * rows_per_slab);
+    if (r < always_from) {
+      bool live;
+      if (back_map != nullptr) {
+        live = r < n_tokens && back_map[(int64_t)r * world + d] >= 0;
+      } else {
+        live = false;
+        for (int s = 0; s < top_k; ++s) live = live || ids[gr * top_k + s] != 0xFFFFFFFFu;
+      }
+      if (!live) continue;                              // block-uniform
     }
-    if (!live) return;                                // block-uniform
+    const uint4* src = send + gr * row_vec;
+    uint4* dst = peers[d] + ((int64_t)rank * rows_per_slab + r) * row_vec;
+    for (int i = threadIdx.x; i < row_vec; i += 256) dst[i] = __ldg(src + i);
   }
-  const uint4* src = send + gr * row_vec;
-  uint4* dst = peers[d] + ((int64_t)rank * rows_per_slab + r) * row_vec;
-  for (int i = threadIdx.x; i < row_vec; i += 256) dst[i] = __ldg(src + i);
   __threadfence_system();
 }
 
@@ -294,7 +295,8 @@ int32_t launch_ep_push_rows(const void* send, void* const* peers, int world, int
                             const uint32_t* ids, int top_k, cudaStream_t stream) {
   const int64_t rows = (int64_t)world * rows_per_slab;
   if (rows <= 0 || row_bytes <= 0) return HQ_OK;
-  ep_push_rows_kernel<<<(unsigned)rows, 256, 0, stream>>>(reinterpret_cast<const uint4*>(send),
+  const int64_t cap = 8 * 148;
+  ep_push_rows_kernel<<<(unsigned)(rows < cap ? rows : cap), 256, 0, stream>>>(reinterpret_cast<const uint4*>(send),
                                                           reinterpret_cast<uint4* const*>(peers), world, rank,
                                                           rows_per_slab, (int)(row_bytes / 16), always_from, back_map,
                                                           n_tokens, ids, top_k);
