@@ -17,6 +17,9 @@ int64_t weight_row_bytes(int format, int64_t k) {
     case HQ_FMT_FP8_BLOCK: return k;
     case HQ_FMT_MXFP4: return k / 2;
     case HQ_FMT_Q6_K: return k / 256 * 210;
+    case HQ_FMT_Q5_K: return k / 256 * 176;
+    case HQ_FMT_Q4_0: return k / 32 * 18;
+    case HQ_FMT_Q5_0: return k / 32 * 22;
     default: return -1;
   }
 }
@@ -29,6 +32,9 @@ int32_t check_weight(const hq_weight* w) {
     case HQ_FMT_Q8_0:
     case HQ_FMT_Q4_K:
     case HQ_FMT_Q6_K:
+    case HQ_FMT_Q5_K:
+    case HQ_FMT_Q4_0:
+    case HQ_FMT_Q5_0:
       if (w->k % 256 != 0) return HQ_ERR_SHAPE;
       break;
     case HQ_FMT_FP8_BLOCK:

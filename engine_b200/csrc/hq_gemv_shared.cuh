@@ -103,6 +103,9 @@ inline int sm_count() {
   return cached[dev];
 }
 
+// the Q5_K / Q4_0 / Q5_0 decode kernel (hq_gemv_ggml.cu)
+int32_t launch_gemv_ggml(const GemvParams& p, int n_y_max, cudaStream_t stream);
+
 // the Q6_K decode kernel (hq_gemv_q6k.cu)
 int32_t launch_gemv_q6k(const GemvParams& p, int n_y_max, cudaStream_t stream);
 

@@ -249,7 +249,8 @@ class QuantMethod:
 
 
 GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = "Q8_0", "Q4_K", "Q6_K"
-_GGML = {GGML_Q8_0: (L.FMT_Q8_0, 32, 34), GGML_Q4_K: (L.FMT_Q4_K, 256, 144), GGML_Q6_K: (L.FMT_Q6_K, 256, 210)}
+_GGML = {GGML_Q8_0: (L.FMT_Q8_0, 32, 34), GGML_Q4_K: (L.FMT_Q4_K, 256, 144), GGML_Q6_K: (L.FMT_Q6_K, 256, 210),
+         "Q5_K": (L.FMT_Q5_K, 256, 176), "Q4_0": (L.FMT_Q4_0, 32, 18), "Q5_0": (L.FMT_Q5_0, 32, 22)}
 
 
 class GgufMatMul(QuantMethod):
@@ -259,7 +260,7 @@ class GgufMatMul(QuantMethod):
     def __init__(self, data: torch.Tensor, qtype: str, k: int, bias: torch.Tensor | None = None):
         super().__init__()
         if qtype not in _GGML:
-            raise L.HqError(f"GGML type {qtype} is not on this path (Q8_0, Q4_K and Q6_K are)")
+            raise L.HqError(f"GGML type {qtype} is not on this path ({', '.join(_GGML)} are)")
         _require_cuda(data, "data")
         self.format, blk, nbytes = _GGML[qtype]
         self.qtype = qtype

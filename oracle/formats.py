@@ -24,6 +24,9 @@ Q8_0_BYTES = 34     # half d + 32 int8
 QK_K = 256          # elements per k-quant super-block
 Q4_K_BYTES = 144    # half d, half dmin, 12 scale bytes, 128 nibble bytes
 Q6_K_BYTES = 210    # 128 low-nibble bytes, 64 high-bit bytes, 16 int8 scales, half d
+Q5_K_BYTES = 176    # half d, half dmin, 12 scale bytes, 32 high-bit bytes, 128 nibble bytes
+Q4_0_BYTES = 18     # half d, 16 nibble bytes (32 weights)
+Q5_0_BYTES = 22     # half d, 4 high-bit bytes, 16 nibble bytes (32 weights)
 MXFP4_BLOCK = 32
 FP8_MAX = 448.0
 
@@ -165,6 +168,76 @@ def q6_k_quantize(w: np.ndarray) -> np.ndarray:
     blk[:, :, 192:208] = isc.reshape(rows, nsb, 16).view(np.uint8)
     blk[:, :, 208:210] = d.reshape(rows, nsb, 1).view(np.uint8)
     return blk.reshape(rows, nsb * Q6_K_BYTES)
+
+
+# ----------------------------------------------------------------------------
+# Q5_K, Q4_0, Q5_0 (the further types of the reference's decode list, hanzo-quant/src/gguf/fast_mmvq.rs:36-50).
+# Layouts as in ggml: Q5_K = Q4_K plus one high bit per weight (qh[l] bit 2c / 2c+1 for the low- / high-nibble
+# sub-block of chunk c); Q4_0 / Q5_0 blocks of 32: element j < 16 from the low nibble of qs[j], element j + 16 from
+# the high nibble, value (q - 8) d resp. (q - 16) d with the fifth bit from qh bit j / j + 16.
+# ----------------------------------------------------------------------------
+
+def q5_k_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/256*176] -> f32 [rows, K]."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    nsb = k // QK_K
+    blk = raw.reshape(rows, nsb, Q5_K_BYTES)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)
+    dmin = blk[:, :, 2:4].copy().view(np.float16).astype(np.float32)
+    sc, mn = q4_k_unpack_scales(blk[:, :, 4:16])
+    qh = blk[:, :, 16:48]                                         # [rows, nsb, 32]
+    qs = blk[:, :, 48:].reshape(rows, nsb, 4, 32)
+    q = np.empty((rows, nsb, 8, 32), np.float32)
+    for c in range(4):
+        q[:, :, 2 * c, :] = ((qs[:, :, c, :] & 0x0F) | (((qh >> (2 * c)) & 1) << 4)).astype(np.float32)
+        q[:, :, 2 * c + 1, :] = ((qs[:, :, c, :] >> 4) | (((qh >> (2 * c + 1)) & 1) << 4)).astype(np.float32)
+    d1 = (d * sc.astype(np.float32))[..., None]
+    m1 = (dmin * mn.astype(np.float32))[..., None]
+    return (d1 * q - m1).reshape(rows, k)
+
+
+def q4_0_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/32*18] -> f32 [rows, K]."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    blk = raw.reshape(rows, k // 32, Q4_0_BYTES)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)
+    qs = blk[:, :, 2:]
+    q = np.concatenate([(qs & 0x0F).astype(np.int32), (qs >> 4).astype(np.int32)], axis=2) - 8
+    return (d * q.astype(np.float32)).reshape(rows, k)
+
+
+def q5_0_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/32*22] -> f32 [rows, K]."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    blk = raw.reshape(rows, k // 32, Q5_0_BYTES)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)
+    qh = blk[:, :, 2:6].copy().view(np.uint32).astype(np.int64)    # [rows, nb, 1]
+    qs = blk[:, :, 6:]
+    j = np.arange(16)
+    lo = (qs & 0x0F).astype(np.int64) | (((qh >> j) & 1) << 4)
+    hi = (qs >> 4).astype(np.int64) | (((qh >> (j + 16)) & 1) << 4)
+    q = np.concatenate([lo, hi], axis=2) - 16
+    return (d * q.astype(np.float32)).reshape(rows, k)
+
+
+def ggml_random_blocks(fmt: str, rng, rows: int, k: int, d_lo: float = 2e-4, d_hi: float = 3e-3) -> np.ndarray:
+    """Random valid blocks of a GGML type whose every bit pattern is valid (Q6_K, Q5_K, Q4_0, Q5_0), with the f16
+    scale fields drawn from [d_lo, d_hi] so that the weights have the magnitude of N(0, 0.02^2) weights: test and
+    benchmark input for types the oracle has no quantizer for."""
+    per, nbytes, scale_off = {"Q6_K": (256, 210, [208]), "Q5_K": (256, 176, [0, 2]), "Q4_0": (32, 18, [0]),
+                              "Q5_0": (32, 22, [0])}[fmt]
+    nb = k // per
+    blk = rng.integers(0, 256, (rows, nb, nbytes), dtype=np.uint8)
+    for off in scale_off:
+        blk[:, :, off:off + 2] = np.asarray(rng.uniform(d_lo, d_hi, (rows, nb, 1)), np.float16).view(np.uint8)
+    return blk.reshape(rows, nb * nbytes)
+
+
+GGML_DEQUANT = {"Q8_0": q8_0_dequant, "Q4_K": q4_k_dequant, "Q6_K": q6_k_dequant, "Q5_K": q5_k_dequant,
+                "Q4_0": q4_0_dequant, "Q5_0": q5_0_dequant}
 
 
 def _nearest_int(f: np.ndarray) -> np.ndarray:

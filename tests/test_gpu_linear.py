@@ -10,7 +10,7 @@ from oracle import formats as F
 from oracle import moe as M
 from tests import hq_testlib as T
 
-TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "Q6_K": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
+TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "Q6_K": 1e-3, "Q5_K": 1e-3, "Q4_0": 1e-3, "Q5_0": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
 DEV = "cuda:0"
 
 
@@ -33,7 +33,7 @@ def run_case(fmt, n, k, m, x_dtype, out_dtype, seed, bias=False):
     return y.to(torch.float32).cpu().numpy(), want
 
 
-@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "Q6_K", "FP8", "MXFP4"])
+@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0", "FP8", "MXFP4"])
 @pytest.mark.parametrize("m", [1, 2, 4, 8])
 def test_decode_rows_f32_out(fmt, m):
     got, want = run_case(fmt, 512, 1024, m, torch.bfloat16, torch.float32, 10 + m)
@@ -73,6 +73,15 @@ def test_q6_k_prefill_rows_on_the_tensor_cores(m, k):
     assert T.rel_l2(got, want) <= 1e-3
 
 
+@pytest.mark.parametrize("fmt", ["Q5_K", "Q4_0", "Q5_0"])
+@pytest.mark.parametrize("dt", ["float32", "float16"])
+def test_further_ggml_types_any_row_count(fmt, dt):
+    # these types stay on the decode kernel for every row count (eight rows per work item); N = 1000 is not a
+    # multiple of the eight rows a CTA covers
+    got, want = run_case(fmt, 1000, 768, 21, getattr(torch, dt), torch.float32, 80)
+    assert T.rel_l2(got, want) <= 1e-3
+
+
 @pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "Q6_K", "FP8", "MXFP4"])
 def test_ragged_rows_and_tile_heights(fmt):
     # N not a multiple of the row tile, M not a multiple of 8, and an N large enough for the tall tiles
@@ -106,7 +115,7 @@ def test_run_twice_is_bit_identical():
 
 def test_dequantize_w_is_exact():
     rng = T.rng_for(1, 70)
-    for fmt in ["Q8_0", "Q4_K", "Q6_K", "FP8", "MXFP4"]:
+    for fmt in ["Q8_0", "Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0", "FP8", "MXFP4"]:
         arrays, deq = T.make_weight(fmt, rng, 128, 256)
         layer = T.make_layer(fmt, arrays, 256, DEV)
         got = layer.dequantize_w().cpu().numpy()

@@ -118,7 +118,8 @@ def test_gather_forward_known_answers():
     assert out2.reshape(-1).cpu().tolist() == [1, 2, 6, 15]
 
 
-@pytest.mark.parametrize("fmt,k,n", [("Q4_K", 512, 192), ("Q8_0", 256, 64), ("FP8", 256, 128), ("MXFP4", 96, 80)])
+@pytest.mark.parametrize("fmt,k,n", [("Q4_K", 512, 192), ("Q8_0", 256, 64), ("FP8", 256, 128), ("MXFP4", 96, 80),
+                                     ("Q6_K", 256, 72), ("Q5_K", 512, 64), ("Q4_0", 256, 40), ("Q5_0", 256, 40)])
 @pytest.mark.parametrize("per_slot", [False, True])
 def test_gather_forward_matches_oracle(fmt, k, n, per_slot):
     rng = T.rng_for(3, k + n)

@@ -133,13 +133,14 @@ def test_bf16_rounding_helpers():
     assert np.array_equal(F.from_bf16_bits(F.to_bf16_bits(x)), want)
 
 
-def test_q6_k_dequant_matches_gguf_py_bit_for_bit():
-    """Q6_K blocks (random valid bytes and blocks built by the oracle's quantizer) against gguf-py's dequantize;
-    vectors from tests/golden/make_golden_q6k.py."""
+@pytest.mark.parametrize("fmt", ["Q6_K", "Q5_K", "Q4_0", "Q5_0"])
+def test_ggml_dequant_matches_gguf_py_bit_for_bit(fmt):
+    """Random valid blocks (and, where a quantizer exists, quantized N(0, 0.02^2) weights) against gguf-py's
+    dequantize; vectors from tests/golden/make_golden_ggml.py."""
     import os
-    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "q6k_vectors.npz"))
-    got = F.q6_k_dequant(z["raw"], 512)
-    assert np.array_equal(got, z["deq"])
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "ggml_vectors.npz"))
+    got = F.GGML_DEQUANT[fmt](z["raw_" + fmt], 512)
+    assert np.array_equal(got, z["deq_" + fmt])
 
 
 def test_q6_k_quantizer_round_trip():
