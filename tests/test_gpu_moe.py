@@ -13,7 +13,7 @@ from oracle import moe as M
 from tests import hq_testlib as T
 
 DEV = "cuda:0"
-TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
+TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "Q6_K": 1e-3, "Q5_K": 1e-3, "Q4_0": 1e-3, "Q5_0": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
 
 
 def margin_ok_rows(sel: np.ndarray, k: int, ulps: int = 4):
