@@ -338,9 +338,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
       if (wi.nrows <= 0) continue;
       const int rb = item & 1;
       const float* rbuf = red + rb * (p.n_banks * kConsumerWarps * 4 * 32);
+      bool failed = false;
       if (!mbar_wait_backoff(&red_full[rb], (item >> 1) & 1, spin)) {
         if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + rb);
         spin = 1;
+        failed = true;                 // nothing is stored for an item whose partial sums never arrived
       }
       float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -357,7 +359,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(&red_free[rb]);
       // rows of this lane: n0 + g (+8); columns 2t, 2t+1
-      gemv_store_item(p, wi, g, 2 * t, true, v);
+      gemv_store_item(p, wi, g, 2 * t, !failed, v);
       ++item;
     }
     return;

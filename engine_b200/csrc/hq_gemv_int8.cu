@@ -693,9 +693,11 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
       if (wi.nrows <= 0) continue;
       const int rb = item & 1;
       const float* rbuf = red + rb * (p.n_banks * WK * 4 * 32);
+      bool failed = false;
       if (!mbar_wait_backoff(&red_full[rb], (item >> 1) & 1, spin)) {
         if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 310 + rb);
         spin = 1;
+        failed = true;                 // nothing is stored for an item whose partial sums never arrived
       }
       float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -730,7 +732,7 @@ __global__ void __launch_bounds__(kQ8Threads, 1) gemv_int8_kernel(const GemvPara
             for (int i = 0; i < 4; ++i) __stcg(mine + (b * 4 + i) * 32 + lane, v[b][i]);
           }
       } else {
-        gemv_store_item(p, wi, g, 2 * t, NCS > 1 || t < (FMT == HQ_FMT_FP8_BLOCK ? 1 : 2), v);
+        gemv_store_item(p, wi, g, 2 * t, !failed && (NCS > 1 || t < (FMT == HQ_FMT_FP8_BLOCK ? 1 : 2)), v);
       }
       ++item;
     }

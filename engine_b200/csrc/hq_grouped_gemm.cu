@@ -443,6 +443,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
     // =========================== epilogue ========================================
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     uint32_t spin = kGgSpin;
+    bool failed = false;
     int tcount = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++tcount) {
       const GgTile t = gg_tile<TN>(p, w, n_nt);
@@ -450,6 +451,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
       if (!mbar_wait_backoff(&acc_full[buf], (tcount / NBUF) & 1, spin)) {
         if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 400 + buf);
         spin = 1;
+        failed = true;                 // nothing is stored once a wait has run out
       }
       tc_fence_after();
       const int n = t.n0 + 32 * q + lane;       // feature owned by this thread
@@ -465,7 +467,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
       }
       const bool interleaved = NB == 1 && p.act.act != HQ_ACT_NONE;
       const int64_t out_n = interleaved ? (n >> 1) : n;
-      const bool writer = n_ok && (!interleaved || (n & 1) == 0);
+      const bool writer = n_ok && !failed && (!interleaved || (n & 1) == 0);
       const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * NB * kTileN);
       // Output row of the token in column 32*cc + lane (-1 past the tile's tokens).  One coalesced load per
       // column group, issued a group ahead, then broadcast by shuffle: a load per stored element would
@@ -884,6 +886,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_ts_kernel(const Gr
     // =========================== epilogue ========================================
     const int q = warp & 3;
     uint32_t spin = kGgSpin;
+    bool failed = false;
     int tcount = 0;
     const bool interleaved = NB == 1 && p.act.act != HQ_ACT_NONE;
     const int bank = NB == 2 ? (lane >> 4) : 0;
@@ -894,6 +897,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_ts_kernel(const Gr
       if (!mbar_wait_backoff(&acc_full[buf], (tcount / NBUF) & 1, spin)) {
         if (lane == 0) report_status(p.status, HQ_DEV_WAIT_TIMEOUT, 800 + buf);
         spin = 1;
+        failed = true;                 // nothing is stored once a wait has run out
       }
       tc_fence_after();
       const int n = t.n0 + frow;
@@ -907,7 +911,7 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_ts_kernel(const Gr
         sc = n_ok ? __ldg(ts + (int64_t)t.expert * p.fp8_nb + n / 128) : 0.f;
       }
       const int64_t out_n = interleaved ? (n >> 1) : n;
-      const bool writer = n_ok && (NB == 2 ? lane < 16 : (!interleaved || (n & 1) == 0));
+      const bool writer = n_ok && !failed && (NB == 2 ? lane < 16 : (!interleaved || (n & 1) == 0));
       const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * TN);
       const int* __restrict__ yrows = p.y_rows;
       auto row_of = [&](int cc) -> int {
