@@ -154,27 +154,45 @@ def gemv_cpu_step(threads, shapes, ws, xs):
     return time.perf_counter() - t0
 
 
-def decode_other_formats(torch, dev, peak_gbs):
+def decode_other_formats(torch, dev, peak_gbs, formats=("Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0", "MXFP4", "FP8"),
+                         n=65536, reps=8, ms=(1, 4)):
     """Decode mat-vec of the other weight formats on one 4096 -> 65536 projection (142 - 268 MB of weights: larger
-    than L2, so every launch streams them from HBM), M = 1 and 4: median isolated launch duration by CUDA events,
-    algorithmic GB/s and the fraction of the measured HBM peak."""
+    than L2, so every launch streams them from HBM), M = 1 and 4: median launch duration by CUDA events, algorithmic
+    GB/s and the fraction of the measured HBM peak.  A 256 MB fill is queued in front of every timed launch: it
+    evicts L2 and keeps the GPU busy while the host enqueues the launch, so the events bracket the kernel alone."""
     import engine_b200 as hq
     from tests import hq_synth as S
     gen = torch.Generator(device=dev)
     gen.manual_seed(2100)
-    n, k = 65536, 4096
+    k = 4096
     out = {}
-    for fmt in ("Q4_K", "Q6_K", "MXFP4", "FP8"):
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)
+
+    def ggml_bytes(block_bytes, weights_per_block, f16_at):
+        # any byte pattern is a valid block of these types; the f16 fields are set to 2^-11 (0x1000)
+        raw = torch.randint(0, 256, (n, k // weights_per_block, block_bytes), generator=gen, device=dev,
+                            dtype=torch.uint8)
+        for o in f16_at:
+            raw[:, :, o] = 0x00
+            raw[:, :, o + 1] = 0x10
+        return raw.reshape(n, -1)
+
+    for fmt in formats:
         if fmt == "Q4_K":
             layer = hq.GgufMatMul(S.q4k_bank(torch, 1, n, k, gen, dev)[0], "Q4_K", k)
             wbytes = n * (k // 256) * 144
         elif fmt == "Q6_K":
-            # any byte pattern is a valid Q6_K block; d (the last two bytes of a block) is set to a small f16
-            raw = torch.randint(0, 256, (n, k // 256, 210), generator=gen, device=dev, dtype=torch.uint8)
-            raw[:, :, 208] = 0x00
-            raw[:, :, 209] = 0x10            # f16 0x1000 = 2^-11
-            layer = hq.GgufMatMul(raw.reshape(n, -1), "Q6_K", k)
+            layer = hq.GgufMatMul(ggml_bytes(210, 256, (208,)), "Q6_K", k)
             wbytes = n * (k // 256) * 210
+        elif fmt == "Q5_K":
+            layer = hq.GgufMatMul(ggml_bytes(176, 256, (0, 2)), "Q5_K", k)
+            wbytes = n * (k // 256) * 176
+        elif fmt == "Q4_0":
+            layer = hq.GgufMatMul(ggml_bytes(18, 32, (0,)), "Q4_0", k)
+            wbytes = n * (k // 32) * 18
+        elif fmt == "Q5_0":
+            layer = hq.GgufMatMul(ggml_bytes(22, 32, (0,)), "Q5_0", k)
+            wbytes = n * (k // 32) * 22
         elif fmt == "MXFP4":
             b, sc = S.mxfp4_bank(torch, 1, n, k, gen, dev)
             layer = hq.MXFP4Layer(b[0], sc[0])
@@ -183,22 +201,23 @@ def decode_other_formats(torch, dev, peak_gbs):
             c, sc = S.fp8_bank(torch, 1, n, k, gen, dev)
             layer = hq.BlockwiseFP8Linear(c[0], sc[0])
             wbytes = n * k + (n // 128) * (k // 128) * 4
-        for m in (1, 4):
+        for m in ms:
             x = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
             ts = []
-            for r in range(8):
+            for r in range(reps):
                 a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 torch.cuda.synchronize()
+                flush.zero_()
                 a.record()
                 layer.forward_raw(x, torch.float32)
                 b_.record()
                 torch.cuda.synchronize()
                 ts.append(a.elapsed_time(b_))
             assert layer.device_status()[0] == 0
-            ms = statistics.median(ts[2:])
+            t_ms = statistics.median(ts[2:] if len(ts) > 4 else ts)
             nbytes = wbytes + m * k * 2 + m * n * 4
-            out[f"{fmt}_4096x65536_m{m}"] = {"us": round(ms * 1e3, 1), "gbs": round(nbytes / ms / 1e6, 1),
-                                              "frac": round(nbytes / ms / 1e6 / peak_gbs, 4)}
+            out[f"{fmt}_4096x{n}_m{m}"] = {"us": round(t_ms * 1e3, 1), "gbs": round(nbytes / t_ms / 1e6, 1),
+                                           "frac": round(nbytes / t_ms / 1e6 / peak_gbs, 4)}
         del layer
         torch.cuda.empty_cache()
     return out
@@ -1016,7 +1035,12 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="moe_fp8", choices=["gemv", "moe_q4k", "moe_fp8", "moe_mxfp4"])
+    ap.add_argument("--workload", default="moe_fp8",
+                    choices=["gemv", "moe_q4k", "moe_fp8", "moe_mxfp4", "decode_formats"])
+    ap.add_argument("--formats", default="", help="decode_formats: comma-separated weight formats (default: all)")
+    ap.add_argument("--rows", type=int, default=65536, help="decode_formats: output rows of the 4096 -> rows matrix")
+    ap.add_argument("--reps", type=int, default=8, help="decode_formats: timed launches per format and row count")
+    ap.add_argument("--m", default="1,4", help="decode_formats: activation row counts")
     ap.add_argument("--tokens", type=int, default=0, help="override the global token count of a MoE workload")
     ap.add_argument("--profiler-range", action="store_true",
                     help="MoE workloads: bracket the timed steps with cudaProfilerStart/Stop, so that a profiler "
@@ -1048,6 +1072,17 @@ def main():
         return
     if args.workload == "gemv":
         run_gemv(args)
+        return
+    if args.workload == "decode_formats":
+        # profiling aid, one GPU: the decode mat-vec record of the default line alone
+        import torch
+        dev = torch.device("cuda:0")
+        torch.cuda.set_device(dev)
+        peak = load_peaks()["hbm_gbs"]
+        kw = {"formats": tuple(args.formats.split(","))} if args.formats else {}
+        print(json.dumps({"workload": "decode_formats", "peak_gbs": peak,
+                          "decode": decode_other_formats(torch, dev, peak, n=args.rows, reps=args.reps,
+                                                         ms=tuple(int(v) for v in args.m.split(",")), **kw)}))
         return
     run_moe(args)
 

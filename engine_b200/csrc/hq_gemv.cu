@@ -570,10 +570,10 @@ int32_t launch_gemv(const GemvParams& p, int n_y_max, cudaStream_t stream) {
       if (max_rows <= 2 && p.k % 256 == 0 && p.n % 16 == 0) return launch_gemv_int8(p, n_y_max, max_rows, stream);
       return launch_cfg<HQ_FMT_FP8_BLOCK, 2048>(p, n_y_max, max_rows, stream);
     case HQ_FMT_MXFP4: return launch_cfg<HQ_FMT_MXFP4, 4096>(p, n_y_max, max_rows, stream);
-    case HQ_FMT_Q6_K: return launch_gemv_q6k(p, n_y_max, stream);
+    case HQ_FMT_Q6_K:
     case HQ_FMT_Q5_K:
     case HQ_FMT_Q4_0:
-    case HQ_FMT_Q5_0: return launch_gemv_ggml(p, n_y_max, stream);
+    case HQ_FMT_Q5_0: return launch_gemv_ggml_mma(p, n_y_max, stream);
     default: return HQ_ERR_FORMAT;
   }
 }

@@ -91,6 +91,21 @@ __device__ __forceinline__ void gemv_store_item(const GemvParams& p, const WorkI
   }
 }
 
+// ---- cp.async pieces of the kernels that stage weight rows through shared memory --------------------------------
+// The GGML block types start on 2-byte boundaries, too narrow for wide loads from global memory.  A warp instead
+// copies the aligned 16-byte pieces that cover a stretch of a row with cp.async (several stretches in flight), into
+// a buffer in which every byte keeps its address modulo 16, and picks the fields out of shared memory.  The first
+// and the last piece may hold up to 15 bytes that are not part of the stretch; they lie in the same aligned
+// 16-byte granule as a byte that is, so they are readable, and they are never looked at.
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 inline int sm_count() {
   static int cached[64] = {};
   int dev = 0;
@@ -103,11 +118,8 @@ inline int sm_count() {
   return cached[dev];
 }
 
-// the Q5_K / Q4_0 / Q5_0 decode kernel (hq_gemv_ggml.cu)
-int32_t launch_gemv_ggml(const GemvParams& p, int n_y_max, cudaStream_t stream);
-
-// the Q6_K decode kernel (hq_gemv_q6k.cu)
-int32_t launch_gemv_q6k(const GemvParams& p, int n_y_max, cudaStream_t stream);
+// the Q6_K / Q5_K / Q4_0 / Q5_0 decode kernel on warp MMAs (hq_gemv_ggml_mma.cu)
+int32_t launch_gemv_ggml_mma(const GemvParams& p, int n_y_max, cudaStream_t stream);
 
 // the Q8_0 / Q4_K decode kernel (hq_gemv_int8.cu)
 int32_t launch_gemv_int8(const GemvParams& p, int n_y_max, int max_rows, cudaStream_t stream);

@@ -42,7 +42,11 @@ def test_decode_rows_f32_out(fmt, m):
 
 @pytest.mark.parametrize("fmt,n,k", [("Q8_0", 4096, 4096), ("Q4_K", 4096, 4096), ("Q8_0", 1000, 14336),
                                      ("FP8", 2048, 7168), ("MXFP4", 5760, 2880), ("Q4_K", 2048, 768),
-                                     ("Q6_K", 2048, 768), ("Q6_K", 1000, 4096)])
+                                     ("Q6_K", 2048, 768), ("Q6_K", 1000, 4096),
+                                     # rows staged four 256-weight spans at a time: a last stretch of one span
+                                     # (K = 1280, 2304) and rows that start 2, 4, .. 14 bytes off a 16-byte boundary
+                                     ("Q6_K", 520, 1280), ("Q5_0", 520, 1280), ("Q4_0", 1000, 4096),
+                                     ("Q5_K", 520, 2304)])
 def test_model_shapes(fmt, n, k):
     got, want = run_case(fmt, n, k, 3, torch.bfloat16, torch.float32, 20, bias=(fmt == "MXFP4"))
     assert T.rel_l2(got, want) <= TOL[fmt]
