@@ -63,6 +63,19 @@ __device__ __forceinline__ void gm_mma(float (&d)[4], uint32_t a0, uint32_t a1, 
   }
 }
 
+// the first MMA of a block: D = A.B (the zero C operands cost no register moves)
+template <bool BF>
+__device__ __forceinline__ void gm_mma0(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  if (BF) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+  } else {
+    mma_f16_16816_c(d, a0, a1, a2, a3, b0, b1, 0.f, 0.f, 0.f, 0.f);
+  }
+}
+
 // The codes in bytes 2 pair and 2 pair + 1 of qq as f16x2 / bf16x2 of (code - ZERO): 0x64qq is 1024 + qq in f16,
 // 0x43qq is 128 + qq in bf16 (qq < 64), and the subtraction is exact.
 template <bool BF, int ZERO>
@@ -81,13 +94,15 @@ __device__ __forceinline__ uint32_t gm_ld32h(const uint8_t* p) {
   return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
 }
 
-// B fragment of one 16-weight group: the activations col .. col + 3 of this lane's activation row (none: zeros)
+// B fragment of one 16-weight group: four consecutive activations of this lane's activation row (none: zeros).
+// xq points at the lane's first activation of the span, `col` (a multiple of 4, known at compile time) counts on
+// from there, so the load takes an immediate offset.
 template <int XDT>
-__device__ __forceinline__ void gm_load_b(const char* xrow, int col, uint32_t& b0, uint32_t& b1, bool& clamped) {
+__device__ __forceinline__ void gm_load_b(const char* xq, int col, uint32_t& b0, uint32_t& b1, bool& clamped) {
   b0 = b1 = 0u;
-  if (xrow == nullptr) return;
+  if (xq == nullptr) return;
   if (XDT == HQ_DT_F32) {
-    const float4 v = __ldg(reinterpret_cast<const float4*>(xrow) + (col >> 2));
+    const float4 v = __ldg(reinterpret_cast<const float4*>(xq) + (col >> 2));
     float f[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -100,22 +115,23 @@ __device__ __forceinline__ void gm_load_b(const char* xrow, int col, uint32_t& b
     b0 = pack_half2(f[0], f[1]);
     b1 = pack_half2(f[2], f[3]);
   } else {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(xrow) + (col >> 2));
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(xq) + (col >> 2));
     b0 = v.x;
     b1 = v.y;
   }
 }
 
-// One 256-weight span of the rows g (block bytes at bA) and g + 8 (bB) against the activations from column col0 on.
+// One 256-weight span of the rows g (block bytes at bA) and g + 8 (bB) against the activations of the span; xq
+// points at activation 4 t of the span in this lane's activation row (nullptr: the lane feeds zeros).
 template <int FMT, bool BF, int XDT>
-__device__ __forceinline__ void gm_decode_span(float (&acc)[4], const uint8_t* bA, const uint8_t* bB,
-                                               const char* xrow, int col0, int t, bool& clamped) {
+__device__ __forceinline__ void gm_decode_span(float (&acc)[4], const uint8_t* bA, const uint8_t* bB, const char* xq,
+                                               int t, bool& clamped) {
   constexpr int Z = GmFmt<FMT>::ZERO;
   if (FMT == HQ_FMT_Q6_K) {
     // {ql[128], qh[64], int8 scales[16], f16 d}: the 16-weight group 8 h + 2 j + u holds the weights
     // 128 h + 32 j + 16 u + i: nibble j / 2 of ql[64 h + 32 (j % 2) + 16 u + i], bits 2 j of qh[32 h + 16 u + i]
-    const float dA = __half2float(*reinterpret_cast<const __half*>(bA + 208));
-    const float dB = __half2float(*reinterpret_cast<const __half*>(bB + 208));
+    // per group: span sum += scale * (codes . x), scale an int8; d multiplies the span sum once
+    float sp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -132,20 +148,26 @@ __device__ __forceinline__ void gm_decode_span(float (&acc)[4], const uint8_t* b
             const uint32_t qa = ((qlA >> (4 * jhi)) & 0x0F0F0F0Fu) | (((qhA >> (2 * j)) & 0x03030303u) << 4);
             const uint32_t qb = ((qlB >> (4 * jhi)) & 0x0F0F0F0Fu) | (((qhB >> (2 * j)) & 0x03030303u) << 4);
             uint32_t b0, b1;
-            gm_load_b<XDT>(xrow, col0 + 16 * s16 + 4 * t, b0, b1, clamped);
-            float blk[4] = {0.f, 0.f, 0.f, 0.f};
-            gm_mma<BF>(blk, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
-                       b0, b1);
-            const float sA = dA * (float)(int)(int8_t)bA[192 + s16];   // exact: f16 x int8
-            const float sB = dB * (float)(int)(int8_t)bB[192 + s16];
-            acc[0] = fmaf(sA, blk[0], acc[0]);
-            acc[1] = fmaf(sA, blk[1], acc[1]);
-            acc[2] = fmaf(sB, blk[2], acc[2]);
-            acc[3] = fmaf(sB, blk[3], acc[3]);
+            gm_load_b<XDT>(xq, 16 * s16, b0, b1, clamped);
+            float blk[4];
+            gm_mma0<BF>(blk, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1),
+                        gm_pair<BF, Z>(qb, 1), b0, b1);
+            const float sA = (float)(int)(int8_t)bA[192 + s16];
+            const float sB = (float)(int)(int8_t)bB[192 + s16];
+            sp[0] = fmaf(sA, blk[0], sp[0]);
+            sp[1] = fmaf(sA, blk[1], sp[1]);
+            sp[2] = fmaf(sB, blk[2], sp[2]);
+            sp[3] = fmaf(sB, blk[3], sp[3]);
           }
         }
       }
     }
+    const float dA = __half2float(*reinterpret_cast<const __half*>(bA + 208));
+    const float dB = __half2float(*reinterpret_cast<const __half*>(bB + 208));
+    acc[0] = fmaf(dA, sp[0], acc[0]);
+    acc[1] = fmaf(dA, sp[1], acc[1]);
+    acc[2] = fmaf(dB, sp[2], acc[2]);
+    acc[3] = fmaf(dB, sp[3], acc[3]);
   } else if (FMT == HQ_FMT_Q5_K) {
     // {f16 d, f16 dmin, scales[12], qh[32], qs[128]}: the 32-weight block j = 2 c + hi holds nibble hi of
     // qs[32 c + l] and bit j of qh[l], l = 0..31; value = d sc_j q - dmin m_j
@@ -183,16 +205,22 @@ __device__ __forceinline__ void gm_decode_span(float (&acc)[4], const uint8_t* b
           scB = ((hB.w >> (8 * jj)) & 0xFu) | (((hB.y >> (8 * jj + 6)) & 3u) << 4);
           mnB = ((hB.w >> (8 * jj + 4)) & 0xFu) | (((hB.z >> (8 * jj + 6)) & 3u) << 4);
         }
-        float bq[4] = {0.f, 0.f, 0.f, 0.f}, b1s[4] = {0.f, 0.f, 0.f, 0.f};
+        float bq[4], b1s[4];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const uint32_t qa = ((wA[u] >> (4 * hi)) & 0x0F0F0F0Fu) | (((qhA[u] >> j) & 0x01010101u) << 4);
           const uint32_t qb = ((wB[u] >> (4 * hi)) & 0x0F0F0F0Fu) | (((qhB[u] >> j) & 0x01010101u) << 4);
           uint32_t b0, b1;
-          gm_load_b<XDT>(xrow, col0 + 32 * j + 16 * u + 4 * t, b0, b1, clamped);
-          gm_mma<BF>(bq, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
-                     b0, b1);
-          gm_mma<BF>(b1s, ONE, ONE, ONE, ONE, b0, b1);               // sums of the activations, per column
+          gm_load_b<XDT>(xq, 32 * j + 16 * u, b0, b1, clamped);
+          if (u == 0) {
+            gm_mma0<BF>(bq, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
+                        b0, b1);
+            gm_mma0<BF>(b1s, ONE, ONE, ONE, ONE, b0, b1);            // sums of the activations, per column
+          } else {
+            gm_mma<BF>(bq, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
+                       b0, b1);
+            gm_mma<BF>(b1s, ONE, ONE, ONE, ONE, b0, b1);
+          }
         }
         const float sA = dA * (float)scA, sB = dB * (float)scB;       // exact
         const float oA = nA * (float)mnA, oB = nB * (float)mnB;
@@ -213,13 +241,16 @@ __device__ __forceinline__ void gm_decode_span(float (&acc)[4], const uint8_t* b
       const uint8_t* kB = bB + BB * b;
       const float dA = __half2float(*reinterpret_cast<const __half*>(kA));
       const float dB = __half2float(*reinterpret_cast<const __half*>(kB));
-      const uint32_t wA = gm_ld32h(kA + QS + 4 * t), wB = gm_ld32h(kB + QS + 4 * t);
+      // rows are 16-byte aligned, so the words of every other block (BB b + 2 a multiple of 4) are aligned
+      const bool AL = (BB * b + 2) % 4 == 0;                      // folded once the loop is unrolled
+      const uint32_t wA = AL ? *reinterpret_cast<const uint32_t*>(kA + QS + 4 * t) : gm_ld32h(kA + QS + 4 * t);
+      const uint32_t wB = AL ? *reinterpret_cast<const uint32_t*>(kB + QS + 4 * t) : gm_ld32h(kB + QS + 4 * t);
       uint32_t qhA = 0u, qhB = 0u;
       if (FMT == HQ_FMT_Q5_0) {
-        qhA = gm_ld32h(kA + 2) >> (4 * t);
-        qhB = gm_ld32h(kB + 2) >> (4 * t);
+        qhA = (AL ? *reinterpret_cast<const uint32_t*>(kA + 2) : gm_ld32h(kA + 2)) >> (4 * t);
+        qhB = (AL ? *reinterpret_cast<const uint32_t*>(kB + 2) : gm_ld32h(kB + 2)) >> (4 * t);
       }
-      float blk[4] = {0.f, 0.f, 0.f, 0.f};
+      float blk[4];
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t qa = (wA >> (4 * hf)) & 0x0F0F0F0Fu, qb = (wB >> (4 * hf)) & 0x0F0F0F0Fu;
@@ -229,9 +260,13 @@ __device__ __forceinline__ void gm_decode_span(float (&acc)[4], const uint8_t* b
           qb |= ((((qhB >> (16 * hf)) & 0xFu) * 0x00204081u) & 0x01010101u) << 4;
         }
         uint32_t b0, b1;
-        gm_load_b<XDT>(xrow, col0 + 32 * b + 16 * hf + 4 * t, b0, b1, clamped);
-        gm_mma<BF>(blk, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1), b0,
-                   b1);
+        gm_load_b<XDT>(xq, 32 * b + 16 * hf, b0, b1, clamped);
+        if (hf == 0)
+          gm_mma0<BF>(blk, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
+                      b0, b1);
+        else
+          gm_mma<BF>(blk, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
+                     b0, b1);
       }
       acc[0] = fmaf(dA, blk[0], acc[0]);
       acc[1] = fmaf(dA, blk[1], acc[1]);
@@ -330,8 +365,8 @@ __global__ void __launch_bounds__(kGmThreads, 2) gemv_ggml_mma_kernel(const Gemv
         const uint8_t* st = ring + cslot * STAGE;
         const int offA = (int)(reinterpret_cast<uintptr_t>(wbank[bank] + rowA + (int64_t)span * F::SPAN) & 15u);
         const int offB = (int)(reinterpret_cast<uintptr_t>(wbank[bank] + rowB + (int64_t)span * F::SPAN) & 15u);
-        gm_decode_span<FMT, BF, XDT>(acc[bank], st + g * F::PITCH + offA, st + (g + 8) * F::PITCH + offB, xrow,
-                                     256 * span, t, clamped);
+        gm_decode_span<FMT, BF, XDT>(acc[bank], st + g * F::PITCH + offA, st + (g + 8) * F::PITCH + offB,
+                                     xrow != nullptr ? xrow + (int64_t)(256 * span + 4 * t) * xsz : nullptr, t, clamped);
         __syncwarp();                                            // the stage is refilled two steps on
         cslot = cslot + 1 == kGmStages ? 0 : cslot + 1;
       }
@@ -371,6 +406,10 @@ static int32_t launch_gm(const GemvParams& p, unsigned grid, cudaStream_t stream
   if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
   if (dev >= 64 || !attr_done[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return HQ_ERR_CUDA;
+    // two CTAs per SM need the largest shared-memory carve-out; the activations only need a few KB of L1
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
+        cudaSuccess)
       return HQ_ERR_CUDA;
     if (dev < 64) attr_done[dev] = true;
   }
