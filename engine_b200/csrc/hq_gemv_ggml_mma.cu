@@ -26,12 +26,12 @@ namespace hq {
 
 constexpr int kGmWarps = 8;
 constexpr int kGmThreads = kGmWarps * 32;
-constexpr int kGmStages = 3;
+constexpr int kGmStages = 2;
 constexpr int kGmRows = 16;
 
 // SPAN: bytes per 256 weights; PITCH: distance of the rows in a stage (a multiple of 16 whose word count spreads the
-// eight row groups over the banks; Q6_K needs room for the up to 15 bytes in front of an unaligned row);
-// ZERO: the code's zero point.
+// eight row groups over the banks, with room for the up to 30 bytes between the 32-byte boundary a copy starts at
+// and the first byte of the span); ZERO: the code's zero point.
 template <int FMT>
 struct GmFmt;
 template <>
@@ -40,15 +40,15 @@ struct GmFmt<HQ_FMT_Q6_K> {
 };
 template <>
 struct GmFmt<HQ_FMT_Q5_K> {
-  static constexpr int SPAN = 176, PITCH = 176, ZERO = 0;
+  static constexpr int SPAN = 176, PITCH = 208, ZERO = 0;
 };
 template <>
 struct GmFmt<HQ_FMT_Q4_0> {
-  static constexpr int SPAN = 144, PITCH = 144, ZERO = 8;
+  static constexpr int SPAN = 144, PITCH = 176, ZERO = 8;
 };
 template <>
 struct GmFmt<HQ_FMT_Q5_0> {
-  static constexpr int SPAN = 176, PITCH = 176, ZERO = 16;
+  static constexpr int SPAN = 176, PITCH = 208, ZERO = 16;
 };
 
 template <bool BF>
@@ -282,7 +282,7 @@ constexpr int gm_smem_bytes() {
 }
 
 template <int FMT, int BANKS, int XDT>
-__global__ void __launch_bounds__(kGmThreads, 2) gemv_ggml_mma_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGmThreads, 3) gemv_ggml_mma_kernel(const GemvParams p) {
   using F = GmFmt<FMT>;
   constexpr bool BF = XDT == HQ_DT_BF16;
   constexpr int STAGE = kGmRows * F::PITCH;
@@ -316,9 +316,12 @@ __global__ void __launch_bounds__(kGmThreads, 2) gemv_ggml_mma_kernel(const Gemv
       const int n = min(iwi.n0 + r, p.n - 1);                    // rows past N repeat the last one; never stored
       const uint8_t* src =
           wbank[ibank] + (int64_t)iwi.expert * p.w_expert_stride + (int64_t)n * row_bytes + (int64_t)ispan * F::SPAN;
-      const int off = (int)(reinterpret_cast<uintptr_t>(src) & 15u);
+      // start at the 32-byte boundary: the two lanes of a row then ask for the two halves of one sector in the
+      // same instruction, and no sector crosses to the SM twice
+      const int off = (int)(reinterpret_cast<uintptr_t>(src) & 31u);
       src -= off;
       const int n16 = (off + F::SPAN + 15) >> 4;
+      static_assert(((30 + F::SPAN + 15) >> 4) * 16 <= F::PITCH, "a row's pieces must fit its pitch");
       const uint32_t dst = smem_u32(ring + islot * STAGE + r * F::PITCH);
       for (int i = lane & 1; i < n16; i += 2) cp_async16(dst + 16u * i, src + 16 * i);
       if (++ibank == BANKS) {
@@ -363,8 +366,8 @@ __global__ void __launch_bounds__(kGmThreads, 2) gemv_ggml_mma_kernel(const Gemv
         cp_async_wait<kGmStages - 1>();
         __syncwarp();
         const uint8_t* st = ring + cslot * STAGE;
-        const int offA = (int)(reinterpret_cast<uintptr_t>(wbank[bank] + rowA + (int64_t)span * F::SPAN) & 15u);
-        const int offB = (int)(reinterpret_cast<uintptr_t>(wbank[bank] + rowB + (int64_t)span * F::SPAN) & 15u);
+        const int offA = (int)(reinterpret_cast<uintptr_t>(wbank[bank] + rowA + (int64_t)span * F::SPAN) & 31u);
+        const int offB = (int)(reinterpret_cast<uintptr_t>(wbank[bank] + rowB + (int64_t)span * F::SPAN) & 31u);
         gm_decode_span<FMT, BF, XDT>(acc[bank], st + g * F::PITCH + offA, st + (g + 8) * F::PITCH + offB,
                                      xrow != nullptr ? xrow + (int64_t)(256 * span + 4 * t) * xsz : nullptr, t, clamped);
         __syncwarp();                                            // the stage is refilled two steps on
@@ -378,7 +381,7 @@ __global__ void __launch_bounds__(kGmThreads, 2) gemv_ggml_mma_kernel(const Gemv
 #pragma unroll
       for (int i = 0; i < 4; ++i) rb[((warp * BANKS + b) * 4 + i) * 32 + lane] = acc[b][i];
     __syncthreads();
-    if (warp == 0) {
+    if (warp == (item & (kGmWarps - 1))) {                       // the adding warp rotates, so none falls behind
       float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
       for (int b = 0; b < BANKS; ++b)
@@ -398,38 +401,44 @@ __global__ void __launch_bounds__(kGmThreads, 2) gemv_ggml_mma_kernel(const Gemv
 }
 
 template <int FMT, int BANKS, int XDT>
-static int32_t launch_gm(const GemvParams& p, unsigned grid, cudaStream_t stream) {
+static int32_t launch_gm(const GemvParams& p, int64_t items, cudaStream_t stream) {
   auto kern = gemv_ggml_mma_kernel<FMT, BANKS, XDT>;
   constexpr int smem = gm_smem_bytes<FMT, BANKS>();
-  static bool attr_done[64] = {};
+  static int ctas_per_sm[64] = {};                               // resident CTAs per SM, asked once per device
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return HQ_ERR_CUDA;
-  if (dev >= 64 || !attr_done[dev]) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return HQ_ERR_CUDA;
+  if (ctas_per_sm[dev] == 0) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return HQ_ERR_CUDA;
-    // two CTAs per SM need the largest shared-memory carve-out; the activations only need a few KB of L1
+    // several CTAs per SM need the largest shared-memory carve-out; the activations only need a few KB of L1
     if (cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
         cudaSuccess)
       return HQ_ERR_CUDA;
-    if (dev < 64) attr_done[dev] = true;
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kGmThreads, smem) != cudaSuccess || occ <= 0)
+      return HQ_ERR_CUDA;
+    ctas_per_sm[dev] = occ;
   }
+  // persistent: as many CTAs as stay resident, each walking the items with that stride
+  const int64_t cap = (int64_t)sm_count() * ctas_per_sm[dev];
+  const unsigned grid = (unsigned)(items < cap ? items : cap);
   kern<<<grid, kGmThreads, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? HQ_OK : HQ_ERR_CUDA;
 }
 
 template <int FMT, int BANKS>
-static int32_t launch_gm_x(const GemvParams& p, unsigned grid, cudaStream_t stream) {
+static int32_t launch_gm_x(const GemvParams& p, int64_t items, cudaStream_t stream) {
   switch (p.x_dtype) {
-    case HQ_DT_F32: return launch_gm<FMT, BANKS, HQ_DT_F32>(p, grid, stream);
-    case HQ_DT_F16: return launch_gm<FMT, BANKS, HQ_DT_F16>(p, grid, stream);
-    case HQ_DT_BF16: return launch_gm<FMT, BANKS, HQ_DT_BF16>(p, grid, stream);
+    case HQ_DT_F32: return launch_gm<FMT, BANKS, HQ_DT_F32>(p, items, stream);
+    case HQ_DT_F16: return launch_gm<FMT, BANKS, HQ_DT_F16>(p, items, stream);
+    case HQ_DT_BF16: return launch_gm<FMT, BANKS, HQ_DT_BF16>(p, items, stream);
     default: return HQ_ERR_FORMAT;
   }
 }
 
 template <int FMT>
-static int32_t launch_gm_fmt(const GemvParams& p, unsigned grid, cudaStream_t stream) {
-  return p.n_banks == 2 ? launch_gm_x<FMT, 2>(p, grid, stream) : launch_gm_x<FMT, 1>(p, grid, stream);
+static int32_t launch_gm_fmt(const GemvParams& p, int64_t items, cudaStream_t stream) {
+  return p.n_banks == 2 ? launch_gm_x<FMT, 2>(p, items, stream) : launch_gm_x<FMT, 1>(p, items, stream);
 }
 
 // Plain projection, or a gate and an up bank with a gated activation; an interleaved gate/up bank is not taken.
@@ -447,13 +456,11 @@ int32_t launch_gemv_ggml_mma(const GemvParams& p, int n_y_max, cudaStream_t stre
   }
   const int64_t items = (int64_t)n_y_max * ((p.n + kGmRows - 1) / kGmRows);
   if (items <= 0) return HQ_OK;
-  const int64_t cap = (int64_t)sm_count() * 2;                   // two CTAs per SM stay resident
-  const unsigned grid = (unsigned)(items < cap ? items : cap);
   switch (p.format) {
-    case HQ_FMT_Q6_K: return launch_gm_fmt<HQ_FMT_Q6_K>(p, grid, stream);
-    case HQ_FMT_Q5_K: return launch_gm_fmt<HQ_FMT_Q5_K>(p, grid, stream);
-    case HQ_FMT_Q4_0: return launch_gm_fmt<HQ_FMT_Q4_0>(p, grid, stream);
-    case HQ_FMT_Q5_0: return launch_gm_fmt<HQ_FMT_Q5_0>(p, grid, stream);
+    case HQ_FMT_Q6_K: return launch_gm_fmt<HQ_FMT_Q6_K>(p, items, stream);
+    case HQ_FMT_Q5_K: return launch_gm_fmt<HQ_FMT_Q5_K>(p, items, stream);
+    case HQ_FMT_Q4_0: return launch_gm_fmt<HQ_FMT_Q4_0>(p, items, stream);
+    case HQ_FMT_Q5_0: return launch_gm_fmt<HQ_FMT_Q5_0>(p, items, stream);
     default: return HQ_ERR_FORMAT;
   }
 }

@@ -98,7 +98,7 @@ __device__ __forceinline__ void gemv_store_item(const GemvParams& p, const WorkI
 // and the last piece may hold up to 15 bytes that are not part of the stretch; they lie in the same aligned
 // 16-byte granule as a byte that is, so they are readable, and they are never looked at.
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+  asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
