@@ -9,11 +9,12 @@
 // fragment of ones delivers in the same layout.  bf16 activations are multiplied as bf16 (nothing is converted or
 // rounded), f16 as f16, f32 activations are rounded to f16 (clamped to +-65504 and flagged beyond).
 //
-// One CTA of eight warps per work item of 16 output rows; the warps take the 256-weight spans of K in turn and
-// their partial sums are added in warp order by warp 0 (two buffers, one CTA barrier per item), so results are
-// bit-reproducible.  Each warp brings its spans in through a three-deep ring of cp.async stages (16 rows x one
-// span; aligned 16-byte pieces, since Q6_K rows start on 2-byte boundaries) that runs across work items, and picks
-// the fields out of shared memory: lane (g, t) decodes the four consecutive weights 4 t .. 4 t + 3 of a 16-weight
+// One CTA of eight warps per work item of 16 output rows (persistent, three CTAs per SM); the warps take the
+// 256-weight spans of K in turn and their partial sums are added in warp order by one warp (the warps take turns;
+// two buffers, one CTA barrier per item), so results are bit-reproducible.  Each warp brings its spans in through a
+// two-deep ring of cp.async stages (16 rows x one span; aligned 16-byte pieces from the 32-byte boundary below the
+// span on, since Q6_K rows start on 2-byte boundaries) that runs across work items, and picks the fields out of
+// shared memory: lane (g, t) decodes the four consecutive weights 4 t .. 4 t + 3 of a 16-weight
 // group for the rows g and g + 8 (the MMA's k index is permuted accordingly on both operands), i.e. one 32-bit
 // word of nibbles plus one of high bits.  Codes become f16 / bf16 by a byte permute into the mantissa of 1024 / 128
 // and one packed subtraction.  Activations are read straight from global memory (8 bytes per lane and group; they
