@@ -116,8 +116,9 @@ struct RawA {
   uint4 hdr;          // Q4_K: super-block header {d, dmin, 12 scale bytes}; Q8_0: .x = fifth payload word
   uint4 q;            // Q4_K: 16 nibble bytes; FP8: 16 codes; MXFP4: .x/.y = 8 nibble bytes; Q8_0: payload words
   uint32_t aux;       // FP8: relative block scale (f32 bits); MXFP4: e8m0 byte; Q8_0: d (f16 bits) | shift << 16
-  uint4 ext;          // Q6_K only: .x / .y = fifth word of the low-nibble / high-bit bytes, .z = d (f16 bits) |
-                      // scale byte << 16, .w = shifts (low-nibble bytes | high-bit bytes << 8)
+  uint4 ext;          // Q6_K: .x / .y = fifth word of the low-nibble / high-bit bytes, .z = d (f16 bits) |
+                      // scale byte << 16, .w = shifts (low-nibble bytes | high-bit bytes << 8); Q5_K: the 16 bytes
+                      // of fifth bits; Q5_0: .x = the 16 fifth bits of this half block
 };
 
 template <int FMT>
@@ -153,6 +154,27 @@ __device__ __forceinline__ void fetch_a(RawA& r, const uint8_t* row_base, const 
               ((uint32_t)__ldg(blk + 192 + 8 * h + 2 * j + sx) << 16);
     r.ext.w = (ml << 3) | (mh << 11);
     r.aux = (uint32_t)j;
+  } else if (FMT == HQ_FMT_Q5_K) {
+    // as Q4_K with 176-byte super-blocks {d, dmin, scales[12], qh[32], qs[128]}: quarter q of the 64 weights 64 c ..
+    // takes nibble q / 2 of qs[32 c + 16 (q % 2) + t] and bit 2 c + q / 2 of qh[16 (q % 2) + t]
+    const int sb = k0 >> 8, c = (k0 & 255) >> 6;
+    const uint8_t* blk = row_base + 176 * sb;
+    r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+    r.q = __ldg(reinterpret_cast<const uint4*>(blk + 48 + 32 * c + 16 * (q & 1)));
+    r.ext = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 16 * (q & 1)));
+  } else if (FMT == HQ_FMT_Q4_0 || FMT == HQ_FMT_Q5_0) {
+    // half a block of 32 {f16 d, [u32 qh,] qs[16]}: weight i < 16 is the low nibble of qs[i], weight i + 16 its high
+    // nibble, so both halves read the same 16 bytes.  Blocks start on 2-byte boundaries: aligned words, five when
+    // the bytes start in the middle of a word (the fifth then shares its word with the block's last bytes)
+    constexpr int BB = FMT == HQ_FMT_Q4_0 ? 18 : 22;
+    const uint8_t* blk = row_base + BB * ((k0 >> 5) + (q >> 1));
+    const uint8_t* pay = blk + (BB - 16);
+    const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(pay) & 2u);
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(pay - mis);
+    r.q = make_uint4(__ldg(wp), __ldg(wp + 1), __ldg(wp + 2), __ldg(wp + 3));
+    r.hdr.x = mis ? __ldg(wp + 4) : 0u;
+    r.aux = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk)) | (mis << 19) | ((uint32_t)(q & 1) << 24);
+    if (FMT == HQ_FMT_Q5_0) r.ext.x = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk + 2 + 2 * (q & 1)));
   } else if (FMT == HQ_FMT_Q8_0) {
     // half a 34-byte block: 16 int8 behind the block's f16 d.  Blocks start on 2-byte boundaries (rows on 4-byte
     // ones), so the payload is fetched as aligned words -- five when it starts in the middle of a word, in which
@@ -254,6 +276,69 @@ __device__ __forceinline__ void emit_q6_k(const RawA& r, uint32_t (&out)[8]) {
     uint32_t p23 = __byte_perm(w6, 0x64646464u, 0x4342);
     __half2 w01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), o2), ds2);
     __half2 w23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), o2), ds2);
+    out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
+    out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
+  }
+}
+
+// Q5_K: w = code * d1 - m1 as for Q4_K, the 5-bit code = nibble | fifth bit << 4.
+__device__ __forceinline__ void emit_q5_k(const RawA& r, int k0, int q, uint32_t (&out)[8]) {
+  const int c = (k0 & 255) >> 6;
+  const int hi = q >> 1;
+  const int j = 2 * c + hi;
+  uint32_t s, m;
+  if (j < 4) {
+    s = (r.hdr.y >> (8 * j)) & 63u;
+    m = (r.hdr.z >> (8 * j)) & 63u;
+  } else {
+    const int jj = j - 4;
+    s = ((r.hdr.w >> (8 * jj)) & 0xFu) | (((r.hdr.y >> (8 * jj + 6)) & 3u) << 4);
+    m = ((r.hdr.w >> (8 * jj + 4)) & 0xFu) | (((r.hdr.z >> (8 * jj + 6)) & 3u) << 4);
+  }
+  const float d1 = half_bits_to_float(r.hdr.x) * (float)s;
+  const float cc = -fmaf(1024.f, d1, half_bits_to_float(r.hdr.x >> 16) * (float)m);
+  const __half dh = __float2half_rn(d1), ch = __float2half_rn(cc);
+  const __half2 dh2 = __half2half2(dh), ch2 = __half2half2(ch);
+  const __half2 dl2 = __float2half2_rn(d1 - __half2float(dh));
+  const __half2 cl2 = __float2half2_rn(cc - __half2float(ch));
+  const uint32_t qw[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
+  const uint32_t hw[4] = {r.ext.x, r.ext.y, r.ext.z, r.ext.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t vm = ((hi ? (qw[i] >> 4) : qw[i]) & 0x0F0F0F0Fu) | (((hw[i] >> j) & 0x01010101u) << 4);
+    uint32_t p01 = __byte_perm(vm, 0x64646464u, 0x4140);   // f16 pair (1024 + e0, 1024 + e1)
+    uint32_t p23 = __byte_perm(vm, 0x64646464u, 0x4342);
+    const __half2 h01 = *reinterpret_cast<__half2*>(&p01), h23 = *reinterpret_cast<__half2*>(&p23);
+    __half2 w01 = __hadd2(__hfma2(h01, dh2, ch2), __hfma2(h01, dl2, cl2));
+    __half2 w23 = __hadd2(__hfma2(h23, dh2, ch2), __hfma2(h23, dl2, cl2));
+    out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
+    out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
+  }
+}
+
+// Q4_0: w = d * (q - 8); Q5_0: w = d * (q - 16) with q = nibble | fifth bit << 4.  The codes become the f16 pair
+// (1024 + q0, 1024 + q1) with one permute, 1024 + zero point is subtracted exactly, and the product with the block's
+// f16 d is rounded once to f16.
+template <int FMT>
+__device__ __forceinline__ void emit_q4_0_q5_0(const RawA& r, uint32_t (&out)[8]) {
+  const uint32_t sh = (r.aux >> 16) & 31u;           // 0 or 16
+  const uint32_t half = (r.aux >> 24) & 1u;
+  const uint32_t raw[5] = {r.q.x, r.q.y, r.q.z, r.q.w, r.hdr.x};
+  const uint32_t d16 = r.aux & 0xFFFFu;
+  const uint32_t dd = d16 | (d16 << 16);
+  const __half2 d2 = *reinterpret_cast<const __half2*>(&dd);
+  const uint32_t off = FMT == HQ_FMT_Q4_0 ? 0x64086408u : 0x64106410u;   // f16 1032 / 1040 twice
+  const __half2 o2 = *reinterpret_cast<const __half2*>(&off);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t w = __funnelshift_r(raw[i], raw[i + 1], sh);
+    uint32_t vm = (half ? (w >> 4) : w) & 0x0F0F0F0Fu;
+    if (FMT == HQ_FMT_Q5_0)   // four bits -> bit 4 of four bytes: x * 0x00204081 puts bit c of x at bit 8 c
+      vm |= ((((r.ext.x >> (4 * i)) & 0xFu) * 0x00204081u) & 0x01010101u) << 4;
+    uint32_t p01 = __byte_perm(vm, 0x64646464u, 0x4140);
+    uint32_t p23 = __byte_perm(vm, 0x64646464u, 0x4342);
+    __half2 w01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), o2), d2);
+    __half2 w23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), o2), d2);
     out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
     out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
   }
@@ -644,6 +729,10 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
             emit_q8_0(use[bank], v);
           } else if (FMT == HQ_FMT_Q6_K) {
             emit_q6_k(use[bank], v);
+          } else if (FMT == HQ_FMT_Q5_K) {
+            emit_q5_k(use[bank], k0, q, v);
+          } else if (FMT == HQ_FMT_Q4_0 || FMT == HQ_FMT_Q5_0) {
+            emit_q4_0_q5_0<FMT>(use[bank], v);
           } else {
             if (!emit_mxfp4(use[bank], v)) report_status(p.status, HQ_DEV_SCALE_RANGE, 600);
           }
@@ -1195,7 +1284,8 @@ static int32_t launch_gg_ts(const GroupedParams& p, int max_tiles, cudaStream_t 
 template <int FMT>
 static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t stream) {
   const bool two = p.w_up != nullptr;
-  if constexpr (FMT != HQ_FMT_Q8_0 && FMT != HQ_FMT_Q6_K) {       // Q8_0 and Q6_K have no tensor-memory variant
+  // only Q4_K, block-FP8 and MXFP4 have the variant that keeps the expanded weights in tensor memory
+  if constexpr (FMT == HQ_FMT_Q4_K || FMT == HQ_FMT_FP8_BLOCK || FMT == HQ_FMT_MXFP4) {
     if (p.tile_rows == 128 && p.weights_in_tmem)
       return two ? launch_gg_ts<FMT, 2>(p, max_tiles, stream) : launch_gg_ts<FMT, 1>(p, max_tiles, stream);
   }
@@ -1207,7 +1297,7 @@ static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t
 
 bool grouped_gemm_supported(int format, int64_t n, int64_t k) {
   if (format != HQ_FMT_Q4_K && format != HQ_FMT_FP8_BLOCK && format != HQ_FMT_MXFP4 && format != HQ_FMT_Q8_0 &&
-      format != HQ_FMT_Q6_K)
+      format != HQ_FMT_Q6_K && format != HQ_FMT_Q5_K && format != HQ_FMT_Q4_0 && format != HQ_FMT_Q5_0)
     return false;
   if (k % kTileK != 0) return false;
   if (format == HQ_FMT_FP8_BLOCK && (n % 128 != 0 || k % 128 != 0)) return false;
@@ -1229,6 +1319,15 @@ int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t 
       if ((reinterpret_cast<uintptr_t>(p.w) & 3u) != 0 || (p.w_up != nullptr && (reinterpret_cast<uintptr_t>(p.w_up) & 3u) != 0))
         return HQ_ERR_ALIGN;
       return launch_gg_fmt<HQ_FMT_Q6_K>(p, max_tiles, stream);
+    case HQ_FMT_Q5_K:
+    case HQ_FMT_Q4_0:
+    case HQ_FMT_Q5_0:
+      // rows are multiples of 16 bytes; the producers read 16-byte pieces (Q5_K) or aligned words (Q4_0 / Q5_0)
+      if ((reinterpret_cast<uintptr_t>(p.w) & 15u) != 0 || (p.w_up != nullptr && (reinterpret_cast<uintptr_t>(p.w_up) & 15u) != 0))
+        return HQ_ERR_ALIGN;
+      if (p.format == HQ_FMT_Q5_K) return launch_gg_fmt<HQ_FMT_Q5_K>(p, max_tiles, stream);
+      if (p.format == HQ_FMT_Q4_0) return launch_gg_fmt<HQ_FMT_Q4_0>(p, max_tiles, stream);
+      return launch_gg_fmt<HQ_FMT_Q5_0>(p, max_tiles, stream);
     default: return HQ_ERR_FORMAT;
   }
 }

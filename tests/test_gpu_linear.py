@@ -80,9 +80,34 @@ def test_q6_k_prefill_rows_on_the_tensor_cores(m, k):
 @pytest.mark.parametrize("fmt", ["Q5_K", "Q4_0", "Q5_0"])
 @pytest.mark.parametrize("dt", ["float32", "float16"])
 def test_further_ggml_types_any_row_count(fmt, dt):
-    # these types stay on the decode kernel for every row count (eight rows per work item); N = 1000 is not a
-    # multiple of the eight rows a CTA covers
+    # 21 rows: past the eight of a decode work item, so these go to the tensor-core GEMM; N = 1000 is not a multiple
+    # of its 128-row tiles
     got, want = run_case(fmt, 1000, 768, 21, getattr(torch, dt), torch.float32, 80)
+    assert T.rel_l2(got, want) <= 1e-3
+
+
+@pytest.mark.parametrize("fmt", ["Q5_K", "Q4_0", "Q5_0"])
+@pytest.mark.parametrize("m", [9, 130, 600])
+@pytest.mark.parametrize("k", [768, 2048])
+def test_further_ggml_types_prefill_rows_on_the_tensor_cores(fmt, m, k):
+    # the blocks are expanded to f16 by the producer warps (Q5_K: d sc q - dmin m in split f16 arithmetic; Q4_0 /
+    # Q5_0: (q - zero) x d rounded once) and multiplied by tcgen05; K = 768 gives Q4_0 / Q5_0 rows whose 18- / 22-byte
+    # blocks alternate between 4-byte aligned and 2 bytes off, both forms of the producers' word loads
+    got, want = run_case(fmt, 1000, k, m, torch.bfloat16, torch.float32, 90 + m)
+    assert T.rel_l2(got, want) <= 1e-3
+
+
+@pytest.mark.parametrize("fmt", ["Q6_K", "Q5_K", "Q4_0", "Q5_0"])
+def test_further_ggml_types_decode_kernel_beyond_eight_rows(fmt):
+    # with the tensor path switched off the decode kernel serves any row count, eight rows per work item
+    from engine_b200 import _lib as L
+    lib = L.lib()
+    old = lib.hq_config_get(L.CFG_DENSE_TENSOR_MIN_ROWS)
+    lib.hq_config_set(L.CFG_DENSE_TENSOR_MIN_ROWS, 1 << 40)
+    try:
+        got, want = run_case(fmt, 520, 1024, 21, torch.bfloat16, torch.float32, 95)
+    finally:
+        lib.hq_config_set(L.CFG_DENSE_TENSOR_MIN_ROWS, old)
     assert T.rel_l2(got, want) <= 1e-3
 
 

@@ -201,6 +201,15 @@ def test_moe_block_q6_k_gate_and_up(t):
     assert T.rel_l2(got, want) <= 1e-3
 
 
+@pytest.mark.parametrize("fmt", ["Q5_K", "Q4_0", "Q5_0"])
+@pytest.mark.parametrize("t", [3, 200])
+def test_moe_block_further_ggml_types(fmt, t):
+    # decode rows (the warp-MMA decode kernel) and prefill rows (the tcgen05 grouped GEMM: 200 tokens x top-2 over 4
+    # experts is 100 rows per expert)
+    got, want = _moe_case(fmt, t, 4, 2, 256, 256, False, L.ACT_SWIGLU, 40 + t)
+    assert T.rel_l2(got, want) <= 1e-3
+
+
 def test_moe_block_fp8_swiglu():
     got, want = _moe_case("FP8", 40, 8, 4, 512, 256, False, L.ACT_SWIGLU, 5)
     assert T.rel_l2(got, want) <= 2e-3
