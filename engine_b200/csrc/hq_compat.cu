@@ -334,6 +334,15 @@ HQ_PLAIN(launch_mmvq_gguf_q4_k_f32_plain, HQ_FMT_Q4_K, HQ_DT_F32)
 HQ_PLAIN(launch_mmvq_gguf_q6_k_bf16_plain, HQ_FMT_Q6_K, HQ_DT_BF16)
 HQ_PLAIN(launch_mmvq_gguf_q6_k_f16_plain, HQ_FMT_Q6_K, HQ_DT_F16)
 HQ_PLAIN(launch_mmvq_gguf_q6_k_f32_plain, HQ_FMT_Q6_K, HQ_DT_F32)
+HQ_PLAIN(launch_mmvq_gguf_q5_k_bf16_plain, HQ_FMT_Q5_K, HQ_DT_BF16)
+HQ_PLAIN(launch_mmvq_gguf_q5_k_f16_plain, HQ_FMT_Q5_K, HQ_DT_F16)
+HQ_PLAIN(launch_mmvq_gguf_q5_k_f32_plain, HQ_FMT_Q5_K, HQ_DT_F32)
+HQ_PLAIN(launch_mmvq_gguf_q4_0_bf16_plain, HQ_FMT_Q4_0, HQ_DT_BF16)
+HQ_PLAIN(launch_mmvq_gguf_q4_0_f16_plain, HQ_FMT_Q4_0, HQ_DT_F16)
+HQ_PLAIN(launch_mmvq_gguf_q4_0_f32_plain, HQ_FMT_Q4_0, HQ_DT_F32)
+HQ_PLAIN(launch_mmvq_gguf_q5_0_bf16_plain, HQ_FMT_Q5_0, HQ_DT_BF16)
+HQ_PLAIN(launch_mmvq_gguf_q5_0_f16_plain, HQ_FMT_Q5_0, HQ_DT_F16)
+HQ_PLAIN(launch_mmvq_gguf_q5_0_f32_plain, HQ_FMT_Q5_0, HQ_DT_F32)
 
 void launch_indexed_moe_forward_q4k_q8_1(const void* all_weights, const void* all_inputs, const uint32_t* indices,
                                          float* all_outputs, int32_t n, int32_t k, int32_t batch, int32_t topk,

@@ -56,7 +56,8 @@ def test_dispatch_and_reduce_shims():
     assert torch.equal(out16, hq.moe_weighted_reduce(y, w, torch.bfloat16))
 
 
-@pytest.mark.parametrize("fmt,sym", [("Q8_0", "q8_0"), ("Q4_K", "q4_k"), ("Q6_K", "q6_k")])
+@pytest.mark.parametrize("fmt,sym", [("Q8_0", "q8_0"), ("Q4_K", "q4_k"), ("Q6_K", "q6_k"), ("Q5_K", "q5_k"),
+                                     ("Q4_0", "q4_0"), ("Q5_0", "q5_0")])
 def test_q8_1_pair_runs_the_mat_vec_on_the_original_activations(fmt, sym):
     lib = _lib()
     rng = T.rng_for(7, 2)
