@@ -63,10 +63,10 @@ extern "C" {
 #define HQ_FMT_Q4_K 1       /* GGUF block_q4_K, 144 B / 256 weights                        */
 #define HQ_FMT_FP8_BLOCK 2  /* e4m3 codes [N,K] + f32 scale[ceil(N/128), ceil(K/128)]      */
 #define HQ_FMT_MXFP4 3      /* e2m1 nibbles [N,K/2] (low nibble = even k) + e8m0 [N,K/32]  */
-#define HQ_FMT_Q6_K 4       /* GGUF block_q6_K, 210 B / 256 weights (plain calls, or a gate and an up bank) */
-#define HQ_FMT_Q5_K 5       /* GGUF block_q5_K, 176 B / 256 weights   (formats 5-7: decode kernel for every row  */
-#define HQ_FMT_Q4_0 6       /* GGUF block_q4_0, 18 B / 32 weights      count, eight rows at a time; plain calls,  */
-#define HQ_FMT_Q5_0 7       /* GGUF block_q5_0, 22 B / 32 weights      or a gate and an up bank)                  */
+#define HQ_FMT_Q6_K 4       /* GGUF block_q6_K, 210 B / 256 weights   (formats 4-7: plain calls, or a gate and an */
+#define HQ_FMT_Q5_K 5       /* GGUF block_q5_K, 176 B / 256 weights    up bank with a gated activation; a decode   */
+#define HQ_FMT_Q4_0 6       /* GGUF block_q4_0, 18 B / 32 weights      kernel up to 8 rows, the tensor-core GEMM   */
+#define HQ_FMT_Q5_0 7       /* GGUF block_q5_0, 22 B / 32 weights      from HQ_CFG_*_TENSOR_MIN_ROWS rows on)      */
 
 /* element types of activations, outputs, biases */
 #define HQ_DT_F32 0
