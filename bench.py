@@ -154,10 +154,11 @@ def gemv_cpu_step(threads, shapes, ws, xs):
     return time.perf_counter() - t0
 
 
-def decode_other_formats(torch, dev, peak_gbs, formats=("Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0", "MXFP4", "FP8"),
+def decode_other_formats(torch, dev, peak_gbs,
+                         formats=("Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0", "Q4_1", "Q5_1", "Q2_K", "Q3_K", "MXFP4", "FP8"),
                          n=65536, reps=8, ms=(1, 4)):
-    """Decode mat-vec of the other weight formats on one 4096 -> 65536 projection (142 - 268 MB of weights: larger
-    than L2, so every launch streams them from HBM), M = 1 and 4: median launch duration by CUDA events, algorithmic
+    """Decode mat-vec of the other weight formats on one 4096 -> 65536 projection (88 - 268 MB of weights, streamed
+    from HBM by every launch: see the fill below), M = 1 and 4: median launch duration by CUDA events, algorithmic
     GB/s and the fraction of the measured HBM peak.  A 256 MB fill is queued in front of every timed launch: it
     evicts L2 and keeps the GPU busy while the host enqueues the launch, so the events bracket the kernel alone."""
     import engine_b200 as hq
@@ -193,6 +194,18 @@ def decode_other_formats(torch, dev, peak_gbs, formats=("Q4_K", "Q6_K", "Q5_K", 
         elif fmt == "Q5_0":
             layer = hq.GgufMatMul(ggml_bytes(22, 32, (0,)), "Q5_0", k)
             wbytes = n * (k // 32) * 22
+        elif fmt == "Q4_1":
+            layer = hq.GgufMatMul(ggml_bytes(20, 32, (0, 2)), "Q4_1", k)
+            wbytes = n * (k // 32) * 20
+        elif fmt == "Q5_1":
+            layer = hq.GgufMatMul(ggml_bytes(24, 32, (0, 2)), "Q5_1", k)
+            wbytes = n * (k // 32) * 24
+        elif fmt == "Q2_K":
+            layer = hq.GgufMatMul(ggml_bytes(84, 256, (80, 82)), "Q2_K", k)
+            wbytes = n * (k // 256) * 84
+        elif fmt == "Q3_K":
+            layer = hq.GgufMatMul(ggml_bytes(110, 256, (108,)), "Q3_K", k)
+            wbytes = n * (k // 256) * 110
         elif fmt == "MXFP4":
             b, sc = S.mxfp4_bank(torch, 1, n, k, gen, dev)
             layer = hq.MXFP4Layer(b[0], sc[0])

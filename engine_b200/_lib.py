@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(HERE, "libhanzoquant_b200.so")
 
 # codes (mirror include/hanzoquant_b200.h)
 FMT_Q8_0, FMT_Q4_K, FMT_FP8_BLOCK, FMT_MXFP4, FMT_Q6_K, FMT_Q5_K, FMT_Q4_0, FMT_Q5_0 = 0, 1, 2, 3, 4, 5, 6, 7
+FMT_Q4_1, FMT_Q5_1, FMT_Q2_K, FMT_Q3_K = 8, 9, 10, 11
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 SCORE_RAW, SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1, 2
 WEIGHT_SCORE, WEIGHT_SOFTMAX, WEIGHT_SIGMOID = 0, 1, 2

@@ -20,6 +20,10 @@ int64_t weight_row_bytes(int format, int64_t k) {
     case HQ_FMT_Q5_K: return k / 256 * 176;
     case HQ_FMT_Q4_0: return k / 32 * 18;
     case HQ_FMT_Q5_0: return k / 32 * 22;
+    case HQ_FMT_Q4_1: return k / 32 * 20;
+    case HQ_FMT_Q5_1: return k / 32 * 24;
+    case HQ_FMT_Q2_K: return k / 256 * 84;
+    case HQ_FMT_Q3_K: return k / 256 * 110;
     default: return -1;
   }
 }
@@ -35,6 +39,10 @@ int32_t check_weight(const hq_weight* w) {
     case HQ_FMT_Q5_K:
     case HQ_FMT_Q4_0:
     case HQ_FMT_Q5_0:
+    case HQ_FMT_Q4_1:
+    case HQ_FMT_Q5_1:
+    case HQ_FMT_Q2_K:
+    case HQ_FMT_Q3_K:
       if (w->k % 256 != 0) return HQ_ERR_SHAPE;
       break;
     case HQ_FMT_FP8_BLOCK:
@@ -49,8 +57,10 @@ int32_t check_weight(const hq_weight* w) {
       return HQ_ERR_FORMAT;
   }
   if (!aligned16(w->data)) return HQ_ERR_ALIGN;
-  // Q6_K rows (210 bytes per super-block) are only 2-byte aligned; its kernels read bytes and aligned words
-  if (w->format != HQ_FMT_Q6_K && weight_row_bytes(w->format, w->k) % 16 != 0) return HQ_ERR_ALIGN;
+  // Q6_K, Q3_K and Q2_K rows (210, 110, 84 bytes per super-block) are only 2- or 4-byte aligned; their kernels read
+  // 16-bit fields and aligned words
+  const bool narrow_rows = w->format == HQ_FMT_Q6_K || w->format == HQ_FMT_Q3_K || w->format == HQ_FMT_Q2_K;
+  if (!narrow_rows && weight_row_bytes(w->format, w->k) % 16 != 0) return HQ_ERR_ALIGN;
   if (w->bias != nullptr && !valid_dtype(w->bias_dtype)) return HQ_ERR_FORMAT;
   return HQ_OK;
 }

@@ -343,6 +343,18 @@ HQ_PLAIN(launch_mmvq_gguf_q4_0_f32_plain, HQ_FMT_Q4_0, HQ_DT_F32)
 HQ_PLAIN(launch_mmvq_gguf_q5_0_bf16_plain, HQ_FMT_Q5_0, HQ_DT_BF16)
 HQ_PLAIN(launch_mmvq_gguf_q5_0_f16_plain, HQ_FMT_Q5_0, HQ_DT_F16)
 HQ_PLAIN(launch_mmvq_gguf_q5_0_f32_plain, HQ_FMT_Q5_0, HQ_DT_F32)
+HQ_PLAIN(launch_mmvq_gguf_q4_1_bf16_plain, HQ_FMT_Q4_1, HQ_DT_BF16)
+HQ_PLAIN(launch_mmvq_gguf_q4_1_f16_plain, HQ_FMT_Q4_1, HQ_DT_F16)
+HQ_PLAIN(launch_mmvq_gguf_q4_1_f32_plain, HQ_FMT_Q4_1, HQ_DT_F32)
+HQ_PLAIN(launch_mmvq_gguf_q5_1_bf16_plain, HQ_FMT_Q5_1, HQ_DT_BF16)
+HQ_PLAIN(launch_mmvq_gguf_q5_1_f16_plain, HQ_FMT_Q5_1, HQ_DT_F16)
+HQ_PLAIN(launch_mmvq_gguf_q5_1_f32_plain, HQ_FMT_Q5_1, HQ_DT_F32)
+HQ_PLAIN(launch_mmvq_gguf_q2_k_bf16_plain, HQ_FMT_Q2_K, HQ_DT_BF16)
+HQ_PLAIN(launch_mmvq_gguf_q2_k_f16_plain, HQ_FMT_Q2_K, HQ_DT_F16)
+HQ_PLAIN(launch_mmvq_gguf_q2_k_f32_plain, HQ_FMT_Q2_K, HQ_DT_F32)
+HQ_PLAIN(launch_mmvq_gguf_q3_k_bf16_plain, HQ_FMT_Q3_K, HQ_DT_BF16)
+HQ_PLAIN(launch_mmvq_gguf_q3_k_f16_plain, HQ_FMT_Q3_K, HQ_DT_F16)
+HQ_PLAIN(launch_mmvq_gguf_q3_k_f32_plain, HQ_FMT_Q3_K, HQ_DT_F32)
 
 void launch_indexed_moe_forward_q4k_q8_1(const void* all_weights, const void* all_inputs, const uint32_t* indices,
                                          float* all_outputs, int32_t n, int32_t k, int32_t batch, int32_t topk,

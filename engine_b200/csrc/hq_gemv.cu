@@ -573,7 +573,11 @@ int32_t launch_gemv(const GemvParams& p, int n_y_max, cudaStream_t stream) {
     case HQ_FMT_Q6_K:
     case HQ_FMT_Q5_K:
     case HQ_FMT_Q4_0:
-    case HQ_FMT_Q5_0: return launch_gemv_ggml_mma(p, n_y_max, stream);
+    case HQ_FMT_Q5_0:
+    case HQ_FMT_Q4_1:
+    case HQ_FMT_Q5_1:
+    case HQ_FMT_Q2_K:
+    case HQ_FMT_Q3_K: return launch_gemv_ggml_mma(p, n_y_max, stream);
     default: return HQ_ERR_FORMAT;
   }
 }

@@ -1,12 +1,12 @@
 // Decode mat-vec (1..8 activation rows per work item, dense and expert-indexed) for the GGML types Q6_K, Q5_K,
-// Q4_0 and Q5_0 of the reference's decode list (hanzo-quant/src/gguf/fast_mmvq.rs:36-50; the reference multiplies
-// them with dp4a against Q8_1 activations, kernels/mmvq_gguf/mmvq_gguf.cu).
+// Q4_0, Q5_0, Q4_1, Q5_1, Q2_K and Q3_K of the reference's decode list (hanzo-quant/src/gguf/fast_mmvq.rs:36-50; the
+// reference multiplies them with dp4a against Q8_1 activations, kernels/mmvq_gguf/mmvq_gguf.cu).
 //
-// The codes of these types are small integers (6, 5, 4, 5 bits), exact in f16 and bf16, so the products run on the
+// The codes of these types are small integers (2 to 6 bits), exact in f16 and bf16, so the products run on the
 // warp MMA m16n8k16 with f32 accumulation: one MMA covers 16 output rows x 16 consecutive weights x 8 activation
 // rows, and the per-block factor (d * scale, or d) multiplies the f32 result of one (Q6_K) or two (32-weight blocks)
-// MMAs.  Q5_K's "- dmin * m" term uses the sum of the activations over the block, which a second MMA against a
-// fragment of ones delivers in the same layout.  bf16 activations are multiplied as bf16 (nothing is converted or
+// MMAs.  The additive term of Q5_K, Q2_K ("- dmin * m") and Q4_1 / Q5_1 ("+ m") uses the sum of the activations over
+// the block, which a second MMA against a fragment of ones delivers in the same layout.  bf16 activations are multiplied as bf16 (nothing is converted or
 // rounded), f16 as f16, f32 activations are rounded to f16 (clamped to +-65504 and flagged beyond).
 //
 // One CTA of eight warps per work item of 16 output rows (persistent, three CTAs per SM); the warps take the
@@ -20,7 +20,7 @@
 // and one packed subtraction.  Activations are read straight from global memory (8 bytes per lane and group; they
 // stay in L1).
 // HBM-bound by design; algorithmic bytes per launch = N*K*bits/8 + M*K*sizeof(x) + M*N*sizeof(y)
-// (bits: 6.5625, 5.5, 4.5, 5.5).
+// (bits: 6.5625, 5.5, 4.5, 5.5, 5, 6, 2.625, 3.4375).
 #include "hq_gemv_shared.cuh"
 
 namespace hq {
@@ -50,6 +50,22 @@ struct GmFmt<HQ_FMT_Q4_0> {
 template <>
 struct GmFmt<HQ_FMT_Q5_0> {
   static constexpr int SPAN = 176, PITCH = 208, ZERO = 16;
+};
+template <>
+struct GmFmt<HQ_FMT_Q4_1> {
+  static constexpr int SPAN = 160, PITCH = 208, ZERO = 0;
+};
+template <>
+struct GmFmt<HQ_FMT_Q5_1> {
+  static constexpr int SPAN = 192, PITCH = 240, ZERO = 0;
+};
+template <>
+struct GmFmt<HQ_FMT_Q2_K> {
+  static constexpr int SPAN = 84, PITCH = 144, ZERO = 0;
+};
+template <>
+struct GmFmt<HQ_FMT_Q3_K> {
+  static constexpr int SPAN = 110, PITCH = 144, ZERO = 4;
 };
 
 template <bool BF>
@@ -231,48 +247,152 @@ __device__ __forceinline__ void gm_decode_span(float (&acc)[4], const uint8_t* b
         acc[3] = fmaf(sB, bq[3], fmaf(-oB, b1s[3], acc[3]));
       }
     }
+  } else if (FMT == HQ_FMT_Q2_K) {
+    // {scales[16], qs[64], f16 d, f16 dmin}, 4-byte aligned: the 16-weight group 8 h + 2 j + u holds bits 2 j,
+    // 2 j + 1 of qs[32 h + 16 u + i]; value = d (s & 15) q - dmin (s >> 4) with s = scales[group]
+    const uint32_t hA = *reinterpret_cast<const uint32_t*>(bA + 80), hB = *reinterpret_cast<const uint32_t*>(bB + 80);
+    const float dA = half_bits_to_float(hA), nA = half_bits_to_float(hA >> 16);
+    const float dB = half_bits_to_float(hB), nB = half_bits_to_float(hB >> 16);
+    uint32_t scA[4], scB[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      scA[i] = *reinterpret_cast<const uint32_t*>(bA + 4 * i);
+      scB[i] = *reinterpret_cast<const uint32_t*>(bB + 4 * i);
+    }
+    constexpr uint32_t ONE = BF ? 0x3F803F80u : 0x3C003C00u;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t wA = *reinterpret_cast<const uint32_t*>(bA + 16 + 32 * h + 16 * u + 4 * t);
+        const uint32_t wB = *reinterpret_cast<const uint32_t*>(bB + 16 + 32 * h + 16 * u + 4 * t);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int s16 = 8 * h + 2 * j + u;
+          const uint32_t qa = (wA >> (2 * j)) & 0x03030303u, qb = (wB >> (2 * j)) & 0x03030303u;
+          uint32_t b0, b1;
+          gm_load_b<XDT>(xq, 16 * s16, b0, b1, clamped);
+          float bq[4], b1s[4];
+          gm_mma0<BF>(bq, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
+                      b0, b1);
+          gm_mma0<BF>(b1s, ONE, ONE, ONE, ONE, b0, b1);              // sums of the activations, per column
+          const uint32_t sa = (scA[s16 >> 2] >> (8 * (s16 & 3))) & 0xFFu, sb = (scB[s16 >> 2] >> (8 * (s16 & 3))) & 0xFFu;
+          const float sA = dA * (float)(sa & 15u), oA = nA * (float)(sa >> 4);      // exact
+          const float sB = dB * (float)(sb & 15u), oB = nB * (float)(sb >> 4);
+          acc[0] = fmaf(sA, bq[0], fmaf(-oA, b1s[0], acc[0]));
+          acc[1] = fmaf(sA, bq[1], fmaf(-oA, b1s[1], acc[1]));
+          acc[2] = fmaf(sB, bq[2], fmaf(-oB, b1s[2], acc[2]));
+          acc[3] = fmaf(sB, bq[3], fmaf(-oB, b1s[3], acc[3]));
+        }
+      }
+    }
+  } else if (FMT == HQ_FMT_Q3_K) {
+    // {hmask[32], qs[64], scales[12], f16 d}, 2-byte aligned: the 16-weight group 8 h + 2 j + u holds bits 2 j,
+    // 2 j + 1 of qs[32 h + 16 u + i] and, as third bit, bit 4 h + j of hmask[16 u + i]; value = d (scale - 32)
+    // (code - 4).  The sixteen 6-bit scales are unpacked four to a word as ggml does it.
+    uint32_t auxA[4], auxB[4];
+    {
+      const uint32_t a0 = gm_ld32h(bA + 96), a1 = gm_ld32h(bA + 100), tm = gm_ld32h(bA + 104);
+      auxA[0] = (a0 & 0x0F0F0F0Fu) | ((tm & 0x03030303u) << 4);
+      auxA[1] = (a1 & 0x0F0F0F0Fu) | (((tm >> 2) & 0x03030303u) << 4);
+      auxA[2] = ((a0 >> 4) & 0x0F0F0F0Fu) | (((tm >> 4) & 0x03030303u) << 4);
+      auxA[3] = ((a1 >> 4) & 0x0F0F0F0Fu) | (((tm >> 6) & 0x03030303u) << 4);
+      const uint32_t c0 = gm_ld32h(bB + 96), c1 = gm_ld32h(bB + 100), tn = gm_ld32h(bB + 104);
+      auxB[0] = (c0 & 0x0F0F0F0Fu) | ((tn & 0x03030303u) << 4);
+      auxB[1] = (c1 & 0x0F0F0F0Fu) | (((tn >> 2) & 0x03030303u) << 4);
+      auxB[2] = ((c0 >> 4) & 0x0F0F0F0Fu) | (((tn >> 4) & 0x03030303u) << 4);
+      auxB[3] = ((c1 >> 4) & 0x0F0F0F0Fu) | (((tn >> 6) & 0x03030303u) << 4);
+    }
+    float sp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const uint32_t hmA = gm_ld32h(bA + 16 * u + 4 * t), hmB = gm_ld32h(bB + 16 * u + 4 * t);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t wA = gm_ld32h(bA + 32 + 32 * h + 16 * u + 4 * t), wB = gm_ld32h(bB + 32 + 32 * h + 16 * u + 4 * t);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int s16 = 8 * h + 2 * j + u;
+          const uint32_t qa = ((wA >> (2 * j)) & 0x03030303u) | (((hmA >> (4 * h + j)) & 0x01010101u) << 2);
+          const uint32_t qb = ((wB >> (2 * j)) & 0x03030303u) | (((hmB >> (4 * h + j)) & 0x01010101u) << 2);
+          uint32_t b0, b1;
+          gm_load_b<XDT>(xq, 16 * s16, b0, b1, clamped);
+          float blk[4];
+          gm_mma0<BF>(blk, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
+                      b0, b1);
+          const float sA = (float)((int)((auxA[s16 >> 2] >> (8 * (s16 & 3))) & 0xFFu) - 32);
+          const float sB = (float)((int)((auxB[s16 >> 2] >> (8 * (s16 & 3))) & 0xFFu) - 32);
+          sp[0] = fmaf(sA, blk[0], sp[0]);
+          sp[1] = fmaf(sA, blk[1], sp[1]);
+          sp[2] = fmaf(sB, blk[2], sp[2]);
+          sp[3] = fmaf(sB, blk[3], sp[3]);
+        }
+      }
+    }
+    const float dA = __half2float(*reinterpret_cast<const __half*>(bA + 108));
+    const float dB = __half2float(*reinterpret_cast<const __half*>(bB + 108));
+    acc[0] = fmaf(dA, sp[0], acc[0]);
+    acc[1] = fmaf(dA, sp[1], acc[1]);
+    acc[2] = fmaf(dB, sp[2], acc[2]);
+    acc[3] = fmaf(dB, sp[3], acc[3]);
   } else {
-    // Q4_0 {f16 d, qs[16]} and Q5_0 {f16 d, u32 qh, qs[16]}: weight i < 16 is the low nibble of qs[i], weight
-    // i >= 16 the high nibble of qs[i - 16]; Q5_0's fifth bit of weight i is bit i of qh
-    constexpr int BB = FMT == HQ_FMT_Q4_0 ? 18 : 22;
-    constexpr int QS = FMT == HQ_FMT_Q4_0 ? 2 : 6;
+    // blocks of 32: Q4_0 {f16 d, qs[16]}, Q5_0 {f16 d, u32 qh, qs[16]}, Q4_1 {f16 d, f16 m, qs[16]}, Q5_1 {f16 d,
+    // f16 m, u32 qh, qs[16]}: weight i < 16 is the low nibble of qs[i], weight i >= 16 the high nibble of
+    // qs[i - 16]; the fifth bit of weight i is bit i of qh; value = d (q - zero) resp. d q + m
+    constexpr bool FIVE = FMT == HQ_FMT_Q5_0 || FMT == HQ_FMT_Q5_1;
+    constexpr bool MIN = FMT == HQ_FMT_Q4_1 || FMT == HQ_FMT_Q5_1;
+    constexpr int BB = 18 + (FIVE ? 4 : 0) + (MIN ? 2 : 0);
+    constexpr int QS = BB - 16;
+    constexpr int QH = MIN ? 4 : 2;
+    constexpr uint32_t ONE = BF ? 0x3F803F80u : 0x3C003C00u;
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
       const uint8_t* kA = bA + BB * b;
       const uint8_t* kB = bB + BB * b;
       const float dA = __half2float(*reinterpret_cast<const __half*>(kA));
       const float dB = __half2float(*reinterpret_cast<const __half*>(kB));
-      // rows are 16-byte aligned, so the words of every other block (BB b + 2 a multiple of 4) are aligned
-      const bool AL = (BB * b + 2) % 4 == 0;                      // folded once the loop is unrolled
+      // rows are 16-byte aligned, so the words of the blocks whose offset BB b + QS is a multiple of 4 are aligned
+      const bool AL = (BB * b + QS) % 4 == 0;                     // folded once the loop is unrolled
       const uint32_t wA = AL ? *reinterpret_cast<const uint32_t*>(kA + QS + 4 * t) : gm_ld32h(kA + QS + 4 * t);
       const uint32_t wB = AL ? *reinterpret_cast<const uint32_t*>(kB + QS + 4 * t) : gm_ld32h(kB + QS + 4 * t);
       uint32_t qhA = 0u, qhB = 0u;
-      if (FMT == HQ_FMT_Q5_0) {
-        qhA = (AL ? *reinterpret_cast<const uint32_t*>(kA + 2) : gm_ld32h(kA + 2)) >> (4 * t);
-        qhB = (AL ? *reinterpret_cast<const uint32_t*>(kB + 2) : gm_ld32h(kB + 2)) >> (4 * t);
+      if (FIVE) {
+        qhA = (AL ? *reinterpret_cast<const uint32_t*>(kA + QH) : gm_ld32h(kA + QH)) >> (4 * t);
+        qhB = (AL ? *reinterpret_cast<const uint32_t*>(kB + QH) : gm_ld32h(kB + QH)) >> (4 * t);
       }
-      float blk[4];
+      float blk[4], b1s[4];
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t qa = (wA >> (4 * hf)) & 0x0F0F0F0Fu, qb = (wB >> (4 * hf)) & 0x0F0F0F0Fu;
-        if (FMT == HQ_FMT_Q5_0) {
+        if (FIVE) {
           // four bits -> bit 4 of four bytes: x * 0x00204081 puts bit c of x at bit 8 c
           qa |= ((((qhA >> (16 * hf)) & 0xFu) * 0x00204081u) & 0x01010101u) << 4;
           qb |= ((((qhB >> (16 * hf)) & 0xFu) * 0x00204081u) & 0x01010101u) << 4;
         }
         uint32_t b0, b1;
         gm_load_b<XDT>(xq, 32 * b + 16 * hf, b0, b1, clamped);
-        if (hf == 0)
+        if (hf == 0) {
           gm_mma0<BF>(blk, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
                       b0, b1);
-        else
+          if (MIN) gm_mma0<BF>(b1s, ONE, ONE, ONE, ONE, b0, b1);     // sums of the activations, per column
+        } else {
           gm_mma<BF>(blk, gm_pair<BF, Z>(qa, 0), gm_pair<BF, Z>(qb, 0), gm_pair<BF, Z>(qa, 1), gm_pair<BF, Z>(qb, 1),
                      b0, b1);
+          if (MIN) gm_mma<BF>(b1s, ONE, ONE, ONE, ONE, b0, b1);
+        }
       }
       acc[0] = fmaf(dA, blk[0], acc[0]);
       acc[1] = fmaf(dA, blk[1], acc[1]);
       acc[2] = fmaf(dB, blk[2], acc[2]);
       acc[3] = fmaf(dB, blk[3], acc[3]);
+      if (MIN) {
+        const float mA = __half2float(*reinterpret_cast<const __half*>(kA + 2));
+        const float mB = __half2float(*reinterpret_cast<const __half*>(kB + 2));
+        acc[0] = fmaf(mA, b1s[0], acc[0]);
+        acc[1] = fmaf(mA, b1s[1], acc[1]);
+        acc[2] = fmaf(mB, b1s[2], acc[2]);
+        acc[3] = fmaf(mB, b1s[3], acc[3]);
+      }
     }
   }
 }
@@ -451,7 +571,12 @@ int32_t launch_gemv_ggml_mma(const GemvParams& p, int n_y_max, cudaStream_t stre
   if (p.n_banks == 2 && p.act.act == HQ_ACT_NONE) return HQ_ERR_FORMAT;
   const int esz = dtype_size(p.x_dtype);
   if ((reinterpret_cast<uintptr_t>(p.x) & 15u) != 0 || (p.x_stride * esz) % 16 != 0) return HQ_ERR_ALIGN;
-  if (p.format != HQ_FMT_Q6_K) {
+  // Q6_K and Q3_K blocks are picked apart with 16-bit loads; Q2_K blocks need 4-byte alignment (any K does, from an
+  // aligned tensor); the other types rely on 16-byte aligned rows
+  if (p.format == HQ_FMT_Q2_K) {
+    if ((reinterpret_cast<uintptr_t>(p.w) & 3u) != 0 || p.w_expert_stride % 4 != 0) return HQ_ERR_ALIGN;
+    if (p.n_banks == 2 && (reinterpret_cast<uintptr_t>(p.w_up) & 3u) != 0) return HQ_ERR_ALIGN;
+  } else if (p.format != HQ_FMT_Q6_K && p.format != HQ_FMT_Q3_K) {
     if ((reinterpret_cast<uintptr_t>(p.w) & 15u) != 0 || p.w_expert_stride % 16 != 0) return HQ_ERR_ALIGN;
     if (p.n_banks == 2 && (reinterpret_cast<uintptr_t>(p.w_up) & 15u) != 0) return HQ_ERR_ALIGN;
   }
@@ -462,6 +587,10 @@ int32_t launch_gemv_ggml_mma(const GemvParams& p, int n_y_max, cudaStream_t stre
     case HQ_FMT_Q5_K: return launch_gm_fmt<HQ_FMT_Q5_K>(p, items, stream);
     case HQ_FMT_Q4_0: return launch_gm_fmt<HQ_FMT_Q4_0>(p, items, stream);
     case HQ_FMT_Q5_0: return launch_gm_fmt<HQ_FMT_Q5_0>(p, items, stream);
+    case HQ_FMT_Q4_1: return launch_gm_fmt<HQ_FMT_Q4_1>(p, items, stream);
+    case HQ_FMT_Q5_1: return launch_gm_fmt<HQ_FMT_Q5_1>(p, items, stream);
+    case HQ_FMT_Q2_K: return launch_gm_fmt<HQ_FMT_Q2_K>(p, items, stream);
+    case HQ_FMT_Q3_K: return launch_gm_fmt<HQ_FMT_Q3_K>(p, items, stream);
     default: return HQ_ERR_FORMAT;
   }
 }

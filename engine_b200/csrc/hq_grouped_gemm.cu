@@ -118,7 +118,8 @@ struct RawA {
   uint32_t aux;       // FP8: relative block scale (f32 bits); MXFP4: e8m0 byte; Q8_0: d (f16 bits) | shift << 16
   uint4 ext;          // Q6_K: .x / .y = fifth word of the low-nibble / high-bit bytes, .z = d (f16 bits) |
                       // scale byte << 16, .w = shifts (low-nibble bytes | high-bit bytes << 8); Q5_K: the 16 bytes
-                      // of fifth bits; Q5_0: .x = the 16 fifth bits of this half block
+                      // of fifth bits; Q5_0 / Q5_1: .x = the 16 fifth bits of this half block; Q3_K: as Q6_K with
+                      // the code words in q and the hmask words in hdr, .z = d | 6-bit scale << 16
 };
 
 template <int FMT>
@@ -162,11 +163,13 @@ __device__ __forceinline__ void fetch_a(RawA& r, const uint8_t* row_base, const 
     r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
     r.q = __ldg(reinterpret_cast<const uint4*>(blk + 48 + 32 * c + 16 * (q & 1)));
     r.ext = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 16 * (q & 1)));
-  } else if (FMT == HQ_FMT_Q4_0 || FMT == HQ_FMT_Q5_0) {
-    // half a block of 32 {f16 d, [u32 qh,] qs[16]}: weight i < 16 is the low nibble of qs[i], weight i + 16 its high
-    // nibble, so both halves read the same 16 bytes.  Blocks start on 2-byte boundaries: aligned words, five when
-    // the bytes start in the middle of a word (the fifth then shares its word with the block's last bytes)
-    constexpr int BB = FMT == HQ_FMT_Q4_0 ? 18 : 22;
+  } else if (FMT == HQ_FMT_Q4_0 || FMT == HQ_FMT_Q5_0 || FMT == HQ_FMT_Q4_1 || FMT == HQ_FMT_Q5_1) {
+    // half a block of 32 {f16 d, [f16 m,] [u32 qh,] qs[16]}: weight i < 16 is the low nibble of qs[i], weight i + 16
+    // its high nibble, so both halves read the same 16 bytes.  Blocks start on 2-byte boundaries: aligned words, five
+    // when the bytes start in the middle of a word (the fifth then shares its word with the block's last bytes)
+    constexpr bool FIVE = FMT == HQ_FMT_Q5_0 || FMT == HQ_FMT_Q5_1;
+    constexpr bool MIN = FMT == HQ_FMT_Q4_1 || FMT == HQ_FMT_Q5_1;
+    constexpr int BB = 18 + (FIVE ? 4 : 0) + (MIN ? 2 : 0);
     const uint8_t* blk = row_base + BB * ((k0 >> 5) + (q >> 1));
     const uint8_t* pay = blk + (BB - 16);
     const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(pay) & 2u);
@@ -174,7 +177,41 @@ __device__ __forceinline__ void fetch_a(RawA& r, const uint8_t* row_base, const 
     r.q = make_uint4(__ldg(wp), __ldg(wp + 1), __ldg(wp + 2), __ldg(wp + 3));
     r.hdr.x = mis ? __ldg(wp + 4) : 0u;
     r.aux = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk)) | (mis << 19) | ((uint32_t)(q & 1) << 24);
-    if (FMT == HQ_FMT_Q5_0) r.ext.x = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk + 2 + 2 * (q & 1)));
+    if (MIN) r.hdr.y = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk + 2));
+    if (FIVE) r.ext.x = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk + (MIN ? 4 : 2) + 2 * (q & 1)));
+  } else if (FMT == HQ_FMT_Q2_K) {
+    // 16 consecutive k of an 84-byte super-block {scales[16], qs[64], d, dmin} (4-byte aligned): position
+    // 128 h + 32 j + 16 u + t takes bits 2 j, 2 j + 1 of qs[32 h + 16 u + t], group 8 h + 2 j + u
+    const int pos = (k0 & 255) + 16 * q;
+    const int h = pos >> 7, j = (pos >> 5) & 3, u = (pos >> 4) & 1;
+    const uint8_t* blk = row_base + 84 * (k0 >> 8);
+    const uint32_t* wq = reinterpret_cast<const uint32_t*>(blk + 16 + 32 * h + 16 * u);
+    r.q = make_uint4(__ldg(wq), __ldg(wq + 1), __ldg(wq + 2), __ldg(wq + 3));
+    r.hdr.x = __ldg(reinterpret_cast<const uint32_t*>(blk + 80));
+    r.aux = (uint32_t)__ldg(blk + 8 * h + 2 * j + u) | ((uint32_t)j << 8);
+  } else if (FMT == HQ_FMT_Q3_K) {
+    // 16 consecutive k of a 110-byte super-block {hmask[32], qs[64], scales[12], d} (2-byte aligned, words fetched
+    // as for Q6_K): position 128 h + 32 j + 16 u + t takes bits 2 j, 2 j + 1 of qs[32 h + 16 u + t] and bit 4 h + j
+    // of hmask[16 u + t]; the 6-bit scale of group 4 a + b = 8 h + 2 j + u is a nibble of byte 4 (a % 2) + b (low for
+    // a < 2) with bits 2 a, 2 a + 1 of byte 8 + b on top
+    const int pos = (k0 & 255) + 16 * q;
+    const int h = pos >> 7, j = (pos >> 5) & 3, u = (pos >> 4) & 1;
+    const uint8_t* blk = row_base + 110 * (k0 >> 8);
+    const uint8_t* pl = blk + 32 + 32 * h + 16 * u;
+    const uint8_t* ph = blk + 16 * u;
+    const uint32_t ml = (uint32_t)(reinterpret_cast<uintptr_t>(pl) & 2u), mh = (uint32_t)(reinterpret_cast<uintptr_t>(ph) & 2u);
+    const uint32_t* wl = reinterpret_cast<const uint32_t*>(pl - ml);
+    const uint32_t* wh = reinterpret_cast<const uint32_t*>(ph - mh);
+    r.q = make_uint4(__ldg(wl), __ldg(wl + 1), __ldg(wl + 2), __ldg(wl + 3));
+    r.hdr = make_uint4(__ldg(wh), __ldg(wh + 1), __ldg(wh + 2), __ldg(wh + 3));
+    r.ext.x = ml ? __ldg(wl + 4) : 0u;
+    r.ext.y = mh ? __ldg(wh + 4) : 0u;
+    const int s16 = 8 * h + 2 * j + u, a = s16 >> 2, b = s16 & 3;
+    const uint32_t nib = __ldg(blk + 96 + 4 * (a & 1) + b), top = __ldg(blk + 104 + b);
+    const uint32_t sc6 = (a < 2 ? (nib & 15u) : (nib >> 4)) | (((top >> (2 * a)) & 3u) << 4);
+    r.ext.z = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(blk + 108)) | (sc6 << 16);
+    r.ext.w = (ml << 3) | (mh << 11);
+    r.aux = (uint32_t)j | ((uint32_t)(4 * h + j) << 8);
   } else if (FMT == HQ_FMT_Q8_0) {
     // half a 34-byte block: 16 int8 behind the block's f16 d.  Blocks start on 2-byte boundaries (rows on 4-byte
     // ones), so the payload is fetched as aligned words -- five when it starts in the middle of a word, in which
@@ -316,29 +353,82 @@ __device__ __forceinline__ void emit_q5_k(const RawA& r, int k0, int q, uint32_t
   }
 }
 
-// Q4_0: w = d * (q - 8); Q5_0: w = d * (q - 16) with q = nibble | fifth bit << 4.  The codes become the f16 pair
-// (1024 + q0, 1024 + q1) with one permute, 1024 + zero point is subtracted exactly, and the product with the block's
-// f16 d is rounded once to f16.
+// Q4_0: w = d * (q - 8); Q5_0: w = d * (q - 16); Q4_1 / Q5_1: w = d * q + m; q = nibble [| fifth bit << 4].  The
+// codes become the f16 pair (1024 + q0, 1024 + q1) with one permute, 1024 + zero point is subtracted exactly, and the
+// product with the block's f16 d (plus m, in one fused multiply-add) is rounded once to f16.
 template <int FMT>
 __device__ __forceinline__ void emit_q4_0_q5_0(const RawA& r, uint32_t (&out)[8]) {
+  constexpr bool FIVE = FMT == HQ_FMT_Q5_0 || FMT == HQ_FMT_Q5_1;
+  constexpr bool MIN = FMT == HQ_FMT_Q4_1 || FMT == HQ_FMT_Q5_1;
   const uint32_t sh = (r.aux >> 16) & 31u;           // 0 or 16
   const uint32_t half = (r.aux >> 24) & 1u;
   const uint32_t raw[5] = {r.q.x, r.q.y, r.q.z, r.q.w, r.hdr.x};
   const uint32_t d16 = r.aux & 0xFFFFu;
   const uint32_t dd = d16 | (d16 << 16);
   const __half2 d2 = *reinterpret_cast<const __half2*>(&dd);
-  const uint32_t off = FMT == HQ_FMT_Q4_0 ? 0x64086408u : 0x64106410u;   // f16 1032 / 1040 twice
+  const uint32_t m16 = MIN ? (r.hdr.y & 0xFFFFu) : 0u;
+  const uint32_t mm = m16 | (m16 << 16);
+  const __half2 m2 = *reinterpret_cast<const __half2*>(&mm);
+  const uint32_t off = MIN ? 0x64006400u : (FMT == HQ_FMT_Q4_0 ? 0x64086408u : 0x64106410u);   // f16 1024 + zero, twice
   const __half2 o2 = *reinterpret_cast<const __half2*>(&off);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const uint32_t w = __funnelshift_r(raw[i], raw[i + 1], sh);
     uint32_t vm = (half ? (w >> 4) : w) & 0x0F0F0F0Fu;
-    if (FMT == HQ_FMT_Q5_0)   // four bits -> bit 4 of four bytes: x * 0x00204081 puts bit c of x at bit 8 c
+    if (FIVE)   // four bits -> bit 4 of four bytes: x * 0x00204081 puts bit c of x at bit 8 c
       vm |= ((((r.ext.x >> (4 * i)) & 0xFu) * 0x00204081u) & 0x01010101u) << 4;
     uint32_t p01 = __byte_perm(vm, 0x64646464u, 0x4140);
     uint32_t p23 = __byte_perm(vm, 0x64646464u, 0x4342);
-    __half2 w01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), o2), d2);
-    __half2 w23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), o2), d2);
+    const __half2 q01 = __hsub2(*reinterpret_cast<__half2*>(&p01), o2), q23 = __hsub2(*reinterpret_cast<__half2*>(&p23), o2);
+    __half2 w01 = MIN ? __hfma2(q01, d2, m2) : __hmul2(q01, d2);
+    __half2 w23 = MIN ? __hfma2(q23, d2, m2) : __hmul2(q23, d2);
+    out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
+    out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
+  }
+}
+
+// Q2_K: w = code * d1 - m1 with d1 = d * (s & 15), m1 = dmin * (s >> 4), in the split f16 arithmetic of emit_q4_k.
+__device__ __forceinline__ void emit_q2_k(const RawA& r, uint32_t (&out)[8]) {
+  const uint32_t j = (r.aux >> 8) & 3u, sc = r.aux & 0xFFu;
+  const float d1 = half_bits_to_float(r.hdr.x) * (float)(sc & 15u);
+  const float cc = -fmaf(1024.f, d1, half_bits_to_float(r.hdr.x >> 16) * (float)(sc >> 4));
+  const __half dh = __float2half_rn(d1), ch = __float2half_rn(cc);
+  const __half2 dh2 = __half2half2(dh), ch2 = __half2half2(ch);
+  const __half2 dl2 = __float2half2_rn(d1 - __half2float(dh));
+  const __half2 cl2 = __float2half2_rn(cc - __half2float(ch));
+  const uint32_t qw[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t vm = (qw[i] >> (2 * j)) & 0x03030303u;
+    uint32_t p01 = __byte_perm(vm, 0x64646464u, 0x4140);   // f16 pair (1024 + e0, 1024 + e1)
+    uint32_t p23 = __byte_perm(vm, 0x64646464u, 0x4342);
+    const __half2 h01 = *reinterpret_cast<__half2*>(&p01), h23 = *reinterpret_cast<__half2*>(&p23);
+    __half2 w01 = __hadd2(__hfma2(h01, dh2, ch2), __hfma2(h01, dl2, cl2));
+    __half2 w23 = __hadd2(__hfma2(h23, dh2, ch2), __hfma2(h23, dl2, cl2));
+    out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
+    out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
+  }
+}
+
+// Q3_K: w = d * (scale - 32) * (q - 4), q = two code bits | hmask bit << 2: as emit_q6_k with 1028 subtracted.
+__device__ __forceinline__ void emit_q3_k(const RawA& r, uint32_t (&out)[8]) {
+  const uint32_t shl = r.ext.w & 31u, shh = (r.ext.w >> 8) & 31u;   // 0 or 16
+  const uint32_t j = r.aux & 3u, hbit = (r.aux >> 8) & 7u;
+  const uint32_t lo[5] = {r.q.x, r.q.y, r.q.z, r.q.w, r.ext.x};
+  const uint32_t hi[5] = {r.hdr.x, r.hdr.y, r.hdr.z, r.hdr.w, r.ext.y};
+  const float ds = half_bits_to_float(r.ext.z & 0xFFFFu) * (float)((int)((r.ext.z >> 16) & 0xFFu) - 32);
+  const __half2 ds2 = __float2half2_rn(ds);
+  const uint32_t off = 0x64046404u;                  // f16 1028 twice
+  const __half2 o2 = *reinterpret_cast<const __half2*>(&off);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lw = __funnelshift_r(lo[i], lo[i + 1], shl);
+    const uint32_t hw = __funnelshift_r(hi[i], hi[i + 1], shh);
+    const uint32_t w3 = ((lw >> (2 * j)) & 0x03030303u) | (((hw >> hbit) & 0x01010101u) << 2);
+    uint32_t p01 = __byte_perm(w3, 0x64646464u, 0x4140);
+    uint32_t p23 = __byte_perm(w3, 0x64646464u, 0x4342);
+    __half2 w01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p01), o2), ds2);
+    __half2 w23 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p23), o2), ds2);
     out[2 * i] = *reinterpret_cast<uint32_t*>(&w01);
     out[2 * i + 1] = *reinterpret_cast<uint32_t*>(&w23);
   }
@@ -731,8 +821,12 @@ __global__ void __launch_bounds__(kGgThreads, 1) grouped_gemm_kernel(const Group
             emit_q6_k(use[bank], v);
           } else if (FMT == HQ_FMT_Q5_K) {
             emit_q5_k(use[bank], k0, q, v);
-          } else if (FMT == HQ_FMT_Q4_0 || FMT == HQ_FMT_Q5_0) {
+          } else if (FMT == HQ_FMT_Q4_0 || FMT == HQ_FMT_Q5_0 || FMT == HQ_FMT_Q4_1 || FMT == HQ_FMT_Q5_1) {
             emit_q4_0_q5_0<FMT>(use[bank], v);
+          } else if (FMT == HQ_FMT_Q2_K) {
+            emit_q2_k(use[bank], v);
+          } else if (FMT == HQ_FMT_Q3_K) {
+            emit_q3_k(use[bank], v);
           } else {
             if (!emit_mxfp4(use[bank], v)) report_status(p.status, HQ_DEV_SCALE_RANGE, 600);
           }
@@ -1297,7 +1391,8 @@ static int32_t launch_gg_fmt(const GroupedParams& p, int max_tiles, cudaStream_t
 
 bool grouped_gemm_supported(int format, int64_t n, int64_t k) {
   if (format != HQ_FMT_Q4_K && format != HQ_FMT_FP8_BLOCK && format != HQ_FMT_MXFP4 && format != HQ_FMT_Q8_0 &&
-      format != HQ_FMT_Q6_K && format != HQ_FMT_Q5_K && format != HQ_FMT_Q4_0 && format != HQ_FMT_Q5_0)
+      format != HQ_FMT_Q6_K && format != HQ_FMT_Q5_K && format != HQ_FMT_Q4_0 && format != HQ_FMT_Q5_0 &&
+      format != HQ_FMT_Q4_1 && format != HQ_FMT_Q5_1 && format != HQ_FMT_Q2_K && format != HQ_FMT_Q3_K)
     return false;
   if (k % kTileK != 0) return false;
   if (format == HQ_FMT_FP8_BLOCK && (n % 128 != 0 || k % 128 != 0)) return false;
@@ -1316,17 +1411,25 @@ int32_t launch_grouped_gemm(const GroupedParams& p, int max_tiles, cudaStream_t 
         return HQ_ERR_ALIGN;
       return launch_gg_fmt<HQ_FMT_Q8_0>(p, max_tiles, stream);
     case HQ_FMT_Q6_K:
+    case HQ_FMT_Q2_K:
+    case HQ_FMT_Q3_K:
       if ((reinterpret_cast<uintptr_t>(p.w) & 3u) != 0 || (p.w_up != nullptr && (reinterpret_cast<uintptr_t>(p.w_up) & 3u) != 0))
         return HQ_ERR_ALIGN;
+      if (p.format == HQ_FMT_Q2_K) return launch_gg_fmt<HQ_FMT_Q2_K>(p, max_tiles, stream);
+      if (p.format == HQ_FMT_Q3_K) return launch_gg_fmt<HQ_FMT_Q3_K>(p, max_tiles, stream);
       return launch_gg_fmt<HQ_FMT_Q6_K>(p, max_tiles, stream);
     case HQ_FMT_Q5_K:
     case HQ_FMT_Q4_0:
     case HQ_FMT_Q5_0:
+    case HQ_FMT_Q4_1:
+    case HQ_FMT_Q5_1:
       // rows are multiples of 16 bytes; the producers read 16-byte pieces (Q5_K) or aligned words (Q4_0 / Q5_0)
       if ((reinterpret_cast<uintptr_t>(p.w) & 15u) != 0 || (p.w_up != nullptr && (reinterpret_cast<uintptr_t>(p.w_up) & 15u) != 0))
         return HQ_ERR_ALIGN;
       if (p.format == HQ_FMT_Q5_K) return launch_gg_fmt<HQ_FMT_Q5_K>(p, max_tiles, stream);
       if (p.format == HQ_FMT_Q4_0) return launch_gg_fmt<HQ_FMT_Q4_0>(p, max_tiles, stream);
+      if (p.format == HQ_FMT_Q4_1) return launch_gg_fmt<HQ_FMT_Q4_1>(p, max_tiles, stream);
+      if (p.format == HQ_FMT_Q5_1) return launch_gg_fmt<HQ_FMT_Q5_1>(p, max_tiles, stream);
       return launch_gg_fmt<HQ_FMT_Q5_0>(p, max_tiles, stream);
     default: return HQ_ERR_FORMAT;
   }

@@ -120,9 +120,9 @@ class GgufFile:
         import torch
         from .quant import GgufMatMul
         t = self.tensors[name]
-        if t.type_name not in ("Q8_0", "Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0"):
+        if t.type_name not in ("Q8_0", "Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0", "Q4_1", "Q5_1", "Q2_K", "Q3_K"):
             raise GgufError(f"{name}: GGML type {t.type_name} is not on this path "
-                            "(Q8_0, Q4_K, Q6_K, Q5_K, Q4_0 and Q5_0 are)")
+                            "(Q8_0, Q4_0, Q4_1, Q5_0, Q5_1 and Q2_K .. Q6_K are)")
         if len(t.shape) not in (2, 3):
             raise GgufError(f"{name}: expected a matrix or an expert bank, got shape {t.shape}")
         data = torch.from_numpy(np.array(self.raw(name), copy=True)).to(device)

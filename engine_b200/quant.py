@@ -250,7 +250,9 @@ class QuantMethod:
 
 GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = "Q8_0", "Q4_K", "Q6_K"
 _GGML = {GGML_Q8_0: (L.FMT_Q8_0, 32, 34), GGML_Q4_K: (L.FMT_Q4_K, 256, 144), GGML_Q6_K: (L.FMT_Q6_K, 256, 210),
-         "Q5_K": (L.FMT_Q5_K, 256, 176), "Q4_0": (L.FMT_Q4_0, 32, 18), "Q5_0": (L.FMT_Q5_0, 32, 22)}
+         "Q5_K": (L.FMT_Q5_K, 256, 176), "Q4_0": (L.FMT_Q4_0, 32, 18), "Q5_0": (L.FMT_Q5_0, 32, 22),
+         "Q4_1": (L.FMT_Q4_1, 32, 20), "Q5_1": (L.FMT_Q5_1, 32, 24), "Q2_K": (L.FMT_Q2_K, 256, 84),
+         "Q3_K": (L.FMT_Q3_K, 256, 110)}
 
 
 class GgufMatMul(QuantMethod):

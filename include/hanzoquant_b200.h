@@ -67,6 +67,10 @@ extern "C" {
 #define HQ_FMT_Q5_K 5       /* GGUF block_q5_K, 176 B / 256 weights    up bank with a gated activation; a decode   */
 #define HQ_FMT_Q4_0 6       /* GGUF block_q4_0, 18 B / 32 weights      kernel up to 8 rows, the tensor-core GEMM   */
 #define HQ_FMT_Q5_0 7       /* GGUF block_q5_0, 22 B / 32 weights      from HQ_CFG_*_TENSOR_MIN_ROWS rows on)      */
+#define HQ_FMT_Q4_1 8       /* GGUF block_q4_1, 20 B / 32 weights     (formats 8-11: as 4-7)                      */
+#define HQ_FMT_Q5_1 9       /* GGUF block_q5_1, 24 B / 32 weights                                                  */
+#define HQ_FMT_Q2_K 10      /* GGUF block_q2_K, 84 B / 256 weights                                                 */
+#define HQ_FMT_Q3_K 11      /* GGUF block_q3_K, 110 B / 256 weights                                                */
 
 /* element types of activations, outputs, biases */
 #define HQ_DT_F32 0

@@ -232,12 +232,14 @@ class QuantMethod {
 // GGUF block-quantized linear / expert bank: `data` = raw GGUF block bytes, u8 [N, row_bytes] or [E, N, row_bytes]
 class GgufMatMul : public QuantMethod {
  public:
-  enum class GgmlType { Q8_0, Q4_K, Q6_K, Q5_K, Q4_0, Q5_0 };
+  enum class GgmlType { Q8_0, Q4_K, Q6_K, Q5_K, Q4_0, Q5_0, Q4_1, Q5_1, Q2_K, Q3_K };
   GgufMatMul(Tensor data, GgmlType type, int64_t k, Tensor bias = Tensor()) : data_(std::move(data)), bias_(std::move(bias)) {
     if (k % 256) throw Error("GgufMatMul: K must be a multiple of 256");
     // {format, weights per block, bytes per block}
-    static constexpr int32_t kTypes[6][3] = {{HQ_FMT_Q8_0, 32, 34},   {HQ_FMT_Q4_K, 256, 144}, {HQ_FMT_Q6_K, 256, 210},
-                                             {HQ_FMT_Q5_K, 256, 176}, {HQ_FMT_Q4_0, 32, 18},   {HQ_FMT_Q5_0, 32, 22}};
+    static constexpr int32_t kTypes[10][3] = {{HQ_FMT_Q8_0, 32, 34},   {HQ_FMT_Q4_K, 256, 144}, {HQ_FMT_Q6_K, 256, 210},
+                                              {HQ_FMT_Q5_K, 256, 176}, {HQ_FMT_Q4_0, 32, 18},   {HQ_FMT_Q5_0, 32, 22},
+                                              {HQ_FMT_Q4_1, 32, 20},   {HQ_FMT_Q5_1, 32, 24},   {HQ_FMT_Q2_K, 256, 84},
+                                              {HQ_FMT_Q3_K, 256, 110}};
     const int32_t* ty = kTypes[(int)type];
     const int64_t row_bytes = k / ty[1] * ty[2];
     if (data_.dtype() != DType::U8 || data_.rank() < 2 || data_.dim(-1) != row_bytes)

@@ -68,6 +68,18 @@ HQ_COMPAT_PLAIN(launch_mmvq_gguf_q4_0_f32_plain);
 HQ_COMPAT_PLAIN(launch_mmvq_gguf_q5_0_bf16_plain);
 HQ_COMPAT_PLAIN(launch_mmvq_gguf_q5_0_f16_plain);
 HQ_COMPAT_PLAIN(launch_mmvq_gguf_q5_0_f32_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q4_1_bf16_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q4_1_f16_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q4_1_f32_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q5_1_bf16_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q5_1_f16_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q5_1_f32_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q2_k_bf16_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q2_k_f16_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q2_k_f32_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q3_k_bf16_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q3_k_f16_plain);
+HQ_COMPAT_PLAIN(launch_mmvq_gguf_q3_k_f32_plain);
 
 /* hanzo-quant/src/gguf/ffi.rs:53-81 and the indexed MoE forward (gguf/ffi.rs:84-247; call site gguf/cuda.rs:213-440):
  * all_inputs is the Q8_1 scratch of a preceding launch_quantize_q8_1* call, outputs f32 [batch, topk, n]. */

@@ -27,6 +27,10 @@ Q6_K_BYTES = 210    # 128 low-nibble bytes, 64 high-bit bytes, 16 int8 scales, h
 Q5_K_BYTES = 176    # half d, half dmin, 12 scale bytes, 32 high-bit bytes, 128 nibble bytes
 Q4_0_BYTES = 18     # half d, 16 nibble bytes (32 weights)
 Q5_0_BYTES = 22     # half d, 4 high-bit bytes, 16 nibble bytes (32 weights)
+Q4_1_BYTES = 20     # half d, half m, 16 nibble bytes (32 weights)
+Q5_1_BYTES = 24     # half d, half m, 4 high-bit bytes, 16 nibble bytes (32 weights)
+Q2_K_BYTES = 84     # 16 scale|min bytes, 64 bytes of 2-bit codes, half d, half dmin
+Q3_K_BYTES = 110    # 32 high-bit bytes, 64 bytes of 2-bit codes, 12 bytes of 6-bit scales, half d
 MXFP4_BLOCK = 32
 FP8_MAX = 448.0
 
@@ -223,12 +227,105 @@ def q5_0_dequant(raw: np.ndarray, k: int) -> np.ndarray:
     return (d * q.astype(np.float32)).reshape(rows, k)
 
 
+# ----------------------------------------------------------------------------
+# Q4_1, Q5_1, Q2_K, Q3_K (the rest of the reference's decode list, hanzo-quant/src/gguf/fast_mmvq.rs:36-50).
+# Layouts as in ggml.  Q4_1 / Q5_1 = Q4_0 / Q5_0 with an f16 minimum behind d and value q d + m.  Q2_K / Q3_K hold
+# 2-bit codes four to a byte: per 128-weight half, byte l (0..31) of its 32 code bytes gives the weights l, l + 32,
+# l + 64, l + 96 (bits 0-1, 2-3, 4-5, 6-7), and the 16-weight group of weight 128 h + 32 j + l is 8 h + 2 j + l // 16.
+# Q2_K: value = d (s & 15) q - dmin (s >> 4) with one byte s per group.  Q3_K: value = d (scale - 32) (q - 4 (1 - hb))
+# with hb = bit 4 h + j of hmask[l] and 6-bit scales packed in 12 bytes (low nibbles of bytes 0..7 for groups 0..7,
+# high nibbles for groups 8..15, bits 4-5 of group 4 a + b in bits 2 a, 2 a + 1 of byte 8 + b).
+# ----------------------------------------------------------------------------
+
+def q4_1_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/32*20] -> f32 [rows, K]."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    blk = raw.reshape(rows, k // 32, Q4_1_BYTES)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)
+    m = blk[:, :, 2:4].copy().view(np.float16).astype(np.float32)
+    qs = blk[:, :, 4:]
+    q = np.concatenate([(qs & 0x0F), (qs >> 4)], axis=2).astype(np.float32)
+    return (d * q + m).reshape(rows, k)
+
+
+def q5_1_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/32*24] -> f32 [rows, K]."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    blk = raw.reshape(rows, k // 32, Q5_1_BYTES)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)
+    m = blk[:, :, 2:4].copy().view(np.float16).astype(np.float32)
+    qh = blk[:, :, 4:8].copy().view(np.uint32).astype(np.int64)    # [rows, nb, 1]
+    qs = blk[:, :, 8:]
+    j = np.arange(16)
+    lo = (qs & 0x0F).astype(np.int64) | (((qh >> j) & 1) << 4)
+    hi = (qs >> 4).astype(np.int64) | (((qh >> (j + 16)) & 1) << 4)
+    q = np.concatenate([lo, hi], axis=2).astype(np.float32)
+    return (d * q + m).reshape(rows, k)
+
+
+def _two_bit_codes(qs: np.ndarray) -> np.ndarray:
+    """uint8 [rows, nsb, 64] -> int32 [rows, nsb, 2, 4, 32]: [half][j][l] = weight 128 half + 32 j + l."""
+    rows, nsb = qs.shape[:2]
+    q = qs.reshape(rows, nsb, 2, 1, 32).astype(np.int32)
+    shifts = (2 * np.arange(4)).reshape(1, 1, 1, 4, 1)
+    return (q >> shifts) & 3
+
+
+def q2_k_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/256*84] -> f32 [rows, K]."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    nsb = k // QK_K
+    blk = raw.reshape(rows, nsb, Q2_K_BYTES)
+    sc = blk[:, :, 0:16]
+    d = blk[:, :, 80:82].copy().view(np.float16).astype(np.float32)       # [rows, nsb, 1]
+    dmin = blk[:, :, 82:84].copy().view(np.float16).astype(np.float32)
+    dl = d * (sc & 0x0F).astype(np.float32)                               # [rows, nsb, 16], group 8 h + 2 j + u
+    ml = dmin * (sc >> 4).astype(np.float32)
+    dl = np.repeat(dl.reshape(rows, nsb, 2, 4, 2), 16, axis=-1)           # [half][j][l]
+    ml = np.repeat(ml.reshape(rows, nsb, 2, 4, 2), 16, axis=-1)
+    q = _two_bit_codes(blk[:, :, 16:80]).astype(np.float32)
+    return (dl * q - ml).reshape(rows, k).astype(np.float32)
+
+
+def q3_k_unpack_scales(sc12: np.ndarray) -> np.ndarray:
+    """uint8 [..., 12] -> int32 [..., 16]: the 6-bit scales (before the -32)."""
+    lo = np.concatenate([sc12[..., 0:8] & 0x0F, sc12[..., 0:8] >> 4], axis=-1).astype(np.int32)   # groups 0..15
+    hb = sc12[..., 8:12].astype(np.int32)
+    a = np.arange(16) // 4
+    b = np.arange(16) % 4
+    hi = (hb[..., b] >> (2 * a)) & 3
+    return lo | (hi << 4)
+
+
+def q3_k_dequant(raw: np.ndarray, k: int) -> np.ndarray:
+    """uint8 [rows, K/256*110] -> f32 [rows, K]."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    rows = raw.shape[0]
+    nsb = k // QK_K
+    blk = raw.reshape(rows, nsb, Q3_K_BYTES)
+    hm = blk[:, :, 0:32].astype(np.int32)                                 # [rows, nsb, 32]
+    d = blk[:, :, 108:110].copy().view(np.float16).astype(np.float32)     # [rows, nsb, 1]
+    scale = (q3_k_unpack_scales(blk[:, :, 96:108]) - 32).astype(np.float32)
+    dl = np.repeat((d * scale).reshape(rows, nsb, 2, 4, 2), 16, axis=-1)  # [half][j][l]
+    q = _two_bit_codes(blk[:, :, 32:96])
+    bit = (4 * np.arange(2).reshape(2, 1) + np.arange(4).reshape(1, 4)).reshape(1, 1, 2, 4, 1)
+    hb = (hm.reshape(rows, nsb, 1, 1, 32) >> bit) & 1
+    q = (q - 4 * (1 - hb)).astype(np.float32)
+    return (dl * q).reshape(rows, k).astype(np.float32)
+
+
+_GGML_LAYOUT = {"Q6_K": (256, 210, [208]), "Q5_K": (256, 176, [0, 2]), "Q4_0": (32, 18, [0]), "Q5_0": (32, 22, [0]),
+                "Q4_1": (32, 20, [0, 2]), "Q5_1": (32, 24, [0, 2]), "Q2_K": (256, 84, [80, 82]), "Q3_K": (256, 110, [108])}
+
+
 def ggml_random_blocks(fmt: str, rng, rows: int, k: int, d_lo: float = 2e-4, d_hi: float = 3e-3) -> np.ndarray:
-    """Random valid blocks of a GGML type whose every bit pattern is valid (Q6_K, Q5_K, Q4_0, Q5_0), with the f16
-    scale fields drawn from [d_lo, d_hi] so that the weights have the magnitude of N(0, 0.02^2) weights: test and
-    benchmark input for types the oracle has no quantizer for."""
-    per, nbytes, scale_off = {"Q6_K": (256, 210, [208]), "Q5_K": (256, 176, [0, 2]), "Q4_0": (32, 18, [0]),
-                              "Q5_0": (32, 22, [0])}[fmt]
+    """Random valid blocks of a GGML type whose every bit pattern is valid (Q6_K, Q5_K, Q4_0, Q5_0, Q4_1, Q5_1, Q2_K,
+    Q3_K), with the f16 scale fields drawn from [d_lo, d_hi] so that the weights have the magnitude of N(0, 0.02^2)
+    weights: test and benchmark input for types the oracle has no quantizer for."""
+    per, nbytes, scale_off = _GGML_LAYOUT[fmt]
     nb = k // per
     blk = rng.integers(0, 256, (rows, nb, nbytes), dtype=np.uint8)
     for off in scale_off:
@@ -237,7 +334,8 @@ def ggml_random_blocks(fmt: str, rng, rows: int, k: int, d_lo: float = 2e-4, d_h
 
 
 GGML_DEQUANT = {"Q8_0": q8_0_dequant, "Q4_K": q4_k_dequant, "Q6_K": q6_k_dequant, "Q5_K": q5_k_dequant,
-                "Q4_0": q4_0_dequant, "Q5_0": q5_0_dequant}
+                "Q4_0": q4_0_dequant, "Q5_0": q5_0_dequant, "Q4_1": q4_1_dequant, "Q5_1": q5_1_dequant,
+                "Q2_K": q2_k_dequant, "Q3_K": q3_k_dequant}
 
 
 def _nearest_int(f: np.ndarray) -> np.ndarray:

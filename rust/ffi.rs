@@ -13,6 +13,10 @@ pub const HQ_FMT_Q6_K: i32 = 4;
 pub const HQ_FMT_Q5_K: i32 = 5;
 pub const HQ_FMT_Q4_0: i32 = 6;
 pub const HQ_FMT_Q5_0: i32 = 7;
+pub const HQ_FMT_Q4_1: i32 = 8;
+pub const HQ_FMT_Q5_1: i32 = 9;
+pub const HQ_FMT_Q2_K: i32 = 10;
+pub const HQ_FMT_Q3_K: i32 = 11;
 pub const HQ_DT_F32: i32 = 0;
 pub const HQ_DT_F16: i32 = 1;
 pub const HQ_DT_BF16: i32 = 2;

@@ -131,7 +131,8 @@ def oracle_router(cfg, logits: np.ndarray, sel_bias: np.ndarray | None):
 
 
 # ---- CPU oracle of a token subset ---------------------------------------------------------------------
-_FMT_NAME = {0: "Q8_0", 1: "Q4_K", 2: "FP8", 3: "MXFP4", 4: "Q6_K", 5: "Q5_K", 6: "Q4_0", 7: "Q5_0"}
+_FMT_NAME = {0: "Q8_0", 1: "Q4_K", 2: "FP8", 3: "MXFP4", 4: "Q6_K", 5: "Q5_K", 6: "Q4_0", 7: "Q5_0", 8: "Q4_1", 9: "Q5_1",
+             10: "Q2_K", 11: "Q3_K"}
 
 
 def _bank_slices(layer, experts):

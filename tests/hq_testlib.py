@@ -32,9 +32,9 @@ def make_weight(fmt: str, rng, n: int, k: int, experts: int = 0, sigma: float = 
         raw = F.q6_k_quantize(w)
         deq = F.q6_k_dequant(raw, k)
         arrays = {"data": raw.reshape(e, n, -1)}
-    elif fmt in ("Q5_K", "Q4_0", "Q5_0"):
+    elif fmt in ("Q5_K", "Q4_0", "Q5_0", "Q4_1", "Q5_1", "Q2_K", "Q3_K"):
         # no quantizer for these types: random valid blocks whose scales give weights of the usual magnitude
-        lo, hi = (2e-5, 1e-4) if fmt == "Q5_K" else (1e-3, 4e-3)
+        lo, hi = {"Q5_K": (2e-5, 1e-4), "Q2_K": (5e-4, 2e-3), "Q3_K": (1e-4, 4e-4)}.get(fmt, (1e-3, 4e-3))
         raw = F.ggml_random_blocks(fmt, rng, e * n, k, lo, hi)
         deq = F.GGML_DEQUANT[fmt](raw, k)
         arrays = {"data": raw.reshape(e, n, -1)}
@@ -62,7 +62,7 @@ def make_layer(fmt: str, arrays: dict, k: int, device, bias=None):
     import torch
     import engine_b200 as hq
     t = {k_: torch.from_numpy(np.ascontiguousarray(v)).to(device) for k_, v in arrays.items()}
-    if fmt in ("Q8_0", "Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0"):
+    if fmt in F.GGML_DEQUANT:
         return hq.GgufMatMul(t["data"], fmt, k, bias)
     if fmt == "FP8":
         return hq.BlockwiseFP8Linear(t["weight"], t["scale"], bias)

@@ -49,7 +49,7 @@ def test_host_side_argument_errors(lib):
     from engine_b200 import _lib as L
     w = L.HqWeight(L.FMT_Q8_0, 1, 64, 100, 16, 0, 0, 0, 0)           # K % 256 != 0
     assert lib.hq_linear_forward(C.byref(w), 16, L.DT_BF16, 100, 16, L.DT_F32, 64, 1, None, None) == -2
-    w = L.HqWeight(9, 1, 64, 256, 16, 0, 0, 0, 0)
+    w = L.HqWeight(99, 1, 64, 256, 16, 0, 0, 0, 0)                     # no such format
     assert lib.hq_linear_forward(C.byref(w), 16, L.DT_BF16, 256, 16, L.DT_F32, 64, 1, None, None) == -4
     w = L.HqWeight(L.FMT_Q8_0, 1, 64, 256, 0, 0, 0, 0, 0)
     assert lib.hq_linear_forward(C.byref(w), 16, L.DT_BF16, 256, 16, L.DT_F32, 64, 1, None, None) == -1

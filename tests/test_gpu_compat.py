@@ -57,7 +57,8 @@ def test_dispatch_and_reduce_shims():
 
 
 @pytest.mark.parametrize("fmt,sym", [("Q8_0", "q8_0"), ("Q4_K", "q4_k"), ("Q6_K", "q6_k"), ("Q5_K", "q5_k"),
-                                     ("Q4_0", "q4_0"), ("Q5_0", "q5_0")])
+                                     ("Q4_0", "q4_0"), ("Q5_0", "q5_0"), ("Q4_1", "q4_1"), ("Q5_1", "q5_1"),
+                                     ("Q2_K", "q2_k"), ("Q3_K", "q3_k")])
 def test_q8_1_pair_runs_the_mat_vec_on_the_original_activations(fmt, sym):
     lib = _lib()
     rng = T.rng_for(7, 2)

@@ -10,7 +10,9 @@ from oracle import formats as F
 from oracle import moe as M
 from tests import hq_testlib as T
 
-TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "Q6_K": 1e-3, "Q5_K": 1e-3, "Q4_0": 1e-3, "Q5_0": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
+TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "Q6_K": 1e-3, "Q5_K": 1e-3, "Q4_0": 1e-3, "Q5_0": 1e-3, "Q4_1": 1e-3, "Q5_1": 1e-3,
+       "Q2_K": 1e-3, "Q3_K": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
+FURTHER = ["Q5_K", "Q4_0", "Q5_0", "Q4_1", "Q5_1", "Q2_K", "Q3_K"]     # the GGML types beyond Q8_0 / Q4_K / Q6_K
 DEV = "cuda:0"
 
 
@@ -33,7 +35,7 @@ def run_case(fmt, n, k, m, x_dtype, out_dtype, seed, bias=False):
     return y.to(torch.float32).cpu().numpy(), want
 
 
-@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0", "FP8", "MXFP4"])
+@pytest.mark.parametrize("fmt", ["Q8_0", "Q4_K", "Q6_K"] + FURTHER + ["FP8", "MXFP4"])
 @pytest.mark.parametrize("m", [1, 2, 4, 8])
 def test_decode_rows_f32_out(fmt, m):
     got, want = run_case(fmt, 512, 1024, m, torch.bfloat16, torch.float32, 10 + m)
@@ -46,7 +48,10 @@ def test_decode_rows_f32_out(fmt, m):
                                      # rows staged four 256-weight spans at a time: a last stretch of one span
                                      # (K = 1280, 2304) and rows that start 2, 4, .. 14 bytes off a 16-byte boundary
                                      ("Q6_K", 520, 1280), ("Q5_0", 520, 1280), ("Q4_0", 1000, 4096),
-                                     ("Q5_K", 520, 2304)])
+                                     ("Q5_K", 520, 2304),
+                                     # Q2_K rows of 420 bytes (4-byte aligned), Q3_K rows of 550 (2-byte aligned)
+                                     ("Q2_K", 520, 1280), ("Q3_K", 520, 1280), ("Q4_1", 520, 1280), ("Q5_1", 520, 1280),
+                                     ("Q2_K", 1000, 4096), ("Q3_K", 1000, 4096)])
 def test_model_shapes(fmt, n, k):
     got, want = run_case(fmt, n, k, 3, torch.bfloat16, torch.float32, 20, bias=(fmt == "MXFP4"))
     assert T.rel_l2(got, want) <= TOL[fmt]
@@ -77,7 +82,7 @@ def test_q6_k_prefill_rows_on_the_tensor_cores(m, k):
     assert T.rel_l2(got, want) <= 1e-3
 
 
-@pytest.mark.parametrize("fmt", ["Q5_K", "Q4_0", "Q5_0"])
+@pytest.mark.parametrize("fmt", FURTHER)
 @pytest.mark.parametrize("dt", ["float32", "float16"])
 def test_further_ggml_types_any_row_count(fmt, dt):
     # 21 rows: past the eight of a decode work item, so these go to the tensor-core GEMM; N = 1000 is not a multiple
@@ -86,18 +91,19 @@ def test_further_ggml_types_any_row_count(fmt, dt):
     assert T.rel_l2(got, want) <= 1e-3
 
 
-@pytest.mark.parametrize("fmt", ["Q5_K", "Q4_0", "Q5_0"])
+@pytest.mark.parametrize("fmt", FURTHER)
 @pytest.mark.parametrize("m", [9, 130, 600])
 @pytest.mark.parametrize("k", [768, 2048])
 def test_further_ggml_types_prefill_rows_on_the_tensor_cores(fmt, m, k):
-    # the blocks are expanded to f16 by the producer warps (Q5_K: d sc q - dmin m in split f16 arithmetic; Q4_0 /
-    # Q5_0: (q - zero) x d rounded once) and multiplied by tcgen05; K = 768 gives Q4_0 / Q5_0 rows whose 18- / 22-byte
-    # blocks alternate between 4-byte aligned and 2 bytes off, both forms of the producers' word loads
+    # the blocks are expanded to f16 by the producer warps (Q5_K / Q2_K: d sc q - dmin m in split f16 arithmetic;
+    # Q4_0 / Q5_0 / Q4_1 / Q5_1: (q - zero) x d [+ m] rounded once; Q3_K: (q - 4) x (d scale)) and multiplied by
+    # tcgen05; K = 768 gives Q4_0 / Q5_0 rows whose 18- / 22-byte blocks alternate between 4-byte aligned and 2 bytes
+    # off, and Q3_K rows of 330 bytes that do the same: both forms of the producers' word loads
     got, want = run_case(fmt, 1000, k, m, torch.bfloat16, torch.float32, 90 + m)
     assert T.rel_l2(got, want) <= 1e-3
 
 
-@pytest.mark.parametrize("fmt", ["Q6_K", "Q5_K", "Q4_0", "Q5_0"])
+@pytest.mark.parametrize("fmt", ["Q6_K"] + FURTHER)
 def test_further_ggml_types_decode_kernel_beyond_eight_rows(fmt):
     # with the tensor path switched off the decode kernel serves any row count, eight rows per work item
     from engine_b200 import _lib as L
@@ -144,7 +150,7 @@ def test_run_twice_is_bit_identical():
 
 def test_dequantize_w_is_exact():
     rng = T.rng_for(1, 70)
-    for fmt in ["Q8_0", "Q4_K", "Q6_K", "Q5_K", "Q4_0", "Q5_0", "FP8", "MXFP4"]:
+    for fmt in ["Q8_0", "Q4_K", "Q6_K"] + FURTHER + ["FP8", "MXFP4"]:
         arrays, deq = T.make_weight(fmt, rng, 128, 256)
         layer = T.make_layer(fmt, arrays, 256, DEV)
         got = layer.dequantize_w().cpu().numpy()

@@ -13,7 +13,8 @@ from oracle import moe as M
 from tests import hq_testlib as T
 
 DEV = "cuda:0"
-TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "Q6_K": 1e-3, "Q5_K": 1e-3, "Q4_0": 1e-3, "Q5_0": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
+TOL = {"Q8_0": 1e-3, "Q4_K": 1e-3, "Q6_K": 1e-3, "Q5_K": 1e-3, "Q4_0": 1e-3, "Q5_0": 1e-3, "Q4_1": 1e-3, "Q5_1": 1e-3,
+       "Q2_K": 1e-3, "Q3_K": 1e-3, "FP8": 2e-3, "MXFP4": 2e-3}
 
 
 def margin_ok_rows(sel: np.ndarray, k: int, ulps: int = 4):
@@ -119,7 +120,8 @@ def test_gather_forward_known_answers():
 
 
 @pytest.mark.parametrize("fmt,k,n", [("Q4_K", 512, 192), ("Q8_0", 256, 64), ("FP8", 256, 128), ("MXFP4", 96, 80),
-                                     ("Q6_K", 256, 72), ("Q5_K", 512, 64), ("Q4_0", 256, 40), ("Q5_0", 256, 40)])
+                                     ("Q6_K", 256, 72), ("Q5_K", 512, 64), ("Q4_0", 256, 40), ("Q5_0", 256, 40),
+                                     ("Q4_1", 256, 40), ("Q5_1", 256, 40), ("Q2_K", 768, 72), ("Q3_K", 768, 72)])
 @pytest.mark.parametrize("per_slot", [False, True])
 def test_gather_forward_matches_oracle(fmt, k, n, per_slot):
     rng = T.rng_for(3, k + n)
@@ -201,7 +203,7 @@ def test_moe_block_q6_k_gate_and_up(t):
     assert T.rel_l2(got, want) <= 1e-3
 
 
-@pytest.mark.parametrize("fmt", ["Q5_K", "Q4_0", "Q5_0"])
+@pytest.mark.parametrize("fmt", ["Q5_K", "Q4_0", "Q5_0", "Q4_1", "Q5_1", "Q2_K", "Q3_K"])
 @pytest.mark.parametrize("t", [3, 200])
 def test_moe_block_further_ggml_types(fmt, t):
     # decode rows (the warp-MMA decode kernel) and prefill rows (the tcgen05 grouped GEMM: 200 tokens x top-2 over 4

@@ -133,7 +133,7 @@ def test_bf16_rounding_helpers():
     assert np.array_equal(F.from_bf16_bits(F.to_bf16_bits(x)), want)
 
 
-@pytest.mark.parametrize("fmt", ["Q6_K", "Q5_K", "Q4_0", "Q5_0"])
+@pytest.mark.parametrize("fmt", ["Q6_K", "Q5_K", "Q4_0", "Q5_0", "Q4_1", "Q5_1", "Q2_K", "Q3_K"])
 def test_ggml_dequant_matches_gguf_py_bit_for_bit(fmt):
     """Random valid blocks (and, where a quantizer exists, quantized N(0, 0.02^2) weights) against gguf-py's
     dequantize; vectors from tests/golden/make_golden_ggml.py."""
