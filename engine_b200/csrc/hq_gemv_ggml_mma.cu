@@ -19,7 +19,7 @@
 // word of nibbles plus one of high bits.  Codes become f16 / bf16 by a byte permute into the mantissa of 1024 / 128
 // and one packed subtraction.  Activations are read straight from global memory (8 bytes per lane and group; they
 // stay in L1).
-// HBM-bound by design; algorithmic bytes per launch = N*K*bits/8 + M*K*sizeof(x) + M*N*sizeof(y)
+// Roofline: HBM; algorithmic bytes per launch = N*K*bits/8 + M*K*sizeof(x) + M*N*sizeof(y)
 // (bits: 6.5625, 5.5, 4.5, 5.5, 5, 6, 2.625, 3.4375).
 #include "hq_gemv_shared.cuh"
 
