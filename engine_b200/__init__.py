@@ -1,7 +1,7 @@
 """B200-native quantized-linear and sparse-MoE expert path behind hanzo-quant's
 QuantMethod API.  Importing the package does not need a GPU; every operation
 does, and fails loudly without libhanzoquant_b200.so."""
-from . import _lib
+from . import _lib, uqff
 from ._lib import HqError
 from .moe import (MoEExperts, MoeRouterTopKConfig, TopKOutput, gated_act, moe_router_forward, moe_router_topk,
                   moe_weighted_reduce)

@@ -116,6 +116,16 @@ class QuantMethod:
         self._w_cached = None
 
     # -- plumbing -------------------------------------------------------------------
+    # QuantizedSerde (hanzo-quant/src/lib.rs:911-945): layer types the reference does not serialise say so
+    def name(self) -> str:
+        return type(self).__name__
+
+    def isq_serde_supported(self) -> bool:
+        return False
+
+    def serialize(self) -> bytes:
+        raise L.HqError(f"{self.name()} has no UQFF form")
+
     def _weight_struct(self) -> L.HqWeight:
         raise NotImplementedError
 
@@ -290,6 +300,32 @@ class GgufMatMul(QuantMethod):
             return self
         return GgufMatMul(self.data[e], self.qtype, self.k)
 
+    # QuantizedSerde (hanzo-quant/src/lib.rs:911-945, gguf/mod.rs:427-674): the layer as a UQFF byte string
+    def name(self) -> str:
+        return "gguf"
+
+    def isq_serde_supported(self) -> bool:
+        return True
+
+    def serialize(self) -> bytes:
+        return self.serialize_with_bias(self.bias)
+
+    def serialize_with_bias(self, bias: torch.Tensor | None) -> bytes:
+        from . import uqff
+        return uqff.serialize_gguf(self.data, self.qtype, self.k, bias)
+
+    @classmethod
+    def deserialize(cls, data, device) -> "GgufMatMul":
+        return cls.deserialize_ext_bias(data, device)[0]
+
+    @classmethod
+    def deserialize_ext_bias(cls, data, device):
+        """Returns (layer, bias): the bias is part of the layer and handed out as well, as in the reference."""
+        from . import uqff
+        raw, qtype, k, bias = uqff.deserialize_gguf(data)
+        bias = None if bias is None else bias.to(device)
+        return cls(raw.to(device), qtype, k, bias), bias
+
 
 class BlockwiseFP8Linear(QuantMethod):
     """e4m3 weight with a 128x128 f32 `weight_scale_inv` grid (hanzo-quant/src/blockwise_fp8/mod.rs:24-198).
@@ -381,6 +417,31 @@ class MXFP4Layer(QuantMethod):
 
     def _expert_view(self, e):
         return self if self.n_experts == 1 else MXFP4Layer(self.blocks[e], self.scales[e])
+
+    # QuantizedSerde (hanzo-quant/src/lib.rs:911-945, mxfp4/mod.rs:742-826)
+    def name(self) -> str:
+        return "mxfp4-layer"
+
+    def isq_serde_supported(self) -> bool:
+        return True
+
+    def serialize(self) -> bytes:
+        return self.serialize_with_bias(self.bias)
+
+    def serialize_with_bias(self, bias: torch.Tensor | None) -> bytes:
+        from . import uqff
+        return uqff.serialize_mxfp4(self.blocks, self.scales, bias)
+
+    @classmethod
+    def deserialize(cls, data, device) -> "MXFP4Layer":
+        return cls.deserialize_ext_bias(data, device)[0]
+
+    @classmethod
+    def deserialize_ext_bias(cls, data, device):
+        from . import uqff
+        blocks, scales, bias = uqff.deserialize_mxfp4(data)
+        bias = None if bias is None else bias.to(device)
+        return cls(blocks.to(device), scales.to(device), bias), bias
 
     def mx_supported(self) -> bool:
         """Shapes the block-scaled tensor-core path takes (K a multiple of 64, at least 128)."""
