@@ -20,6 +20,25 @@ fn dt_code(dt: DType) -> Result<i32> {
     })
 }
 
+/// The library's format code of a GGML weight type, `None` for types it does not run: the list of
+/// `fast_mmvq::supports` (hanzo-quant/src/gguf/fast_mmvq.rs:36-50), served for any row count.
+pub fn gguf_format(dtype: hanzo_ml::quantized::GgmlDType) -> Option<i32> {
+    use hanzo_ml::quantized::GgmlDType as G;
+    Some(match dtype {
+        G::Q8_0 => HQ_FMT_Q8_0,
+        G::Q4_0 => HQ_FMT_Q4_0,
+        G::Q4_1 => HQ_FMT_Q4_1,
+        G::Q5_0 => HQ_FMT_Q5_0,
+        G::Q5_1 => HQ_FMT_Q5_1,
+        G::Q2K => HQ_FMT_Q2_K,
+        G::Q3K => HQ_FMT_Q3_K,
+        G::Q4K => HQ_FMT_Q4_K,
+        G::Q5K => HQ_FMT_Q5_K,
+        G::Q6K => HQ_FMT_Q6_K,
+        _ => return None,
+    })
+}
+
 fn check(rc: i32, what: &str) -> Result<()> {
     if rc == HQ_OK {
         return Ok(());
