@@ -61,3 +61,27 @@ def test_reader_rejects_what_it_does_not_know(tmp_path):
         fh.write(b"NOPE" + b"\0" * 64)
     with pytest.raises(GgufError):
         GgufFile(path)
+
+
+def test_reader_knows_every_ggml_type_the_kernels_run(tmp_path):
+    """One tensor of each type of the reference's decode list (hanzo-quant/src/gguf/fast_mmvq.rs:36-50), written by
+    gguf-py: type name, block geometry and bytes come back, and the bytes dequantize (oracle) to what gguf-py says."""
+    from engine_b200.gguf_file import GgufFile
+    from gguf import quants
+    rng = np.random.Generator(np.random.PCG64(13))
+    n, k = 4, 512
+    tensors, raws = {}, {}
+    for name in ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K", "Q5_K", "Q6_K"]:
+        raws[name] = F.ggml_random_blocks(name, rng, n, k)
+        tensors[f"t.{name}.weight"] = (raws[name], getattr(gguf.GGMLQuantizationType, name))
+    path = os.path.join(tmp_path, "types.gguf")
+    _write(path, tensors, {"general.name": "types"})
+    f = GgufFile(path)
+    for name, raw in raws.items():
+        t = f.tensors[f"t.{name}.weight"]
+        assert t.type_name == name and t.shape == (n, k) and t.row_bytes == raw.shape[1]
+        got = np.array(f.raw(f"t.{name}.weight"))                 # a copy: views keep the file mapped
+        assert np.array_equal(got, raw)
+        want = quants.dequantize(raw, getattr(gguf.GGMLQuantizationType, name)).astype(np.float32)
+        assert np.array_equal(F.GGML_DEQUANT[name](got, k), want)
+    f.close()
