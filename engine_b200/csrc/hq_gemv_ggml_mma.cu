@@ -4,21 +4,22 @@
 //
 // The codes of these types are small integers (2 to 6 bits), exact in f16 and bf16, so the products run on the
 // warp MMA m16n8k16 with f32 accumulation: one MMA covers 16 output rows x 16 consecutive weights x 8 activation
-// rows, and the per-block factor (d * scale, or d) multiplies the f32 result of one (Q6_K) or two (32-weight blocks)
-// MMAs.  The additive term of Q5_K, Q2_K ("- dmin * m") and Q4_1 / Q5_1 ("+ m") uses the sum of the activations over
-// the block, which a second MMA against a fragment of ones delivers in the same layout.  bf16 activations are multiplied as bf16 (nothing is converted or
-// rounded), f16 as f16, f32 activations are rounded to f16 (clamped to +-65504 and flagged beyond).
+// rows, and the per-block factor (d * scale, or d) multiplies the f32 result of one (16-weight groups of Q6_K, Q3_K,
+// Q2_K) or two (32-weight blocks) MMAs.  The additive term of Q5_K, Q2_K ("- dmin * m") and Q4_1 / Q5_1 ("+ m") uses
+// the sum of the activations over the block, which a second MMA against a fragment of ones delivers in the same
+// layout.  bf16 activations are multiplied as bf16 (nothing is converted or rounded), f16 as f16, f32 activations
+// are rounded to f16 (clamped to +-65504 and flagged beyond).
 //
 // One CTA of eight warps per work item of 16 output rows (persistent, three CTAs per SM); the warps take the
 // 256-weight spans of K in turn and their partial sums are added in warp order by one warp (the warps take turns;
 // two buffers, one CTA barrier per item), so results are bit-reproducible.  Each warp brings its spans in through a
 // two-deep ring of cp.async stages (16 rows x one span; aligned 16-byte pieces from the 32-byte boundary below the
-// span on, since Q6_K rows start on 2-byte boundaries) that runs across work items, and picks the fields out of
-// shared memory: lane (g, t) decodes the four consecutive weights 4 t .. 4 t + 3 of a 16-weight
-// group for the rows g and g + 8 (the MMA's k index is permuted accordingly on both operands), i.e. one 32-bit
-// word of nibbles plus one of high bits.  Codes become f16 / bf16 by a byte permute into the mantissa of 1024 / 128
-// and one packed subtraction.  Activations are read straight from global memory (8 bytes per lane and group; they
-// stay in L1).
+// span on, since Q6_K and Q3_K rows start on 2-byte boundaries and Q2_K rows on 4-byte ones) that runs across work
+// items, and picks the fields out of shared memory: lane (g, t) decodes the four consecutive weights 4 t .. 4 t + 3
+// of a 16-weight group for the rows g and g + 8 (the MMA's k index is permuted accordingly on both operands), i.e.
+// one 32-bit word of code bits plus one of high bits.  Codes become f16 / bf16 by a byte permute into the mantissa of
+// 1024 / 128 and one packed subtraction.  Activations are read straight from global memory (8 bytes per lane and
+// group; they stay in L1).
 // Roofline: HBM; algorithmic bytes per launch = N*K*bits/8 + M*K*sizeof(x) + M*N*sizeof(y)
 // (bits: 6.5625, 5.5, 4.5, 5.5, 5, 6, 2.625, 3.4375).
 #include "hq_gemv_shared.cuh"
