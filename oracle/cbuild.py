@@ -37,7 +37,8 @@ def lib():
     return _lib
 
 
-FMT = {"Q8_0": 0, "Q4_K": 1, "FP8": 2, "MXFP4": 3}
+FMT = {"Q8_0": 0, "Q4_K": 1, "FP8": 2, "MXFP4": 3, "Q6_K": 4, "Q5_K": 5, "Q4_0": 6, "Q5_0": 7, "Q4_1": 8, "Q5_1": 9,
+       "Q2_K": 10, "Q3_K": 11}
 
 
 def _p(a):

@@ -7,7 +7,9 @@ from oracle import moe as M
 from tests import hq_testlib as T
 
 
-@pytest.mark.parametrize("fmt,k", [("Q8_0", 512), ("Q4_K", 512), ("FP8", 384), ("MXFP4", 96)])
+@pytest.mark.parametrize("fmt,k", [("Q8_0", 512), ("Q4_K", 512), ("FP8", 384), ("MXFP4", 96), ("Q6_K", 512), ("Q5_K", 512),
+                                   ("Q4_0", 256), ("Q5_0", 256), ("Q4_1", 256), ("Q5_1", 256), ("Q2_K", 768),
+                                   ("Q3_K", 768)])
 def test_c_linear_matches_numpy(fmt, k):
     rng = T.rng_for(7, k)
     n = 256 if fmt == "FP8" else 70
